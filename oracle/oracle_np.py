@@ -1,0 +1,373 @@
+"""CPU oracle (numpy) for the per-mini-batch data path.  TEST INFRASTRUCTURE ONLY.
+
+This file restates, in plain numpy, the algorithm of the reference's CPU path so that the CUDA
+kernels can be checked against it.  Only the tests, the smoke check and the benchmark's CPU-baseline
+leg may import it; nothing in the shipped package does.
+
+Parity pin: every function here is checked in ``tests/test_oracle_golden.py`` against vectors produced
+by running the reference itself (``tests/golden/make_golden.py``).
+
+Reference locations restated (paths inside the reference project):
+
+* T-CSR order                      prepare_sample.py:192-203
+* temporal sampling                prepare_sample.py:32-172 (continuous graph branch), :248-265
+  optional window flags            csrc/include/starrygl/sample.cu.hpp:706-734, :783-827
+* (node, ts) pair relabel + CSC    prepare_sample.py:205-246, :313-377
+* node-level relabel               csrc/include/starrygl/sample.cu.hpp:1766-1852
+* id packing                       starrygl/utils/partition_book.py:7-52
+* id -> slot map, master test      starrygl/utils/partition_book.py:98-133, :160-168
+* node state read / write          starrygl/cache/NodeState.py:36-61
+* chunk-cache hit / miss split     starrygl/cache/NodeState.py:152-194 (commented design)
+* replica lookup                   starrygl/cache/replica_table.py:16-82, :178-215
+* cache route                      starrygl/cache/cache_route.py:211-277, starrygl/cache/NodeState.py:245-282
+* halo route                       starrygl/route/route.py:427-466
+"""
+import numpy as np
+
+I64 = np.int64
+
+# ----------------------------------------------------------------------------------------------
+# T-CSR
+# ----------------------------------------------------------------------------------------------
+
+
+def tcsr_build(key, nbr, ts, eid, num_nodes):
+    """Rows keyed by ``key`` in ascending node id; inside a row ascending ``ts``; ties keep input order.
+
+    prepare_sample.py:192-203 -- ``np.lexsort((ts, dst))`` is stable, row pointer = cumsum of counts.
+    Returns (indptr[num_nodes+1], nbr_sorted, ts_sorted, eid_sorted, perm).
+    """
+    key = np.asarray(key, I64)
+    order = np.lexsort((np.asarray(ts, I64), key))
+    indptr = np.zeros(num_nodes + 1, I64)
+    valid = key[(key >= 0) & (key < num_nodes)]
+    np.add.at(indptr, valid + 1, 1)
+    np.cumsum(indptr, out=indptr)
+    return indptr, np.asarray(nbr, I64)[order], np.asarray(ts, I64)[order], np.asarray(eid, I64)[order], order
+
+
+# ----------------------------------------------------------------------------------------------
+# Philox4x32-10 (the counter-based generator of the uniform policy; published algorithm:
+# Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11)
+# ----------------------------------------------------------------------------------------------
+
+_PH_M0, _PH_M1 = 0xD2511F53, 0xCD9E8D57
+_PH_W0, _PH_W1 = 0x9E3779B9, 0xBB67AE85
+_M32 = 0xFFFFFFFF
+
+
+def philox4x32_10(ctr, key):
+    c0, c1, c2, c3 = ctr
+    k0, k1 = key
+    for _ in range(10):
+        p0 = _PH_M0 * c0
+        p1 = _PH_M1 * c2
+        hi0, lo0 = (p0 >> 32) & _M32, p0 & _M32
+        hi1, lo1 = (p1 >> 32) & _M32, p1 & _M32
+        c0, c1, c2, c3 = (hi1 ^ c1 ^ k0) & _M32, lo1, (hi0 ^ c3 ^ k1) & _M32, lo0
+        k0 = (k0 + _PH_W0) & _M32
+        k1 = (k1 + _PH_W1) & _M32
+    return c0, c1, c2, c3
+
+
+def uniform_positions(n_cand, k, seed, stream, slot):
+    """k distinct positions of [0, n_cand), ascending -- Floyd's subset algorithm driven by Philox.
+
+    Draw j (j = 0..k-1) uses counter (slot_lo, slot_hi, j, stream), key (seed_lo, seed_hi) and the
+    first two output words as one 64-bit integer u; t = u mod (n_cand - k + j + 1).  If t is already
+    chosen the value n_cand - k + j is taken instead.  Every k-subset is equally likely (the distribution of
+    ``np.random.choice(cut, k, replace=False)`` followed by ``sort``, prepare_sample.py:124-125).
+    """
+    chosen = []
+    for j in range(k):
+        bound = n_cand - k + j + 1
+        o = philox4x32_10((slot & _M32, (slot >> 32) & _M32, j, stream & _M32), (seed & _M32, (seed >> 32) & _M32))
+        u = o[0] | (o[1] << 32)
+        t = u % bound
+        chosen.append(bound - 1 if t in chosen else t)
+    return sorted(chosen)
+
+
+# ----------------------------------------------------------------------------------------------
+# temporal neighbour sampling
+# ----------------------------------------------------------------------------------------------
+
+RECENT, UNIFORM = 0, 1
+
+
+def sample_layer(indptr, nbr, ts, eid, targets, target_ts, fanout, policy=RECENT, *, equal_root_time=False,
+                 allowed_offset=-1, keep_root_time=False, seed=0, stream=0):
+    """One hop.  prepare_sample.py:32-172 (continuous branch) / :248-265.
+
+    For target i (node ``targets[i]``, query time ``t = target_ts[i]``): candidates are the row's
+    edges with ``ts < t`` (``ts <= t`` with equal_root_time; additionally ``ts >= t - allowed_offset``
+    when allowed_offset >= 0).  recent: the last min(k, cand) in ascending time.  uniform: all if
+    cand <= k else k distinct positions, ascending.  Returns (nbr, dst_slot, ts, dt float32 = t - ts, eid)
+    concatenated over targets in target order, plus the per-target counts.
+    """
+    targets = np.asarray(targets, I64)
+    target_ts = np.asarray(target_ts, I64)
+    o_n, o_d, o_t, o_dt, o_e = [], [], [], [], []
+    counts = np.zeros(len(targets), I64)
+    for i in range(len(targets)):
+        s, e = int(indptr[targets[i]]), int(indptr[targets[i] + 1])
+        t = int(target_ts[i])
+        row = ts[s:e]
+        cut = int(np.searchsorted(row, t + (1 if equal_root_time else 0), side="left"))
+        lo = int(np.searchsorted(row, t - allowed_offset, side="left")) if allowed_offset >= 0 else 0
+        lo = min(lo, cut)
+        cand = cut - lo
+        if cand <= 0:
+            continue
+        if policy == RECENT:
+            pos = np.arange(max(lo, cut - fanout), cut)
+        elif cand <= fanout:
+            pos = np.arange(lo, cut)
+        else:
+            pos = lo + np.array(uniform_positions(cand, fanout, seed, stream, i), I64)
+        idx = s + pos
+        counts[i] = len(idx)
+        o_n.append(nbr[idx])
+        o_d.append(np.full(len(idx), i, I64))
+        o_t.append(np.full(len(idx), t, I64) if keep_root_time else ts[idx])
+        o_dt.append((t - ts[idx]).astype(np.float32))
+        o_e.append(eid[idx])
+
+    def cat(parts, dt):
+        return np.concatenate(parts).astype(dt) if parts else np.zeros(0, dt)
+    return cat(o_n, I64), cat(o_d, I64), cat(o_t, I64), cat(o_dt, np.float32), cat(o_e, I64), counts
+
+
+# ----------------------------------------------------------------------------------------------
+# relabel: (node, ts) pairs (batch dictionaries) and node level (pybind result type)
+# ----------------------------------------------------------------------------------------------
+
+
+def _pairs(ids, ts):
+    a = np.empty(len(ids), dtype=[("id", I64), ("ts", I64)])
+    a["id"], a["ts"] = ids, ts
+    return a
+
+
+def unique_pairs(ids, ts):
+    """prepare_sample.py:205-213 -- sorted unique (id, ts) pairs and the rank of every input item."""
+    u, inv = np.unique(_pairs(ids, ts), return_inverse=True)
+    return u["id"].copy(), u["ts"].copy(), inv.astype(I64)
+
+
+def merge_and_map(cur_ids, cur_ts, raw_ids, raw_ts):
+    """prepare_sample.py:231-246 -- sorted unique union; rank of each raw item in it."""
+    raw = _pairs(raw_ids, raw_ts)
+    u = np.unique(np.concatenate([_pairs(cur_ids, cur_ts), raw]))
+    return u["id"].copy(), u["ts"].copy(), np.searchsorted(u, raw).astype(I64)
+
+
+def build_csc(src_local, dst_local, ts, dt, eid, num_dst):
+    """prepare_sample.py:215-229 -- stable order by (dst_local, ts); indptr over the previous list."""
+    if len(src_local) == 0:
+        return np.zeros(num_dst + 1, I64), np.zeros(0, I64), np.zeros(0, I64), np.zeros(0, np.float32), np.zeros(0, I64)
+    perm = np.lexsort((ts, dst_local))
+    indptr = np.zeros(num_dst + 1, I64)
+    d = dst_local[perm]
+    np.add.at(indptr, d[d < num_dst] + 1, 1)
+    np.cumsum(indptr, out=indptr)
+    return indptr, src_local[perm], ts[perm], dt[perm], eid[perm]
+
+
+def build_batch(indptr, nbr, ts, eid, roots, root_ts, fanouts, policy=RECENT, **kw):
+    """prepare_sample.py:313-377 without route planning: list of per-layer dicts.
+
+    Layer 0: unique (id, ts) pairs of the roots + inv_map.  Layer l+1: targets are the current unique list
+    (l = 0) or one target per sampled edge of the previous hop (l > 0) at that edge's timestamp.
+    """
+    cur_id, cur_ts, inv0 = unique_pairs(roots, root_ts)
+    out = [{"gids": cur_id, "ts": cur_ts, "inv_map": inv0}]
+    last_inv = None
+    for l, k in enumerate(fanouts):
+        tgt = cur_id if l == 0 else cur_id[last_inv]
+        tgt_t = cur_ts if l == 0 else cur_ts[last_inv]
+        r_n, r_d, r_t, r_dt, r_e, _ = sample_layer(indptr, nbr, ts, eid, tgt, tgt_t, k, policy, stream=l, **kw)
+        if len(r_n) == 0 and not ((indptr[tgt + 1] - indptr[tgt]) > 0).any():
+            # the reference stops here when no target has any edge (prepare_sample.py:352-361)
+            out.append({"indptr": np.zeros(1, I64), "indices": np.zeros(0, I64), "eid": np.zeros(0, I64),
+                        "edge_ts": np.zeros(0, I64), "edge_dt": np.zeros(0, np.float32),
+                        "gids": np.zeros(0, I64), "ts": np.zeros(0, I64)})
+            break
+        d_map = last_inv[r_d] if last_inv is not None else r_d
+        n_id, n_ts, n_inv = merge_and_map(cur_id, cur_ts, r_n, r_t)
+        ptr, idx, b_ts, b_dt, b_e = build_csc(n_inv, d_map, r_t, r_dt, r_e, len(cur_id))
+        out.append({"indptr": ptr, "indices": idx, "eid": b_e, "edge_ts": b_ts, "edge_dt": b_dt,
+                    "gids": n_id, "ts": n_ts})
+        cur_id, cur_ts, last_inv = n_id, n_ts, n_inv
+    return out
+
+
+def relabel_nodes(id_lists):
+    """Node-level relabel of csrc/include/starrygl/sample.cu.hpp:1766-1852.
+
+    ``id_lists`` = [roots, layer-1 neighbours, layer-2 neighbours, ...].  Local ids are handed out list by
+    list; inside a list the not-yet-seen ids get consecutive numbers in ascending global id.  Returns
+    (list of local-id arrays, nodes_remapper_id) with nodes_remapper_id[local] = global.
+    """
+    seen = {}
+    order = []
+    out = []
+    for ids in id_lists:
+        new = sorted(set(int(x) for x in ids if int(x) not in seen))
+        for g in new:
+            seen[g] = len(order)
+            order.append(g)
+        out.append(np.array([seen[int(x)] for x in ids], I64))
+    return out, np.array(order, I64)
+
+
+# ----------------------------------------------------------------------------------------------
+# ids, gather, cache
+# ----------------------------------------------------------------------------------------------
+
+LOC_MASK = (1 << 48) - 1
+PART_MASK = 0x3FFF
+
+
+def dist_pack(loc, part, shared=None):
+    """starrygl/utils/partition_book.py:19-37."""
+    d = (np.asarray(loc, I64) & LOC_MASK) | ((np.asarray(part, I64) & PART_MASK) << 48)
+    if shared is not None:
+        d = d | (np.asarray(shared, I64) << 62)
+    return d
+
+
+def dist_unpack(d):
+    """starrygl/utils/partition_book.py:28-41 -> (loc, part, is_shared)."""
+    d = np.asarray(d, I64)
+    return d & LOC_MASK, (d >> 48) & PART_MASK, (d >> 62).astype(bool)
+
+
+def build_g2l(loc_ids, global_num):
+    """starrygl/utils/partition_book.py:98-104."""
+    m = np.full(global_num + 1, -1, I64)
+    m[loc_ids] = np.arange(len(loc_ids), dtype=I64)
+    return m
+
+
+def gather_rows(table, idx):
+    return table[idx]
+
+
+def state_read(data, ts, g2l, gids):
+    """starrygl/cache/NodeState.py:36-44 with IDMapper mode 'map'."""
+    loc = g2l[gids]
+    return data[loc], ts[loc]
+
+
+def state_update(data, ts, g2l, gids, values, new_ts):
+    """starrygl/cache/NodeState.py:46-61: rows whose id is not stored locally (slot < 0) are skipped."""
+    loc = g2l[gids]
+    m = loc >= 0
+    data[loc[m]] = values[m]
+    if new_ts is not None:
+        ts[loc[m]] = new_ts[m]
+
+
+def cache_gather(cache_rows, hitmap, backing, ids):
+    """Hit/miss split of the GPU-cache design in starrygl/cache/NodeState.py:152-194.
+
+    slot = hitmap[id]; slot >= 0 -> row from ``cache_rows[slot]``, else from ``backing[id]``.  Returns
+    (rows, hit_mask, miss_pos ascending, miss_ids).
+    """
+    slot = hitmap[ids]
+    hit = slot >= 0
+    out = np.empty((len(ids), backing.shape[1]), backing.dtype)
+    out[hit] = cache_rows[slot[hit]]
+    miss_pos = np.nonzero(~hit)[0].astype(I64)
+    out[miss_pos] = backing[ids[miss_pos]]
+    return out, hit, miss_pos, ids[miss_pos]
+
+
+def build_replica_table(num_nodes, partition_book):
+    """starrygl/cache/replica_table.py:178-215 -- CSR over node id of (rank, loc), sorted by (node, rank, loc)."""
+    trip = []
+    for p, nodes in enumerate(partition_book):
+        nodes = np.asarray(nodes, I64)
+        trip.append(np.stack([nodes, np.full(len(nodes), p, I64), np.arange(len(nodes), dtype=I64)]))
+    allp = np.concatenate(trip, axis=1) if trip else np.zeros((3, 0), I64)
+    u = np.unique(allp, axis=1)
+    indptr = np.zeros(num_nodes + 1, I64)
+    indptr[1:] = np.cumsum(np.bincount(u[0], minlength=num_nodes))
+    return indptr, u[1].copy(), u[2].copy()
+
+
+def replica_lookup(indptr, ranks, locs, ids):
+    """starrygl/cache/replica_table.py:16-82 -> (src_indices, target_ranks, target_locs)."""
+    s, e = indptr[ids], indptr[ids + 1]
+    ln = e - s
+    src = np.repeat(np.arange(len(ids), dtype=I64), ln)
+    base = np.repeat(s, ln)
+    inner = np.arange(ln.sum(), dtype=I64) - np.repeat(np.cumsum(ln) - ln, ln)
+    g = base + inner
+    return src, ranks[g], locs[g]
+
+
+# ----------------------------------------------------------------------------------------------
+# route (all ranks simulated in one process)
+# ----------------------------------------------------------------------------------------------
+
+
+def cache_route(feats, send_sizes, send_indices, send_remote, data, ts):
+    """starrygl/cache/cache_route.py:211-277 + starrygl/cache/NodeState.py:269-274, all ranks at once.
+
+    ``feats[r]`` [n_r, D+1]; ``send_sizes[r]`` [P]; ``send_indices[r]`` / ``send_remote[r]`` [S_r] grouped by
+    destination rank.  Receiver q gets the segments of senders 0..P-1 in rank order and writes
+    ``data[q][idx] = row[:-1]``, ``ts[q][idx] = row[-1]``.  Returns per receiver (recv_idx, recv_rows).
+    """
+    P = len(feats)
+    offs = [np.concatenate([[0], np.cumsum(send_sizes[r])]) for r in range(P)]
+    got = []
+    for q in range(P):
+        idx, rows = [], []
+        for r in range(P):
+            a, b = int(offs[r][q]), int(offs[r][q + 1])
+            idx.append(np.asarray(send_remote[r][a:b], I64))
+            rows.append(feats[r][np.asarray(send_indices[r][a:b], I64)])
+        idx = np.concatenate(idx)
+        rows = np.concatenate(rows) if len(idx) else np.zeros((0, feats[q].shape[1]), feats[q].dtype)
+        if len(idx):
+            data[q][idx] = rows[:, :-1]
+            ts[q][idx] = rows[:, -1]
+        got.append((idx, rows))
+    return got
+
+
+def route_forward(xs, send_sizes, recv_sizes, send_index):
+    """starrygl/route/route.py:427-442 on every rank: ``cat([x, a2a(x[send_index])])``."""
+    P = len(xs)
+    offs = [np.concatenate([[0], np.cumsum(send_sizes[r])]).astype(int) for r in range(P)]
+    ys = []
+    for q in range(P):
+        parts = [xs[q]]
+        for r in range(P):
+            seg = send_index[r][offs[r][q]:offs[r][q + 1]]
+            assert len(seg) == recv_sizes[q][r]
+            parts.append(xs[r][seg])
+        ys.append(np.concatenate(parts))
+    return ys
+
+
+def route_reverse(gs, send_sizes, recv_sizes, send_index):
+    """starrygl/route/route.py:444-466 on every rank: the halo tail goes back to its owners and is
+    added into ``x[send_index[seg]]`` peer segment by peer segment (duplicates inside one segment keep
+    the last write of ``x[idx] += v``, exactly as torch advanced indexing does)."""
+    P = len(gs)
+    roffs = [np.concatenate([[0], np.cumsum(recv_sizes[r])]).astype(int) for r in range(P)]
+    soffs = [np.concatenate([[0], np.cumsum(send_sizes[r])]).astype(int) for r in range(P)]
+    outs = []
+    for r in range(P):
+        n = len(gs[r]) - int(np.sum(recv_sizes[r]))
+        x = gs[r][:n].copy()
+        for q in range(P):   # what q received from r comes back to r
+            tail = gs[q][len(gs[q]) - int(np.sum(recv_sizes[q])):]
+            back = tail[roffs[q][r]:roffs[q][r + 1]]
+            seg = send_index[r][soffs[r][q]:soffs[r][q + 1]]
+            x[seg] += back
+        outs.append(x)
+    return outs

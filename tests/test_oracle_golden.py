@@ -1,0 +1,137 @@
+"""The numpy oracle against vectors produced by running the reference (tests/golden/make_golden.py)."""
+import os
+
+import numpy as np
+import pytest
+from scipy import stats
+
+from oracle import oracle_np as O
+
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def load(name):
+    return np.load(os.path.join(G, name))
+
+
+@pytest.mark.parametrize("case", ["tiny", "rand_sorted", "rand_ties"])
+def test_tcsr_and_recent(case):
+    z = load(f"sampler_{case}.npz")
+    n = int(z["n"])
+    # the reference keys rows by dst and returns src as the neighbour
+    indptr, nbr, ts, eid, _ = O.tcsr_build(z["dst"], z["src"], z["ts"], z["eid"], n)
+    assert np.array_equal(indptr, z["indptr"])
+    assert np.array_equal(nbr, z["s_src"])
+    assert np.array_equal(ts, z["s_ts"])
+    assert np.array_equal(eid, z["s_eid"])
+    for k in (1, 3, 10):
+        for e in (0, 1):
+            o = O.sample_layer(indptr, nbr, ts, eid, z["q"], z["qt"], k, O.RECENT, equal_root_time=bool(e))
+            tag = f"recent_k{k}_e{e}"
+            for nm, a in zip(("src", "dst", "ts", "dt", "eid"), o[:5]):
+                ref = z[f"{tag}_{nm}"]
+                assert a.dtype == ref.dtype, (tag, nm)
+                assert np.array_equal(a, ref), (tag, nm)
+
+
+def test_worked_example():
+    z = load("sampler_tiny.npz")
+    indptr, nbr, ts, eid, _ = O.tcsr_build(z["dst"], z["src"], z["ts"], z["eid"], 8)
+    o = O.sample_layer(indptr, nbr, ts, eid, [0, 7, 3], [51, 51, 51], 3)
+    assert o[0].tolist() == [4, 5, 6, 0, 0]
+    assert o[1].tolist() == [0, 0, 0, 1, 1]
+    assert o[2].tolist() == [30, 40, 50, 25, 35]
+    assert o[3].tolist() == [21.0, 11.0, 1.0, 26.0, 16.0]
+    assert o[4].tolist() == [3, 4, 5, 6, 7]
+    o = O.sample_layer(indptr, nbr, ts, eid, [0, 7, 3], [10, 10, 10], 3)
+    assert len(o[0]) == 0
+
+
+@pytest.mark.parametrize("case", ["tiny", "rand", "rand_k10"])
+def test_batch(case):
+    z = load(f"batch_{case}.npz")
+    n = int(z["n"])
+    indptr, nbr, ts, eid, _ = O.tcsr_build(z["dst"], z["src"], z["ts"], z["eid"], n)
+    roots = np.concatenate([z["task_src"], z["task_dst"]])
+    rts = np.concatenate([z["task_ts"], z["task_ts"]])
+    out = O.build_batch(indptr, nbr, ts, eid, roots, rts, z["fanouts"].tolist())
+    assert len(out) == int(z["num_layers"])
+    for i, d in enumerate(out):
+        for k, v in d.items():
+            ref = z[f"L{i}_{k}"]
+            assert v.dtype == ref.dtype, (i, k, v.dtype, ref.dtype)
+            assert np.array_equal(v, ref), (i, k)
+
+
+def test_uniform_distribution_matches_reference():
+    z = load("uniform_hist.npz")
+    m, k, trials = int(z["cands"]), int(z["k"]), int(z["trials"])
+    hist = np.zeros(m, np.int64)
+    for i in range(trials):
+        p = O.uniform_positions(m, k, seed=0, stream=0, slot=i)
+        assert len(set(p)) == k and p == sorted(p) and 0 <= p[0] and p[-1] < m
+        hist[p] += 1
+    # both histograms against the exact law (every position equally likely) ...
+    exp = np.full(m, trials * k / m)
+    assert stats.chisquare(hist, exp).pvalue > 1e-3
+    assert stats.chisquare(z["hist"], exp).pvalue > 1e-3
+    # ... and against each other (homogeneity)
+    assert stats.chi2_contingency(np.stack([hist, z["hist"]]))[1] > 1e-3
+
+
+def test_philox_known_answer():
+    # Random123 known-answer vectors for philox4x32-10
+    assert O.philox4x32_10((0, 0, 0, 0), (0, 0)) == (0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8)
+    assert O.philox4x32_10((0xffffffff,) * 4, (0xffffffff, 0xffffffff)) == (0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd)
+    assert O.philox4x32_10((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0)) == \
+        (0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1)
+
+
+def test_ids_and_replicas():
+    z = load("ids.npz")
+    sh = np.zeros(64, np.int64)
+    sh[z["shared_idx"]] = 1
+    d = O.dist_pack(z["loc"], z["part"], sh)
+    assert np.array_equal(d, z["dist"])
+    loc, part, shared = O.dist_unpack(z["dist"])
+    assert np.array_equal(loc, z["u_loc"]) and np.array_equal(part, z["u_part"]) and np.array_equal(shared, z["u_shared"])
+    book = [z[f"book{p}"] for p in range(4)]
+    indptr, ranks, locs = O.build_replica_table(200, book)
+    assert np.array_equal(indptr, z["rt_indptr"]) and np.array_equal(ranks, z["rt_ranks"]) and np.array_equal(locs, z["rt_locs"])
+    s, r, l = O.replica_lookup(indptr, ranks, locs, z["lk_ids"])
+    assert np.array_equal(s, z["lk_src"]) and np.array_equal(r, z["lk_ranks"]) and np.array_equal(l, z["lk_locs"])
+
+
+def test_nodestate():
+    z = load("nodestate.npz")
+    g2l = O.build_g2l(z["loc_ids"], int(z["num_nodes"]))
+    data = np.zeros_like(z["data"])
+    ts = np.zeros_like(z["ts"])
+    O.state_update(data, ts, g2l, z["upd"], z["vals"], z["uts"])
+    assert np.array_equal(data, z["data"]) and np.array_equal(ts, z["ts"])
+    got, gts = O.state_read(data, ts, g2l, z["rd"])
+    assert np.array_equal(got, z["got"]) and np.array_equal(gts, z["got_ts"])
+    loc = g2l[z["rd"]]
+    assert np.array_equal((loc >= 0) & (loc < 25), z["is_master"])
+
+
+def test_route_two_ranks():
+    z = load("route_2rank.npz")
+    P = 2
+    feats = [z[f"r{r}_feats"] for r in range(P)]
+    data = [np.zeros_like(z[f"r{r}_data"]) for r in range(P)]
+    ts = [np.zeros_like(z[f"r{r}_ts"]) for r in range(P)]
+    O.cache_route(feats, [z[f"r{r}_send_sizes"] for r in range(P)], [z[f"r{r}_send_indices"] for r in range(P)],
+                  [z[f"r{r}_send_remote"] for r in range(P)], data, ts)
+    for r in range(P):
+        assert np.array_equal(data[r], z[f"r{r}_data"]) and np.array_equal(ts[r], z[f"r{r}_ts"])
+    ss = [z[f"r{r}_r_send_sizes"] for r in range(P)]
+    rs = [z[f"r{r}_r_recv_sizes"] for r in range(P)]
+    si = [z[f"r{r}_r_send_index"] for r in range(P)]
+    ys = O.route_forward([z[f"r{r}_x"] for r in range(P)], ss, rs, si)
+    for r in range(P):
+        assert np.array_equal(ys[r], z[f"r{r}_y"])
+    # backward of sum(y*w) w.r.t. x = reverse route of w
+    gx = O.route_reverse([z[f"r{r}_w"] for r in range(P)], ss, rs, si)
+    for r in range(P):
+        assert np.allclose(gx[r], z[f"r{r}_gx"], rtol=0, atol=0)
