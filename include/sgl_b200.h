@@ -1,0 +1,266 @@
+/*
+ * sgl_b200.h -- C ABI of libsgl_b200.so: the per-mini-batch data path of a temporal-GNN trainer
+ * (T-CSR build, temporal neighbour sampling, relabel, feature/memory gather through a cache, route
+ * pack/unpack) as hand-written sm_100a CUDA kernels.
+ *
+ * Conventions
+ *   - Every function returns 0 on success or a negative SGL_ERR_* code; sgl_last_error() gives the
+ *     message of the last failure on the calling thread.  Nothing throws across this boundary.
+ *   - Pointers are DEVICE pointers unless the parameter name starts with h_.  `stream` is a
+ *     cudaStream_t passed as void*; work is only ever enqueued on that stream (never on the default
+ *     stream unless the caller passes it) and, unless stated, the call returns without synchronising.
+ *   - The library allocates no device memory on these paths: scratch comes from the caller as
+ *     (ws, ws_bytes); the *_ws_bytes() functions give the required size.  ws must be 256-byte aligned.
+ *   - `d_status` is an optional device int32 the kernels OR error bits into (SGL_DEV_*); the caller
+ *     zeroes it and reads it back at its own synchronisation points.
+ *   - Counts that are only known on the device (the number of edges a hop produced) can be chained to
+ *     the next call through `d_n` parameters: a device int64 that overrides the host count, which then
+ *     only acts as the capacity the launch is sized for.
+ *   - Callable from any host thread (no Python, no global locks); the device of the pointers must be
+ *     current on the calling thread.
+ *
+ * Each entry point names the reference interface it replaces (path inside the reference project).
+ */
+#ifndef SGL_B200_H
+#define SGL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SGL_OK 0
+#define SGL_ERR_ARG (-1)         /* bad argument (null pointer, negative size, misaligned buffer) */
+#define SGL_ERR_WORKSPACE (-2)   /* workspace too small */
+#define SGL_ERR_CUDA (-3)        /* a CUDA runtime call failed */
+#define SGL_ERR_RANGE (-4)       /* an id or timestamp outside the declared range was found */
+#define SGL_ERR_UNSUPPORTED (-5) /* valid request the kernels do not cover (see message) */
+
+/* bits OR-ed into *d_status by kernels */
+#define SGL_DEV_BAD_NODE 1   /* node id outside [0, num_nodes) */
+#define SGL_DEV_BAD_TS 2     /* timestamp outside the declared [ts_base, ts_base + 2^ts_bits) window */
+#define SGL_DEV_BAD_INDEX 4  /* row index outside the table */
+#define SGL_DEV_OVERFLOW 8   /* an output capacity was exceeded */
+#define SGL_DEV_TIMEOUT 16   /* a bounded device-side wait gave up (copy engine did not signal in time) */
+
+#define SGL_POLICY_RECENT 0
+#define SGL_POLICY_UNIFORM 1
+#define SGL_MAX_UNIFORM_FANOUT 32
+
+const char* sgl_last_error(void);
+/* Library version and the SM architecture the kernels were compiled for ("sm_100a"). */
+const char* sgl_build_info(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Stable LSD radix sort of 64-bit keys carrying a 32-bit payload (used by the T-CSR build and the
+ * relabel; exported so it can be tested on its own).  Sorts on key bits [0, num_bits).  On return
+ * *h_result_in_alt tells whether the sorted data are in (keys, vals) [0] or in (keys_alt, vals_alt) [1].
+ * Replaces: thrust::sort calls in csrc/include/starrygl/sample.cu.hpp:1078, :1197, :1795.
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_radix_sort_ws_bytes(int64_t n);
+int sgl_radix_sort_u64_u32(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_t* vals_alt, int64_t n,
+                           int num_bits, int* h_result_in_alt, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * T-CSR construction.  Rows are keyed by `key` (node id in [0, num_nodes)); inside a row edges are in
+ * ascending `ts`, ties in input order.  eid may be NULL (edge id = input position).
+ * Outputs: indptr[num_nodes+1], nbr/ts/eid[m] in row order, perm[m] (optional) = input position of
+ * every sorted edge.  h_ts_range[2] (optional, host) receives min and max timestamp.
+ * Synchronises the stream once (the number of sort passes depends on the timestamp range).
+ * Replaces: Graph::Graph + build_graph_kernel (csrc/include/starrygl/sample.cu.hpp:985-1185, :83-114)
+ * reached through from_edge_index (csrc/srcs/starrygl/export.cu:229-250); CPU twin
+ * MaterializedMultiLayerBuilder.__init__ (prepare_sample.py:179-203).
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_tcsr_build_ws_bytes(int64_t num_nodes, int64_t m);
+int sgl_tcsr_build(int64_t num_nodes, int64_t m, const int64_t* key, const int64_t* nbr, const int64_t* ts,
+                   const int64_t* eid, int64_t* indptr, int64_t* out_nbr, int64_t* out_ts, int64_t* out_eid,
+                   int64_t* out_perm, int64_t* h_ts_range, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * One hop of temporal neighbour sampling, one warp per target.
+ * Target i = (targets[i], target_ts[i]).  Candidates: row edges with ts < t (ts <= t when
+ * equal_root_time; additionally ts >= t - allowed_offset when allowed_offset >= 0).
+ *   RECENT : the last min(fanout, candidates), ascending time.
+ *   UNIFORM: all candidates if there are <= fanout, else fanout distinct positions chosen with
+ *            Philox4x32-10 keyed by (seed; target index i, rng_stream), ascending position.
+ * Outputs are compact, in target order: out_nbr/out_dst/out_ts/out_eid int64, out_dt float32 = t - ts,
+ * out_dst = i; out_offsets[n_targets+1] (exclusive prefix of per-target counts; last = total).
+ * out_dt_i64 (optional) additionally receives ts - t as int64, the sign and type of the reference's
+ * CUDA result type (TemporalNeighbor.neighbors_dt, csrc/include/starrygl/sample.cu.hpp:751, :811).
+ * Output arrays need capacity n_targets * fanout.  keep_root_time writes t instead of the edge time.
+ * d_n (optional): device count of valid targets (<= n_targets).
+ * Replaces: sample_src_in_chunks_khop + static_recent_neighbor_num / recent_sample_single_hop_kernel /
+ * static_neighbor_num / uniform_sample_single_hop_kernel (csrc/include/starrygl/sample.cu.hpp:1532-1716,
+ * :706-827); CPU twin _jit_sample_kernel (prepare_sample.py:32-172).
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_sample_ws_bytes(int64_t n_targets);
+int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                     int64_t num_nodes, const int64_t* targets, const int64_t* target_ts, int64_t n_targets,
+                     const int64_t* d_n, int fanout, int policy, int equal_root_time, int64_t allowed_offset,
+                     int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* out_nbr, int64_t* out_dst,
+                     int64_t* out_ts, float* out_dt, int64_t* out_dt_i64, int64_t* out_eid, int64_t* out_offsets,
+                     int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * (node, ts)-pair relabel.  Input = two concatenated segments A (n_a items) then B (n_b items);
+ * output = the sorted (id, then ts) unique union, its size (*d_n_unique, device), and for every input
+ * item the rank of its pair in the union (inv_a, inv_b; either may be NULL).  Timestamps must lie in
+ * [ts_base, ts_base + 2^ts_bits) and ids in [0, 2^id_bits); id_bits + ts_bits <= 64.
+ * d_n_a / d_n_b (optional) are device counts overriding n_a / n_b (which remain the capacities).
+ * Replaces: _get_unique_pairs (A only) and _merge_and_map_nodes (A = current list, B = new pairs)
+ * (prepare_sample.py:205-213, :231-246).
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_unique_pairs_ws_bytes(int64_t n_total);
+int sgl_unique_pairs(const int64_t* a_id, const int64_t* a_ts, int64_t n_a, const int64_t* d_n_a,
+                     const int64_t* b_id, const int64_t* b_ts, int64_t n_b, const int64_t* d_n_b, int id_bits,
+                     int ts_bits, int64_t ts_base, int64_t* out_id, int64_t* out_ts, int64_t* inv_a, int64_t* inv_b,
+                     int64_t* d_n_unique, int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * CSC of one sampled hop: stable order by (dst_local, ts); indptr over the num_dst rows of the
+ * previous node list.  dst_map (optional): dst_local = dst_map[dst[e]] (the previous hop's inverse map),
+ * else dst_local = dst[e].  num_dst may be overridden by the device count d_num_dst (indptr is then
+ * written for d_num_dst+1 entries; capacity num_dst+1).
+ * Replaces: _build_csc_from_pairs (prepare_sample.py:215-229).
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_build_csc_ws_bytes(int64_t n_edges, int64_t num_dst);
+int sgl_build_csc(const int64_t* src_local, const int64_t* dst, const int64_t* dst_map, const int64_t* ts,
+                  const float* dt, const int64_t* eid, int64_t n_edges, const int64_t* d_n_edges, int64_t num_dst,
+                  const int64_t* d_num_dst, int dst_bits, int ts_bits, int64_t ts_base, int64_t* out_indptr,
+                  int64_t* out_indices, int64_t* out_ts, float* out_dt, int64_t* out_eid, int32_t* d_status,
+                  void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Node-level relabel of one id list against an epoch table.  mapper[num_nodes] and mask[num_nodes]
+ * persist across calls; ids whose mask != epoch are new: they get consecutive local ids starting at
+ * *d_next_local in ascending global id, are appended to out_new_ids, and the tables are updated.
+ * out_local[i] = local id of ids[i].  *d_next_local is advanced; *d_n_new receives the number appended.
+ * Replaces: Remapper::remapper + mark_new_ids_kernel / update_new_ids_kernel
+ * (csrc/include/starrygl/sample.cu.hpp:1719-1824).
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_relabel_nodes_ws_bytes(int64_t n);
+int sgl_relabel_nodes(const int64_t* ids, int64_t n, const int64_t* d_n, int64_t num_nodes, int64_t* mapper,
+                      int64_t* mask, int64_t epoch, int64_t* d_next_local, int64_t* out_local, int64_t* out_new_ids,
+                      int64_t* d_n_new, int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Row gather: out[i, :] = table[row(i), :], row(i) = map ? map[idx[i]] : idx[i]; a negative row counts
+ * from the end (the indexing rule of the reference's tensor indexing).  row_bytes is the payload per
+ * row, src_pitch / dst_pitch the distance between rows in bytes.  ts_table (optional, float32): also
+ * out_ts[i] = ts_table[row(i)].  Rows that are 16-byte multiples on 16-byte aligned bases move as
+ * 128-bit lanes or as bulk asynchronous copies staged through shared memory; others as 4-byte lanes.
+ * Replaces: DistNodeState.__getitem__ / IDMapper.to_local (starrygl/cache/NodeState.py:36-44,
+ * starrygl/utils/partition_book.py:106-133), edge-feature and mailbox row reads
+ * (starrygl/nn/model/tgn.py:161-162, starrygl/nn/memory/mailbox.py:92-93), tensor_gather
+ * (csrc/include/starrygl/feature.cu.hpp:42-88).
+ * ---------------------------------------------------------------------------------------------- */
+#define SGL_GATHER_AUTO 0
+#define SGL_GATHER_VEC 1   /* 128-bit lanes */
+#define SGL_GATHER_BULK 2  /* cp.async.bulk through shared memory */
+int sgl_gather_rows(const void* table, int64_t table_rows, int64_t row_bytes, int64_t src_pitch, const int64_t* idx,
+                    const int64_t* map, int64_t map_len, int64_t n, const int64_t* d_n, void* out, int64_t dst_pitch,
+                    const float* ts_table, float* out_ts, int mode, int32_t* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Gather through a device-resident cache.  slot = hitmap[ids[i]] (int32; < 0 = miss).  Hits are copied
+ * from cache_rows[slot]; misses from backing[ids[i]] when backing != NULL (any device-accessible
+ * memory, e.g. mapped pinned host memory), else left untouched.  The misses are compacted in
+ * ascending i into miss_pos (position i) and miss_ids (ids[i]); counts[0] = hits, counts[1] = misses.
+ * Replaces: the hit/miss split designed in CachedNodeState.get (starrygl/cache/NodeState.py:152-194).
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_cache_gather_ws_bytes(int64_t n);
+int sgl_cache_gather(const void* cache_rows, int64_t cache_slots, const int32_t* hitmap, int64_t num_ids,
+                     const void* backing, int64_t row_bytes, const int64_t* ids, int64_t n, void* out,
+                     int64_t* miss_pos, int64_t* miss_ids, int64_t* d_counts, int32_t* d_status, void* ws,
+                     size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Row scatter: table[row(i), :] = rows[i, :] for rows with row(i) >= 0 (row(i) = map ? map[idx[i]] :
+ * idx[i]); optional ts_table[row(i)] = ts[i].  With split_last_col the source rows carry one extra
+ * trailing float32 column that goes to ts_table instead of `ts` (the embedding||ts wire rows).
+ * Duplicate destination rows inside one call are a data race (as in the reference).
+ * Replaces: DistNodeState.update (starrygl/cache/NodeState.py:46-61), remote_write_callback
+ * (starrygl/cache/NodeState.py:269-274).
+ * ---------------------------------------------------------------------------------------------- */
+int sgl_scatter_rows(void* table, int64_t table_rows, int64_t row_bytes, int64_t dst_pitch, const int64_t* idx,
+                     const int64_t* map, int64_t map_len, int64_t n, const int64_t* d_n, const void* rows,
+                     int64_t src_pitch, float* ts_table, const float* ts, int split_last_col, int32_t* d_status,
+                     void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Route pack: the send buffer of the all-to-all, already grouped by destination rank because send_idx is.
+ *   packed[i, 0:D] = feats[send_idx[i], 0:D]
+ *   packed[i, D]   = ts[send_idx[i]]                 when ts != NULL
+ *   packed[i, W:W+2] = remote_idx[i] (int64 as two 32-bit words, W = D or D+1)   when remote_idx != NULL
+ * float32 rows of width W (+2).  Replaces: torch.cat([emb, ts]) + local_features[plan.send_indices] and the
+ * separate index message (starrygl/cache/NodeState.py:267, starrygl/cache/cache_route.py:243-258), and
+ * x[send_index] (starrygl/route/route.py:428).
+ * ---------------------------------------------------------------------------------------------- */
+int sgl_route_pack(const float* feats, int64_t n_rows, int64_t dim, const float* ts, const int64_t* send_idx,
+                   const int64_t* remote_idx, int64_t n_send, float* packed, int32_t* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Route unpack (receiver side of the wire format above, rows of `width` + 2 floats): slot = the trailing
+ * int64; data[slot, 0:dim] = row[0:dim]; ts_table[slot] = row[dim] when ts_table != NULL (width = dim + 1).
+ * Replaces: remote_write_callback (starrygl/cache/NodeState.py:269-274).
+ * ---------------------------------------------------------------------------------------------- */
+int sgl_route_unpack(const float* packed, int64_t n, int64_t width, float* data, int64_t data_rows, int64_t dim,
+                     float* ts_table, int32_t* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Reverse route accumulate: x[send_idx[s + j], :] += outs[s + j, :] for the peer segment [s, s + len);
+ * one call per peer segment, in peer order, keeps the reference's summation order.
+ * Replaces: the per-peer loop of RouteContext._recv_post (starrygl/route/route.py:461-464).
+ * ---------------------------------------------------------------------------------------------- */
+int sgl_route_add_rows(float* x, int64_t n_rows, int64_t dim, const int64_t* send_idx, const float* outs,
+                       int64_t seg_len, int32_t* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * DistRouteIndex packing: dist = (loc & (2^48-1)) | ((part & 0x3FFF) << 48) | (shared << 62).
+ * Replaces: DistRouteIndex (starrygl/utils/partition_book.py:7-52); device twins get_partition /
+ * get_loc / is_shared (csrc/include/starrygl/feature.cu.hpp:16-28).
+ * ---------------------------------------------------------------------------------------------- */
+int sgl_dist_pack(const int64_t* loc, const int64_t* part, const uint8_t* shared, int64_t n, int64_t* dist,
+                  void* stream);
+int sgl_dist_unpack(const int64_t* dist, int64_t n, int64_t* loc, int64_t* part, uint8_t* shared, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Replica lookup: for ids[i] the CSR row [indptr[id], indptr[id+1]) of (rank, loc) replicas is expanded:
+ * out_src = i repeated, out_rank, out_loc; out_offsets[n+1] = exclusive prefix of row lengths.
+ * Output capacity `cap`; overflow sets SGL_DEV_OVERFLOW.
+ * Replaces: CSRReplicaTable.lookup (starrygl/cache/replica_table.py:16-82).
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_replica_lookup_ws_bytes(int64_t n);
+int sgl_replica_lookup(const int64_t* indptr, const int64_t* ranks, const int64_t* locs, int64_t num_nodes,
+                       const int64_t* ids, int64_t n, int64_t cap, int64_t* out_src, int64_t* out_rank,
+                       int64_t* out_loc, int64_t* out_offsets, int32_t* d_status, void* ws, size_t ws_bytes,
+                       void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Roots of a batch = the events of one time window.  Input: the window's slice of the time-ordered event
+ * arrays (source node, timestamp, edge id; n_events items).  Events whose source node lies in a selected
+ * chunk (chunk_mask[node_chunk[src]] != 0; both NULL = every node) are grouped by (src, ts):
+ *   out_roots[r]                     distinct source nodes, ascending
+ *   out_ts[out_ts_ptr[r] .. out_ts_ptr[r+1])   the root's distinct event timestamps, ascending
+ *   out_q_eid[out_q_ptr[q] .. out_q_ptr[q+1])  edge ids of the events behind (root, timestamp) pair q, input order
+ * d_counts[3] = {#roots, #pairs, #selected events}.  All outputs need capacity n_events (+1 for the ptr arrays).
+ * Replaces: get_seeds_in_chunks + filter_seeds_kernel / collect_seeds_kernel
+ * (csrc/include/starrygl/sample.cu.hpp:1303-1449, :517-705) for using_full_timestamp = false.
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_seeds_ws_bytes(int64_t n_events);
+int sgl_seeds_in_window(const int64_t* ev_src, const int64_t* ev_ts, const int64_t* ev_eid, int64_t n_events,
+                        const int64_t* node_chunk, const uint8_t* chunk_mask, int64_t num_chunks, int64_t num_nodes,
+                        int id_bits, int ts_bits, int64_t ts_base, int64_t* out_roots, int64_t* out_ts_ptr,
+                        int64_t* out_ts, int64_t* out_q_ptr, int64_t* out_q_eid, int64_t* d_counts, int32_t* d_status,
+                        void* ws, size_t ws_bytes, void* stream);
+
+/* out[i] = first position p with sorted[p] >= values[i] (n when none); k values.  Used to find the slice of the
+ * time-ordered event arrays that a window [t_begin, t_end) covers. */
+int sgl_lower_bound_i64(const int64_t* sorted, int64_t n, const int64_t* values, int k, int64_t* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SGL_B200_H */

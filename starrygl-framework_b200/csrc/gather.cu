@@ -1,0 +1,686 @@
+// Row gather / scatter kernels of the feature and node-memory path.
+//
+//   gather_lanes_kernel<V>  flattened copy: consecutive threads move consecutive V-byte lanes (V = 16: 128-bit
+//                           loads/stores; V = 4 for rows that are not 16-byte multiples), so every warp reads one
+//                           contiguous piece of a source row and writes one contiguous piece of the output.
+//   gather_bulk_kernel      per-warp pipeline of bulk asynchronous copies: each lane asks the copy engine for one
+//                           source row (global -> shared, completion counted on an mbarrier), then one lane
+//                           writes the whole stage back with a single shared -> global bulk copy.  The payload
+//                           never passes through registers.  All waits are bounded.
+//   cache_lookup_kernel +   hit-map lookup, deterministic miss compaction (CTA scan + last-CTA scan of CTA
+//   cache_copy_kernel       totals), then one flattened copy that picks cache or backing store per row.
+//   scatter_lanes_kernel    the reverse of the gather, optionally splitting a trailing timestamp column.
+//
+// Algorithmic HBM bytes: rows * (2 * row_bytes + 8) (+4 per id for the hit-map, +16 per miss for the miss list).
+#include "common.cuh"
+#include "scan.cuh"
+
+namespace sgl {
+namespace {
+
+constexpr int kLaneThreads = 256;
+constexpr int kLaneUnroll = 4;
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_stream(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream(uint4* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_stream(uint32_t* p, uint32_t v) {
+  asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// resolve the source/destination row of item i; returns false when the row must be skipped
+__device__ __forceinline__ bool resolve_row(const int64_t* __restrict__ idx, const int64_t* __restrict__ map,
+                                            int64_t map_len, int64_t table_rows, int64_t i, bool wrap_negative,
+                                            int32_t* d_status, int64_t* row) {
+  int64_t r = __ldg(idx + i);
+  if (map) {
+    if (r < 0 || r >= map_len) {
+      dev_flag(d_status, SGL_DEV_BAD_INDEX);
+      return false;
+    }
+    r = __ldg(map + r);
+  }
+  if (r < 0) {
+    if (!wrap_negative) return false;  // "not stored here": skipped silently
+    r += table_rows;
+  }
+  if (r < 0 || r >= table_rows) {
+    dev_flag(d_status, SGL_DEV_BAD_INDEX);
+    return false;
+  }
+  *row = r;
+  return true;
+}
+
+template <typename V>
+__global__ void __launch_bounds__(kLaneThreads)
+gather_lanes_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t lanes_per_row, int64_t src_pitch,
+                    const int64_t* __restrict__ idx, const int64_t* __restrict__ map, int64_t map_len, int64_t n_cap,
+                    const int64_t* d_n, char* __restrict__ out, int64_t dst_pitch, const float* __restrict__ ts_table,
+                    float* __restrict__ out_ts, int32_t* d_status) {
+  const int64_t n = eff_count(n_cap, d_n);
+  const int64_t total = n * lanes_per_row;
+  const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
+  for (int64_t q0 = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q0 < total; q0 += stride * kLaneUnroll) {
+    V v[kLaneUnroll];
+    V* dst[kLaneUnroll];
+#pragma unroll
+    for (int u = 0; u < kLaneUnroll; ++u) {
+      int64_t q = q0 + u * stride;
+      dst[u] = nullptr;
+      if (q < total) {
+        int64_t i = q / lanes_per_row;
+        uint32_t l = (uint32_t)(q - i * lanes_per_row);
+        int64_t r;
+        if (resolve_row(idx, map, map_len, table_rows, i, true, d_status, &r)) {
+          v[u] = ld_stream((const V*)(table + r * src_pitch) + l);
+          dst[u] = (V*)(out + i * dst_pitch) + l;
+          if (l == 0 && ts_table) out_ts[i] = __ldg(ts_table + r);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kLaneUnroll; ++u)
+      if (dst[u]) st_stream(dst[u], v[u]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// bulk asynchronous copy path
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kBulkWarps = 4;
+constexpr int kBulkStages = 3;
+constexpr unsigned long long kBulkWaitLimitNs = 2000000000ull;  // a wait gives up after two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded wait: false when the barrier did not flip within the limit
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  while (global_ns() - t0 < kBulkWaitLimitNs)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Output rows must be contiguous (dst_pitch == row_bytes); row_bytes multiple of 16; rows_per_stage <= 32.
+__global__ void __launch_bounds__(kBulkWarps * 32)
+gather_bulk_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t row_bytes, int64_t src_pitch,
+                   const int64_t* __restrict__ idx, const int64_t* __restrict__ map, int64_t map_len, int64_t n_cap,
+                   const int64_t* d_n, char* __restrict__ out, const float* __restrict__ ts_table,
+                   float* __restrict__ out_ts, int rows_per_stage, int32_t* d_status) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bars[kBulkWarps][kBulkStages];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t n = eff_count(n_cap, d_n);
+  const uint32_t stage_bytes = (uint32_t)rows_per_stage * row_bytes;
+  unsigned char* my_smem = smem_raw + (size_t)warp * kBulkStages * stage_bytes;
+  const int64_t num_chunks = (n + rows_per_stage - 1) / rows_per_stage;
+  const int64_t warps_total = (int64_t)gridDim.x * kBulkWarps;
+  const int64_t gwarp = (int64_t)blockIdx.x * kBulkWarps + warp;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < kBulkStages; ++s) mbar_init(smem_u32(&bars[warp][s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  __syncwarp();
+
+  // issue the loads of this warp's k-th chunk into stage k % kBulkStages
+  auto issue = [&](int64_t k) {
+    const int64_t chunk = gwarp + k * warps_total;
+    if (chunk >= num_chunks) return;
+    const int s = (int)(k % kBulkStages);
+    const int64_t row0 = chunk * rows_per_stage;
+    const int rows = (int)((n - row0) < rows_per_stage ? (n - row0) : rows_per_stage);
+    const uint32_t bar = smem_u32(&bars[warp][s]);
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * row_bytes);
+    __syncwarp();
+    if (lane < rows) {
+      int64_t r;
+      if (!resolve_row(idx, map, map_len, table_rows, row0 + lane, true, d_status, &r)) r = 0;  // flagged; keep byte count
+      bulk_g2s(smem_u32(my_smem + (size_t)s * stage_bytes + (size_t)lane * row_bytes), table + r * src_pitch, row_bytes,
+               bar);
+      if (ts_table) out_ts[row0 + lane] = __ldg(ts_table + r);
+    }
+  };
+
+  for (int k = 0; k < kBulkStages; ++k) issue(k);
+  bool failed = false;
+  for (int64_t k = 0;; ++k) {
+    const int64_t chunk = gwarp + k * warps_total;
+    if (chunk >= num_chunks) break;
+    const int s = (int)(k % kBulkStages);
+    const uint32_t parity = (uint32_t)((k / kBulkStages) & 1);
+    const int64_t row0 = chunk * rows_per_stage;
+    const int rows = (int)((n - row0) < rows_per_stage ? (n - row0) : rows_per_stage);
+    bool ok = mbar_wait_bounded(smem_u32(&bars[warp][s]), parity);
+    if (!__all_sync(0xffffffffu, ok)) {
+      failed = true;
+      break;
+    }
+    if (lane == 0) {
+      fence_async_smem();
+      bulk_s2g(out + row0 * (int64_t)row_bytes, smem_u32(my_smem + (size_t)s * stage_bytes), (uint32_t)rows * row_bytes);
+      bulk_commit();
+      // the stage written back one iteration ago may be refilled once its store has finished reading shared memory
+      bulk_wait_read<1>();
+    }
+    __syncwarp();
+    if (k >= 1) issue(k - 1 + kBulkStages);
+  }
+  if (lane == 0) bulk_wait_all();
+  if (failed) {
+    if (lane == 0) dev_flag(d_status, SGL_DEV_TIMEOUT);
+    // give copies still in flight a bounded chance to land before the CTA's shared memory is released
+    for (int s = 0; s < kBulkStages; ++s) mbar_wait_bounded(smem_u32(&bars[warp][s]), 0);
+  }
+  __syncwarp();
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// cache
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kCacheThreads = 256;
+
+__global__ void __launch_bounds__(kCacheThreads)
+cache_lookup_kernel(const int32_t* __restrict__ hitmap, int64_t num_ids, const int64_t* __restrict__ ids, int64_t n,
+                    int32_t* __restrict__ slot_ws, int32_t* __restrict__ rank_ws, int64_t* __restrict__ cta_miss,
+                    unsigned int* done_counter, int64_t* d_counts, int32_t* d_status) {
+  const int64_t i = (int64_t)blockIdx.x * kCacheThreads + threadIdx.x;
+  int32_t slot = -1;
+  int miss = 0;
+  if (i < n) {
+    int64_t id = __ldg(ids + i);
+    if (id < 0 || id >= num_ids) {
+      dev_flag(d_status, SGL_DEV_BAD_INDEX);
+      slot = -2;  // neither hit nor reportable miss: row is left untouched
+    } else {
+      slot = __ldg(hitmap + id);
+      miss = slot < 0 ? 1 : 0;
+      if (slot < 0) slot = -1;
+    }
+  }
+  int total;
+  int rank = cta_exclusive_scan<kCacheThreads, int>(miss, &total);
+  if (i < n) {
+    slot_ws[i] = slot;
+    rank_ws[i] = rank;
+  }
+  publish_and_scan_cta_totals<kCacheThreads>((int64_t)total, cta_miss, done_counter, d_counts + 1);
+}
+
+template <typename V>
+__global__ void __launch_bounds__(kLaneThreads)
+cache_copy_kernel(const char* __restrict__ cache_rows, int64_t cache_slots, const char* __restrict__ backing,
+                  uint32_t lanes_per_row, int64_t row_bytes, const int64_t* __restrict__ ids, int64_t n,
+                  const int32_t* __restrict__ slot_ws, const int32_t* __restrict__ rank_ws,
+                  const int64_t* __restrict__ cta_miss, char* __restrict__ out, int64_t* __restrict__ miss_pos,
+                  int64_t* __restrict__ miss_ids, int64_t* d_counts, int32_t* d_status) {
+  const int64_t total = n * lanes_per_row;
+  const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
+  if (blockIdx.x == 0 && threadIdx.x == 0) d_counts[0] = n - d_counts[1];
+  for (int64_t q0 = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q0 < total; q0 += stride * kLaneUnroll) {
+    V v[kLaneUnroll];
+    V* dst[kLaneUnroll];
+#pragma unroll
+    for (int u = 0; u < kLaneUnroll; ++u) {
+      int64_t q = q0 + u * stride;
+      dst[u] = nullptr;
+      if (q < total) {
+        int64_t i = q / lanes_per_row;
+        uint32_t l = (uint32_t)(q - i * lanes_per_row);
+        int32_t slot = __ldg(slot_ws + i);
+        const char* src = nullptr;
+        if (slot >= 0) {
+          if (slot < cache_slots) src = cache_rows + (int64_t)slot * row_bytes;
+          else dev_flag(d_status, SGL_DEV_BAD_INDEX);
+        } else if (slot == -1) {
+          int64_t id = __ldg(ids + i);
+          if (l == 0) {
+            int64_t p = cta_miss[i / kCacheThreads] + rank_ws[i];
+            miss_pos[p] = i;
+            miss_ids[p] = id;
+          }
+          if (backing) src = backing + id * row_bytes;
+        }
+        if (src) {
+          v[u] = ld_stream((const V*)src + l);
+          dst[u] = (V*)(out + i * row_bytes) + l;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kLaneUnroll; ++u)
+      if (dst[u]) st_stream(dst[u], v[u]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// scatter / route helpers
+// ---------------------------------------------------------------------------------------------------------------
+template <typename V>
+__global__ void __launch_bounds__(kLaneThreads)
+scatter_lanes_kernel(char* __restrict__ table, int64_t table_rows, uint32_t lanes_per_row, int64_t row_bytes,
+                     int64_t dst_pitch,
+                     const int64_t* __restrict__ idx, const int64_t* __restrict__ map, int64_t map_len, int64_t n_cap,
+                     const int64_t* d_n, const char* __restrict__ rows, int64_t src_pitch, float* __restrict__ ts_table,
+                     const float* __restrict__ ts, int split_last_col, int32_t* d_status) {
+  const int64_t n = eff_count(n_cap, d_n);
+  const int64_t total = n * lanes_per_row;
+  const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
+  for (int64_t q = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q < total; q += stride) {
+    int64_t i = q / lanes_per_row;
+    uint32_t l = (uint32_t)(q - i * lanes_per_row);
+    int64_t r;
+    if (!resolve_row(idx, map, map_len, table_rows, i, false, d_status, &r)) continue;
+    ((V*)(table + r * dst_pitch))[l] = ((const V*)(rows + i * src_pitch))[l];
+    if (l == 0 && ts_table) {
+      if (split_last_col) ts_table[r] = *(const float*)(rows + i * src_pitch + row_bytes);
+      else if (ts) ts_table[r] = ts[i];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kLaneThreads)
+route_pack_kernel(const float* __restrict__ feats, int64_t n_rows, uint32_t dim, const float* __restrict__ ts,
+                  const int64_t* __restrict__ send_idx, const int64_t* __restrict__ remote_idx, int64_t n_send,
+                  float* __restrict__ packed, int32_t* d_status) {
+  const uint32_t payload = dim + (ts ? 1u : 0u);
+  const uint32_t width = payload + (remote_idx ? 2u : 0u);
+  const int64_t total = n_send * width;
+  const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
+  for (int64_t q = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q < total; q += stride) {
+    int64_t i = q / width;
+    uint32_t l = (uint32_t)(q - i * width);
+    if (l >= payload) {
+      uint64_t slot = (uint64_t)__ldg(remote_idx + i);
+      ((uint32_t*)packed)[q] = l == payload ? (uint32_t)slot : (uint32_t)(slot >> 32);
+      continue;
+    }
+    int64_t r = __ldg(send_idx + i);
+    if (r < 0) r += n_rows;
+    if (r < 0 || r >= n_rows) {
+      dev_flag(d_status, SGL_DEV_BAD_INDEX);
+      continue;
+    }
+    packed[q] = l < dim ? __ldg(feats + r * dim + l) : __ldg(ts + r);
+  }
+}
+
+__global__ void __launch_bounds__(kLaneThreads)
+route_unpack_kernel(const float* __restrict__ packed, int64_t n, uint32_t width, float* __restrict__ data,
+                    int64_t data_rows, uint32_t dim, float* __restrict__ ts_table, int32_t* d_status) {
+  const uint32_t pitch = width + 2;
+  const int64_t total = n * width;
+  const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
+  for (int64_t q = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q < total; q += stride) {
+    int64_t i = q / width;
+    uint32_t l = (uint32_t)(q - i * width);
+    const uint32_t* row = (const uint32_t*)packed + i * pitch;
+    int64_t slot = (int64_t)((uint64_t)__ldg(row + width) | ((uint64_t)__ldg(row + width + 1) << 32));
+    if (slot < 0 || slot >= data_rows) {
+      dev_flag(d_status, SGL_DEV_BAD_INDEX);
+      continue;
+    }
+    float v = __uint_as_float(__ldg(row + l));
+    if (l < dim) data[slot * dim + l] = v;
+    else if (ts_table) ts_table[slot] = v;
+  }
+}
+
+__global__ void __launch_bounds__(kLaneThreads)
+route_add_kernel(float* __restrict__ x, int64_t n_rows, uint32_t dim, const int64_t* __restrict__ send_idx,
+                 const float* __restrict__ outs, int64_t seg_len, int32_t* d_status) {
+  const int64_t total = seg_len * dim;
+  const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
+  for (int64_t q = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q < total; q += stride) {
+    int64_t i = q / dim;
+    uint32_t l = (uint32_t)(q - i * dim);
+    int64_t r = __ldg(send_idx + i);
+    if (r < 0) r += n_rows;
+    if (r < 0 || r >= n_rows) {
+      dev_flag(d_status, SGL_DEV_BAD_INDEX);
+      continue;
+    }
+    x[r * dim + l] += outs[q];
+  }
+}
+
+__global__ void dist_pack_kernel(const int64_t* __restrict__ loc, const int64_t* __restrict__ part,
+                                 const uint8_t* __restrict__ shared, int64_t n, int64_t* __restrict__ dist) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    uint64_t d = ((uint64_t)loc[i] & 0xFFFFFFFFFFFFull) | (((uint64_t)part[i] & 0x3FFFull) << 48);
+    if (shared && shared[i]) d |= (1ull << 62);
+    dist[i] = (int64_t)d;
+  }
+}
+
+__global__ void dist_unpack_kernel(const int64_t* __restrict__ dist, int64_t n, int64_t* __restrict__ loc,
+                                   int64_t* __restrict__ part, uint8_t* __restrict__ shared) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t d = dist[i];
+    if (loc) loc[i] = d & 0xFFFFFFFFFFFFll;
+    if (part) part[i] = (d >> 48) & 0x3FFF;
+    if (shared) shared[i] = (d >> 62) != 0;  // arithmetic shift, then "non-zero", as the reference's bool cast
+  }
+}
+
+constexpr int kReplicaThreads = 256;
+
+__global__ void __launch_bounds__(kReplicaThreads)
+replica_count_kernel(const int64_t* __restrict__ indptr, int64_t num_nodes, const int64_t* __restrict__ ids, int64_t n,
+                     int64_t* __restrict__ local_off, int64_t* __restrict__ cta_sums, unsigned int* done_counter,
+                     int64_t* out_total, int32_t* d_status) {
+  const int64_t i = (int64_t)blockIdx.x * kReplicaThreads + threadIdx.x;
+  int64_t len = 0;
+  if (i < n) {
+    int64_t id = ids[i];
+    if (id < 0 || id >= num_nodes) dev_flag(d_status, SGL_DEV_BAD_NODE);
+    else len = indptr[id + 1] - indptr[id];
+  }
+  int64_t total;
+  int64_t ex = cta_exclusive_scan<kReplicaThreads, int64_t>(len, &total);
+  if (i < n) local_off[i] = ex;
+  publish_and_scan_cta_totals<kReplicaThreads>(total, cta_sums, done_counter, out_total);
+}
+
+__global__ void __launch_bounds__(kReplicaThreads)
+replica_expand_kernel(const int64_t* __restrict__ indptr, const int64_t* __restrict__ ranks,
+                      const int64_t* __restrict__ locs, int64_t num_nodes, const int64_t* __restrict__ ids, int64_t n,
+                      int64_t cap, const int64_t* __restrict__ local_off, const int64_t* __restrict__ cta_sums,
+                      int64_t* __restrict__ out_src, int64_t* __restrict__ out_rank, int64_t* __restrict__ out_loc,
+                      int64_t* __restrict__ out_offsets, int32_t* d_status) {
+  const int64_t i = (int64_t)blockIdx.x * kReplicaThreads + threadIdx.x;
+  if (i >= n) return;
+  int64_t off = cta_sums[blockIdx.x] + local_off[i];
+  out_offsets[i] = off;
+  int64_t id = ids[i];
+  if (id < 0 || id >= num_nodes) return;
+  int64_t s = indptr[id], e = indptr[id + 1];
+  for (int64_t p = s; p < e; ++p, ++off) {
+    if (off >= cap) {
+      dev_flag(d_status, SGL_DEV_OVERFLOW);
+      return;
+    }
+    out_src[off] = i;
+    out_rank[off] = ranks[p];
+    out_loc[off] = locs[p];
+  }
+}
+
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+}  // namespace
+}  // namespace sgl
+
+using namespace sgl;
+
+extern "C" int sgl_gather_rows(const void* table, int64_t table_rows, int64_t row_bytes, int64_t src_pitch,
+                               const int64_t* idx, const int64_t* map, int64_t map_len, int64_t n, const int64_t* d_n,
+                               void* out, int64_t dst_pitch, const float* ts_table, float* out_ts, int mode,
+                               int32_t* d_status, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(n >= 0 && table_rows >= 0 && row_bytes > 0, SGL_ERR_ARG, "gather_rows: bad size");
+  SGL_REQUIRE(src_pitch >= row_bytes && dst_pitch >= row_bytes, SGL_ERR_ARG, "gather_rows: pitch smaller than row");
+  SGL_REQUIRE(row_bytes % 4 == 0 && src_pitch % 4 == 0 && dst_pitch % 4 == 0, SGL_ERR_UNSUPPORTED,
+              "gather_rows: rows must be multiples of 4 bytes");
+  SGL_REQUIRE((ts_table == nullptr) == (out_ts == nullptr), SGL_ERR_ARG, "gather_rows: ts_table/out_ts must come together");
+  if (n == 0) return SGL_OK;
+  SGL_REQUIRE(table && idx && out, SGL_ERR_ARG, "gather_rows: null array");
+  SGL_REQUIRE(map == nullptr || map_len > 0, SGL_ERR_ARG, "gather_rows: empty map");
+  const bool vec_ok = row_bytes % 16 == 0 && src_pitch % 16 == 0 && dst_pitch % 16 == 0 && aligned16(table) && aligned16(out);
+  if (mode == SGL_GATHER_AUTO) mode = vec_ok ? SGL_GATHER_VEC : 0;
+  if (mode == SGL_GATHER_BULK) {
+    SGL_REQUIRE(vec_ok && dst_pitch == row_bytes, SGL_ERR_UNSUPPORTED,
+                "gather_rows: bulk mode needs 16-byte rows and a dense output");
+    const int64_t budget = 200 * 1024;
+    int rows_per_stage = (int)(budget / ((int64_t)kBulkWarps * kBulkStages * row_bytes));
+    if (rows_per_stage > 32) rows_per_stage = 32;
+    SGL_REQUIRE(rows_per_stage >= 2, SGL_ERR_UNSUPPORTED, "gather_rows: row of %lld bytes too large for bulk mode",
+                (long long)row_bytes);
+    const size_t smem = (size_t)kBulkWarps * kBulkStages * rows_per_stage * row_bytes;
+    SGL_CUDA_CHECK(cudaFuncSetAttribute(gather_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    const int64_t chunks = (n + rows_per_stage - 1) / rows_per_stage;
+    int64_t ctas = (chunks + kBulkWarps - 1) / kBulkWarps;
+    if (ctas > kNumSM) ctas = kNumSM;  // one persistent CTA per SM (shared memory allows one)
+    gather_bulk_kernel<<<(unsigned)ctas, kBulkWarps * 32, smem, stream>>>(
+        (const char*)table, table_rows, (uint32_t)row_bytes, src_pitch, idx, map, map_len, n, d_n, (char*)out, ts_table,
+        out_ts, rows_per_stage, d_status);
+    SGL_LAUNCH_CHECK();
+    return SGL_OK;
+  }
+  if (mode == SGL_GATHER_VEC) {
+    SGL_REQUIRE(vec_ok, SGL_ERR_UNSUPPORTED, "gather_rows: 128-bit mode needs 16-byte aligned rows");
+    const uint32_t lanes = (uint32_t)(row_bytes / 16);
+    const int grid = stream_grid(n * lanes, kLaneThreads * kLaneUnroll, 8);
+    gather_lanes_kernel<uint4><<<grid, kLaneThreads, 0, stream>>>((const char*)table, table_rows, lanes, src_pitch, idx,
+                                                                 map, map_len, n, d_n, (char*)out, dst_pitch, ts_table,
+                                                                 out_ts, d_status);
+  } else {
+    const uint32_t lanes = (uint32_t)(row_bytes / 4);
+    const int grid = stream_grid(n * lanes, kLaneThreads * kLaneUnroll, 8);
+    gather_lanes_kernel<uint32_t><<<grid, kLaneThreads, 0, stream>>>((const char*)table, table_rows, lanes, src_pitch,
+                                                                    idx, map, map_len, n, d_n, (char*)out, dst_pitch,
+                                                                    ts_table, out_ts, d_status);
+  }
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" size_t sgl_cache_gather_ws_bytes(int64_t n) {
+  if (n < 1) n = 1;
+  int64_t ctas = (n + kCacheThreads - 1) / kCacheThreads;
+  return 2 * align_up((size_t)n * 4) + align_up((size_t)ctas * 8) + align_up(sizeof(unsigned int));
+}
+
+extern "C" int sgl_cache_gather(const void* cache_rows, int64_t cache_slots, const int32_t* hitmap, int64_t num_ids,
+                                const void* backing, int64_t row_bytes, const int64_t* ids, int64_t n, void* out,
+                                int64_t* miss_pos, int64_t* miss_ids, int64_t* d_counts, int32_t* d_status, void* ws,
+                                size_t ws_bytes, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(n >= 0 && row_bytes > 0 && row_bytes % 4 == 0, SGL_ERR_ARG, "cache_gather: bad size");
+  SGL_REQUIRE(d_counts, SGL_ERR_ARG, "cache_gather: d_counts is null");
+  if (n == 0) {
+    SGL_CUDA_CHECK(cudaMemsetAsync(d_counts, 0, 2 * sizeof(int64_t), stream));
+    return SGL_OK;
+  }
+  SGL_REQUIRE(cache_rows && hitmap && ids && out && miss_pos && miss_ids, SGL_ERR_ARG, "cache_gather: null array");
+  WsCarver c(ws, ws_bytes);
+  int32_t* slot_ws = c.take<int32_t>(n);
+  int32_t* rank_ws = c.take<int32_t>(n);
+  const int64_t ctas = (n + kCacheThreads - 1) / kCacheThreads;
+  int64_t* cta_miss = c.take<int64_t>(ctas);
+  unsigned int* done = c.take<unsigned int>(1);
+  SGL_REQUIRE(c.ok(), SGL_ERR_WORKSPACE, "cache_gather: workspace %zu < %zu bytes", ws_bytes, sgl_cache_gather_ws_bytes(n));
+  SGL_CUDA_CHECK(cudaMemsetAsync(done, 0, sizeof(unsigned int), stream));
+  cache_lookup_kernel<<<(unsigned)ctas, kCacheThreads, 0, stream>>>(hitmap, num_ids, ids, n, slot_ws, rank_ws, cta_miss,
+                                                                   done, d_counts, d_status);
+  const bool vec_ok = row_bytes % 16 == 0 && aligned16(cache_rows) && aligned16(out) && (backing == nullptr || aligned16(backing));
+  if (vec_ok) {
+    const uint32_t lanes = (uint32_t)(row_bytes / 16);
+    const int grid = stream_grid(n * lanes, kLaneThreads * kLaneUnroll, 8);
+    cache_copy_kernel<uint4><<<grid, kLaneThreads, 0, stream>>>((const char*)cache_rows, cache_slots, (const char*)backing,
+                                                               lanes, row_bytes, ids, n, slot_ws, rank_ws, cta_miss,
+                                                               (char*)out, miss_pos, miss_ids, d_counts, d_status);
+  } else {
+    const uint32_t lanes = (uint32_t)(row_bytes / 4);
+    const int grid = stream_grid(n * lanes, kLaneThreads * kLaneUnroll, 8);
+    cache_copy_kernel<uint32_t><<<grid, kLaneThreads, 0, stream>>>((const char*)cache_rows, cache_slots,
+                                                                  (const char*)backing, lanes, row_bytes, ids, n, slot_ws,
+                                                                  rank_ws, cta_miss, (char*)out, miss_pos, miss_ids,
+                                                                  d_counts, d_status);
+  }
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" int sgl_scatter_rows(void* table, int64_t table_rows, int64_t row_bytes, int64_t dst_pitch, const int64_t* idx,
+                                const int64_t* map, int64_t map_len, int64_t n, const int64_t* d_n, const void* rows,
+                                int64_t src_pitch, float* ts_table, const float* ts, int split_last_col,
+                                int32_t* d_status, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(n >= 0 && table_rows >= 0 && row_bytes > 0 && row_bytes % 4 == 0, SGL_ERR_ARG, "scatter_rows: bad size");
+  SGL_REQUIRE(dst_pitch >= row_bytes && src_pitch >= row_bytes + (split_last_col ? 4 : 0), SGL_ERR_ARG,
+              "scatter_rows: pitch smaller than row");
+  SGL_REQUIRE(!split_last_col || ts_table, SGL_ERR_ARG, "scatter_rows: split_last_col needs ts_table");
+  if (n == 0) return SGL_OK;
+  SGL_REQUIRE(table && idx && rows, SGL_ERR_ARG, "scatter_rows: null array");
+  const bool vec_ok = row_bytes % 16 == 0 && src_pitch % 16 == 0 && dst_pitch % 16 == 0 && aligned16(table) && aligned16(rows);
+  if (vec_ok) {
+    const uint32_t lanes = (uint32_t)(row_bytes / 16);
+    const int grid = stream_grid(n * lanes, kLaneThreads, 16);
+    scatter_lanes_kernel<uint4><<<grid, kLaneThreads, 0, stream>>>((char*)table, table_rows, lanes, row_bytes, dst_pitch, idx,
+                                                                  map, map_len, n, d_n, (const char*)rows, src_pitch,
+                                                                  ts_table, ts, split_last_col, d_status);
+  } else {
+    const uint32_t lanes = (uint32_t)(row_bytes / 4);
+    const int grid = stream_grid(n * lanes, kLaneThreads, 16);
+    scatter_lanes_kernel<uint32_t><<<grid, kLaneThreads, 0, stream>>>((char*)table, table_rows, lanes, row_bytes, dst_pitch,
+                                                                     idx, map, map_len, n, d_n, (const char*)rows,
+                                                                     src_pitch, ts_table, ts, split_last_col, d_status);
+  }
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" int sgl_route_pack(const float* feats, int64_t n_rows, int64_t dim, const float* ts, const int64_t* send_idx,
+                              const int64_t* remote_idx, int64_t n_send, float* packed, int32_t* d_status,
+                              void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(n_send >= 0 && n_rows >= 0 && dim > 0, SGL_ERR_ARG, "route_pack: bad size");
+  if (n_send == 0) return SGL_OK;
+  SGL_REQUIRE(feats && send_idx && packed, SGL_ERR_ARG, "route_pack: null array");
+  const int grid = stream_grid(n_send * (dim + 3), kLaneThreads, 16);
+  route_pack_kernel<<<grid, kLaneThreads, 0, stream>>>(feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, n_send,
+                                                      packed, d_status);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" int sgl_route_unpack(const float* packed, int64_t n, int64_t width, float* data, int64_t data_rows,
+                                int64_t dim, float* ts_table, int32_t* d_status, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(n >= 0 && data_rows >= 0 && dim > 0, SGL_ERR_ARG, "route_unpack: bad size");
+  SGL_REQUIRE(width == dim || width == dim + 1, SGL_ERR_ARG, "route_unpack: width %lld must be dim or dim+1 (dim=%lld)",
+              (long long)width, (long long)dim);
+  SGL_REQUIRE(width == dim || ts_table, SGL_ERR_ARG, "route_unpack: rows carry a timestamp but ts_table is null");
+  if (n == 0) return SGL_OK;
+  SGL_REQUIRE(packed && data, SGL_ERR_ARG, "route_unpack: null array");
+  const int grid = stream_grid(n * width, kLaneThreads, 16);
+  route_unpack_kernel<<<grid, kLaneThreads, 0, stream>>>(packed, n, (uint32_t)width, data, data_rows, (uint32_t)dim,
+                                                        ts_table, d_status);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" int sgl_route_add_rows(float* x, int64_t n_rows, int64_t dim, const int64_t* send_idx, const float* outs,
+                                  int64_t seg_len, int32_t* d_status, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(seg_len >= 0 && n_rows >= 0 && dim > 0, SGL_ERR_ARG, "route_add_rows: bad size");
+  if (seg_len == 0) return SGL_OK;
+  SGL_REQUIRE(x && send_idx && outs, SGL_ERR_ARG, "route_add_rows: null array");
+  const int grid = stream_grid(seg_len * dim, kLaneThreads, 16);
+  route_add_kernel<<<grid, kLaneThreads, 0, stream>>>(x, n_rows, (uint32_t)dim, send_idx, outs, seg_len, d_status);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" int sgl_dist_pack(const int64_t* loc, const int64_t* part, const uint8_t* shared, int64_t n, int64_t* dist,
+                             void* stream_) {
+  SGL_REQUIRE(n >= 0, SGL_ERR_ARG, "dist_pack: negative size");
+  if (n == 0) return SGL_OK;
+  SGL_REQUIRE(loc && part && dist, SGL_ERR_ARG, "dist_pack: null array");
+  dist_pack_kernel<<<stream_grid(n, 256, 8), 256, 0, (cudaStream_t)stream_>>>(loc, part, shared, n, dist);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" int sgl_dist_unpack(const int64_t* dist, int64_t n, int64_t* loc, int64_t* part, uint8_t* shared,
+                               void* stream_) {
+  SGL_REQUIRE(n >= 0, SGL_ERR_ARG, "dist_unpack: negative size");
+  if (n == 0) return SGL_OK;
+  SGL_REQUIRE(dist, SGL_ERR_ARG, "dist_unpack: null array");
+  dist_unpack_kernel<<<stream_grid(n, 256, 8), 256, 0, (cudaStream_t)stream_>>>(dist, n, loc, part, shared);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" size_t sgl_replica_lookup_ws_bytes(int64_t n) {
+  if (n < 1) n = 1;
+  int64_t ctas = (n + kReplicaThreads - 1) / kReplicaThreads;
+  return align_up((size_t)n * 8) + align_up((size_t)ctas * 8) + align_up(sizeof(unsigned int));
+}
+
+extern "C" int sgl_replica_lookup(const int64_t* indptr, const int64_t* ranks, const int64_t* locs, int64_t num_nodes,
+                                  const int64_t* ids, int64_t n, int64_t cap, int64_t* out_src, int64_t* out_rank,
+                                  int64_t* out_loc, int64_t* out_offsets, int32_t* d_status, void* ws, size_t ws_bytes,
+                                  void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(n >= 0 && cap >= 0 && num_nodes >= 0, SGL_ERR_ARG, "replica_lookup: negative size");
+  SGL_REQUIRE(out_offsets, SGL_ERR_ARG, "replica_lookup: out_offsets is null");
+  if (n == 0) {
+    SGL_CUDA_CHECK(cudaMemsetAsync(out_offsets, 0, sizeof(int64_t), stream));
+    return SGL_OK;
+  }
+  SGL_REQUIRE(indptr && ranks && locs && ids && out_src && out_rank && out_loc, SGL_ERR_ARG, "replica_lookup: null array");
+  WsCarver c(ws, ws_bytes);
+  int64_t* local_off = c.take<int64_t>(n);
+  const int64_t ctas = (n + kReplicaThreads - 1) / kReplicaThreads;
+  int64_t* cta_sums = c.take<int64_t>(ctas);
+  unsigned int* done = c.take<unsigned int>(1);
+  SGL_REQUIRE(c.ok(), SGL_ERR_WORKSPACE, "replica_lookup: workspace %zu < %zu bytes", ws_bytes,
+              sgl_replica_lookup_ws_bytes(n));
+  SGL_CUDA_CHECK(cudaMemsetAsync(done, 0, sizeof(unsigned int), stream));
+  replica_count_kernel<<<(unsigned)ctas, kReplicaThreads, 0, stream>>>(indptr, num_nodes, ids, n, local_off, cta_sums, done,
+                                                                      out_offsets + n, d_status);
+  replica_expand_kernel<<<(unsigned)ctas, kReplicaThreads, 0, stream>>>(indptr, ranks, locs, num_nodes, ids, n, cap,
+                                                                       local_off, cta_sums, out_src, out_rank, out_loc,
+                                                                       out_offsets, d_status);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}

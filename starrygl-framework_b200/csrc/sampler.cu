@@ -1,0 +1,257 @@
+// Temporal neighbour sampling, one warp per target, two kernels per hop:
+//
+//   sample_count_kernel  warp-cooperative 32-ary search of the row's time-sorted timestamps for the
+//                        candidate window [lo, cut); stores the window and min(fanout, cut-lo); the last
+//                        CTA to finish turns the per-CTA totals into CTA base offsets (no spinning: a
+//                        fence + counter decides who is last).
+//   sample_fill_kernel   CTA-local exclusive scan of the counts (+ CTA base) gives every target its
+//                        output offset; lane j of the target's warp copies element j (recent: the tail
+//                        of the window; uniform: Floyd's k-subset with Philox4x32-10, ranked ascending).
+//
+// Algorithmic HBM bytes per target: 16 (indptr pair) + 16 (target id, time) + 8*ceil(log2 deg) (search
+// probes) + k_eff*24 (nbr, ts, eid reads) + k_eff*36 (five output arrays) + 8 (offset).
+#include "common.cuh"
+#include "scan.cuh"
+
+namespace sgl {
+namespace {
+
+constexpr int kWarpsPerCta = 8;
+constexpr int kTargetsPerWarp = 4;                                  // consecutive targets handled by one warp
+constexpr int kTargetsPerCta = kWarpsPerCta * kTargetsPerWarp;      // 32
+constexpr int kCtaThreads = kWarpsPerCta * 32;
+
+// first position p in [lo, hi) with ts[p] >= bound (hi when none); all 32 lanes cooperate and agree
+__device__ __forceinline__ int64_t warp_lower_bound(const int64_t* __restrict__ ts, int64_t lo, int64_t hi,
+                                                    int64_t bound, int lane) {
+  while (hi - lo > 32) {
+    int64_t stride = (hi - lo + 31) >> 5;
+    int64_t p = lo + (int64_t)(lane + 1) * stride - 1;
+    if (p > hi - 1) p = hi - 1;
+    bool less = __ldg(ts + p) < bound;
+    unsigned b = __ballot_sync(0xffffffffu, less);
+    int c = __popc(b);  // probes are monotone, so the true ones are lanes [0, c)
+    if (c == 32) return hi;
+    int64_t p_first_false = lo + (int64_t)(c + 1) * stride - 1;
+    if (p_first_false > hi - 1) p_first_false = hi - 1;
+    if (c > 0) {
+      int64_t p_last_true = lo + (int64_t)c * stride - 1;
+      if (p_last_true > hi - 1) p_last_true = hi - 1;
+      lo = p_last_true + 1;
+    }
+    hi = p_first_false;
+  }
+  bool less = (lo + lane < hi) && (__ldg(ts + lo + lane) < bound);
+  return lo + __popc(__ballot_sync(0xffffffffu, less));
+}
+
+struct Philox {
+  uint32_t c[4];
+  __device__ __forceinline__ Philox(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1) {
+    c[0] = c0; c[1] = c1; c[2] = c2; c[3] = c3;
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+      uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+      uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+      uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+      c[0] = n0; c[1] = lo1; c[2] = n2; c[3] = lo0;
+      k0 += 0x9E3779B9u;
+      k1 += 0xBB67AE85u;
+    }
+  }
+};
+
+__global__ void __launch_bounds__(kCtaThreads)
+sample_count_kernel(const int64_t* __restrict__ indptr, const int64_t* __restrict__ ts, int64_t num_nodes,
+                    const int64_t* __restrict__ targets, const int64_t* __restrict__ target_ts, int64_t n_cap,
+                    const int64_t* d_n, int fanout, int equal_root_time, int64_t allowed_offset,
+                    int64_t* __restrict__ win_lo, int64_t* __restrict__ win_cut, int32_t* __restrict__ cnt,
+                    int64_t* __restrict__ cta_sums, unsigned int* done_counter, int64_t* __restrict__ out_offsets,
+                    int32_t* d_status) {
+  __shared__ int32_t s_cnt[kTargetsPerCta];
+  const int64_t n = eff_count(n_cap, d_n);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int j = 0; j < kTargetsPerWarp; ++j) {
+    const int slot = warp * kTargetsPerWarp + j;
+    const int64_t i = (int64_t)blockIdx.x * kTargetsPerCta + slot;
+    int32_t c = 0;
+    if (i < n) {
+      int64_t node = targets[i];
+      int64_t t = target_ts[i];
+      int64_t lo = 0, cut = 0;
+      if (node < 0 || node >= num_nodes) {
+        if (lane == 0) dev_flag(d_status, SGL_DEV_BAD_NODE);
+      } else {
+        int64_t s = __ldg(indptr + node), e = __ldg(indptr + node + 1);
+        lo = s;
+        cut = s;
+        if (e > s) {
+          cut = warp_lower_bound(ts, s, e, t + (equal_root_time ? 1 : 0), lane);
+          if (allowed_offset >= 0 && cut > s) lo = warp_lower_bound(ts, s, cut, t - allowed_offset, lane);
+        }
+      }
+      int64_t cand = cut - lo;
+      c = (int32_t)(cand < fanout ? cand : fanout);
+      if (lane == 0) {
+        win_lo[i] = lo;
+        win_cut[i] = cut;
+        cnt[i] = c;
+      }
+    }
+    if (lane == 0) s_cnt[slot] = c;
+  }
+  __syncthreads();
+  int64_t cta_total = 0;
+#pragma unroll
+  for (int s = 0; s < kTargetsPerCta; ++s) cta_total += s_cnt[s];
+  // grand total -> out_offsets[n_cap]; the slots of the targets themselves are written by the fill kernel
+  publish_and_scan_cta_totals<kCtaThreads>(cta_total, cta_sums, done_counter, out_offsets + n_cap);
+}
+
+__global__ void __launch_bounds__(kCtaThreads)
+sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ ts, const int64_t* __restrict__ eid,
+                   const int64_t* __restrict__ target_ts, int64_t n_cap, const int64_t* d_n, int fanout, int policy,
+                   int keep_root_time, uint64_t seed, uint32_t rng_stream, const int64_t* __restrict__ win_lo,
+                   const int64_t* __restrict__ win_cut, const int32_t* __restrict__ cnt,
+                   const int64_t* __restrict__ cta_base, int64_t* __restrict__ out_nbr, int64_t* __restrict__ out_dst,
+                   int64_t* __restrict__ out_ts, float* __restrict__ out_dt, int64_t* __restrict__ out_dt_i64,
+                   int64_t* __restrict__ out_eid, int64_t* __restrict__ out_offsets) {
+  __shared__ int64_t s_off[kTargetsPerCta];
+  const int64_t n = eff_count(n_cap, d_n);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t first = (int64_t)blockIdx.x * kTargetsPerCta;
+  if (warp == 0) {
+    int64_t i = first + lane;
+    int32_t c = i < n ? cnt[i] : 0;
+    int32_t x = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int32_t y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    int64_t off = cta_base[blockIdx.x] + (x - c);
+    s_off[lane] = off;
+    if (i < n) out_offsets[i] = off;
+    // offsets past the valid targets all equal the total, so out_offsets[n..n_cap] is a valid prefix array
+    if (i >= n && i < n_cap) out_offsets[i] = off;
+  }
+  __syncthreads();
+#pragma unroll 1
+  for (int j = 0; j < kTargetsPerWarp; ++j) {
+    const int slot = warp * kTargetsPerWarp + j;
+    const int64_t i = first + slot;
+    if (i >= n) break;
+    const int32_t c = cnt[i];
+    if (c == 0) continue;
+    const int64_t lo = win_lo[i], cut = win_cut[i];
+    const int64_t t = target_ts[i];
+    const int64_t off = s_off[slot];
+    const int64_t cand = cut - lo;
+    if (policy == SGL_POLICY_UNIFORM && cand > fanout) {
+      // Floyd's subset selection: draw j picks t_j uniform in [0, cand-k+j]; a repeat is replaced by cand-k+j
+      uint64_t pick = 0;
+      if (lane < fanout) {
+        Philox ph((uint32_t)i, (uint32_t)((uint64_t)i >> 32), (uint32_t)lane, rng_stream, (uint32_t)seed,
+                  (uint32_t)(seed >> 32));
+        uint64_t u = (uint64_t)ph.c[0] | ((uint64_t)ph.c[1] << 32);
+        uint64_t bound = (uint64_t)(cand - fanout + lane + 1);
+        pick = u % bound;
+      }
+      for (int d = 1; d < fanout; ++d) {
+        uint64_t mine = __shfl_sync(0xffffffffu, pick, d);
+        bool clash = lane < d && pick == mine;
+        if (__any_sync(0xffffffffu, clash) && lane == d) pick = (uint64_t)(cand - fanout + d);
+      }
+      // rank ascending
+      int rank = 0;
+      for (int d = 0; d < fanout; ++d) {
+        uint64_t other = __shfl_sync(0xffffffffu, pick, d);
+        rank += (other < pick) ? 1 : 0;
+      }
+      if (lane < fanout) {
+        int64_t p = lo + (int64_t)pick;
+        int64_t o = off + rank;
+        int64_t ets = __ldg(ts + p);
+        out_nbr[o] = __ldg(nbr + p);
+        out_eid[o] = __ldg(eid + p);
+        out_ts[o] = keep_root_time ? t : ets;
+        out_dt[o] = (float)(t - ets);
+        if (out_dt_i64) out_dt_i64[o] = ets - t;
+        out_dst[o] = i;
+      }
+    } else {
+      const int64_t start = cut - c;  // recent: tail of the window; uniform with cand <= k: the whole window
+      for (int e = lane; e < c; e += 32) {
+        int64_t p = start + e;
+        int64_t o = off + e;
+        int64_t ets = __ldg(ts + p);
+        out_nbr[o] = __ldg(nbr + p);
+        out_eid[o] = __ldg(eid + p);
+        out_ts[o] = keep_root_time ? t : ets;
+        out_dt[o] = (float)(t - ets);
+        if (out_dt_i64) out_dt_i64[o] = ets - t;
+        out_dst[o] = i;
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace sgl
+
+using namespace sgl;
+
+static inline int64_t sample_num_ctas(int64_t n) {
+  int64_t b = (n + kTargetsPerCta - 1) / kTargetsPerCta;
+  return b < 1 ? 1 : b;
+}
+
+extern "C" size_t sgl_sample_ws_bytes(int64_t n_targets) {
+  if (n_targets < 1) n_targets = 1;
+  return 2 * align_up((size_t)n_targets * 8) + align_up((size_t)n_targets * 4) +
+         align_up((size_t)sample_num_ctas(n_targets) * 8) + align_up(sizeof(unsigned int));
+}
+
+extern "C" int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                                int64_t num_nodes, const int64_t* targets, const int64_t* target_ts, int64_t n_targets,
+                                const int64_t* d_n, int fanout, int policy, int equal_root_time, int64_t allowed_offset,
+                                int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* out_nbr,
+                                int64_t* out_dst, int64_t* out_ts, float* out_dt, int64_t* out_dt_i64,
+                                int64_t* out_eid, int64_t* out_offsets, int32_t* d_status, void* ws, size_t ws_bytes,
+                                void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(n_targets >= 0 && num_nodes >= 0, SGL_ERR_ARG, "sample_layer: negative size");
+  SGL_REQUIRE(fanout >= 1, SGL_ERR_ARG, "sample_layer: fanout=%d must be >= 1", fanout);
+  SGL_REQUIRE(policy == SGL_POLICY_RECENT || policy == SGL_POLICY_UNIFORM, SGL_ERR_ARG,
+              "sample_layer: unknown policy %d", policy);
+  SGL_REQUIRE(policy != SGL_POLICY_UNIFORM || fanout <= SGL_MAX_UNIFORM_FANOUT, SGL_ERR_UNSUPPORTED,
+              "sample_layer: uniform fanout %d > %d", fanout, SGL_MAX_UNIFORM_FANOUT);
+  SGL_REQUIRE(out_offsets, SGL_ERR_ARG, "sample_layer: out_offsets is null");
+  SGL_REQUIRE(n_targets < ((int64_t)1 << 31) * kTargetsPerCta, SGL_ERR_UNSUPPORTED, "sample_layer: too many targets");
+  if (n_targets == 0) {
+    SGL_CUDA_CHECK(cudaMemsetAsync(out_offsets, 0, sizeof(int64_t), stream));
+    return SGL_OK;
+  }
+  SGL_REQUIRE(indptr && nbr && ts && eid && targets && target_ts && out_nbr && out_dst && out_ts && out_dt && out_eid,
+              SGL_ERR_ARG, "sample_layer: null array");
+  WsCarver c(ws, ws_bytes);
+  int64_t* win_lo = c.take<int64_t>(n_targets);
+  int64_t* win_cut = c.take<int64_t>(n_targets);
+  int32_t* cnt = c.take<int32_t>(n_targets);
+  const int64_t ctas = sample_num_ctas(n_targets);
+  int64_t* cta_sums = c.take<int64_t>(ctas);
+  unsigned int* done = c.take<unsigned int>(1);
+  SGL_REQUIRE(c.ok(), SGL_ERR_WORKSPACE, "sample_layer: workspace %zu < %zu bytes", ws_bytes,
+              sgl_sample_ws_bytes(n_targets));
+  SGL_CUDA_CHECK(cudaMemsetAsync(done, 0, sizeof(unsigned int), stream));
+  sample_count_kernel<<<(unsigned)ctas, kCtaThreads, 0, stream>>>(indptr, ts, num_nodes, targets, target_ts, n_targets,
+                                                                  d_n, fanout, equal_root_time, allowed_offset, win_lo,
+                                                                  win_cut, cnt, cta_sums, done, out_offsets, d_status);
+  sample_fill_kernel<<<(unsigned)ctas, kCtaThreads, 0, stream>>>(nbr, ts, eid, target_ts, n_targets, d_n, fanout, policy,
+                                                                 keep_root_time, seed, rng_stream, win_lo, win_cut, cnt,
+                                                                 cta_sums, out_nbr, out_dst, out_ts, out_dt, out_dt_i64,
+                                                                 out_eid, out_offsets);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}

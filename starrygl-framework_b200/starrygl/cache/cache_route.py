@@ -1,0 +1,150 @@
+"""Owner -> replica push of node rows between graph partitions (the "cache route").
+
+Mirrors starrygl/cache/cache_route.py (``CommPlan`` :121-166, ``CacheUpdateFuture`` :172-198,
+``CacheRoute.update_with_plan`` :211-277, ``CacheRouteManager`` :426-432) with a different wire format:
+the reference sends three collectives per call (counts, write slots, rows) around two host synchronisations
+and separate gather / scatter passes.  Here one kernel packs ``[row | ts | write slot]`` straight into the
+send buffer (grouped by destination rank because the plan's ``send_indices`` are), ONE variable-size
+all-to-all moves it over NCCL, and one kernel on the receiver scatters rows and timestamps to their slots.
+The receive counts are exchanged once per plan and cached on it (``CommPlan.recv_sizes``), so a plan that is
+reused -- or that was saved with its receive counts -- costs no host synchronisation at all.
+"""
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+from .. import ops
+
+__all__ = ['CommPlan', 'CacheUpdateFuture', 'CacheRoute', 'CacheRouteManager']
+
+
+@dataclass
+class CommPlan:
+    """What this rank sends during one slot: for every row the destination rank (sorted), the local row to
+    read and the slot to write on the receiver."""
+    send_ranks: torch.Tensor           # [S] destination rank of every row, ascending
+    send_sizes: torch.Tensor           # [P] rows per destination rank
+    send_indices: torch.Tensor         # [S] local row to read
+    send_remote_indices: torch.Tensor  # [S] slot to write on the receiver
+    recv_sizes: Optional[List[int]] = field(default=None, compare=False)   # [P] rows arriving per source rank
+    _send_list: Optional[List[int]] = field(default=None, compare=False, repr=False)
+
+    def __repr__(self):
+        if self.is_empty():
+            return "CommPlan(Empty)"
+        return f"CommPlan(send={self.send_indices.numel()} items -> {int(torch.count_nonzero(self.send_sizes))} parts)"
+
+    def is_empty(self) -> bool:
+        return self.send_indices.numel() == 0
+
+    def send_list(self) -> List[int]:
+        if self._send_list is None:
+            self._send_list = [int(v) for v in self.send_sizes.tolist()]
+        return self._send_list
+
+    def to(self, device: torch.device, non_blocking: bool = False):
+        self.send_list()   # keep the host copy of the split sizes before the tensor leaves the host
+        self.send_ranks = self.send_ranks.to(device, non_blocking=non_blocking)
+        self.send_sizes = self.send_sizes.to(device, non_blocking=non_blocking)
+        self.send_indices = self.send_indices.to(device, non_blocking=non_blocking)
+        self.send_remote_indices = self.send_remote_indices.to(device, non_blocking=non_blocking)
+        return self
+
+    def pin_memory(self):
+        self.send_ranks = self.send_ranks.pin_memory()
+        self.send_sizes = self.send_sizes.pin_memory()
+        self.send_indices = self.send_indices.pin_memory()
+        self.send_remote_indices = self.send_remote_indices.pin_memory()
+        return self
+
+    @classmethod
+    def empty(cls, num_parts: int = 0):
+        return cls(send_ranks=torch.empty(0, dtype=torch.long),
+                   send_sizes=torch.zeros(num_parts, dtype=torch.long) if num_parts > 0 else torch.empty(0, dtype=torch.long),
+                   send_indices=torch.empty(0, dtype=torch.long), send_remote_indices=torch.empty(0, dtype=torch.long))
+
+
+class CacheUpdateFuture:
+    """Handle of one push; ``wait()`` completes the collective and applies the remote writes."""
+
+    def __init__(self, works, recv_ids: Optional[Tensor], recv_feats: Tensor, write_callback: Callable, mode: str,
+                 width: int = 0):
+        self.works = works
+        self.recv_ids = recv_ids
+        self.recv_feats = recv_feats
+        self.write_callback = write_callback
+        self.mode = mode
+        self._width = width
+        self._done = False
+
+    def wait(self):
+        if self._done:
+            return
+        self._done = True
+        for work in self.works:
+            if work is not None:
+                work.wait()
+        if self.recv_feats.shape[0] == 0:
+            return
+        if self.recv_ids is None:
+            # wire rows are [payload(width) | slot as two 32-bit words]
+            w = self._width
+            state = getattr(self.write_callback, "fused_state", None)
+            if state is not None:   # one kernel: slot decode + row scatter + timestamp scatter
+                state.write_wire(self.recv_feats, w)
+                return
+            self.recv_ids = ops.wire_slots(self.recv_feats, w)
+            self.recv_feats = self.recv_feats[:, :w]
+        self.write_callback(self.recv_ids, self.recv_feats, self.mode)
+
+
+class CacheRoute:
+    def __init__(self, group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.world_size = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+
+    def _exchange_counts(self, plan: CommPlan, device) -> List[int]:
+        if plan.recv_sizes is None:
+            send = plan.send_sizes.to(device)
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=self.group)
+            plan.recv_sizes = [int(v) for v in recv.tolist()]
+        return plan.recv_sizes
+
+    @torch.no_grad()
+    def update_with_plan(self, local_features: Tensor, plan: CommPlan, write_callback: Callable,
+                         slice_size: int = 0, local_ts: Optional[Tensor] = None) -> List[CacheUpdateFuture]:
+        """Push ``local_features[plan.send_indices]`` (optionally with ``local_ts`` appended as last column) to the
+        ranks of the plan.  ``write_callback(slots, rows, mode)`` runs on the receiver inside ``wait()``.
+        ``slice_size`` is accepted for compatibility; the single packed message makes column slicing unnecessary.
+        Every rank of the group must call this (an empty plan still takes part in the exchange)."""
+        device = local_features.device
+        feats = local_features.contiguous()
+        width = feats.shape[1] + (1 if local_ts is not None else 0)
+        recv_list = self._exchange_counts(plan, device)
+        send_list = plan.send_list()
+        send_idx = plan.send_indices.to(device)
+        remote = plan.send_remote_indices.to(device)
+        packed = ops.route_pack(feats, local_ts, send_idx, remote_idx=remote)          # [S, width + 2]
+        recv = torch.empty(sum(recv_list), width + 2, dtype=torch.float32, device=device)
+        work = dist.all_to_all_single(recv, packed, output_split_sizes=recv_list, input_split_sizes=send_list,
+                                      group=self.group, async_op=True)
+        return [CacheUpdateFuture([work], None, recv, write_callback, 'cold', width)]
+
+
+class CacheRouteManager:
+    _instance = None
+
+    @classmethod
+    def get_instance(cls, group: Optional[dist.ProcessGroup] = None) -> CacheRoute:
+        if cls._instance is None:
+            cls._instance = CacheRoute(group)
+        return cls._instance
+
+    @classmethod
+    def reset(cls):
+        cls._instance = None

@@ -1,0 +1,111 @@
+"""Multi-hop mini-batch builder on the GPU: sampling, (node, ts)-pair dedup/relabel and per-hop CSC.
+
+Produces the per-layer dictionaries of the reference's offline builder
+(``MaterializedMultiLayerBuilder.build_aligned_batch``, prepare_sample.py:313-377) without its route
+planning: layer 0 = sorted unique (id, ts) pairs of the roots + ``inv_map``; layer l+1 = CSC over the
+previous list (``indptr``, ``indices``, ``eid``, ``edge_ts``, ``edge_dt``) + the merged sorted pair list
+(``gids``, ``ts``).  All hops are enqueued on the current stream without an intermediate host
+synchronisation: the number of edges a hop produced is handed to the next kernels as a device count.
+``finish()`` performs the single synchronisation that is needed to give the tensors their final shapes.
+"""
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import ops
+
+
+class DeviceBatch:
+    """Un-trimmed result of :func:`build_batch_async` (all arrays at capacity, counts on the device)."""
+
+    def __init__(self, g, layers, counts, status, fanouts, targets_first):
+        self.g = g
+        self.layers = layers          # list of dicts of capacity-sized tensors
+        self.counts = counts          # list of device int64 scalars (1-element tensors), see finish()
+        self.status = status
+        self.fanouts = list(fanouts)
+        self._targets_first = targets_first
+
+    def finish(self) -> List[dict]:
+        """One host synchronisation: read every count, check the device status word, trim the arrays."""
+        host = self._host = torch.cat(self.counts).tolist()
+        self.status.check("build_batch")
+        n_list = host[0]
+        out = [{"gids": self.layers[0]["gids"][:n_list], "ts": self.layers[0]["ts"][:n_list],
+                "inv_map": self.layers[0]["inv_map"]}]
+        prev_n = n_list
+        for l in range(len(self.fanouts)):
+            n_edges, n_next = host[1 + 2 * l], host[2 + 2 * l]
+            L = self.layers[l + 1]
+            if n_edges == 0 and not self._any_target_has_edges(l, out, prev_n):
+                # the reference emits an empty layer and stops when no target has any edge at all
+                # (prepare_sample.py:352-361)
+                z = torch.zeros(0, dtype=torch.int64, device=self.g.device)
+                out.append({"indptr": torch.zeros(1, dtype=torch.int64, device=self.g.device), "indices": z,
+                            "eid": z, "edge_ts": z, "edge_dt": torch.zeros(0, dtype=torch.float32, device=self.g.device),
+                            "gids": z, "ts": z})
+                break
+            out.append({"indptr": L["indptr"][:prev_n + 1], "indices": L["indices"][:n_edges], "eid": L["eid"][:n_edges],
+                        "edge_ts": L["edge_ts"][:n_edges], "edge_dt": L["edge_dt"][:n_edges],
+                        "gids": L["gids"][:n_next], "ts": L["ts"][:n_next]})
+            prev_n = n_next
+        return out
+
+    def _any_target_has_edges(self, l, out, prev_n):
+        tgt = out[0]["gids"] if l == 0 else self.layers[l]["raw_nbr"][:self._host[1 + 2 * (l - 1)]]
+        if tgt.numel() == 0:
+            return False
+        deg = self.g.indptr[tgt + 1] - self.g.indptr[tgt]
+        return bool((deg > 0).any().item())
+
+
+def build_batch_async(g: ops.TCSR, roots: torch.Tensor, root_ts: torch.Tensor, fanouts: Sequence[int],
+                      policy: str = "recent", *, ts_range: Optional[Sequence[int]] = None, equal_root_time=False,
+                      allowed_offset=-1, seed=0, status: Optional[ops.StatusWord] = None) -> DeviceBatch:
+    """Enqueue the whole batch construction on the current stream.
+
+    ``ts_range`` = (lowest, highest) timestamp that can occur among the roots' query times; together with the
+    graph's own timestamp range it fixes the width of the (id, ts) sort key.  When omitted it is read from
+    ``root_ts`` (one extra synchronisation).
+    """
+    dev = g.device
+    status = status or ops.StatusWord(dev)
+    if ts_range is None:
+        if root_ts.numel():
+            lo, hi = root_ts.aminmax()
+            ts_range = (int(lo.item()), int(hi.item()))
+        else:
+            ts_range = (g.ts_min, g.ts_max)
+    ts_base = min(g.ts_min, int(ts_range[0]))
+    ts_bits = ops.bits_for(max(g.ts_max, int(ts_range[1])) - ts_base)
+    id_bits = ops.bits_for(g.num_nodes - 1)
+
+    cur_id, cur_ts, inv0, _, d_cur = ops.unique_pairs(roots, root_ts, id_bits=id_bits, ts_bits=ts_bits, ts_base=ts_base,
+                                                      status=status)
+    layers = [{"gids": cur_id, "ts": cur_ts, "inv_map": inv0[:roots.numel()]}]
+    counts = [d_cur]
+    last_inv = None
+    tgt, tgt_ts, d_tgt = cur_id, cur_ts, d_cur
+    for l, k in enumerate(fanouts):
+        cap_cur = cur_id.numel()
+        hop = ops.sample_layer(g, tgt, tgt_ts, k, policy, d_n=d_tgt, equal_root_time=equal_root_time,
+                               allowed_offset=allowed_offset, seed=seed, rng_stream=l, status=status)
+        nxt_id, nxt_ts, _, nxt_inv, d_nxt = ops.unique_pairs(cur_id, cur_ts, hop.nbr, hop.ts, id_bits=id_bits,
+                                                             ts_bits=ts_bits, ts_base=ts_base, d_n_a=d_cur,
+                                                             d_n_b=hop.d_total, status=status)
+        indptr, idx, e_ts, e_dt, e_eid = ops.build_csc(nxt_inv, hop.dst, last_inv, hop.ts, hop.dt, hop.eid, cap_cur,
+                                                       dst_bits=ops.bits_for(cap_cur), ts_bits=ts_bits, ts_base=ts_base,
+                                                       d_n_edges=hop.d_total, d_num_dst=d_cur, status=status)
+        layers.append({"indptr": indptr, "indices": idx, "eid": e_eid, "edge_ts": e_ts, "edge_dt": e_dt,
+                       "gids": nxt_id, "ts": nxt_ts, "raw_nbr": hop.nbr, "raw_ts": hop.ts, "inv": nxt_inv, "hop": hop})
+        counts += [hop.d_total, d_nxt]
+        # the next hop samples one target per edge sampled here, at that edge's timestamp (prepare_sample.py:345-346);
+        # cur_id[last_inv[j]] is by construction the j-th sampled neighbour, so no extra gather is needed
+        tgt, tgt_ts, d_tgt = hop.nbr, hop.ts, hop.d_total
+        cur_id, cur_ts, d_cur, last_inv = nxt_id, nxt_ts, d_nxt, nxt_inv
+    return DeviceBatch(g, layers, counts, status, fanouts, None)
+
+
+def build_batch(g, roots, root_ts, fanouts, policy="recent", **kw) -> List[dict]:
+    """Synchronous form of :func:`build_batch_async`."""
+    return build_batch_async(g, roots, root_ts, fanouts, policy, **kw).finish()

@@ -135,3 +135,43 @@ def test_route_two_ranks():
     gx = O.route_reverse([z[f"r{r}_w"] for r in range(P)], ss, rs, si)
     for r in range(P):
         assert np.allclose(gx[r], z[f"r{r}_gx"], rtol=0, atol=0)
+
+
+# ---- the C oracle (timed CPU baseline) against the numpy oracle and the golden vectors -------------------------
+
+@pytest.mark.parametrize("case", ["tiny", "rand_sorted", "rand_ties"])
+def test_c_oracle_matches_reference(case):
+    from oracle import oracle_c as OC
+    z = load(f"sampler_{case}.npz")
+    n = int(z["n"])
+    indptr, nbr, ts, eid, perm = OC.tcsr_build(z["dst"], z["src"], z["ts"], z["eid"], n)
+    assert np.array_equal(indptr, z["indptr"]) and np.array_equal(nbr, z["s_src"])
+    assert np.array_equal(ts, z["s_ts"]) and np.array_equal(eid, z["s_eid"])
+    for k in (1, 3, 10):
+        for e in (0, 1):
+            o = OC.sample_layer(indptr, nbr, ts, eid, z["q"], z["qt"], k, 0, equal_root_time=bool(e))
+            for nm, a in zip(("src", "dst", "ts", "dt", "eid"), o[:5]):
+                assert np.array_equal(a, z[f"recent_k{k}_e{e}_{nm}"]), (k, e, nm)
+    rng = np.random.default_rng(0)
+    q = rng.integers(0, n, 300)
+    qt = rng.integers(0, int(z["ts"].max()) + 2, 300)
+    for kw in ({}, {"allowed_offset": 7}, {"keep_root_time": True, "equal_root_time": True}):
+        a = OC.sample_layer(indptr, nbr, ts, eid, q, qt, 4, 1, seed=9, stream=2, **kw)
+        b = O.sample_layer(indptr, nbr, ts, eid, q, qt, 4, O.UNIFORM, seed=9, stream=2, **kw)
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y)
+
+
+def test_c_oracle_gather():
+    from oracle import oracle_c as OC
+    rng = np.random.default_rng(1)
+    table = rng.standard_normal((500, 43)).astype(np.float32)
+    idx = rng.integers(-500, 500, 2000)
+    assert np.array_equal(OC.gather_rows(table, idx), table[idx])
+    hitmap = np.full(500, -1, np.int32)
+    hot = rng.permutation(500)[:60]
+    hitmap[hot] = np.arange(60, dtype=np.int32)
+    ids = rng.integers(0, 500, 900)
+    out, mp, mi = OC.cache_gather(table[hot].copy(), hitmap, table, ids)
+    ref, hit, rp, ri = O.cache_gather(table[hot], hitmap, table, ids)
+    assert np.array_equal(out, ref) and np.array_equal(mp, rp) and np.array_equal(mi, ri)
