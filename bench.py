@@ -1,0 +1,338 @@
+#!/usr/bin/env python
+"""Benchmark of the per-mini-batch data path (temporal sampling + feature gather [+ route]) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step = one mini-batch of 4,096 roots on a synthetic temporal graph of 1 M nodes / 50 M edges (out-degree
+power law, alpha 2.1; int64 ids; timestamps uniform in [0, 1e7)): most-recent-20 sampling of every root before
+its query time, then the gather of the sampled edges' feature rows (172 x fp32) from a table that is much
+larger than L2.  An "event" is one root query.  Prints ONE JSON line (rank 0).
+
+  value      events/s with the batch's roots already in HBM (CUDA-event time of K steps, max over ranks)
+  e2e        the same through the host-facing call: pinned host roots -> H2D -> sample -> gather -> block
+             structure back to pinned host memory (the gathered rows stay on the GPU for the model)
+  roofline   the dominant kernel (the edge-feature gather): algorithmic bytes / its CUDA-event time
+  cpu_baseline  the CPU oracle (C/OpenMP restatement of the reference's CPU sampler + row gather) on the
+             host cores, on a bounded sample of the same batches
+With --gpus N > 1 (under torchrun) every rank owns one partition of equal size (weak scaling) and every step
+additionally pushes node-memory rows (100 x fp32 + ts) to the other partitions through the cache route.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "starrygl-framework_b200"))
+sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+
+NUM_NODES = 1_000_000
+NUM_EDGES = 50_000_000
+BATCH = 4096
+FANOUT = 20
+EDGE_DIM = 172
+MEM_DIM = 100
+TS_MAX = 10_000_000
+NUM_BATCHES = 64          # distinct pre-generated batches cycled through the steps
+ROUTE_ROWS = 800          # rows per step a partition pushes to its peers (20 % cut edges of a 4,096-root batch)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return json.load(open(p)).get("hbm_gbs", 6650.0), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def make_graph(dev, seed):
+    """Seeded synthetic stand-in for the sampler microbenchmark graph (generated on the GPU)."""
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    u = torch.rand(NUM_NODES, device=dev, generator=gen).clamp_min_(1e-9)
+    w = u.pow(-1.0 / 1.1).double()                      # Pareto tail index 1.1 <=> degree pdf exponent 2.1
+    cdf = torch.cumsum(w, 0)
+    cdf /= cdf[-1].clone()
+    src = torch.searchsorted(cdf, torch.rand(NUM_EDGES, device=dev, dtype=torch.double, generator=gen)).clamp_max_(NUM_NODES - 1)
+    dst = torch.randint(0, NUM_NODES, (NUM_EDGES,), device=dev, generator=gen)
+    ts = (torch.rand(NUM_EDGES, device=dev, dtype=torch.double, generator=gen) * TS_MAX).long()
+    return src, dst, ts, gen
+
+
+def make_batches(src, ts, gen, dev):
+    pick = torch.randint(0, NUM_EDGES, (NUM_BATCHES, BATCH), device=dev, generator=gen)
+    return src[pick].contiguous(), ts[pick].contiguous()       # query time = the drawn edge's own timestamp
+
+
+def run_reference(args, rank):
+    """The reference's CPU path (its C/OpenMP restatement: the reference is numba/Python and cannot travel) on
+    the host cores, same batches, bounded sample."""
+    if rank != 0:
+        return
+    from oracle import oracle_c as OC
+    dev = torch.device("cuda", 0) if torch.cuda.is_available() else None
+    out = cpu_baseline_measure(dev, steps=args.steps, warmup=args.warmup, budget_s=60.0)
+    line = {"metric": "sampled+gathered events/sec", "value": out["value"], "unit": "events/s", "n_gpus": args.gpus,
+            "steps": out["steps"], "warmup": args.warmup, "ms_per_step": out["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic", "impl": "reference",
+            "config": workload_config(1), "cpu_baseline": out["cpu_baseline"],
+            "e2e": {"value": out["value"], "unit": "events/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus):
+    return {"workload": "1xB200 sampler microbench + sampled edge-feature gather (BASELINE configs[1] graph, configs[2] rows)",
+            "graph": f"{NUM_NODES} nodes, {NUM_EDGES} edges, out-degree power law alpha 2.1, int64 ids, ts U[0,1e7)",
+            "batch_roots": BATCH, "policy": f"recent-{FANOUT}, 1 hop", "edge_feat": f"{EDGE_DIM} x fp32",
+            "edge_feat_rows": NUM_EDGES, "event": "one root query",
+            "l2": "inputs larger than L2: 64 distinct batches over a 34 GB feature table and a 1.2 GB adjacency",
+            "parallelism": f"{n_gpus} partition(s), one process per GPU" + (", cache route all-to-all per step" if n_gpus > 1 else "")}
+
+
+def cpu_baseline_measure(dev, steps, warmup, budget_s):
+    """Times the C oracle on the same graph and batches.  The graph is generated with the same seeded generator
+    (on the GPU when there is one, and copied to the host); the feature table is a 1 M-row host sample
+    (edge id modulo 1 M) because 34 GB of host rows are not needed to time a row gather."""
+    from oracle import oracle_c as OC
+    gdev = dev if dev is not None else torch.device("cpu")
+    if dev is None:
+        raise RuntimeError("the benchmark graph is generated on the GPU")
+    src, dst, ts, gen = make_graph(gdev, 0)
+    b_roots, b_ts = make_batches(src, ts, gen, gdev)
+    src_h, dst_h, ts_h = src.cpu().numpy(), dst.cpu().numpy(), ts.cpu().numpy()
+    del src, dst, ts
+    torch.cuda.empty_cache()
+    cores = os.cpu_count() or 1
+    OC.set_threads(cores)
+    t0 = time.perf_counter()
+    indptr, nbr, tss, eid, _ = OC.tcsr_build(src_h, dst_h, ts_h, None, NUM_NODES)
+    build_s = time.perf_counter() - t0
+    del src_h, dst_h
+    rows_h = 1_000_000
+    feats = np.random.default_rng(0).standard_normal((rows_h, EDGE_DIM), dtype=np.float32)
+    roots_h, rts_h = b_roots.cpu().numpy(), b_ts.cpu().numpy()
+    out_rows = np.empty((BATCH * FANOUT, EDGE_DIM), np.float32)
+
+    def step(i):
+        o = OC.sample_layer(indptr, nbr, tss, eid, roots_h[i % NUM_BATCHES], rts_h[i % NUM_BATCHES], FANOUT, 0, trim=False)
+        tot = int(o[5][-1])
+        OC.gather_rows(feats, o[4][:tot] % rows_h, out_rows)
+        return tot
+    for i in range(max(warmup, 3)):
+        step(i)
+    n_done, t0 = 0, time.perf_counter()
+    while n_done < max(steps, 1) * 50 and time.perf_counter() - t0 < min(budget_s, 20.0):
+        step(n_done)
+        n_done += 1
+    dt = time.perf_counter() - t0
+    val = n_done * BATCH / dt
+    return {"value": val, "steps": n_done, "ms_per_step": dt / n_done * 1e3,
+            "cpu_baseline": {"value": val, "unit": "events/s", "cores": cores, "kind": "port",
+                             "sample": f"{n_done} of the benchmark's batches (recent-{FANOUT} sampling on the full 50 M-edge graph + gather "
+                                       f"of the sampled rows from a {rows_h}-row host table), C/OpenMP restatement of the reference's numba "
+                                       f"sampler; T-CSR build on the host took {build_s:.1f} s"}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather-mode", default="auto")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        return run_reference(args, rank)
+
+    import torch.distributed as dist
+    from starrygl import ops, _C
+    from starrygl.graph.pipeline import SampleGatherPipeline
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    multi = world > 1
+    if multi:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    # ---- set-up (untimed): graph, T-CSR, feature table, batches -------------------------------------------
+    src, dst, ts, gen = make_graph(dev, seed=rank)
+    g = ops.tcsr_build(src, dst, ts, None, NUM_NODES)
+    b_roots, b_ts = make_batches(src, ts, gen, dev)
+    del src, dst, ts
+    feats = torch.empty(NUM_EDGES, EDGE_DIM, dtype=torch.float32, device=dev)
+    for s in range(0, NUM_EDGES, 5_000_000):
+        feats[s:s + 5_000_000].normal_(generator=gen)
+    stream = torch.cuda.Stream(dev)
+    pipe = SampleGatherPipeline(g, feats, FANOUT, "recent", BATCH, gather_mode=args.gather_mode, stream=stream)
+    h_roots = b_roots.cpu().pin_memory()
+    h_ts = b_ts.cpu().pin_memory()
+
+    route = None
+    if multi:
+        from starrygl.cache.cache_route import CacheRoute, CommPlan
+        from starrygl.cache.NodeState import DistNodeState
+        from starrygl.utils.partition_book import PartitionState
+        rgen = torch.Generator().manual_seed(100 + rank)
+        # per step: ROUTE_ROWS owned rows go to the other ranks (round-robin), slots on the receiver are unique
+        per = ROUTE_ROWS // (world - 1)
+        ranks = torch.cat([torch.full((per,), p, dtype=torch.long) for p in range(world) if p != rank])
+        sizes = torch.bincount(ranks, minlength=world)
+        plans = []
+        for b in range(NUM_BATCHES):
+            plans.append(CommPlan(send_ranks=ranks, send_sizes=sizes,
+                                  send_indices=torch.randint(0, NUM_NODES, (ranks.numel(),), generator=rgen),
+                                  send_remote_indices=(torch.randperm(NUM_NODES, generator=rgen)[:ranks.numel()])).to(dev))
+        ps = PartitionState(loc_ids=torch.arange(NUM_NODES, device=dev), num_master_nums=NUM_NODES, node_mode='identity',
+                            num_nodes=NUM_NODES)
+        state = DistNodeState(ps, MEM_DIM, device=dev)
+        mem = torch.randn(NUM_NODES, MEM_DIM, device=dev)
+        mem_ts = torch.rand(NUM_NODES, device=dev)
+        cr = CacheRoute()
+
+        def cb(idx, rows, mode):
+            state.write_packed(idx, rows)
+        cb.fused_state = state
+        route = (cr, plans, mem, mem_ts, cb)
+        for p in plans:     # receive counts are exchanged once per plan (set-up), steps then need no host sync
+            cr._exchange_counts(p, dev)
+
+    def step_device(i, ev=None):
+        b = i % NUM_BATCHES
+        pipe.run_device(b_roots[b], b_ts[b], 0, ev)
+        if route is not None:
+            cr, plans, mem, mem_ts, cb = route
+            with torch.cuda.stream(stream):
+                futs = cr.update_with_plan(mem, plans[b], cb, local_ts=mem_ts)
+                for f in futs:
+                    f.wait()
+
+    def barrier():
+        if multi:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- value: inputs resident in HBM --------------------------------------------------------------------
+    for i in range(args.warmup):
+        step_device(i)
+    barrier()
+    pipe.status.check("bench warmup")
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
+    gev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for i in range(args.steps):
+        step_device(args.warmup + i, gev[i])
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    pipe.status.check("bench")
+    gather_ms = [a.elapsed_time(b) for a, b in gev]
+    # edges actually gathered per step (for the algorithmic byte count), read after the timed region
+    edges = []
+    for i in range(args.steps):
+        pipe.run_device(b_roots[(args.warmup + i) % NUM_BATCHES], b_ts[(args.warmup + i) % NUM_BATCHES])
+        edges.append(int(pipe.offsets[BATCH].item()))
+
+    # ---- e2e: host buffers in, block structure out ---------------------------------------------------------
+    for i in range(args.warmup):
+        pipe.run_host(h_roots[i % NUM_BATCHES], h_ts[i % NUM_BATCHES])
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps = args.steps
+    for i in range(e2e_steps):
+        pipe.run_host(h_roots[(args.warmup + i) % NUM_BATCHES], h_ts[(args.warmup + i) % NUM_BATCHES])
+        if route is not None:
+            cr, plans, mem, mem_ts, cb = route
+            with torch.cuda.stream(stream):
+                for f in cr.update_with_plan(mem, plans[(args.warmup + i) % NUM_BATCHES], cb, local_ts=mem_ts):
+                    f.wait()
+            stream.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    clk = clocks.stop() if rank == 0 else None
+
+    t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if multi:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        row_bytes = EDGE_DIM * 4
+        alg = statistics.mean(edges) * (2 * row_bytes + 8)
+        g_ms = statistics.mean(gather_ms)
+        achieved = alg / g_ms / 1e6
+        line = {"metric": "sampled+gathered events/sec", "value": world * BATCH * args.steps / (ms / 1e3),
+                "unit": "events/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "int64", "data": "synthetic", "config": workload_config(world),
+                "e2e": {"value": world * BATCH * e2e_steps / (e2e_ms / 1e3), "unit": "events/s",
+                        "h2d_bytes_per_step": pipe.h2d_bytes(BATCH), "d2h_bytes_per_step": pipe.d2h_bytes(),
+                        "note": "pinned host roots/times in; offsets, neighbour ids, slots, timestamps, edge ids and dt out; "
+                                "gathered feature rows stay on the GPU for the model"},
+                "gpu_launches": args.steps * (pipe.kernel_launches_per_step + (2 if multi else 0)),
+                "roofline": {"bound": "hbm", "kernel": "gather_bulk_kernel" if pipe.mode != 1 else "gather_lanes_kernel",
+                             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "peak_source": peak_kind, "traffic": None,
+                             "bytes_per_launch": alg, "ms_per_launch": g_ms,
+                             "edges_per_step": statistics.mean(edges)},
+                "clocks": clk}
+        if not args.no_cpu_baseline and world == 1:
+            del feats, pipe
+            torch.cuda.empty_cache()
+            line["cpu_baseline"] = cpu_baseline_measure(dev, args.steps, args.warmup, 20.0)["cpu_baseline"]
+        print(json.dumps(line))
+    if multi:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

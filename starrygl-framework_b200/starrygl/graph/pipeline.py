@@ -1,0 +1,113 @@
+"""Pre-bound sample -> gather pipeline for one mini-batch of roots.
+
+The per-call work of :func:`starrygl.ops.sample_layer` / :func:`starrygl.ops.gather_rows` that does not depend
+on the batch (output buffers, scratch, argument marshalling) is done once here, so that a step is a handful of
+foreign calls: copy the roots in, sample one hop, gather the edge-feature rows of the sampled edges, and --
+for callers whose consumer is on the host -- copy the block structure back.  It is what a prefetcher calls per
+mini-batch (the reference's prefetcher/collator modules consume the sampler through ``AsyncBlock``,
+starrygl/graph/graph.py:139-151, and read edge features as ``block.e_future``, starrygl/nn/model/tgn.py:161-162).
+
+Buffers are reused from call to call: consume (or copy) a result before running the next batch on the same
+pipeline object; use two objects for double buffering.
+"""
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from .. import _C, ops
+
+I64 = torch.int64
+
+
+class SampleGatherPipeline:
+    def __init__(self, g: ops.TCSR, edge_feats: Optional[torch.Tensor], fanout: int, policy: str = "recent",
+                 max_roots: int = 4096, *, equal_root_time=False, allowed_offset=-1, keep_root_time=False, seed=0,
+                 gather_mode="auto", stream: Optional[torch.cuda.Stream] = None):
+        self.g, self.feats, self.k, self.max_roots = g, edge_feats, int(fanout), int(max_roots)
+        dev = g.device
+        self.dev = dev
+        self.stream = stream or torch.cuda.current_stream(dev)
+        self.L = _C.lib()
+        cap = self.max_roots * self.k
+        self.cap = cap
+        self.roots = torch.empty(self.max_roots, dtype=I64, device=dev)
+        self.root_ts = torch.empty(self.max_roots, dtype=I64, device=dev)
+        # one int64 block for the index outputs so that the block structure goes back to the host in ONE copy:
+        # [offsets (max_roots+1) | nbr | dst | ts | eid] each of capacity cap, then dt (float32) separately
+        self.blk = torch.empty(self.max_roots + 1 + 4 * cap, dtype=I64, device=dev)
+        o = self.max_roots + 1
+        self.offsets = self.blk[:o]
+        self.nbr, self.dst, self.ts, self.eid = (self.blk[o + i * cap:o + (i + 1) * cap] for i in range(4))
+        self.dt = torch.empty(cap, dtype=torch.float32, device=dev)
+        self.status = ops.StatusWord(dev)
+        self.ws = torch.empty(self.L.sgl_sample_ws_bytes(self.max_roots), dtype=torch.uint8, device=dev)
+        self.out_feats = None
+        if edge_feats is not None:
+            self.out_feats = torch.empty((cap,) + tuple(edge_feats.shape[1:]), dtype=edge_feats.dtype, device=dev)
+            self.row_bytes, self.src_pitch = ops._row_bytes(edge_feats)
+        self.mode = _C.GATHER_MODE[gather_mode]
+        self.args = dict(pol=_C.POLICY[policy], eq=int(bool(equal_root_time)), off=int(allowed_offset),
+                         keep=int(bool(keep_root_time)), seed=int(seed) & (2 ** 64 - 1))
+        # pinned host mirrors for callers with host buffers
+        self.h_roots = torch.empty(self.max_roots, dtype=I64).pin_memory()
+        self.h_root_ts = torch.empty(self.max_roots, dtype=I64).pin_memory()
+        self.h_blk = torch.empty(self.blk.numel(), dtype=I64).pin_memory()
+        self.h_dt = torch.empty(cap, dtype=torch.float32).pin_memory()
+        self.kernel_launches_per_step = 2 + (1 if edge_feats is not None else 0)
+
+    # ---- device-resident inputs ------------------------------------------------------------------------
+    def run_device(self, roots: torch.Tensor, root_ts: torch.Tensor, rng_stream: int = 0, gather_events=None):
+        """Sample + gather for roots already on the GPU.  Returns nothing: results are in ``self.offsets``,
+        ``self.nbr`` ... ``self.out_feats`` (valid prefix = ``self.offsets[n]`` edges).  No synchronisation.
+        ``gather_events`` = (start, end) CUDA events recorded around the gather launch (profiling hook)."""
+        n = roots.numel()
+        if n > self.max_roots:
+            raise _C.SglError(f"batch of {n} roots exceeds max_roots={self.max_roots}")
+        L, g, a, sp = self.L, self.g, self.args, self.stream.cuda_stream
+        rc = L.sgl_sample_layer(g.indptr.data_ptr(), g.nbr.data_ptr(), g.ts.data_ptr(), g.eid.data_ptr(), g.num_nodes,
+                                roots.data_ptr(), root_ts.data_ptr(), n, None, self.k, a["pol"], a["eq"], a["off"],
+                                a["keep"], a["seed"], rng_stream, self.nbr.data_ptr(), self.dst.data_ptr(),
+                                self.ts.data_ptr(), self.dt.data_ptr(), None, self.eid.data_ptr(),
+                                self.offsets.data_ptr(), self.status.ptr(), self.ws.data_ptr(), self.ws.numel(), sp)
+        _C.check(rc)
+        if self.feats is not None:
+            if gather_events:
+                gather_events[0].record(self.stream)
+            d_total = self.offsets.data_ptr() + 8 * n
+            rc = L.sgl_gather_rows(self.feats.data_ptr(), self.feats.shape[0], self.row_bytes, self.src_pitch,
+                                   self.eid.data_ptr(), None, 0, n * self.k, d_total, self.out_feats.data_ptr(),
+                                   self.row_bytes, None, None, self.mode, self.status.ptr(), sp)
+            _C.check(rc)
+            if gather_events:
+                gather_events[1].record(self.stream)
+        return n
+
+    # ---- host inputs / host results --------------------------------------------------------------------
+    def run_host(self, h_roots: torch.Tensor, h_root_ts: torch.Tensor, rng_stream: int = 0):
+        """Roots and query times from (pinned) host tensors; the block structure (offsets, neighbour ids, target
+        slots, timestamps, edge ids, dt) comes back to pinned host memory.  The gathered feature rows stay on the
+        GPU (``self.out_feats``): their consumer is the model.  Returns (n_edges, host views) after synchronising."""
+        n = h_roots.numel()
+        with torch.cuda.stream(self.stream):
+            self.roots[:n].copy_(h_roots, non_blocking=True)
+            self.root_ts[:n].copy_(h_root_ts, non_blocking=True)
+            self.run_device(self.roots[:n], self.root_ts[:n], rng_stream)
+            # offsets first (tiny), then only the used prefix of every array would need the count on the host;
+            # one fixed-size copy of the whole block avoids that round trip
+            self.h_blk.copy_(self.blk, non_blocking=True)
+            self.h_dt.copy_(self.dt, non_blocking=True)
+        self.stream.synchronize()
+        o = self.max_roots + 1
+        tot = int(self.h_blk[n])
+        cap = self.cap
+        views = {"offsets": self.h_blk[:n + 1], "nbr": self.h_blk[o:o + tot], "dst": self.h_blk[o + cap:o + cap + tot],
+                 "ts": self.h_blk[o + 2 * cap:o + 2 * cap + tot], "eid": self.h_blk[o + 3 * cap:o + 3 * cap + tot],
+                 "dt": self.h_dt[:tot]}
+        return tot, views
+
+    def h2d_bytes(self, n):
+        return 16 * n
+
+    def d2h_bytes(self):
+        return self.blk.numel() * 8 + self.dt.numel() * 4
