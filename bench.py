@@ -41,6 +41,8 @@ EDGE_DIM = 172
 MEM_DIM = 100
 TS_MAX = 10_000_000
 NUM_BATCHES = 64          # distinct pre-generated batches cycled through the steps
+STREAMS = 6
+GRAPHS = True
 ROUTE_ROWS = 800          # rows per step a partition pushes to its peers (20 % cut edges of a 4,096-root batch)
 
 
@@ -125,7 +127,7 @@ def workload_config(n_gpus):
             "batch_roots": BATCH, "policy": f"recent-{FANOUT}, 1 hop", "edge_feat": f"{EDGE_DIM} x fp32",
             "edge_feat_rows": NUM_EDGES, "event": "one root query",
             "l2": "inputs larger than L2: 64 distinct batches over a 34 GB feature table and a 1.2 GB adjacency",
-            "parallelism": f"{n_gpus} partition(s), one process per GPU" + (", cache route all-to-all per step" if n_gpus > 1 else "")}
+            "batches_in_flight": STREAMS, "parallelism": f"{n_gpus} partition(s), one process per GPU" + (", cache route all-to-all per step" if n_gpus > 1 else "")}
 
 
 def cpu_baseline_measure(dev, steps, warmup, budget_s):
@@ -173,6 +175,7 @@ def cpu_baseline_measure(dev, steps, warmup, budget_s):
 
 
 def main():
+    global NUM_NODES, NUM_EDGES, STREAMS, GRAPHS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -180,8 +183,15 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather-mode", default="auto")
+    ap.add_argument("--streams", type=int, default=6, help="mini-batches in flight (one pipeline object + stream each)")
+    ap.add_argument("--graph-value", action="store_true",
+                    help="replay a CUDA graph per step in the device-resident loop too (default: one fused C call per step; "
+                         "the host-buffer loop always replays a graph that includes its copies)")
+    ap.add_argument("--num-nodes", type=int, default=NUM_NODES, help="smaller graphs are for profiler captures only")
+    ap.add_argument("--num-edges", type=int, default=NUM_EDGES)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    NUM_NODES, NUM_EDGES, STREAMS, GRAPHS = args.num_nodes, args.num_edges, max(1, args.streams), True
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -206,8 +216,15 @@ def main():
     feats = torch.empty(NUM_EDGES, EDGE_DIM, dtype=torch.float32, device=dev)
     for s in range(0, NUM_EDGES, 5_000_000):
         feats[s:s + 5_000_000].normal_(generator=gen)
-    stream = torch.cuda.Stream(dev)
-    pipe = SampleGatherPipeline(g, feats, FANOUT, "recent", BATCH, gather_mode=args.gather_mode, stream=stream)
+    S = max(1, args.streams)
+    streams = [torch.cuda.Stream(dev) for _ in range(S)]
+    pipes = [SampleGatherPipeline(g, feats, FANOUT, "recent", BATCH, gather_mode=args.gather_mode, stream=st)
+             for st in streams]
+    pipe, stream = pipes[0], streams[0]
+    use_graph = args.graph_value
+    for p_ in pipes:
+        p_.capture()
+    main_stream = torch.cuda.Stream(dev)
     h_roots = b_roots.cpu().pin_memory()
     h_ts = b_ts.cpu().pin_memory()
 
@@ -240,12 +257,19 @@ def main():
         for p in plans:     # receive counts are exchanged once per plan (set-up), steps then need no host sync
             cr._exchange_counts(p, dev)
 
+    batch_ptrs = [(b_roots[b].data_ptr(), b_ts[b].data_ptr()) for b in range(NUM_BATCHES)]
+
     def step_device(i, ev=None):
         b = i % NUM_BATCHES
-        pipe.run_device(b_roots[b], b_ts[b], 0, ev)
+        if ev is not None:
+            pipes[i % S].run_device(b_roots[b], b_ts[b], 0, ev)
+        elif use_graph:
+            pipes[i % S].replay_device(b_roots[b], b_ts[b])
+        else:
+            pipes[i % S].run_device_ptr(batch_ptrs[b][0], batch_ptrs[b][1], BATCH)
         if route is not None:
             cr, plans, mem, mem_ts, cb = route
-            with torch.cuda.stream(stream):
+            with torch.cuda.stream(streams[i % S]):
                 futs = cr.update_with_plan(mem, plans[b], cb, local_ts=mem_ts)
                 for f in futs:
                     f.wait()
@@ -259,41 +283,67 @@ def main():
     for i in range(args.warmup):
         step_device(i)
     barrier()
-    pipe.status.check("bench warmup")
+    for p_ in pipes:
+        p_.status.check("bench warmup")
     clocks = ClockSampler(local)
     if rank == 0:
         clocks.start()
     gev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    e0.record(stream)
+    # K steps, up to S of them in flight: the streams fork from / join into main_stream, whose two events bracket
+    # the whole region on the device
+    e0.record(main_stream)
+    for st in streams:
+        st.wait_stream(main_stream)
+    t_issue = time.perf_counter()
     for i in range(args.steps):
-        step_device(args.warmup + i, gev[i])
-    e1.record(stream)
+        step_device(args.warmup + i, None)
+    t_issue = time.perf_counter() - t_issue
+    for st in streams:
+        main_stream.wait_stream(st)
+    e1.record(main_stream)
     barrier()
     ms = e0.elapsed_time(e1)
-    pipe.status.check("bench")
+    for p_ in pipes:
+        p_.status.check("bench")
+    if True:
+        # the step is one foreign call (or one graph replay), so its kernels cannot be bracketed individually:
+        # the dominant kernel is timed in a second pass over the same K batches, kernel by kernel on one stream
+        for i in range(args.steps):
+            pipe.run_device(b_roots[(args.warmup + i) % NUM_BATCHES], b_ts[(args.warmup + i) % NUM_BATCHES], 0, gev[i])
+        pipe.stream.synchronize()
     gather_ms = [a.elapsed_time(b) for a, b in gev]
     # edges actually gathered per step (for the algorithmic byte count), read after the timed region
     edges = []
     for i in range(args.steps):
         pipe.run_device(b_roots[(args.warmup + i) % NUM_BATCHES], b_ts[(args.warmup + i) % NUM_BATCHES])
+        pipe.stream.synchronize()
         edges.append(int(pipe.offsets[BATCH].item()))
 
-    # ---- e2e: host buffers in, block structure out ---------------------------------------------------------
-    for i in range(args.warmup):
-        pipe.run_host(h_roots[i % NUM_BATCHES], h_ts[i % NUM_BATCHES])
+    # ---- e2e: host buffers in, block structure out, up to S batches in flight -------------------------------
+    def e2e_loop(first, count):
+        tot = 0
+        for i in range(count):
+            p_ = pipes[i % S]
+            if i >= S:                          # retire the batch that used this pipeline object before reusing it
+                tot += p_.result()[0]
+            b = (first + i) % NUM_BATCHES
+            p_.submit_host(h_roots[b], h_ts[b])
+            if route is not None:
+                cr, plans, mem, mem_ts, cb = route
+                with torch.cuda.stream(streams[i % S]):
+                    for f in cr.update_with_plan(mem, plans[b], cb, local_ts=mem_ts):
+                        f.wait()
+        for i in range(max(0, count - S), count):
+            tot += pipes[i % S].result()[0]
+        return tot
+    e2e_loop(0, args.warmup)
     barrier()
     t0 = time.perf_counter()
     e2e_steps = args.steps
-    for i in range(e2e_steps):
-        pipe.run_host(h_roots[(args.warmup + i) % NUM_BATCHES], h_ts[(args.warmup + i) % NUM_BATCHES])
-        if route is not None:
-            cr, plans, mem, mem_ts, cb = route
-            with torch.cuda.stream(stream):
-                for f in cr.update_with_plan(mem, plans[(args.warmup + i) % NUM_BATCHES], cb, local_ts=mem_ts):
-                    f.wait()
-            stream.synchronize()
+    e2e_edges = e2e_loop(args.warmup, e2e_steps)
+    torch.cuda.synchronize(dev)
     e2e_s = time.perf_counter() - t0
     barrier()
     clk = clocks.stop() if rank == 0 else None
@@ -311,12 +361,13 @@ def main():
         achieved = alg / g_ms / 1e6
         line = {"metric": "sampled+gathered events/sec", "value": world * BATCH * args.steps / (ms / 1e3),
                 "unit": "events/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "ms_per_step": ms / args.steps, "host_issue_ms_per_step": t_issue * 1e3 / args.steps,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "int64", "data": "synthetic", "config": workload_config(world),
                 "e2e": {"value": world * BATCH * e2e_steps / (e2e_ms / 1e3), "unit": "events/s",
                         "h2d_bytes_per_step": pipe.h2d_bytes(BATCH), "d2h_bytes_per_step": pipe.d2h_bytes(),
-                        "note": "pinned host roots/times in; offsets, neighbour ids, slots, timestamps, edge ids and dt out; "
-                                "gathered feature rows stay on the GPU for the model"},
+                        "note": "pinned host roots/times in; offsets, neighbour ids, timestamps, edge ids and dt out; "
+                                "gathered feature rows stay on the GPU for the model", "edges_per_step": e2e_edges / e2e_steps},
                 "gpu_launches": args.steps * (pipe.kernel_launches_per_step + (2 if multi else 0)),
                 "roofline": {"bound": "hbm", "kernel": "gather_bulk_kernel" if pipe.mode != 1 else "gather_lanes_kernel",
                              "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -325,7 +376,7 @@ def main():
                              "edges_per_step": statistics.mean(edges)},
                 "clocks": clk}
         if not args.no_cpu_baseline and world == 1:
-            del feats, pipe
+            del feats, pipe, pipes
             torch.cuda.empty_cache()
             line["cpu_baseline"] = cpu_baseline_measure(dev, args.steps, args.warmup, 20.0)["cpu_baseline"]
         print(json.dumps(line))

@@ -104,6 +104,22 @@ int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const int64_t* t
                      int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * One hop of sampling followed by the gather of the sampled edges' feature rows, in one call:
+ * sgl_sample_layer(...) and then out_feats[j, :] = feat_table[out_eid[j], :] for the edges the hop produced
+ * (their number never reaches the host: the gather reads it from out_offsets[n_targets]).  out_feats needs
+ * capacity n_targets * fanout rows of row_bytes.  gather_mode is an SGL_GATHER_* value.
+ * Replaces: the sampler call plus the edge-feature read a mini-batch triggers
+ * (starrygl/graph/graph.py:139-151 and starrygl/nn/model/tgn.py:161-162).
+ * ---------------------------------------------------------------------------------------------- */
+int sgl_sample_gather(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                      int64_t num_nodes, const int64_t* targets, const int64_t* target_ts, int64_t n_targets,
+                      int fanout, int policy, int equal_root_time, int64_t allowed_offset, int keep_root_time,
+                      uint64_t seed, uint32_t rng_stream, int64_t* out_nbr, int64_t* out_dst, int64_t* out_ts,
+                      float* out_dt, int64_t* out_eid, int64_t* out_offsets, const void* feat_table,
+                      int64_t feat_rows, int64_t row_bytes, int64_t src_pitch, void* out_feats, int gather_mode,
+                      int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * (node, ts)-pair relabel.  Input = two concatenated segments A (n_a items) then B (n_b items);
  * output = the sorted (id, then ts) unique union, its size (*d_n_unique, device), and for every input
  * item the rank of its pair in the union (inv_a, inv_b; either may be NULL).  Timestamps must lie in

@@ -12,6 +12,8 @@
 //   scatter_lanes_kernel    the reverse of the gather, optionally splitting a trailing timestamp column.
 //
 // Algorithmic HBM bytes: rows * (2 * row_bytes + 8) (+4 per id for the hit-map, +16 per miss for the miss list).
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "scan.cuh"
 
@@ -99,7 +101,7 @@ gather_lanes_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t
 // ---------------------------------------------------------------------------------------------------------------
 // bulk asynchronous copy path
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kBulkWarps = 4;
+constexpr int kBulkWarps = 4;     // default configuration; the kernel is templated for tuning
 constexpr int kBulkStages = 3;
 constexpr unsigned long long kBulkWaitLimitNs = 2000000000ull;  // a wait gives up after two seconds
 
@@ -147,6 +149,7 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Output rows must be contiguous (dst_pitch == row_bytes); row_bytes multiple of 16; rows_per_stage <= 32.
+template <int kBulkWarps, int kBulkStages>
 __global__ void __launch_bounds__(kBulkWarps * 32)
 gather_bulk_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t row_bytes, int64_t src_pitch,
                    const int64_t* __restrict__ idx, const int64_t* __restrict__ map, int64_t map_len, int64_t n_cap,
@@ -474,23 +477,51 @@ extern "C" int sgl_gather_rows(const void* table, int64_t table_rows, int64_t ro
   SGL_REQUIRE(table && idx && out, SGL_ERR_ARG, "gather_rows: null array");
   SGL_REQUIRE(map == nullptr || map_len > 0, SGL_ERR_ARG, "gather_rows: empty map");
   const bool vec_ok = row_bytes % 16 == 0 && src_pitch % 16 == 0 && dst_pitch % 16 == 0 && aligned16(table) && aligned16(out);
-  if (mode == SGL_GATHER_AUTO) mode = vec_ok ? SGL_GATHER_VEC : 0;
+  if (mode == SGL_GATHER_AUTO) {
+    // measured on B200: the bulk-copy pipeline beats 128-bit lanes from 512-byte rows up; below that they tie
+    const bool bulk_ok = vec_ok && dst_pitch == row_bytes && row_bytes >= 512 && row_bytes <= 8192 && n >= 1024;
+    mode = bulk_ok ? SGL_GATHER_BULK : (vec_ok ? SGL_GATHER_VEC : 0);
+  }
   if (mode == SGL_GATHER_BULK) {
     SGL_REQUIRE(vec_ok && dst_pitch == row_bytes, SGL_ERR_UNSUPPORTED,
                 "gather_rows: bulk mode needs 16-byte rows and a dense output");
-    const int64_t budget = 200 * 1024;
-    int rows_per_stage = (int)(budget / ((int64_t)kBulkWarps * kBulkStages * row_bytes));
+    // configuration: warps per CTA, stages per warp, rows per stage, CTAs per SM (SGL_BULK_CFG="w,s,r,c" overrides)
+    static int cfg[4] = {-1, 0, 0, 0};
+    if (cfg[0] < 0) {
+      cfg[0] = kBulkWarps; cfg[1] = kBulkStages; cfg[2] = 0; cfg[3] = 2;   // measured best on B200 (two CTAs per SM)
+      const char* e = getenv("SGL_BULK_CFG");
+      if (e) sscanf(e, "%d,%d,%d,%d", &cfg[0], &cfg[1], &cfg[2], &cfg[3]);
+    }
+    const int warps = cfg[0], stages = cfg[1], ctas_per_sm = cfg[3] < 1 ? 1 : cfg[3];
+    const int64_t budget = 200 * 1024 / ctas_per_sm;
+    int rows_per_stage = (int)(budget / ((int64_t)warps * stages * row_bytes));
+    // about 5.5 KB per stage (8 rows of 688 bytes) unless overridden
+    const int want_rows = cfg[2] > 0 ? cfg[2] : (int)((5632 + row_bytes - 1) / row_bytes);
+    if (rows_per_stage > want_rows) rows_per_stage = want_rows;
     if (rows_per_stage > 32) rows_per_stage = 32;
     SGL_REQUIRE(rows_per_stage >= 2, SGL_ERR_UNSUPPORTED, "gather_rows: row of %lld bytes too large for bulk mode",
                 (long long)row_bytes);
-    const size_t smem = (size_t)kBulkWarps * kBulkStages * rows_per_stage * row_bytes;
-    SGL_CUDA_CHECK(cudaFuncSetAttribute(gather_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    const size_t smem = (size_t)warps * stages * rows_per_stage * row_bytes;
     const int64_t chunks = (n + rows_per_stage - 1) / rows_per_stage;
-    int64_t ctas = (chunks + kBulkWarps - 1) / kBulkWarps;
-    if (ctas > kNumSM) ctas = kNumSM;  // one persistent CTA per SM (shared memory allows one)
-    gather_bulk_kernel<<<(unsigned)ctas, kBulkWarps * 32, smem, stream>>>(
-        (const char*)table, table_rows, (uint32_t)row_bytes, src_pitch, idx, map, map_len, n, d_n, (char*)out, ts_table,
-        out_ts, rows_per_stage, d_status);
+    int64_t ctas = (chunks + warps - 1) / warps;
+    if (ctas > (int64_t)kNumSM * ctas_per_sm) ctas = (int64_t)kNumSM * ctas_per_sm;  // persistent CTAs
+#define SGL_BULK_LAUNCH(W, S)                                                                                          \
+  do {                                                                                                                 \
+    SGL_CUDA_CHECK(cudaFuncSetAttribute(gather_bulk_kernel<W, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
+    gather_bulk_kernel<W, S><<<(unsigned)ctas, W * 32, smem, stream>>>(                                                \
+        (const char*)table, table_rows, (uint32_t)row_bytes, src_pitch, idx, map, map_len, n, d_n, (char*)out, ts_table, \
+        out_ts, rows_per_stage, d_status);                                                                             \
+  } while (0)
+    if (warps == 4 && stages == 3) SGL_BULK_LAUNCH(4, 3);
+    else if (warps == 4 && stages == 2) SGL_BULK_LAUNCH(4, 2);
+    else if (warps == 4 && stages == 4) SGL_BULK_LAUNCH(4, 4);
+    else if (warps == 8 && stages == 2) SGL_BULK_LAUNCH(8, 2);
+    else if (warps == 8 && stages == 3) SGL_BULK_LAUNCH(8, 3);
+    else if (warps == 8 && stages == 4) SGL_BULK_LAUNCH(8, 4);
+    else if (warps == 2 && stages == 4) SGL_BULK_LAUNCH(2, 4);
+    else if (warps == 16 && stages == 2) SGL_BULK_LAUNCH(16, 2);
+    else SGL_REQUIRE(false, SGL_ERR_ARG, "gather_rows: unsupported SGL_BULK_CFG %d,%d", warps, stages);
+#undef SGL_BULK_LAUNCH
     SGL_LAUNCH_CHECK();
     return SGL_OK;
   }

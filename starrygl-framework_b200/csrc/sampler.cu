@@ -10,6 +10,8 @@
 //
 // Algorithmic HBM bytes per target: 16 (indptr pair) + 16 (target id, time) + 8*ceil(log2 deg) (search
 // probes) + k_eff*24 (nbr, ts, eid reads) + k_eff*36 (five output arrays) + 8 (offset).
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "scan.cuh"
 
@@ -17,9 +19,11 @@ namespace sgl {
 namespace {
 
 constexpr int kWarpsPerCta = 8;
-constexpr int kTargetsPerWarp = 4;                                  // consecutive targets handled by one warp
-constexpr int kTargetsPerCta = kWarpsPerCta * kTargetsPerWarp;      // 32
 constexpr int kCtaThreads = kWarpsPerCta * 32;
+// Targets per warp (TPW) is chosen per launch: 1 for small batches (every target gets its own warp, shortest
+// dependent-load chain), 4 for medium ones, 32 for very large ones, where the searches run one target per LANE
+// (plain binary search: one 32-byte sector per step instead of 32 sectors per warp-wide step) and the number of
+// CTAs -- hence the length of the last-CTA scan -- stays small.
 
 // first position p in [lo, hi) with ts[p] >= bound (hi when none); all 32 lanes cooperate and agree
 __device__ __forceinline__ int64_t warp_lower_bound(const int64_t* __restrict__ ts, int64_t lo, int64_t hi,
@@ -61,6 +65,15 @@ struct Philox {
   }
 };
 
+__device__ __forceinline__ int64_t lane_lower_bound(const int64_t* __restrict__ ts, int64_t lo, int64_t hi, int64_t bound) {
+  while (lo < hi) {
+    int64_t mid = lo + ((hi - lo) >> 1);
+    if (__ldg(ts + mid) < bound) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+template <int TPW>
 __global__ void __launch_bounds__(kCtaThreads)
 sample_count_kernel(const int64_t* __restrict__ indptr, const int64_t* __restrict__ ts, int64_t num_nodes,
                     const int64_t* __restrict__ targets, const int64_t* __restrict__ target_ts, int64_t n_cap,
@@ -68,47 +81,69 @@ sample_count_kernel(const int64_t* __restrict__ indptr, const int64_t* __restric
                     int64_t* __restrict__ win_lo, int64_t* __restrict__ win_cut, int32_t* __restrict__ cnt,
                     int64_t* __restrict__ cta_sums, unsigned int* done_counter, int64_t* __restrict__ out_offsets,
                     int32_t* d_status) {
-  __shared__ int32_t s_cnt[kTargetsPerCta];
+  constexpr int TPC = kWarpsPerCta * TPW;
   const int64_t n = eff_count(n_cap, d_n);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#pragma unroll
-  for (int j = 0; j < kTargetsPerWarp; ++j) {
-    const int slot = warp * kTargetsPerWarp + j;
-    const int64_t i = (int64_t)blockIdx.x * kTargetsPerCta + slot;
-    int32_t c = 0;
+  int32_t my_cnt = 0;   // count of target (blockIdx.x * TPC + threadIdx.x), held by thread threadIdx.x < TPC
+  if (TPW == 32) {
+    const int64_t i = (int64_t)blockIdx.x * TPC + threadIdx.x;
     if (i < n) {
-      int64_t node = targets[i];
-      int64_t t = target_ts[i];
-      int64_t lo = 0, cut = 0;
+      int64_t node = targets[i], t = target_ts[i], lo = 0, cut = 0;
       if (node < 0 || node >= num_nodes) {
-        if (lane == 0) dev_flag(d_status, SGL_DEV_BAD_NODE);
+        dev_flag(d_status, SGL_DEV_BAD_NODE);
       } else {
         int64_t s = __ldg(indptr + node), e = __ldg(indptr + node + 1);
-        lo = s;
-        cut = s;
-        if (e > s) {
-          cut = warp_lower_bound(ts, s, e, t + (equal_root_time ? 1 : 0), lane);
-          if (allowed_offset >= 0 && cut > s) lo = warp_lower_bound(ts, s, cut, t - allowed_offset, lane);
-        }
+        cut = lane_lower_bound(ts, s, e, t + (equal_root_time ? 1 : 0));
+        lo = allowed_offset >= 0 ? lane_lower_bound(ts, s, cut, t - allowed_offset) : s;
       }
       int64_t cand = cut - lo;
-      c = (int32_t)(cand < fanout ? cand : fanout);
-      if (lane == 0) {
-        win_lo[i] = lo;
-        win_cut[i] = cut;
-        cnt[i] = c;
-      }
+      my_cnt = (int32_t)(cand < fanout ? cand : fanout);
+      win_lo[i] = lo;
+      win_cut[i] = cut;
+      cnt[i] = my_cnt;
     }
-    if (lane == 0) s_cnt[slot] = c;
-  }
-  __syncthreads();
-  int64_t cta_total = 0;
+  } else {
+    __shared__ int32_t s_cnt[TPC];
 #pragma unroll
-  for (int s = 0; s < kTargetsPerCta; ++s) cta_total += s_cnt[s];
+    for (int j = 0; j < TPW; ++j) {
+      const int slot = warp * TPW + j;
+      const int64_t i = (int64_t)blockIdx.x * TPC + slot;
+      int32_t c = 0;
+      if (i < n) {
+        int64_t node = targets[i];
+        int64_t t = target_ts[i];
+        int64_t lo = 0, cut = 0;
+        if (node < 0 || node >= num_nodes) {
+          if (lane == 0) dev_flag(d_status, SGL_DEV_BAD_NODE);
+        } else {
+          int64_t s = __ldg(indptr + node), e = __ldg(indptr + node + 1);
+          lo = s;
+          cut = s;
+          if (e > s) {
+            cut = warp_lower_bound(ts, s, e, t + (equal_root_time ? 1 : 0), lane);
+            if (allowed_offset >= 0 && cut > s) lo = warp_lower_bound(ts, s, cut, t - allowed_offset, lane);
+          }
+        }
+        int64_t cand = cut - lo;
+        c = (int32_t)(cand < fanout ? cand : fanout);
+        if (lane == 0) {
+          win_lo[i] = lo;
+          win_cut[i] = cut;
+          cnt[i] = c;
+        }
+      }
+      if (lane == 0) s_cnt[slot] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x < TPC) my_cnt = s_cnt[threadIdx.x];
+  }
+  int cta_total;
+  cta_exclusive_scan<kCtaThreads, int>(my_cnt, &cta_total);
   // grand total -> out_offsets[n_cap]; the slots of the targets themselves are written by the fill kernel
-  publish_and_scan_cta_totals<kCtaThreads>(cta_total, cta_sums, done_counter, out_offsets + n_cap);
+  publish_and_scan_cta_totals<kCtaThreads>((int64_t)cta_total, cta_sums, done_counter, out_offsets + n_cap);
 }
 
+template <int TPW>
 __global__ void __launch_bounds__(kCtaThreads)
 sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ ts, const int64_t* __restrict__ eid,
                    const int64_t* __restrict__ target_ts, int64_t n_cap, const int64_t* d_n, int fanout, int policy,
@@ -117,29 +152,27 @@ sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ 
                    const int64_t* __restrict__ cta_base, int64_t* __restrict__ out_nbr, int64_t* __restrict__ out_dst,
                    int64_t* __restrict__ out_ts, float* __restrict__ out_dt, int64_t* __restrict__ out_dt_i64,
                    int64_t* __restrict__ out_eid, int64_t* __restrict__ out_offsets) {
-  __shared__ int64_t s_off[kTargetsPerCta];
+  constexpr int TPC = kWarpsPerCta * TPW;
+  __shared__ int64_t s_off[TPC];
   const int64_t n = eff_count(n_cap, d_n);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t first = (int64_t)blockIdx.x * kTargetsPerCta;
-  if (warp == 0) {
-    int64_t i = first + lane;
-    int32_t c = i < n ? cnt[i] : 0;
-    int32_t x = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      int32_t y = __shfl_up_sync(0xffffffffu, x, o);
-      if (lane >= o) x += y;
+  const int64_t first = (int64_t)blockIdx.x * TPC;
+  {
+    const int64_t i = first + threadIdx.x;
+    const bool mine = threadIdx.x < TPC;
+    int c = (mine && i < n) ? cnt[i] : 0;
+    int ex = cta_exclusive_scan<kCtaThreads, int>(c, nullptr);
+    if (mine) {
+      int64_t off = cta_base[blockIdx.x] + ex;
+      s_off[threadIdx.x] = off;
+      // offsets past the valid targets all equal the total, so out_offsets[n..n_cap] stays a valid prefix array
+      if (i < n_cap) out_offsets[i] = off;
     }
-    int64_t off = cta_base[blockIdx.x] + (x - c);
-    s_off[lane] = off;
-    if (i < n) out_offsets[i] = off;
-    // offsets past the valid targets all equal the total, so out_offsets[n..n_cap] is a valid prefix array
-    if (i >= n && i < n_cap) out_offsets[i] = off;
   }
   __syncthreads();
 #pragma unroll 1
-  for (int j = 0; j < kTargetsPerWarp; ++j) {
-    const int slot = warp * kTargetsPerWarp + j;
+  for (int j = 0; j < TPW; ++j) {
+    const int slot = warp * TPW + j;
     const int64_t i = first + slot;
     if (i >= n) break;
     const int32_t c = cnt[i];
@@ -202,15 +235,44 @@ sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ 
 
 using namespace sgl;
 
-static inline int64_t sample_num_ctas(int64_t n) {
-  int64_t b = (n + kTargetsPerCta - 1) / kTargetsPerCta;
+static inline int sample_tpw(int64_t n) {
+  static int forced = -1;   // SGL_SAMPLE_TPW=1|4|32 pins the variant (tuning aid)
+  if (forced < 0) {
+    const char* e = getenv("SGL_SAMPLE_TPW");
+    forced = e ? atoi(e) : 0;
+  }
+  if (forced == 1 || forced == 4 || forced == 32) return forced;
+  return n <= 16384 ? 1 : (n <= 262144 ? 4 : 32);
+}
+
+static inline int64_t sample_num_ctas(int64_t n, int tpw) {
+  int64_t tpc = (int64_t)kWarpsPerCta * tpw;
+  int64_t b = (n + tpc - 1) / tpc;
   return b < 1 ? 1 : b;
 }
 
 extern "C" size_t sgl_sample_ws_bytes(int64_t n_targets) {
   if (n_targets < 1) n_targets = 1;
   return 2 * align_up((size_t)n_targets * 8) + align_up((size_t)n_targets * 4) +
-         align_up((size_t)sample_num_ctas(n_targets) * 8) + align_up(sizeof(unsigned int));
+         align_up((size_t)sample_num_ctas(n_targets, 1) * 8) + align_up(sizeof(unsigned int));
+}
+
+template <int TPW>
+static void launch_sample(int64_t ctas, cudaStream_t stream, const int64_t* indptr, const int64_t* nbr, const int64_t* ts,
+                          const int64_t* eid, int64_t num_nodes, const int64_t* targets, const int64_t* target_ts,
+                          int64_t n_targets, const int64_t* d_n, int fanout, int policy, int equal_root_time,
+                          int64_t allowed_offset, int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* win_lo,
+                          int64_t* win_cut, int32_t* cnt, int64_t* cta_sums, unsigned int* done, int64_t* out_nbr,
+                          int64_t* out_dst, int64_t* out_ts, float* out_dt, int64_t* out_dt_i64, int64_t* out_eid,
+                          int64_t* out_offsets, int32_t* d_status) {
+  sample_count_kernel<TPW><<<(unsigned)ctas, kCtaThreads, 0, stream>>>(indptr, ts, num_nodes, targets, target_ts,
+                                                                       n_targets, d_n, fanout, equal_root_time,
+                                                                       allowed_offset, win_lo, win_cut, cnt, cta_sums, done,
+                                                                       out_offsets, d_status);
+  sample_fill_kernel<TPW><<<(unsigned)ctas, kCtaThreads, 0, stream>>>(nbr, ts, eid, target_ts, n_targets, d_n, fanout,
+                                                                      policy, keep_root_time, seed, rng_stream, win_lo,
+                                                                      win_cut, cnt, cta_sums, out_nbr, out_dst, out_ts,
+                                                                      out_dt, out_dt_i64, out_eid, out_offsets);
 }
 
 extern "C" int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
@@ -228,7 +290,7 @@ extern "C" int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const
   SGL_REQUIRE(policy != SGL_POLICY_UNIFORM || fanout <= SGL_MAX_UNIFORM_FANOUT, SGL_ERR_UNSUPPORTED,
               "sample_layer: uniform fanout %d > %d", fanout, SGL_MAX_UNIFORM_FANOUT);
   SGL_REQUIRE(out_offsets, SGL_ERR_ARG, "sample_layer: out_offsets is null");
-  SGL_REQUIRE(n_targets < ((int64_t)1 << 31) * kTargetsPerCta, SGL_ERR_UNSUPPORTED, "sample_layer: too many targets");
+  SGL_REQUIRE(n_targets < ((int64_t)1 << 34), SGL_ERR_UNSUPPORTED, "sample_layer: too many targets");
   if (n_targets == 0) {
     SGL_CUDA_CHECK(cudaMemsetAsync(out_offsets, 0, sizeof(int64_t), stream));
     return SGL_OK;
@@ -239,19 +301,36 @@ extern "C" int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const
   int64_t* win_lo = c.take<int64_t>(n_targets);
   int64_t* win_cut = c.take<int64_t>(n_targets);
   int32_t* cnt = c.take<int32_t>(n_targets);
-  const int64_t ctas = sample_num_ctas(n_targets);
-  int64_t* cta_sums = c.take<int64_t>(ctas);
+  const int tpw = sample_tpw(n_targets);
+  const int64_t ctas = sample_num_ctas(n_targets, tpw);
+  int64_t* cta_sums = c.take<int64_t>(sample_num_ctas(n_targets, 1));
   unsigned int* done = c.take<unsigned int>(1);
   SGL_REQUIRE(c.ok(), SGL_ERR_WORKSPACE, "sample_layer: workspace %zu < %zu bytes", ws_bytes,
               sgl_sample_ws_bytes(n_targets));
   SGL_CUDA_CHECK(cudaMemsetAsync(done, 0, sizeof(unsigned int), stream));
-  sample_count_kernel<<<(unsigned)ctas, kCtaThreads, 0, stream>>>(indptr, ts, num_nodes, targets, target_ts, n_targets,
-                                                                  d_n, fanout, equal_root_time, allowed_offset, win_lo,
-                                                                  win_cut, cnt, cta_sums, done, out_offsets, d_status);
-  sample_fill_kernel<<<(unsigned)ctas, kCtaThreads, 0, stream>>>(nbr, ts, eid, target_ts, n_targets, d_n, fanout, policy,
-                                                                 keep_root_time, seed, rng_stream, win_lo, win_cut, cnt,
-                                                                 cta_sums, out_nbr, out_dst, out_ts, out_dt, out_dt_i64,
-                                                                 out_eid, out_offsets);
+#define SGL_SAMPLE_ARGS                                                                                               \
+  ctas, stream, indptr, nbr, ts, eid, num_nodes, targets, target_ts, n_targets, d_n, fanout, policy, equal_root_time, \
+      allowed_offset, keep_root_time, seed, rng_stream, win_lo, win_cut, cnt, cta_sums, done, out_nbr, out_dst,       \
+      out_ts, out_dt, out_dt_i64, out_eid, out_offsets, d_status
+  if (tpw == 1) launch_sample<1>(SGL_SAMPLE_ARGS);
+  else if (tpw == 4) launch_sample<4>(SGL_SAMPLE_ARGS);
+  else launch_sample<32>(SGL_SAMPLE_ARGS);
+#undef SGL_SAMPLE_ARGS
   SGL_LAUNCH_CHECK();
   return SGL_OK;
+}
+
+extern "C" int sgl_sample_gather(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                                 int64_t num_nodes, const int64_t* targets, const int64_t* target_ts, int64_t n_targets,
+                                 int fanout, int policy, int equal_root_time, int64_t allowed_offset, int keep_root_time,
+                                 uint64_t seed, uint32_t rng_stream, int64_t* out_nbr, int64_t* out_dst, int64_t* out_ts,
+                                 float* out_dt, int64_t* out_eid, int64_t* out_offsets, const void* feat_table,
+                                 int64_t feat_rows, int64_t row_bytes, int64_t src_pitch, void* out_feats, int gather_mode,
+                                 int32_t* d_status, void* ws, size_t ws_bytes, void* stream) {
+  int rc = sgl_sample_layer(indptr, nbr, ts, eid, num_nodes, targets, target_ts, n_targets, nullptr, fanout, policy,
+                            equal_root_time, allowed_offset, keep_root_time, seed, rng_stream, out_nbr, out_dst, out_ts,
+                            out_dt, nullptr, out_eid, out_offsets, d_status, ws, ws_bytes, stream);
+  if (rc != SGL_OK || n_targets == 0) return rc;
+  return sgl_gather_rows(feat_table, feat_rows, row_bytes, src_pitch, out_eid, nullptr, 0, n_targets * fanout,
+                         out_offsets + n_targets, out_feats, row_bytes, nullptr, nullptr, gather_mode, d_status, stream);
 }

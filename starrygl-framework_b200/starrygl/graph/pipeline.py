@@ -34,12 +34,15 @@ class SampleGatherPipeline:
         self.roots = torch.empty(self.max_roots, dtype=I64, device=dev)
         self.root_ts = torch.empty(self.max_roots, dtype=I64, device=dev)
         # one int64 block for the index outputs so that the block structure goes back to the host in ONE copy:
-        # [offsets (max_roots+1) | nbr | dst | ts | eid] each of capacity cap, then dt (float32) separately
-        self.blk = torch.empty(self.max_roots + 1 + 4 * cap, dtype=I64, device=dev)
+        # [offsets (max_roots+1) | nbr | ts | eid] each of capacity cap, then dt (float32) separately.  The target
+        # slot of every edge (dst) stays on the device: on the host it is implied by the offsets.
+        self.blk = torch.empty(self.max_roots + 1 + 3 * cap, dtype=I64, device=dev)
         o = self.max_roots + 1
         self.offsets = self.blk[:o]
-        self.nbr, self.dst, self.ts, self.eid = (self.blk[o + i * cap:o + (i + 1) * cap] for i in range(4))
+        self.nbr, self.ts, self.eid = (self.blk[o + i * cap:o + (i + 1) * cap] for i in range(3))
+        self.dst = torch.empty(cap, dtype=I64, device=dev)
         self.dt = torch.empty(cap, dtype=torch.float32, device=dev)
+        self.done = torch.cuda.Event()
         self.status = ops.StatusWord(dev)
         self.ws = torch.empty(self.L.sgl_sample_ws_bytes(self.max_roots), dtype=torch.uint8, device=dev)
         self.out_feats = None
@@ -55,6 +58,65 @@ class SampleGatherPipeline:
         self.h_blk = torch.empty(self.blk.numel(), dtype=I64).pin_memory()
         self.h_dt = torch.empty(cap, dtype=torch.float32).pin_memory()
         self.kernel_launches_per_step = 2 + (1 if edge_feats is not None else 0)
+        self._g_dev = self._g_host = None
+        # pre-converted argument list of the fused C call; per batch only the two input pointers and n change
+        self._fused = None
+        if edge_feats is not None:
+            g_, a = g, self.args
+            v = C.c_void_p
+            self._a_roots, self._a_ts, self._a_n, self._a_rng = v(0), v(0), C.c_int64(0), C.c_uint32(0)
+            self._fused = [v(g_.indptr.data_ptr()), v(g_.nbr.data_ptr()), v(g_.ts.data_ptr()), v(g_.eid.data_ptr()),
+                           C.c_int64(g_.num_nodes), self._a_roots, self._a_ts, self._a_n, C.c_int(self.k),
+                           C.c_int(a["pol"]), C.c_int(a["eq"]), C.c_int64(a["off"]), C.c_int(a["keep"]),
+                           C.c_uint64(a["seed"]), self._a_rng, v(self.nbr.data_ptr()), v(self.dst.data_ptr()),
+                           v(self.ts.data_ptr()), v(self.dt.data_ptr()), v(self.eid.data_ptr()),
+                           v(self.offsets.data_ptr()), v(edge_feats.data_ptr()), C.c_int64(edge_feats.shape[0]),
+                           C.c_int64(self.row_bytes), C.c_int64(self.src_pitch), v(self.out_feats.data_ptr()),
+                           C.c_int(self.mode), v(self.status.ptr()), v(self.ws.data_ptr()), C.c_size_t(self.ws.numel()),
+                           v(self.stream.cuda_stream)]
+            self._fn = self.L.sgl_sample_gather
+
+    def run_device_ptr(self, roots_ptr: int, root_ts_ptr: int, n: int, rng_stream: int = 0):
+        """:meth:`run_device` for callers that already hold raw device pointers: one foreign call per batch
+        (sampling and gather are enqueued back to back by the library)."""
+        if n > self.max_roots:
+            raise _C.SglError(f"batch of {n} roots exceeds max_roots={self.max_roots}")
+        self._a_roots.value, self._a_ts.value, self._a_n.value, self._a_rng.value = roots_ptr, root_ts_ptr, n, rng_stream
+        rc = self._fn(*self._fused)
+        if rc:
+            _C.check(rc)
+
+    # ---- CUDA graphs: one replay per batch instead of one foreign call per kernel -----------------------------
+    def capture(self):
+        """Capture the full-batch (``max_roots`` roots) step twice -- device inputs and host inputs -- as CUDA
+        graphs on this pipeline's stream.  Afterwards :meth:`replay_device` / :meth:`submit_host` cost one
+        graph launch per batch.  Call once, after the tables exist and before the timed loop."""
+        n = self.max_roots
+        self.roots.zero_()
+        self.root_ts.zero_()
+        torch.cuda.synchronize(self.dev)
+        self.run_device(self.roots, self.root_ts)          # warm-up outside capture (lazy module loading etc.)
+        self.stream.synchronize()
+        self._g_dev = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._g_dev, stream=self.stream):
+            self.run_device(self.roots, self.root_ts)
+        self._g_host = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._g_host, stream=self.stream):
+            self.roots.copy_(self.h_roots, non_blocking=True)
+            self.root_ts.copy_(self.h_root_ts, non_blocking=True)
+            self.run_device(self.roots, self.root_ts)
+            self.h_blk.copy_(self.blk, non_blocking=True)
+            self.h_dt.copy_(self.dt, non_blocking=True)
+        self.stream.synchronize()
+        return self
+
+    def replay_device(self, roots: torch.Tensor, root_ts: torch.Tensor):
+        """Graph form of :meth:`run_device` for a full batch: copy the roots into the captured input buffers
+        (device to device) and replay."""
+        with torch.cuda.stream(self.stream):
+            self.roots.copy_(roots, non_blocking=True)
+            self.root_ts.copy_(root_ts, non_blocking=True)
+            self._g_dev.replay()
 
     # ---- device-resident inputs ------------------------------------------------------------------------
     def run_device(self, roots: torch.Tensor, root_ts: torch.Tensor, rng_stream: int = 0, gather_events=None):
@@ -84,27 +146,44 @@ class SampleGatherPipeline:
         return n
 
     # ---- host inputs / host results --------------------------------------------------------------------
-    def run_host(self, h_roots: torch.Tensor, h_root_ts: torch.Tensor, rng_stream: int = 0):
-        """Roots and query times from (pinned) host tensors; the block structure (offsets, neighbour ids, target
-        slots, timestamps, edge ids, dt) comes back to pinned host memory.  The gathered feature rows stay on the
-        GPU (``self.out_feats``): their consumer is the model.  Returns (n_edges, host views) after synchronising."""
+    def submit_host(self, h_roots: torch.Tensor, h_root_ts: torch.Tensor, rng_stream: int = 0):
+        """Enqueue one batch whose roots and query times are in (pinned) host tensors: H2D copy, sampling, gather,
+        and the copy of the block structure (offsets, neighbour ids, timestamps, edge ids, dt) back to pinned host
+        memory.  Returns immediately; :meth:`result` waits for it.  The gathered feature rows stay on the GPU
+        (``self.out_feats``): their consumer is the model."""
         n = h_roots.numel()
+        self._n = n
+        if self._g_host is not None and n == self.max_roots and rng_stream == 0:
+            # staged through this object's pinned buffers (their addresses are baked into the graph)
+            self.h_roots.copy_(h_roots)
+            self.h_root_ts.copy_(h_root_ts)
+            with torch.cuda.stream(self.stream):
+                self._g_host.replay()
+                self.done.record(self.stream)
+            return
         with torch.cuda.stream(self.stream):
             self.roots[:n].copy_(h_roots, non_blocking=True)
             self.root_ts[:n].copy_(h_root_ts, non_blocking=True)
             self.run_device(self.roots[:n], self.root_ts[:n], rng_stream)
-            # offsets first (tiny), then only the used prefix of every array would need the count on the host;
-            # one fixed-size copy of the whole block avoids that round trip
+            # one fixed-size copy of the whole block: copying only the used prefix would need the edge count on
+            # the host first, i.e. an extra round trip
             self.h_blk.copy_(self.blk, non_blocking=True)
             self.h_dt.copy_(self.dt, non_blocking=True)
-        self.stream.synchronize()
-        o = self.max_roots + 1
+            self.done.record(self.stream)
+
+    def result(self):
+        """(n_edges, dict of host views) of the batch submitted last; blocks until its copies have landed."""
+        self.done.synchronize()
+        n, cap, o = self._n, self.cap, self.max_roots + 1
         tot = int(self.h_blk[n])
-        cap = self.cap
-        views = {"offsets": self.h_blk[:n + 1], "nbr": self.h_blk[o:o + tot], "dst": self.h_blk[o + cap:o + cap + tot],
-                 "ts": self.h_blk[o + 2 * cap:o + 2 * cap + tot], "eid": self.h_blk[o + 3 * cap:o + 3 * cap + tot],
-                 "dt": self.h_dt[:tot]}
+        views = {"offsets": self.h_blk[:n + 1], "nbr": self.h_blk[o:o + tot], "ts": self.h_blk[o + cap:o + cap + tot],
+                 "eid": self.h_blk[o + 2 * cap:o + 2 * cap + tot], "dt": self.h_dt[:tot]}
         return tot, views
+
+    def run_host(self, h_roots: torch.Tensor, h_root_ts: torch.Tensor, rng_stream: int = 0):
+        """Synchronous form: :meth:`submit_host` followed by :meth:`result`."""
+        self.submit_host(h_roots, h_root_ts, rng_stream)
+        return self.result()
 
     def h2d_bytes(self, n):
         return 16 * n
