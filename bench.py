@@ -43,6 +43,9 @@ TS_MAX = 10_000_000
 NUM_BATCHES = 64          # distinct pre-generated batches cycled through the steps
 STREAMS = 6
 GRAPHS = True
+# DRAM bytes per gathered row measured with ncu on the small case (profiles/gather_bulk_kernel_172xfp32_small_case.txt:
+# 57.1 MB for 65,160 rows); roofline.traffic scales it by the rows of a full-size launch
+GATHER_TRAFFIC_BYTES_PER_ROW = 876.0
 ROUTE_ROWS = 800          # rows per step a partition pushes to its peers (20 % cut edges of a 4,096-root batch)
 
 
@@ -104,7 +107,7 @@ def make_batches(src, ts, gen, dev):
     return src[pick].contiguous(), ts[pick].contiguous()       # query time = the drawn edge's own timestamp
 
 
-def run_reference(args, rank):
+def run_reference(args, rank, out_stream):
     """The reference's CPU path (its C/OpenMP restatement: the reference is numba/Python and cannot travel) on
     the host cores, same batches, bounded sample."""
     if rank != 0:
@@ -118,7 +121,7 @@ def run_reference(args, rank):
             "config": workload_config(1), "cpu_baseline": out["cpu_baseline"],
             "e2e": {"value": out["value"], "unit": "events/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line))
+    print(json.dumps(line), file=out_stream, flush=True)
 
 
 def workload_config(n_gpus):
@@ -174,6 +177,15 @@ def cpu_baseline_measure(dev, steps, warmup, budget_s):
                                        f"sampler; T-CSR build on the host took {build_s:.1f} s"}}
 
 
+def _protect_stdout():
+    """Libraries may print banners to stdout (NCCL does with NCCL_DEBUG=VERSION); the JSON line must stay alone
+    there.  File descriptor 1 is pointed at stderr and the original is returned for the final print."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    return os.fdopen(saved, "w")
+
+
 def main():
     global NUM_NODES, NUM_EDGES, STREAMS, GRAPHS
     ap = argparse.ArgumentParser()
@@ -191,12 +203,13 @@ def main():
     ap.add_argument("--num-edges", type=int, default=NUM_EDGES)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    out_stream = _protect_stdout()
     NUM_NODES, NUM_EDGES, STREAMS, GRAPHS = args.num_nodes, args.num_edges, max(1, args.streams), True
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
-        return run_reference(args, rank)
+        return run_reference(args, rank, out_stream)
 
     import torch.distributed as dist
     from starrygl import ops, _C
@@ -225,6 +238,7 @@ def main():
     for p_ in pipes:
         p_.capture()
     main_stream = torch.cuda.Stream(dev)
+    route_stream = torch.cuda.Stream(dev, priority=-1)     # its few CTAs must not queue behind the persistent gather CTAs
     h_roots = b_roots.cpu().pin_memory()
     h_ts = b_ts.cpu().pin_memory()
 
@@ -259,8 +273,11 @@ def main():
 
     batch_ptrs = [(b_roots[b].data_ptr(), b_ts[b].data_ptr()) for b in range(NUM_BATCHES)]
 
+    issue_t = {"sample_gather": 0.0, "route_send": 0.0, "route_apply": 0.0}
+
     def step_device(i, ev=None):
         b = i % NUM_BATCHES
+        t_a = time.perf_counter()
         if ev is not None:
             pipes[i % S].run_device(b_roots[b], b_ts[b], 0, ev)
         elif use_graph:
@@ -268,11 +285,19 @@ def main():
         else:
             pipes[i % S].run_device_ptr(batch_ptrs[b][0], batch_ptrs[b][1], BATCH)
         if route is not None:
+            # the memory rows pushed to the other partitions do not depend on this batch's samples: the route runs
+            # on its own stream, concurrently with sampling and gather
             cr, plans, mem, mem_ts, cb = route
-            with torch.cuda.stream(streams[i % S]):
+            t_b = time.perf_counter()
+            with torch.cuda.stream(route_stream):
                 futs = cr.update_with_plan(mem, plans[b], cb, local_ts=mem_ts)
+                t_c = time.perf_counter()
                 for f in futs:
                     f.wait()
+            t_d = time.perf_counter()
+            issue_t["sample_gather"] += t_b - t_a
+            issue_t["route_send"] += t_c - t_b
+            issue_t["route_apply"] += t_d - t_c
 
     def barrier():
         if multi:
@@ -288,19 +313,21 @@ def main():
     clocks = ClockSampler(local)
     if rank == 0:
         clocks.start()
+    for k_ in issue_t:
+        issue_t[k_] = 0.0
     gev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     # K steps, up to S of them in flight: the streams fork from / join into main_stream, whose two events bracket
     # the whole region on the device
     e0.record(main_stream)
-    for st in streams:
+    for st in streams + [route_stream]:
         st.wait_stream(main_stream)
     t_issue = time.perf_counter()
     for i in range(args.steps):
         step_device(args.warmup + i, None)
     t_issue = time.perf_counter() - t_issue
-    for st in streams:
+    for st in streams + [route_stream]:
         main_stream.wait_stream(st)
     e1.record(main_stream)
     barrier()
@@ -332,7 +359,7 @@ def main():
             p_.submit_host(h_roots[b], h_ts[b])
             if route is not None:
                 cr, plans, mem, mem_ts, cb = route
-                with torch.cuda.stream(streams[i % S]):
+                with torch.cuda.stream(route_stream):
                     for f in cr.update_with_plan(mem, plans[b], cb, local_ts=mem_ts):
                         f.wait()
         for i in range(max(0, count - S), count):
@@ -362,6 +389,7 @@ def main():
         line = {"metric": "sampled+gathered events/sec", "value": world * BATCH * args.steps / (ms / 1e3),
                 "unit": "events/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms / args.steps, "host_issue_ms_per_step": t_issue * 1e3 / args.steps,
+                "host_issue_breakdown_ms": {k: v * 1e3 / args.steps for k, v in issue_t.items()},
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "int64", "data": "synthetic", "config": workload_config(world),
                 "e2e": {"value": world * BATCH * e2e_steps / (e2e_ms / 1e3), "unit": "events/s",
@@ -371,7 +399,9 @@ def main():
                 "gpu_launches": args.steps * (pipe.kernel_launches_per_step + (2 if multi else 0)),
                 "roofline": {"bound": "hbm", "kernel": "gather_bulk_kernel" if pipe.mode != 1 else "gather_lanes_kernel",
                              "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "peak_source": peak_kind, "traffic": None,
+                             "peak_source": peak_kind, "traffic": statistics.mean(edges) * GATHER_TRAFFIC_BYTES_PER_ROW,
+                             "traffic_note": "ncu dram read+write of a 65 k-row launch scaled by rows; the output is still in L2 when "
+                                             "the kernel ends, so write-back is under-counted (see profiles/)",
                              "bytes_per_launch": alg, "ms_per_launch": g_ms,
                              "edges_per_step": statistics.mean(edges)},
                 "clocks": clk}
@@ -379,9 +409,11 @@ def main():
             del feats, pipe, pipes
             torch.cuda.empty_cache()
             line["cpu_baseline"] = cpu_baseline_measure(dev, args.steps, args.warmup, 20.0)["cpu_baseline"]
-        print(json.dumps(line))
+        print(json.dumps(line), file=out_stream, flush=True)
     if multi:
         dist.barrier()
+        from starrygl.cache.cache_route import NativeComm
+        NativeComm.shutdown()
         dist.destroy_process_group()
 
 

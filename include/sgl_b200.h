@@ -210,20 +210,51 @@ int sgl_scatter_rows(void* table, int64_t table_rows, int64_t row_bytes, int64_t
  *   packed[i, 0:D] = feats[send_idx[i], 0:D]
  *   packed[i, D]   = ts[send_idx[i]]                 when ts != NULL
  *   packed[i, W:W+2] = remote_idx[i] (int64 as two 32-bit words, W = D or D+1)   when remote_idx != NULL
- * float32 rows of width W (+2).  Replaces: torch.cat([emb, ts]) + local_features[plan.send_indices] and the
+ * float32 rows; the row pitch is sgl_wire_pitch(D, ts != NULL, remote_idx != NULL) floats: W without slots, else
+ * W + 2 rounded up to a multiple of 4 (zero padded) so that rows move as 128-bit lanes when D % 4 == 0.  Replaces: torch.cat([emb, ts]) + local_features[plan.send_indices] and the
  * separate index message (starrygl/cache/NodeState.py:267, starrygl/cache/cache_route.py:243-258), and
  * x[send_index] (starrygl/route/route.py:428).
  * ---------------------------------------------------------------------------------------------- */
+int64_t sgl_wire_pitch(int64_t dim, int has_ts, int has_slot);
 int sgl_route_pack(const float* feats, int64_t n_rows, int64_t dim, const float* ts, const int64_t* send_idx,
                    const int64_t* remote_idx, int64_t n_send, float* packed, int32_t* d_status, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
- * Route unpack (receiver side of the wire format above, rows of `width` + 2 floats): slot = the trailing
- * int64; data[slot, 0:dim] = row[0:dim]; ts_table[slot] = row[dim] when ts_table != NULL (width = dim + 1).
+ * Route unpack (receiver side of the wire format above, row pitch sgl_wire_pitch(dim, width > dim, 1)): slot =
+ * the int64 after the payload; data[slot, 0:dim] = row[0:dim]; ts_table[slot] = row[dim] when ts_table != NULL (width = dim + 1).
  * Replaces: remote_write_callback (starrygl/cache/NodeState.py:269-274).
  * ---------------------------------------------------------------------------------------------- */
 int sgl_route_unpack(const float* packed, int64_t n, int64_t width, float* data, int64_t data_rows, int64_t dim,
                      float* ts_table, int32_t* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Native communicator (one per process / GPU) for the variable-size all-to-all of the route layer: grouped
+ * ncclSend/ncclRecv on the caller's stream.  Rank 0 creates the id (SGL_COMM_ID_BYTES bytes) and hands it to
+ * the other ranks out of band (e.g. through the launcher's key-value store); every rank then calls sgl_comm_init
+ * with its device current.  Replaces: create_nccl_id / DistContext (csrc/include/starrygl/commContext.cu.hpp:11-51).
+ * ---------------------------------------------------------------------------------------------- */
+#define SGL_COMM_ID_BYTES 128
+int sgl_comm_unique_id(char* out_id, size_t id_bytes);
+int sgl_comm_init(void** out_comm, int rank, int world, const char* id_bytes);
+int sgl_comm_destroy(void* comm);
+
+/* Rows of row_floats float32: segment p of `send` (h_send_rows[p] rows, host array of world entries) goes to rank
+ * p; segment p of `recv` (h_recv_rows[p] rows) arrives from rank p.  Enqueued on `stream`, no synchronisation.
+ * Replaces: DistContext::send_data_to_all / send_indices_to_all (csrc/include/starrygl/commContext.cu.hpp:85-174)
+ * and dist.all_to_all_single with split sizes (starrygl/cache/cache_route.py:243-258, starrygl/route/route.py:430). */
+int sgl_route_exchange(void* comm, const float* send, const int64_t* h_send_rows, float* recv,
+                       const int64_t* h_recv_rows, int64_t row_floats, void* stream);
+
+/* One cache-route step in one call: pack (sgl_route_pack into send_buf), exchange, and -- when apply != 0 --
+ * unpack (sgl_route_unpack from recv_buf into data / ts_table).  send_buf / recv_buf hold sum(h_send_rows) /
+ * sum(h_recv_rows) rows of sgl_wire_pitch(dim, ts != NULL, 1) floats.  With apply == 0 the caller applies the received rows
+ * later with sgl_route_unpack (the reference applies them when the returned future is waited on).
+ * Replaces: CacheRoute.update_with_plan + remote_write_callback (starrygl/cache/cache_route.py:211-277,
+ * starrygl/cache/NodeState.py:245-282). */
+int sgl_cache_route_step(void* comm, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
+                         const int64_t* send_idx, const int64_t* remote_idx, const int64_t* h_send_rows,
+                         const int64_t* h_recv_rows, float* send_buf, float* recv_buf, float* data, int64_t data_rows,
+                         float* ts_table, int apply, int32_t* d_status, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Reverse route accumulate: x[send_idx[s + j], :] += outs[s + j, :] for the peer segment [s, s + len);

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "lib")
 OUT = os.path.join(OUT_DIR, "libsgl_b200.so")
-SOURCES = ["api.cu", "sort.cu", "tcsr.cu", "sampler.cu", "relabel.cu", "gather.cu"]
+SOURCES = ["api.cu", "sort.cu", "tcsr.cu", "sampler.cu", "relabel.cu", "gather.cu", "comm.cu"]
 FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "--expt-relaxed-constexpr",
          "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared"]
 
@@ -30,7 +30,7 @@ def build(force=False, verbose=False):
         return OUT
     os.makedirs(OUT_DIR, exist_ok=True)
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + [os.path.join(SRC, s) for s in SOURCES] + ["-o", OUT]
+    cmd = [nvcc] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + [os.path.join(SRC, s) for s in SOURCES] + ["-ldl", "-o", OUT]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)

@@ -329,50 +329,80 @@ scatter_lanes_kernel(char* __restrict__ table, int64_t table_rows, uint32_t lane
   }
 }
 
+// Wire rows: [dim features | ts (optional) | slot low word | slot high word | zero padding to a multiple of 4 floats]
+// (the slot words and the padding exist only when remote_idx is given).  VEC = 4: 128-bit lanes, needs dim % 4 == 0.
+__device__ __forceinline__ uint32_t wire_word(uint32_t e, uint32_t dim, uint32_t payload, const float* __restrict__ frow,
+                                              const float* __restrict__ ts, int64_t r, uint64_t slot) {
+  if (e < dim) return __float_as_uint(__ldg(frow + e));
+  if (e < payload) return __float_as_uint(__ldg(ts + r));
+  if (e == payload) return (uint32_t)slot;
+  if (e == payload + 1) return (uint32_t)(slot >> 32);
+  return 0u;
+}
+
+template <int VEC>
 __global__ void __launch_bounds__(kLaneThreads)
 route_pack_kernel(const float* __restrict__ feats, int64_t n_rows, uint32_t dim, const float* __restrict__ ts,
                   const int64_t* __restrict__ send_idx, const int64_t* __restrict__ remote_idx, int64_t n_send,
-                  float* __restrict__ packed, int32_t* d_status) {
+                  uint32_t pitch, float* __restrict__ packed, int32_t* d_status) {
   const uint32_t payload = dim + (ts ? 1u : 0u);
-  const uint32_t width = payload + (remote_idx ? 2u : 0u);
-  const int64_t total = n_send * width;
+  const uint32_t lanes = pitch / VEC;
+  const int64_t total = n_send * lanes;
   const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
   for (int64_t q = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q < total; q += stride) {
-    int64_t i = q / width;
-    uint32_t l = (uint32_t)(q - i * width);
-    if (l >= payload) {
-      uint64_t slot = (uint64_t)__ldg(remote_idx + i);
-      ((uint32_t*)packed)[q] = l == payload ? (uint32_t)slot : (uint32_t)(slot >> 32);
-      continue;
-    }
+    int64_t i = q / lanes;
+    uint32_t l = (uint32_t)(q - i * lanes);
     int64_t r = __ldg(send_idx + i);
     if (r < 0) r += n_rows;
     if (r < 0 || r >= n_rows) {
       dev_flag(d_status, SGL_DEV_BAD_INDEX);
       continue;
     }
-    packed[q] = l < dim ? __ldg(feats + r * dim + l) : __ldg(ts + r);
+    const float* frow = feats + r * dim;
+    if (VEC == 4) {
+      uint4 v;
+      if ((l + 1) * 4 <= dim) {
+        v = ld_stream((const uint4*)frow + l);
+      } else {
+        uint64_t slot = remote_idx ? (uint64_t)__ldg(remote_idx + i) : 0ull;
+        v.x = wire_word(4 * l + 0, dim, payload, frow, ts, r, slot);
+        v.y = wire_word(4 * l + 1, dim, payload, frow, ts, r, slot);
+        v.z = wire_word(4 * l + 2, dim, payload, frow, ts, r, slot);
+        v.w = wire_word(4 * l + 3, dim, payload, frow, ts, r, slot);
+      }
+      ((uint4*)packed)[q] = v;
+    } else {
+      uint64_t slot = (remote_idx && l >= payload) ? (uint64_t)__ldg(remote_idx + i) : 0ull;
+      ((uint32_t*)packed)[q] = wire_word(l, dim, payload, frow, ts, r, slot);
+    }
   }
 }
 
+template <int VEC>
 __global__ void __launch_bounds__(kLaneThreads)
-route_unpack_kernel(const float* __restrict__ packed, int64_t n, uint32_t width, float* __restrict__ data,
+route_unpack_kernel(const float* __restrict__ packed, int64_t n, uint32_t width, uint32_t pitch, float* __restrict__ data,
                     int64_t data_rows, uint32_t dim, float* __restrict__ ts_table, int32_t* d_status) {
-  const uint32_t pitch = width + 2;
-  const int64_t total = n * width;
+  const uint32_t lanes = (width + VEC - 1) / VEC;   // lanes that carry payload
+  const int64_t total = n * lanes;
   const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
   for (int64_t q = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q < total; q += stride) {
-    int64_t i = q / width;
-    uint32_t l = (uint32_t)(q - i * width);
+    int64_t i = q / lanes;
+    uint32_t l = (uint32_t)(q - i * lanes);
     const uint32_t* row = (const uint32_t*)packed + i * pitch;
     int64_t slot = (int64_t)((uint64_t)__ldg(row + width) | ((uint64_t)__ldg(row + width + 1) << 32));
     if (slot < 0 || slot >= data_rows) {
       dev_flag(d_status, SGL_DEV_BAD_INDEX);
       continue;
     }
-    float v = __uint_as_float(__ldg(row + l));
-    if (l < dim) data[slot * dim + l] = v;
-    else if (ts_table) ts_table[slot] = v;
+    if (VEC == 4) {
+      uint4 v = ld_stream((const uint4*)row + l);
+      if ((l + 1) * 4 <= dim) ((uint4*)(data + slot * dim))[l] = v;
+      else if (ts_table) ts_table[slot] = __uint_as_float(v.x);   // dim % 4 == 0: the lane after the features starts with ts
+    } else {
+      float v = __uint_as_float(__ldg(row + l));
+      if (l < dim) data[slot * dim + l] = v;
+      else if (ts_table) ts_table[slot] = v;
+    }
   }
 }
 
@@ -619,6 +649,11 @@ extern "C" int sgl_scatter_rows(void* table, int64_t table_rows, int64_t row_byt
   return SGL_OK;
 }
 
+extern "C" int64_t sgl_wire_pitch(int64_t dim, int has_ts, int has_slot) {
+  int64_t w = dim + (has_ts ? 1 : 0);
+  return has_slot ? (w + 2 + 3) / 4 * 4 : w;
+}
+
 extern "C" int sgl_route_pack(const float* feats, int64_t n_rows, int64_t dim, const float* ts, const int64_t* send_idx,
                               const int64_t* remote_idx, int64_t n_send, float* packed, int32_t* d_status,
                               void* stream_) {
@@ -626,9 +661,17 @@ extern "C" int sgl_route_pack(const float* feats, int64_t n_rows, int64_t dim, c
   SGL_REQUIRE(n_send >= 0 && n_rows >= 0 && dim > 0, SGL_ERR_ARG, "route_pack: bad size");
   if (n_send == 0) return SGL_OK;
   SGL_REQUIRE(feats && send_idx && packed, SGL_ERR_ARG, "route_pack: null array");
-  const int grid = stream_grid(n_send * (dim + 3), kLaneThreads, 16);
-  route_pack_kernel<<<grid, kLaneThreads, 0, stream>>>(feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, n_send,
-                                                      packed, d_status);
+  const int64_t pitch = sgl_wire_pitch(dim, ts != nullptr, remote_idx != nullptr);
+  const bool vec = dim % 4 == 0 && pitch % 4 == 0 && aligned16(feats) && aligned16(packed);
+  if (vec) {
+    const int grid = stream_grid(n_send * (pitch / 4), kLaneThreads, 16);
+    route_pack_kernel<4><<<grid, kLaneThreads, 0, stream>>>(feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, n_send,
+                                                           (uint32_t)pitch, packed, d_status);
+  } else {
+    const int grid = stream_grid(n_send * pitch, kLaneThreads, 16);
+    route_pack_kernel<1><<<grid, kLaneThreads, 0, stream>>>(feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, n_send,
+                                                           (uint32_t)pitch, packed, d_status);
+  }
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }
@@ -642,9 +685,17 @@ extern "C" int sgl_route_unpack(const float* packed, int64_t n, int64_t width, f
   SGL_REQUIRE(width == dim || ts_table, SGL_ERR_ARG, "route_unpack: rows carry a timestamp but ts_table is null");
   if (n == 0) return SGL_OK;
   SGL_REQUIRE(packed && data, SGL_ERR_ARG, "route_unpack: null array");
-  const int grid = stream_grid(n * width, kLaneThreads, 16);
-  route_unpack_kernel<<<grid, kLaneThreads, 0, stream>>>(packed, n, (uint32_t)width, data, data_rows, (uint32_t)dim,
-                                                        ts_table, d_status);
+  const int64_t pitch = sgl_wire_pitch(dim, width > dim, 1);
+  const bool vec = dim % 4 == 0 && aligned16(packed) && aligned16(data);
+  if (vec) {
+    const int grid = stream_grid(n * ((width + 3) / 4), kLaneThreads, 16);
+    route_unpack_kernel<4><<<grid, kLaneThreads, 0, stream>>>(packed, n, (uint32_t)width, (uint32_t)pitch, data, data_rows,
+                                                             (uint32_t)dim, ts_table, d_status);
+  } else {
+    const int grid = stream_grid(n * width, kLaneThreads, 16);
+    route_unpack_kernel<1><<<grid, kLaneThreads, 0, stream>>>(packed, n, (uint32_t)width, (uint32_t)pitch, data, data_rows,
+                                                             (uint32_t)dim, ts_table, d_status);
+  }
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }

@@ -48,8 +48,15 @@ _SIGNATURES = {
     "sgl_cache_gather_ws_bytes": (_sz, [_i64]),
     "sgl_cache_gather": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "sgl_scatter_rows": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _vp]),
+    "sgl_wire_pitch": (_i64, [_i64, _i32, _i32]),
     "sgl_route_pack": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp]),
     "sgl_route_unpack": (_i32, [_vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp, _vp]),
+    "sgl_comm_unique_id": (_i32, [C.c_char_p, _sz]),
+    "sgl_comm_init": (_i32, [C.POINTER(C.c_void_p), _i32, _i32, C.c_char_p]),
+    "sgl_comm_destroy": (_i32, [_vp]),
+    "sgl_route_exchange": (_i32, [_vp, _vp, C.POINTER(C.c_int64), _vp, C.POINTER(C.c_int64), _i64, _vp]),
+    "sgl_cache_route_step": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), _vp,
+                                    _vp, _vp, _i64, _vp, _i32, _vp, _vp]),
     "sgl_route_add_rows": (_i32, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),
     "sgl_dist_pack": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp]),
     "sgl_dist_unpack": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp]),

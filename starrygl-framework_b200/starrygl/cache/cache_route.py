@@ -16,7 +16,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-from .. import ops
+from .. import _C, ops
 
 __all__ = ['CommPlan', 'CacheUpdateFuture', 'CacheRoute', 'CacheRouteManager']
 
@@ -101,11 +101,88 @@ class CacheUpdateFuture:
         self.write_callback(self.recv_ids, self.recv_feats, self.mode)
 
 
+class NativeComm:
+    """The library's own NCCL communicator over all ranks of the default process group (the reference keeps a
+    private ``ncclComm_t`` next to torch.distributed too: starrygl/utils/context.py:109-122).  The unique id
+    travels through the process group that already exists."""
+    _instance = None
+
+    def __init__(self):
+        import ctypes as C
+        L = _C.lib()
+        rank, world = dist.get_rank(), dist.get_world_size()
+        buf = C.create_string_buffer(128)
+        if rank == 0:
+            _C.check(L.sgl_comm_unique_id(buf, 128))
+        box = [buf.raw]
+        dist.broadcast_object_list(box, src=0)
+        self.handle = C.c_void_p()
+        _C.check(L.sgl_comm_init(C.byref(self.handle), rank, world, box[0]))
+        self.rank, self.world = rank, world
+
+    @classmethod
+    def get(cls) -> "NativeComm":
+        if cls._instance is None:
+            cls._instance = cls()
+        return cls._instance
+
+    @classmethod
+    def shutdown(cls):
+        if cls._instance is not None:
+            _C.lib().sgl_comm_destroy(cls._instance.handle)
+            cls._instance = None
+
+
+class _NativeBinding:
+    """Everything of one (plan, feature width) pair that does not change from call to call: device copies of the
+    index arrays, host split arrays, send / receive buffers and the pre-converted argument list."""
+
+    def __init__(self, plan: "CommPlan", recv_list, feats: Tensor, has_ts: bool, comm: NativeComm):
+        import ctypes as C
+        dev = feats.device
+        self.send_idx = plan.send_indices.to(dev, torch.int64).contiguous()
+        self.remote = plan.send_remote_indices.to(dev, torch.int64).contiguous()
+        P = comm.world
+        self.h_send = (C.c_int64 * P)(*plan.send_list())
+        self.h_recv = (C.c_int64 * P)(*recv_list)
+        self.dim = feats.shape[1]
+        self.width = self.dim + (1 if has_ts else 0)
+        self.n_send, self.n_recv = sum(plan.send_list()), sum(recv_list)
+        pitch = ops.wire_pitch(self.width, False)
+        self.send_buf = torch.empty(max(self.n_send, 1), pitch, dtype=torch.float32, device=dev)
+        self.recv_buf = torch.empty(max(self.n_recv, 1), pitch, dtype=torch.float32, device=dev)
+        self.status = ops.StatusWord(dev)
+
+
 class CacheRoute:
     def __init__(self, group: Optional[dist.ProcessGroup] = None):
         self.group = group
         self.world_size = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+
+    def _use_native(self, t: Tensor) -> bool:
+        return (t.is_cuda and dist.is_initialized() and self.group in (None, dist.GroupMember.WORLD)
+                and dist.get_backend() == "nccl")
+
+    def _update_native(self, feats, plan, write_callback, local_ts):
+        """GPU ranks on the default NCCL group: pack, grouped send/recv and (inside ``wait``) unpack are issued by the
+        library on the current stream -- one foreign call to send, one to apply, no torch collective, no host sync."""
+        comm = NativeComm.get()
+        recv_list = self._exchange_counts(plan, feats.device)
+        key = (feats.shape[1], local_ts is not None, feats.device)
+        cache = plan.__dict__.setdefault("_native", {})
+        b = cache.get(key)
+        if b is None:
+            b = cache[key] = _NativeBinding(plan, recv_list, feats, local_ts is not None, comm)
+        L = _C.lib()
+        ts = None if local_ts is None else local_ts.to(torch.float32).contiguous()
+        rc = L.sgl_cache_route_step(comm.handle, feats.data_ptr(), feats.shape[0], b.dim, _C.ptr(ts), b.send_idx.data_ptr(),
+                                    b.remote.data_ptr(), b.h_send, b.h_recv, b.send_buf.data_ptr(), b.recv_buf.data_ptr(),
+                                    None, 0, None, 0, b.status.ptr(), _C.stream_ptr())
+        _C.check(rc)
+        fut = CacheUpdateFuture([], None, b.recv_buf[:b.n_recv], write_callback, 'cold', b.width)
+        fut._keep = (feats, ts)     # inputs of kernels that may still be queued
+        return [fut]
 
     def _exchange_counts(self, plan: CommPlan, device) -> List[int]:
         if plan.recv_sizes is None:
@@ -124,13 +201,15 @@ class CacheRoute:
         Every rank of the group must call this (an empty plan still takes part in the exchange)."""
         device = local_features.device
         feats = local_features.contiguous()
+        if self._use_native(feats) and feats.dtype == torch.float32:
+            return self._update_native(feats, plan, write_callback, local_ts)
         width = feats.shape[1] + (1 if local_ts is not None else 0)
         recv_list = self._exchange_counts(plan, device)
         send_list = plan.send_list()
         send_idx = plan.send_indices.to(device)
         remote = plan.send_remote_indices.to(device)
-        packed = ops.route_pack(feats, local_ts, send_idx, remote_idx=remote)          # [S, width + 2]
-        recv = torch.empty(sum(recv_list), width + 2, dtype=torch.float32, device=device)
+        packed = ops.route_pack(feats, local_ts, send_idx, remote_idx=remote)          # [S, wire pitch]
+        recv = torch.empty(sum(recv_list), ops.wire_pitch(width, False), dtype=torch.float32, device=device)
         work = dist.all_to_all_single(recv, packed, output_split_sizes=recv_list, input_split_sizes=send_list,
                                       group=self.group, async_op=True)
         return [CacheUpdateFuture([work], None, recv, write_callback, 'cold', width)]

@@ -364,6 +364,12 @@ def cache_gather(cache_rows, hitmap, backing, ids, *, status: Optional[StatusWor
 # route helpers, ids
 # --------------------------------------------------------------------------------------------------------------
 
+def wire_pitch(dim: int, has_ts: bool, has_slot: bool = True) -> int:
+    """Floats per wire row: payload, and with slots two slot words plus zero padding to a multiple of four."""
+    w = dim + (1 if has_ts else 0)
+    return (w + 2 + 3) // 4 * 4 if has_slot else w
+
+
 def route_pack(feats, ts, send_idx, *, remote_idx=None, status: Optional[StatusWord] = None):
     """Send buffer rows ``[feats[send_idx[i]] | ts[send_idx[i]] | remote_idx[i] as two 32-bit words]`` (float32);
     the timestamp column and the slot words are present only when ``ts`` / ``remote_idx`` are given."""
@@ -374,8 +380,8 @@ def route_pack(feats, ts, send_idx, *, remote_idx=None, status: Optional[StatusW
     if ts is not None:
         ts = ts.to(torch.float32).contiguous()
     n, d = send_idx.numel(), feats.shape[1]
-    width = d + (1 if ts is not None else 0) + (2 if remote_idx is not None else 0)
-    packed = torch.empty(n, width, dtype=torch.float32, device=send_idx.device)
+    packed = torch.empty(n, wire_pitch(d, ts is not None, remote_idx is not None), dtype=torch.float32,
+                         device=send_idx.device)
     _C.check(L.sgl_route_pack(_C.ptr(feats), feats.shape[0], d, _C.ptr(ts), _C.ptr(send_idx),
                               None if remote_idx is None else _C.ptr(_i64(remote_idx)), n,
                               packed.data_ptr() if n else None, status.ptr() if status else None, _C.stream_ptr()))
@@ -388,8 +394,8 @@ def route_unpack(wire, width: int, data, ts_table=None, *, status: Optional[Stat
     n = wire.shape[0]
     if n == 0:
         return
-    if wire.dtype != torch.float32 or not wire.is_contiguous() or wire.shape[1] != width + 2:
-        raise _C.SglError("route_unpack: wire rows must be contiguous float32 of width payload + 2")
+    if wire.dtype != torch.float32 or not wire.is_contiguous() or wire.shape[1] != wire_pitch(width, False):
+        raise _C.SglError("route_unpack: wire rows must be contiguous float32 with the pitch of wire_pitch()")
     _C.check(L.sgl_route_unpack(_C.ptr(wire), n, width, _C.ptr(data), data.shape[0], data.shape[1], _C.ptr(ts_table),
                                 status.ptr() if status else None, _C.stream_ptr()))
 

@@ -60,5 +60,8 @@ class DistributedContext:
     @classmethod
     def shutdown(cls):
         cls._default = None
+        from ..cache.cache_route import CacheRouteManager, NativeComm
+        NativeComm.shutdown()
+        CacheRouteManager.reset()
         if dist.is_initialized():
             dist.destroy_process_group()

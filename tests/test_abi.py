@@ -13,7 +13,7 @@ def _declared():
     txt = open(HEADER).read()
     txt = re.sub(r"/\*.*?\*/", "", txt, flags=re.S)
     decls = {}
-    for m in re.finditer(r"\b(?:int|size_t|const char\*)\s+(sgl_\w+)\s*\(([^;]*?)\)\s*;", txt, flags=re.S):
+    for m in re.finditer(r"\b(?:int64_t|int|size_t|const char\*)\s+(sgl_\w+)\s*\(([^;]*?)\)\s*;", txt, flags=re.S):
         args = m.group(2).strip()
         n = 0 if args in ("", "void") else len([a for a in args.split(",") if a.strip()])
         decls[m.group(1)] = n

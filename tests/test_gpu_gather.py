@@ -105,7 +105,7 @@ def test_scatter_and_wire_format():
     send_idx = cu(rng.integers(0, N, S).astype(np.int64))
     remote = cu(rng.permutation(N)[:S].astype(np.int64))
     wire = ops.route_pack(feats, ts, send_idx, remote_idx=remote)
-    assert wire.shape == (S, D + 3)
+    assert wire.shape == (S, ops.wire_pitch(D, True)) and ops.wire_pitch(D, True) % 4 == 0
     assert torch.equal(wire[:, :D], feats[send_idx]) and torch.equal(wire[:, D], ts[send_idx])
     assert torch.equal(ops.wire_slots(wire, D + 1), remote)
     data, tst = torch.zeros(N, D).cuda(), torch.zeros(N).cuda()
@@ -114,6 +114,15 @@ def test_scatter_and_wire_format():
     ref_d[remote] = feats[send_idx]
     ref_t[remote] = ts[send_idx]
     assert torch.equal(data, ref_d) and torch.equal(tst, ref_t)
+    # odd dimension: narrow-lane path, same format
+    f7 = torch.randn(N, 7).cuda()
+    w7 = ops.route_pack(f7, ts, send_idx, remote_idx=remote)
+    assert w7.shape[1] == 12 and torch.equal(w7[:, :7], f7[send_idx]) and torch.equal(w7[:, 7], ts[send_idx])
+    d7, t7 = torch.zeros(N, 7).cuda(), torch.zeros(N).cuda()
+    ops.route_unpack(w7, 8, d7, t7)
+    r7 = torch.zeros(N, 7).cuda()
+    r7[remote] = f7[send_idx]
+    assert torch.equal(d7, r7) and torch.equal(t7, ref_t)
     # plain pack (no ts, no slots) = x[send_index]
     assert torch.equal(ops.route_pack(feats, None, send_idx), feats[send_idx])
     # scatter with a trailing timestamp column and ids that are not stored locally (slot -1 is skipped)
