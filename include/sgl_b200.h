@@ -104,6 +104,32 @@ int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const int64_t* t
                      int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * sgl_sample_layer for callers that cannot provide scratch memory.  (No counterpart in the reference: its
+ * sampler allocates thrust vectors inside every call.)
+ *
+ * Who needs it: a sampler thread running beside a training loop, where a cudaMalloc would stall every stream
+ * of the GPU for its duration, and hosts whose device memory belongs entirely to another framework's pool, so
+ * that there is nothing left to allocate from.  Here the scratch of the hop is a fixed array inside the
+ * library itself (about 1.3 MB, resident on every GPU that loads the library until the process exits); the
+ * call performs no cudaMalloc / cudaFree and uses no allocating library routine.  Inputs and outputs are the
+ * caller's, exactly as for sgl_sample_layer (no device-side target count, no int64 dt output).
+ *
+ * Limits and rules:
+ *   - at most SGL_STATIC_SAMPLE_MAX_TARGETS targets per call; more is refused with SGL_ERR_ARG and a message;
+ *   - the first call on each device looks up the array's device address (that device must be current); make
+ *     that first call before starting any stream capture;
+ *   - all calls on a device share the one array, which still holds whatever the previous call left there;
+ *     the word that must start at zero is cleared on the stream by the call itself.  Two calls that can run
+ *     at the same time on the GPU (different streams, different host threads) race on it: serialise them.
+ * ---------------------------------------------------------------------------------------------- */
+#define SGL_STATIC_SAMPLE_MAX_TARGETS 65536
+int sgl_sample_layer_static(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                            int64_t num_nodes, const int64_t* targets, const int64_t* target_ts, int64_t n_targets,
+                            int fanout, int policy, int equal_root_time, int64_t allowed_offset, int keep_root_time,
+                            uint64_t seed, uint32_t rng_stream, int64_t* out_nbr, int64_t* out_dst, int64_t* out_ts,
+                            float* out_dt, int64_t* out_eid, int64_t* out_offsets, int32_t* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * One hop of sampling followed by the gather of the sampled edges' feature rows, in one call:
  * sgl_sample_layer(...) and then out_feats[j, :] = feat_table[out_eid[j], :] for the edges the hop produced
  * (their number never reaches the host: the gather reads it from out_offsets[n_targets]).  out_feats needs

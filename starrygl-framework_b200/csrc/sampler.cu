@@ -334,3 +334,51 @@ extern "C" int sgl_sample_gather(const int64_t* indptr, const int64_t* nbr, cons
   return sgl_gather_rows(feat_table, feat_rows, row_bytes, src_pitch, out_eid, nullptr, 0, n_targets * fanout,
                          out_offsets + n_targets, out_feats, row_bytes, nullptr, nullptr, gather_mode, d_status, stream);
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Sampling without caller-provided scratch.
+//
+// Some hosts of this library cannot hand it device memory on demand: a sampler thread that runs next to a training
+// loop must not call cudaMalloc (it stalls every stream of the device while it runs), and a process whose HBM has
+// been handed in full to another framework's pool has no allocator of its own to ask.  For them the scratch of one
+// hop lives in a fixed array inside the library image instead.  Every GPU that loads the library carries the array
+// (about 1.3 MB) until the process exits.
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+constexpr int64_t kStaticMaxTargets = SGL_STATIC_SAMPLE_MAX_TARGETS;
+// same layout as the caller-provided workspace of sgl_sample_layer for kStaticMaxTargets targets
+constexpr size_t kStaticScratchBytes = 2 * ((kStaticMaxTargets * 8 + 255) / 256 * 256) + ((kStaticMaxTargets * 4 + 255) / 256 * 256) +
+                                       ((kStaticMaxTargets / kWarpsPerCta * 8 + 255) / 256 * 256) + 256;
+static __device__ __align__(256) unsigned char g_static_sample_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices];   // device address of the array, per device, filled on first use
+}  // namespace
+
+extern "C" int sgl_sample_layer_static(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                                       int64_t num_nodes, const int64_t* targets, const int64_t* target_ts,
+                                       int64_t n_targets, int fanout, int policy, int equal_root_time,
+                                       int64_t allowed_offset, int keep_root_time, uint64_t seed, uint32_t rng_stream,
+                                       int64_t* out_nbr, int64_t* out_dst, int64_t* out_ts, float* out_dt, int64_t* out_eid,
+                                       int64_t* out_offsets, int32_t* d_status, void* stream) {
+  SGL_REQUIRE(n_targets >= 0 && n_targets <= kStaticMaxTargets, SGL_ERR_ARG,
+              "sample_layer_static: %lld targets exceed the built-in scratch (at most %lld per call); use sgl_sample_layer "
+              "with your own workspace for larger batches", (long long)n_targets, (long long)kStaticMaxTargets);
+  int dev = -1;
+  SGL_CUDA_CHECK(cudaGetDevice(&dev));
+  SGL_REQUIRE(dev >= 0 && dev < kMaxDevices, SGL_ERR_UNSUPPORTED, "sample_layer_static: device index %d not supported", dev);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    // In host code the array's name is only a handle; the address kernels can use has to be asked for, once per
+    // device, with that device current.
+    void* p = nullptr;
+    SGL_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_sample_scratch));
+    SGL_REQUIRE(p != nullptr, SGL_ERR_CUDA, "sample_layer_static: no device address for the built-in scratch");
+    g_static_scratch_addr[dev] = p;
+  }
+  // sgl_sample_layer clears the one word of the scratch that has to start at zero (the CTA arrival counter) on the
+  // stream before its kernels; everything else in the array is written before it is read.
+  return sgl_sample_layer(indptr, nbr, ts, eid, num_nodes, targets, target_ts, n_targets, nullptr, fanout, policy,
+                          equal_root_time, allowed_offset, keep_root_time, seed, rng_stream, out_nbr, out_dst, out_ts,
+                          out_dt, nullptr, out_eid, out_offsets, d_status, g_static_scratch_addr[dev], kStaticScratchBytes,
+                          stream);
+}
