@@ -42,6 +42,7 @@ MEM_DIM = 100
 TS_MAX = 10_000_000
 NUM_BATCHES = 64          # distinct pre-generated batches cycled through the steps
 STREAMS = 6
+ROUTE = "p2p"
 GRAPHS = True
 # DRAM bytes per gathered row measured with ncu on the small case (profiles/gather_bulk_kernel_172xfp32_small_case.txt:
 # 57.1 MB for 65,160 rows); roofline.traffic scales it by the rows of a full-size launch
@@ -130,7 +131,8 @@ def workload_config(n_gpus):
             "batch_roots": BATCH, "policy": f"recent-{FANOUT}, 1 hop", "edge_feat": f"{EDGE_DIM} x fp32",
             "edge_feat_rows": NUM_EDGES, "event": "one root query",
             "l2": "inputs larger than L2: 64 distinct batches over a 34 GB feature table and a 1.2 GB adjacency",
-            "batches_in_flight": STREAMS, "parallelism": f"{n_gpus} partition(s), one process per GPU" + (", cache route all-to-all per step" if n_gpus > 1 else "")}
+            "batches_in_flight": STREAMS, "parallelism": f"{n_gpus} partition(s), one process per GPU" +
+                           (f", cache route ({ROUTE}) of {ROUTE_ROWS} memory rows per step" if n_gpus > 1 else "")}
 
 
 def cpu_baseline_measure(dev, steps, warmup, budget_s):
@@ -187,7 +189,7 @@ def _protect_stdout():
 
 
 def main():
-    global NUM_NODES, NUM_EDGES, STREAMS, GRAPHS
+    global NUM_NODES, NUM_EDGES, STREAMS, GRAPHS, ROUTE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -199,11 +201,14 @@ def main():
     ap.add_argument("--graph-value", action="store_true",
                     help="replay a CUDA graph per step in the device-resident loop too (default: one fused C call per step; "
                          "the host-buffer loop always replays a graph that includes its copies)")
+    ap.add_argument("--route", default="p2p", choices=["p2p", "nccl", "none"],
+                    help="transport of the cache route at N > 1: peer-memory kernels (default) or grouped NCCL send/recv")
     ap.add_argument("--num-nodes", type=int, default=NUM_NODES, help="smaller graphs are for profiler captures only")
     ap.add_argument("--num-edges", type=int, default=NUM_EDGES)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     out_stream = _protect_stdout()
+    ROUTE = args.route
     NUM_NODES, NUM_EDGES, STREAMS, GRAPHS = args.num_nodes, args.num_edges, max(1, args.streams), True
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -229,6 +234,9 @@ def main():
     feats = torch.empty(NUM_EDGES, EDGE_DIM, dtype=torch.float32, device=dev)
     for s in range(0, NUM_EDGES, 5_000_000):
         feats[s:s + 5_000_000].normal_(generator=gen)
+    h_roots = b_roots.cpu().pin_memory()
+    h_ts = b_ts.cpu().pin_memory()
+
     S = max(1, args.streams)
     streams = [torch.cuda.Stream(dev) for _ in range(S)]
     pipes = [SampleGatherPipeline(g, feats, FANOUT, "recent", BATCH, gather_mode=args.gather_mode, stream=st)
@@ -239,11 +247,10 @@ def main():
         p_.capture()
     main_stream = torch.cuda.Stream(dev)
     route_stream = torch.cuda.Stream(dev, priority=-1)     # its few CTAs must not queue behind the persistent gather CTAs
-    h_roots = b_roots.cpu().pin_memory()
-    h_ts = b_ts.cpu().pin_memory()
-
+    route_recv_stream = torch.cuda.Stream(dev, priority=-1)
     route = None
-    if multi:
+    route_steps = None
+    if multi and args.route != "none":
         from starrygl.cache.cache_route import CacheRoute, CommPlan
         from starrygl.cache.NodeState import DistNodeState
         from starrygl.utils.partition_book import PartitionState
@@ -267,15 +274,24 @@ def main():
         def cb(idx, rows, mode):
             state.write_packed(idx, rows)
         cb.fused_state = state
-        route = (cr, plans, mem, mem_ts, cb)
         for p in plans:     # receive counts are exchanged once per plan (set-up), steps then need no host sync
             cr._exchange_counts(p, dev)
+        if args.route == "p2p":
+            from starrygl.cache.p2p_route import P2PCacheRoute
+            p2p = P2PCacheRoute(MEM_DIM, True, cap_rows=max(1024, ROUTE_ROWS), ring=8)
+
+            class _P2PAdapter:      # same call shape as CacheRoute.update_with_plan for the loops below
+                def update_with_plan(self, feats, plan, cb_, local_ts=None):
+                    return [p2p.push(feats, plan, state, local_ts)]
+            cr = _P2PAdapter()
+            route_steps = [p2p.bind_step(mem, mem_ts, pl_, state, route_stream, route_recv_stream) for pl_ in plans]
+        route = (cr, plans, mem, mem_ts, cb)
 
     batch_ptrs = [(b_roots[b].data_ptr(), b_ts[b].data_ptr()) for b in range(NUM_BATCHES)]
 
     issue_t = {"sample_gather": 0.0, "route_send": 0.0, "route_apply": 0.0}
 
-    def step_device(i, ev=None):
+    def step_device(i, ev=None, route_inline=True):
         b = i % NUM_BATCHES
         t_a = time.perf_counter()
         if ev is not None:
@@ -284,16 +300,20 @@ def main():
             pipes[i % S].replay_device(b_roots[b], b_ts[b])
         else:
             pipes[i % S].run_device_ptr(batch_ptrs[b][0], batch_ptrs[b][1], BATCH)
-        if route is not None:
+        if route is not None and route_inline:
             # the memory rows pushed to the other partitions do not depend on this batch's samples: the route runs
             # on its own stream, concurrently with sampling and gather
             cr, plans, mem, mem_ts, cb = route
             t_b = time.perf_counter()
-            with torch.cuda.stream(route_stream):
-                futs = cr.update_with_plan(mem, plans[b], cb, local_ts=mem_ts)
+            if route_steps is not None:
+                route_steps[b]()                # one pre-bound foreign call: send + apply of this step
                 t_c = time.perf_counter()
-                for f in futs:
-                    f.wait()
+            else:
+                with torch.cuda.stream(route_stream):
+                    futs = cr.update_with_plan(mem, plans[b], cb, local_ts=mem_ts)
+                    t_c = time.perf_counter()
+                    for f in futs:
+                        f.wait()
             t_d = time.perf_counter()
             issue_t["sample_gather"] += t_b - t_a
             issue_t["route_send"] += t_c - t_b
@@ -321,13 +341,25 @@ def main():
     # K steps, up to S of them in flight: the streams fork from / join into main_stream, whose two events bracket
     # the whole region on the device
     e0.record(main_stream)
-    for st in streams + [route_stream]:
+    for st in streams + [route_stream, route_recv_stream]:
         st.wait_stream(main_stream)
+    route_thread = None
+    if route_steps is not None:
+        # the route is driven from its own host thread, as a trainer would (the foreign calls release the GIL): the two
+        # issue loops run side by side, the device-side ring bounds how far a rank can run ahead of its peers
+        def route_loop():
+            torch.cuda.set_device(dev)
+            for i in range(args.steps):
+                route_steps[(args.warmup + i) % NUM_BATCHES]()
+        route_thread = threading.Thread(target=route_loop)
+        route_thread.start()
     t_issue = time.perf_counter()
     for i in range(args.steps):
-        step_device(args.warmup + i, None)
+        step_device(args.warmup + i, None, route_inline=route_thread is None)
     t_issue = time.perf_counter() - t_issue
-    for st in streams + [route_stream]:
+    if route_thread is not None:
+        route_thread.join()
+    for st in streams + [route_stream, route_recv_stream]:
         main_stream.wait_stream(st)
     e1.record(main_stream)
     barrier()

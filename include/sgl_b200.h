@@ -283,6 +283,41 @@ int sgl_cache_route_step(void* comm, const float* feats, int64_t n_rows, int64_t
                          float* ts_table, int apply, int32_t* d_status, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Cache route over NVLink peer memory (one node): the pack and the transfer are ONE kernel that stores the wire
+ * rows straight into the receivers' staging buffers; a second kernel on the receiver applies them.  No
+ * collective-library call per step.  Set-up (not on the batch path, allocates): every rank allocates one buffer
+ * of sgl_p2p_buffer_bytes() with sgl_p2p_alloc (zeroed, returns a 64-byte inter-process handle), the handles
+ * are exchanged out of band, every rank maps the others with sgl_p2p_open and builds a context from the
+ * world-sized array of base pointers (its own entry = its own buffer).
+ * Per step, on every rank, with the same `step` number (0, 1, 2, ...): sgl_p2p_route_send (rows for rank p =
+ * h_send_rows[p], grouped by destination like the plan's send_indices), later sgl_p2p_route_recv
+ * (h_recv_rows[q] rows from rank q) which writes data[slot] / ts_table[slot].  Both are asynchronous on the
+ * stream.  A rank may run ahead of a peer by at most `ring` steps; device-side waits are bounded (2 s) and end
+ * in SGL_DEV_TIMEOUT in *d_status instead of hanging.  At most cap_rows rows per (sender, receiver, step).
+ * Replaces: the same reference code as sgl_cache_route_step; ShardTensor's peer-memory design
+ * (csrc/include/starrygl/feature.cu.hpp:142-422) is the closest reference counterpart.
+ * ---------------------------------------------------------------------------------------------- */
+#define SGL_P2P_HANDLE_BYTES 64
+size_t sgl_p2p_buffer_bytes(int world, int ring, int64_t cap_rows, int64_t pitch_floats);
+int sgl_p2p_alloc(size_t bytes, void** out_ptr, char* out_handle, size_t handle_bytes);
+int sgl_p2p_open(const char* handle, void** out_ptr);
+int sgl_p2p_close(void* peer_ptr);
+int sgl_p2p_free(void* ptr);
+int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_rows, int64_t pitch_floats, void* const* h_bases,
+                         void** out_ctx);
+int sgl_p2p_route_destroy(void* ctx);
+int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
+                       const int64_t* send_idx, const int64_t* remote_idx, const int64_t* h_send_rows, uint64_t step,
+                       int32_t* d_status, void* stream);
+int sgl_p2p_route_recv(void* ctx, const int64_t* h_recv_rows, float* data, int64_t data_rows, int64_t dim, int has_ts,
+                       float* ts_table, uint64_t step, int32_t* d_status, void* stream);
+/* send + recv of one step in one call (for callers that apply the received rows right away) */
+int sgl_p2p_route_step(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
+                       const int64_t* send_idx, const int64_t* remote_idx, const int64_t* h_send_rows,
+                       const int64_t* h_recv_rows, float* data, int64_t data_rows, float* ts_table, uint64_t step,
+                       int32_t* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Reverse route accumulate: x[send_idx[s + j], :] += outs[s + j, :] for the peer segment [s, s + len);
  * one call per peer segment, in peer order, keeps the reference's summation order.
  * Replaces: the per-peer loop of RouteContext._recv_post (starrygl/route/route.py:461-464).

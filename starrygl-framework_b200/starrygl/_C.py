@@ -59,6 +59,17 @@ _SIGNATURES = {
     "sgl_route_exchange": (_i32, [_vp, _vp, C.POINTER(C.c_int64), _vp, C.POINTER(C.c_int64), _i64, _vp]),
     "sgl_cache_route_step": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), _vp,
                                     _vp, _vp, _i64, _vp, _i32, _vp, _vp]),
+    "sgl_p2p_buffer_bytes": (_sz, [_i32, _i32, _i64, _i64]),
+    "sgl_p2p_alloc": (_i32, [_sz, C.POINTER(C.c_void_p), C.c_char_p, _sz]),
+    "sgl_p2p_open": (_i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "sgl_p2p_close": (_i32, [_vp]),
+    "sgl_p2p_free": (_i32, [_vp]),
+    "sgl_p2p_route_create": (_i32, [_i32, _i32, _i32, _i64, _i64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "sgl_p2p_route_destroy": (_i32, [_vp]),
+    "sgl_p2p_route_send": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, C.POINTER(C.c_int64), _u64, _vp, _vp]),
+    "sgl_p2p_route_recv": (_i32, [_vp, C.POINTER(C.c_int64), _vp, _i64, _i64, _i32, _vp, _u64, _vp, _vp]),
+    "sgl_p2p_route_step": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), _vp, _i64,
+                                  _vp, _u64, _vp, _vp]),
     "sgl_route_add_rows": (_i32, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),
     "sgl_dist_pack": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp]),
     "sgl_dist_unpack": (_i32, [_vp, _i64, _vp, _vp, _vp, _vp]),

@@ -1,0 +1,161 @@
+"""Cache route over NVLink peer memory (single node): owner -> replica push of node rows without a collective
+library call per step.
+
+Same job as :class:`starrygl.cache.cache_route.CacheRoute` (reference: starrygl/cache/cache_route.py:211-277 +
+starrygl/cache/NodeState.py:245-282), different transport: one kernel on the sender packs the rows
+``[row | ts | slot]`` and stores them straight into the receivers' staging buffers (mapped with CUDA IPC); one
+kernel on the receiver applies them to the node state.  Every rank must call :meth:`push` (and wait on the returned
+future) for every step, in the same order -- an empty plan is fine.
+"""
+import ctypes as C
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _C, ops
+from .cache_route import CommPlan
+
+
+class P2PFuture:
+    def __init__(self, route, step, recv_arr, state):
+        self.route, self.step, self.recv_arr, self.state = route, step, recv_arr, state
+        self._done = False
+
+    def wait(self):
+        """Enqueue the receive kernel of this step on the current stream (it waits on the device, bounded, for the
+        senders' rows) -- the point at which the remote writes become part of the stream's order."""
+        if self._done:
+            return
+        self._done = True
+        r, st = self.route, self.state
+        has_ts = r.has_ts
+        rc = r.L.sgl_p2p_route_recv(r.ctx, self.recv_arr, st._d_data.data_ptr(), st._d_data.shape[0], r.dim, int(has_ts),
+                                    st._d_ts.data_ptr() if has_ts else None, self.step, r.status.ptr(), _C.stream_ptr())
+        _C.check(rc)
+        r._outstanding -= 1
+
+
+class P2PCacheRoute:
+    def __init__(self, dim: int, has_ts: bool = True, cap_rows: int = 16384, ring: int = 4,
+                 device: Optional[torch.device] = None):
+        if not dist.is_initialized():
+            raise RuntimeError("P2PCacheRoute needs an initialised process group (handles are exchanged through it)")
+        self.L = _C.lib()
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.dim, self.has_ts, self.cap_rows, self.ring = int(dim), bool(has_ts), int(cap_rows), int(ring)
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.pitch = ops.wire_pitch(self.dim + (1 if has_ts else 0), False)
+        nbytes = self.L.sgl_p2p_buffer_bytes(self.world, self.ring, self.cap_rows, self.pitch)
+        self.base = C.c_void_p()
+        hbuf = C.create_string_buffer(64)
+        _C.check(self.L.sgl_p2p_alloc(nbytes, C.byref(self.base), hbuf, 64))
+        handles: List[bytes] = [None] * self.world
+        dist.all_gather_object(handles, hbuf.raw)
+        self.bases = (C.c_void_p * self.world)()
+        self._opened = []
+        for p in range(self.world):
+            if p == self.rank:
+                self.bases[p] = self.base.value
+            else:
+                ptr = C.c_void_p()
+                _C.check(self.L.sgl_p2p_open(handles[p], C.byref(ptr)))
+                self.bases[p] = ptr.value
+                self._opened.append(ptr)
+        self.ctx = C.c_void_p()
+        _C.check(self.L.sgl_p2p_route_create(self.rank, self.world, self.ring, self.cap_rows, self.pitch, self.bases,
+                                             C.byref(self.ctx)))
+        self.status = ops.StatusWord(self.device)
+        self.step = 0
+        self._outstanding = 0
+        dist.barrier()        # every rank has mapped every buffer before the first store
+
+    def recv_sizes(self, plan: CommPlan) -> List[int]:
+        if plan.recv_sizes is None:
+            send = plan.send_sizes.to(self.device)
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send)
+            plan.recv_sizes = [int(v) for v in recv.tolist()]
+        return plan.recv_sizes
+
+    @torch.no_grad()
+    def push(self, feats: torch.Tensor, plan: CommPlan, state, local_ts: Optional[torch.Tensor] = None) -> P2PFuture:
+        """Send ``feats[plan.send_indices]`` (+ ``local_ts``) to the plan's ranks; ``state`` (a ``DistNodeState``) receives
+        what the other ranks send here when the returned future is waited on."""
+        if (local_ts is not None) != self.has_ts or feats.shape[1] != self.dim or feats.dtype != torch.float32:
+            raise _C.SglError("P2PCacheRoute.push: row layout differs from the one the route was created for")
+        if self._outstanding >= self.ring - 1:
+            raise _C.SglError("P2PCacheRoute: too many steps in flight -- wait on earlier futures first")
+        send_idx, remote, h_send, h_recv = self._bind(plan)
+        feats = feats.contiguous()
+        ts = None if local_ts is None else local_ts.contiguous()
+        rc = self.L.sgl_p2p_route_send(self.ctx, feats.data_ptr(), feats.shape[0], self.dim,
+                                       None if ts is None else ts.data_ptr(), send_idx.data_ptr(), remote.data_ptr(), h_send,
+                                       self.step, self.status.ptr(), _C.stream_ptr())
+        _C.check(rc)
+        fut = P2PFuture(self, self.step, h_recv, state)
+        fut._keep = (feats, ts)
+        self.step += 1
+        self._outstanding += 1
+        return fut
+
+    def _bind(self, plan: CommPlan):
+        b = plan.__dict__.get("_p2p")
+        if b is None:
+            recv_list = self.recv_sizes(plan)
+            b = plan.__dict__["_p2p"] = (plan.send_indices.to(self.device, torch.int64).contiguous(),
+                                         plan.send_remote_indices.to(self.device, torch.int64).contiguous(),
+                                         (C.c_int64 * self.world)(*plan.send_list()), (C.c_int64 * self.world)(*recv_list))
+        return b
+
+    def bind_step(self, feats: torch.Tensor, local_ts: Optional[torch.Tensor], plan: CommPlan, state, stream,
+                  recv_stream=None):
+        """Pre-convert every argument of ``push`` + ``wait`` for one (table, plan, state) combination and return a
+        callable that runs the step (the step number is filled in per call).  With one stream the step is ONE foreign
+        call; with a separate ``recv_stream`` the send kernels and the apply kernels form two independent chains
+        (the apply kernel of a step only depends on the senders' flags, not on this rank's stream order), which
+        halves the per-step latency of the route."""
+        send_idx, remote, h_send, h_recv = self._bind(plan)
+        v = C.c_void_p
+        step_a, step_b = C.c_uint64(0), C.c_uint64(0)
+        f_ptr, n_rows, dim = v(feats.data_ptr()), C.c_int64(feats.shape[0]), C.c_int64(self.dim)
+        ts_ptr = v(local_ts.data_ptr()) if local_ts is not None else None
+        d_ptr, d_rows = v(state._d_data.data_ptr()), C.c_int64(state._d_data.shape[0])
+        dts_ptr = v(state._d_ts.data_ptr()) if local_ts is not None else None
+        st_ptr = v(self.status.ptr())
+        keep = (feats, local_ts, send_idx, remote, state)
+        if recv_stream is None:
+            args = [self.ctx, f_ptr, n_rows, dim, ts_ptr, v(send_idx.data_ptr()), v(remote.data_ptr()), h_send, h_recv, d_ptr,
+                    d_rows, dts_ptr, step_a, st_ptr, v(stream.cuda_stream)]
+            fn = self.L.sgl_p2p_route_step
+
+            def run(_keep=keep):
+                step_a.value = self.step
+                rc = fn(*args)
+                if rc:
+                    _C.check(rc)
+                self.step += 1
+            return run
+        a_send = [self.ctx, f_ptr, n_rows, dim, ts_ptr, v(send_idx.data_ptr()), v(remote.data_ptr()), h_send, step_a, st_ptr,
+                  v(stream.cuda_stream)]
+        a_recv = [self.ctx, h_recv, d_ptr, d_rows, dim, C.c_int(1 if local_ts is not None else 0), dts_ptr, step_b, st_ptr,
+                  v(recv_stream.cuda_stream)]
+        f_send, f_recv = self.L.sgl_p2p_route_send, self.L.sgl_p2p_route_recv
+
+        def run2(_keep=keep):
+            step_a.value = step_b.value = self.step
+            rc = f_send(*a_send) or f_recv(*a_recv)
+            if rc:
+                _C.check(rc)
+            self.step += 1
+        return run2
+
+    def close(self):
+        if self.ctx:
+            torch.cuda.synchronize(self.device)
+            dist.barrier()
+            self.L.sgl_p2p_route_destroy(self.ctx)
+            for p in self._opened:
+                self.L.sgl_p2p_close(p)
+            self.L.sgl_p2p_free(self.base)
+            self.ctx = None

@@ -80,3 +80,104 @@ def test_routes_on_two_gpus():
         assert a, f"rank {rank}: remote writes differ from the reference"
         assert b, f"rank {rank}: local writes"
         assert c, f"rank {rank}: halo route forward/backward differs from the reference"
+
+
+def _worker_p2p(rank, world, port, q):
+    try:
+        import torch.distributed as dist
+        for p in (ROOT, os.path.join(ROOT, "starrygl-framework_b200"), HERE):
+            if p not in sys.path:
+                sys.path.insert(0, p)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", RANK=str(rank),
+                          WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+        from starrygl.utils.context import DistributedContext
+        ctx = DistributedContext.init("nccl")
+        dev = ctx.device
+        from starrygl.cache.cache_route import CommPlan
+        from starrygl.cache.p2p_route import P2PCacheRoute
+        from starrygl.cache.NodeState import DistNodeState
+        from starrygl.utils.partition_book import PartitionState
+
+        # (1) the reference's 2-rank case
+        z = np.load(os.path.join(HERE, "golden", "route_2rank.npz"))
+        t = lambda k: torch.from_numpy(z[f"r{rank}_{k}"]).to(dev)
+        feats = t("feats")
+        n_loc, D = feats.shape[0], feats.shape[1] - 1
+        plan = CommPlan(send_ranks=torch.repeat_interleave(torch.arange(world), torch.from_numpy(z[f"r{rank}_send_sizes"])),
+                        send_sizes=torch.from_numpy(z[f"r{rank}_send_sizes"]), send_indices=t("send_indices"),
+                        send_remote_indices=t("send_remote"))
+        ps = PartitionState(loc_ids=torch.arange(n_loc, device=dev), num_master_nums=n_loc, node_mode='identity', num_nodes=n_loc)
+        state = DistNodeState(ps, D, device=dev)
+        route = P2PCacheRoute(D, True, cap_rows=64, ring=4)
+        route.push(feats[:, :D].contiguous(), plan, state, feats[:, D].contiguous()).wait()
+        torch.cuda.synchronize()
+        route.status.check("p2p route")
+        ok_golden = torch.equal(state.data, t("data")) and torch.equal(state.ts, t("ts"))
+        route.close()
+
+        # (2) 40 steps through a ring of 4 with changing sizes (including empty ones); dim 100 -> 128-bit lanes
+        D2, N, K = 100, 4096, 512
+        route = P2PCacheRoute(D2, True, cap_rows=K, ring=4)
+        ps2 = PartitionState(loc_ids=torch.arange(N, device=dev), num_master_nums=N, node_mode='identity', num_nodes=N)
+        state2 = DistNodeState(ps2, D2, device=dev)
+        all_feats = [torch.randn(N, D2, generator=torch.Generator().manual_seed(50 + r)) for r in range(world)]
+        all_ts = [torch.rand(N, generator=torch.Generator().manual_seed(70 + r)) for r in range(world)]
+        my_f, my_t = all_feats[rank].to(dev), all_ts[rank].to(dev)
+        ref_d, ref_t = torch.zeros(N, D2), torch.zeros(N)
+
+        def plan_of(step, sender):
+            g = torch.Generator().manual_seed(1000 * step + sender)
+            sizes = torch.randint(0, K // 2, (world,), generator=g)
+            if step % 7 == 3:
+                sizes[:] = 0
+            idx, slots = [], []
+            for p in range(world):
+                idx.append(torch.randint(0, N, (int(sizes[p]),), generator=g))
+                # slots of different senders never collide inside a step: sender s owns [s*K, (s+1)*K)
+                slots.append(torch.randperm(K, generator=g)[:int(sizes[p])] + sender * K)
+            return sizes, torch.cat(idx), torch.cat(slots)
+
+        pending = []
+        for step in range(40):
+            sizes, idx, slots = plan_of(step, rank)
+            pl = CommPlan(send_ranks=torch.repeat_interleave(torch.arange(world), sizes), send_sizes=sizes, send_indices=idx,
+                          send_remote_indices=slots)
+            pl.recv_sizes = [int(plan_of(step, s)[0][rank]) for s in range(world)]
+            pending.append(route.push(my_f, pl, state2, my_t))
+            if len(pending) == 2:            # keep two steps in flight
+                pending.pop(0).wait()
+            for s in range(world):           # expected state, applied in step order
+                sz, ix, sl = plan_of(step, s)
+                off = int(sz[:rank].sum())
+                seg = slice(off, off + int(sz[rank]))
+                ref_d[sl[seg]] = all_feats[s][ix[seg]]
+                ref_t[sl[seg]] = all_ts[s][ix[seg]]
+        for f in pending:
+            f.wait()
+        torch.cuda.synchronize()
+        route.status.check("p2p route ring")
+        ok_ring = torch.equal(state2.data.cpu(), ref_d) and torch.equal(state2.ts.cpu(), ref_t)
+        route.close()
+        q.put((rank, ok_golden, ok_ring, True, None))
+        dist.barrier()
+        DistributedContext.shutdown()
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, False, False, False, traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_p2p_cache_route_on_two_gpus():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_p2p, args=(r, 2, 29652, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = sorted(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(60)
+    for rank, a, b, _, err in out:
+        assert err is None, err
+        assert a, f"rank {rank}: peer-memory route differs from the reference's result"
+        assert b, f"rank {rank}: 40 steps through the staging ring differ from the expected state"
