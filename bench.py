@@ -135,6 +135,78 @@ def workload_config(n_gpus):
                            (f", cache route ({ROUTE}) of {ROUTE_ROWS} memory rows per step" if n_gpus > 1 else "")}
 
 
+def _time_ms(fn, stream, iters, warm=3):
+    for _ in range(warm):
+        fn()
+    stream.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(iters):
+        fn()
+    b.record(stream)
+    stream.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def secondary_measurements(g, dev, peak):
+    """The other single-GPU configurations of the baseline, reported next to the headline (not part of `value`):
+    uniform [10,10] two-hop batches with (node, ts) dedup/relabel on the same graph, and the node-feature gather through a
+    10 % GPU cache (10 M x 128 table, 200,000 ids per batch drawn Zipf(1.1) over a seeded permutation), fp32 and bf16."""
+    from starrygl import ops
+    from starrygl.graph.batch import build_batch_async
+    out = {}
+    cur = torch.cuda.current_stream(dev)
+    gen = torch.Generator(device=dev).manual_seed(7)
+    # ---- uniform [10,10] + relabel --------------------------------------------------------------------------------
+    m = g.num_edges
+    picks = [torch.randint(0, m, (BATCH,), device=dev, generator=gen) for _ in range(8)]
+    # roots = source node of a drawn edge; the row of a node lists its edges, so a drawn position identifies (node, ts)
+    node_of_edge = torch.repeat_interleave(torch.arange(g.num_nodes, device=dev), g.indptr[1:] - g.indptr[:-1])
+    batches = [(node_of_edge[p].contiguous(), g.ts[p].contiguous()) for p in picks]
+    del node_of_edge
+    it = [0]
+
+    def two_hop():
+        q, qt = batches[it[0] % 8]
+        it[0] += 1
+        return build_batch_async(g, q, qt, [10, 10], "uniform", ts_range=(0, TS_MAX), seed=0)
+    ms = _time_ms(two_hop, cur, 20)
+    layers = two_hop().finish()
+    out["uniform_10_10_relabel"] = {"ms_per_batch": ms, "events_per_s": BATCH / ms * 1e3, "roots": BATCH,
+                                    "unique_pairs_per_layer": [int(d["gids"].numel()) for d in layers],
+                                    "edges_per_layer": [int(d["indices"].numel()) for d in layers[1:]],
+                                    "note": "sampling + (node, ts) dedup/relabel + CSC per hop, ~100 small launches issued from "
+                                            "Python: launch-bound at this batch size"}
+    # ---- node features through the cache ---------------------------------------------------------------------------
+    N, D, IDS = 10_000_000, 128, 200_000
+    perm = torch.randperm(N, device=dev, generator=gen)
+    C_ = N // 10
+    hitmap = torch.full((N,), -1, dtype=torch.int32, device=dev)
+    hitmap[perm[:C_]] = torch.arange(C_, dtype=torch.int32, device=dev)
+    rng = np.random.default_rng(0)
+    ids = [perm[torch.from_numpy(np.minimum(rng.zipf(1.1, IDS) - 1, N - 1)).to(dev)].contiguous() for _ in range(8)]
+    for name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        table = torch.empty(N, D, dtype=dt, device=dev)
+        for s_ in range(0, N, 2_000_000):
+            table[s_:s_ + 2_000_000].normal_(generator=gen)
+        cache = table[perm[:C_]].contiguous()
+        it[0] = 0
+
+        def cg():
+            r = ops.cache_gather(cache, hitmap, table, ids[it[0] % 8])
+            it[0] += 1
+            return r
+        ms = _time_ms(cg, cur, 30)
+        hits, misses = cg()[3].tolist()
+        rb = D * table.element_size()
+        alg = IDS * (2 * rb + 8 + 4) + misses * 16
+        out[f"cache_gather_{name}"] = {"ms_per_batch": ms, "ids": IDS, "hit_rate": hits / IDS, "misses_compacted": misses,
+                                       "algorithmic_bytes": alg, "achieved_GBps": alg / ms / 1e6,
+                                       "frac_of_peak": alg / ms / 1e6 / peak}
+        del table, cache
+    return out
+
+
 def cpu_baseline_measure(dev, steps, warmup, budget_s):
     """Times the C oracle on the same graph and batches.  The graph is generated with the same seeded generator
     (on the GPU when there is one, and copied to the host); the feature table is a 1 M-row host sample
@@ -196,6 +268,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the uniform two-hop and cache-gather measurements")
     ap.add_argument("--gather-mode", default="auto")
     ap.add_argument("--streams", type=int, default=6, help="mini-batches in flight (one pipeline object + stream each)")
     ap.add_argument("--graph-value", action="store_true",
@@ -437,8 +510,13 @@ def main():
                              "bytes_per_launch": alg, "ms_per_launch": g_ms,
                              "edges_per_step": statistics.mean(edges)},
                 "clocks": clk}
-        if not args.no_cpu_baseline and world == 1:
+        if world == 1 and not args.no_secondary:
             del feats, pipe, pipes
+            feats = pipe = pipes = None
+            torch.cuda.empty_cache()
+            line["secondary"] = secondary_measurements(g, dev, peak)
+        if not args.no_cpu_baseline and world == 1:
+            del feats, pipe, pipes, g
             torch.cuda.empty_cache()
             line["cpu_baseline"] = cpu_baseline_measure(dev, args.steps, args.warmup, 20.0)["cpu_baseline"]
         print(json.dumps(line), file=out_stream, flush=True)

@@ -347,6 +347,22 @@ int sgl_replica_lookup(const int64_t* indptr, const int64_t* ranks, const int64_
                        void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Route plan of one layer: which rows of the layer's node list this partition pushes to which other ranks.
+ * layer_ids[n] = node ids of the layer list, sorted (rows of one node adjacent, latest timestamp last -- the
+ * (id, ts) order of sgl_unique_pairs).  For every node owned here (node_parts[id] == pid) the LAST row of its run
+ * is sent to every replica on another rank (replica table: CSR rep_indptr / rep_ranks / rep_locs over node id).
+ * Outputs, grouped by destination rank, ascending row inside a rank: out_ranks, out_rows (row of the layer list
+ * to read), out_locs (slot on the receiver); d_send_sizes[num_parts]; *d_total entries (capacity cap, overflow
+ * raises SGL_DEV_OVERFLOW).  These are the four arrays of a CommPlan.
+ * Replaces: MaterializedMultiLayerBuilder._compute_layer_route (prepare_sample.py:266-310).
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_plan_route_ws_bytes(int64_t n, int64_t cap);
+int sgl_plan_route(const int64_t* layer_ids, int64_t n, const int64_t* d_n, const int64_t* node_parts, int64_t num_nodes,
+                   int64_t pid, const int64_t* rep_indptr, const int64_t* rep_ranks, const int64_t* rep_locs,
+                   int64_t num_parts, int64_t cap, int64_t* out_ranks, int64_t* out_rows, int64_t* out_locs,
+                   int64_t* d_send_sizes, int64_t* d_total, int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Roots of a batch = the events of one time window.  Input: the window's slice of the time-ordered event
  * arrays (source node, timestamp, edge id; n_events items).  Events whose source node lies in a selected
  * chunk (chunk_mask[node_chunk[src]] != 0; both NULL = every node) are grouped by (src, ts):

@@ -371,3 +371,39 @@ def route_reverse(gs, send_sizes, recv_sizes, send_index):
             x[seg] += back
         outs.append(x)
     return outs
+
+
+# ----------------------------------------------------------------------------------------------
+# route plan of one layer
+# ----------------------------------------------------------------------------------------------
+
+
+def compute_layer_route(layer_ids, layer_ts, node_parts, pid, rep_indptr, rep_ranks, rep_locs, num_parts):
+    """prepare_sample.py:266-310.  For every distinct node id of the layer list: the list row with the latest timestamp
+    (first such row on ties); nodes this partition owns are sent to every OTHER rank holding a replica.  Returns
+    (send_ranks, send_sizes[num_parts], send_indices = list row, send_remote_indices = slot on the receiver), grouped by
+    rank in ascending list-row order (the reference's order inside a rank segment is unspecified: unstable argsort),
+    or None when nothing is sent."""
+    layer_ids = np.asarray(layer_ids, I64)
+    layer_ts = np.asarray(layer_ts, I64)
+    if len(layer_ids) == 0:
+        return None
+    uniq, inv = np.unique(layer_ids, return_inverse=True)
+    arg = np.full(len(uniq), -1, I64)
+    best = np.full(len(uniq), np.iinfo(np.int64).min, I64)
+    for i in range(len(layer_ids)):
+        if layer_ts[i] > best[inv[i]]:
+            best[inv[i]], arg[inv[i]] = layer_ts[i], i
+    mine = np.asarray(node_parts)[uniq] == pid
+    q_ids, q_rows = uniq[mine], arg[mine]
+    if len(q_ids) == 0:
+        return None
+    src, ranks, locs = replica_lookup(rep_indptr, rep_ranks, rep_locs, q_ids)
+    keep = ranks != pid
+    src, ranks, locs = src[keep], ranks[keep], locs[keep]
+    if len(ranks) == 0:
+        return None
+    rows = q_rows[src]
+    order = np.lexsort((rows, ranks))          # by rank, then list row (stable, ascending)
+    sizes = np.bincount(ranks, minlength=num_parts).astype(I64)
+    return ranks[order], sizes, rows[order], locs[order]

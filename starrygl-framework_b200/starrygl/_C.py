@@ -77,6 +77,9 @@ _SIGNATURES = {
     "sgl_seeds_in_window": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp,
                                    _vp, _vp, _vp, _sz, _vp]),
     "sgl_lower_bound_i64": (_i32, [_vp, _i64, _vp, _i32, _vp, _vp]),
+    "sgl_plan_route_ws_bytes": (_sz, [_i64, _i64]),
+    "sgl_plan_route": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                              _sz, _vp]),
     "sgl_replica_lookup_ws_bytes": (_sz, [_i64]),
     "sgl_replica_lookup": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
 }

@@ -18,7 +18,7 @@ from torch import Tensor
 
 from .. import _C, ops
 
-__all__ = ['CommPlan', 'CacheUpdateFuture', 'CacheRoute', 'CacheRouteManager']
+__all__ = ['CommPlan', 'CacheUpdateFuture', 'CacheRoute', 'CacheRouteManager', 'compute_layer_route']
 
 
 @dataclass
@@ -65,6 +65,28 @@ class CommPlan:
         return cls(send_ranks=torch.empty(0, dtype=torch.long),
                    send_sizes=torch.zeros(num_parts, dtype=torch.long) if num_parts > 0 else torch.empty(0, dtype=torch.long),
                    send_indices=torch.empty(0, dtype=torch.long), send_remote_indices=torch.empty(0, dtype=torch.long))
+
+
+def compute_layer_route(layer_ids: Tensor, node_parts: Tensor, pid: int, replica_table, num_parts: int,
+                        max_replicas_per_node: int = 0) -> Optional["CommPlan"]:
+    """Build the plan of one layer on the GPU (reference: ``_compute_layer_route``, prepare_sample.py:266-310): the rows of
+    nodes owned by partition ``pid`` -- for every node the row with its latest timestamp -- go to every other rank that
+    holds a replica.  ``layer_ids`` is the layer's node-id list in (id, ts) order (what the batch builder returns);
+    ``replica_table`` a ``CSRReplicaTable`` on the same GPU.  Returns ``None`` when nothing has to be sent (as the
+    reference does); the receive sizes are not known yet and are exchanged on first use of the plan."""
+    if not layer_ids.is_cuda:
+        raise RuntimeError("compute_layer_route runs on the GPU")
+    if max_replicas_per_node <= 0:
+        max_replicas_per_node = max(num_parts - 1, 1)
+    cap = layer_ids.numel() * max_replicas_per_node
+    st = ops.StatusWord(layer_ids.device)
+    ranks, rows, locs, sizes, total = ops.plan_route(layer_ids, node_parts.to(layer_ids.device), pid, replica_table.indptr,
+                                                     replica_table.indices, replica_table.locs, num_parts, cap, status=st)
+    n = int(total.item())
+    st.check("compute_layer_route")
+    if n == 0:
+        return None
+    return CommPlan(send_ranks=ranks[:n], send_sizes=sizes, send_indices=rows[:n], send_remote_indices=locs[:n])
 
 
 class CacheUpdateFuture:

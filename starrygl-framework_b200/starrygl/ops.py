@@ -448,3 +448,22 @@ def replica_lookup(indptr, ranks, locs, ids, cap: int, *, status: Optional[Statu
                                   _C.ptr(src), _C.ptr(rk), _C.ptr(lc), _C.ptr(offs), status.ptr() if status else None,
                                   wp, wn, _C.stream_ptr()))
     return src, rk, lc, offs
+
+
+def plan_route(layer_ids, node_parts, pid: int, rep_indptr, rep_ranks, rep_locs, num_parts: int, cap: int, *, d_n=None,
+               status: Optional[StatusWord] = None):
+    """Route plan of one layer (see ``sgl_plan_route``).  Returns (ranks, rows, locs, send_sizes[num_parts], d_total);
+    the three lists have capacity ``cap``, valid length ``d_total`` (device scalar)."""
+    L = _C.lib()
+    layer_ids = _i64(layer_ids)
+    n = layer_ids.numel()
+    dev = layer_ids.device
+    ranks, rows, locs = (torch.empty(max(cap, 1), dtype=I64, device=dev) for _ in range(3))
+    sizes = torch.zeros(num_parts, dtype=I64, device=dev)
+    total = torch.zeros(1, dtype=I64, device=dev)
+    _, wp, wn = _C.workspace(L.sgl_plan_route_ws_bytes(n, cap), dev)
+    _C.check(L.sgl_plan_route(_C.ptr(layer_ids), n, _C.ptr(d_n), _C.ptr(_i64(node_parts)), node_parts.numel(), int(pid),
+                              _C.ptr(rep_indptr), _C.ptr(rep_ranks), _C.ptr(rep_locs), int(num_parts), int(cap), _C.ptr(ranks),
+                              _C.ptr(rows), _C.ptr(locs), _C.ptr(sizes), _C.ptr(total), status.ptr() if status else None, wp, wn,
+                              _C.stream_ptr()))
+    return ranks, rows, locs, sizes, total

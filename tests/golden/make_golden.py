@@ -19,6 +19,7 @@ What is pinned, and the reference code that produced it:
 * ``route_2rank.npz`` -- ``CacheRoute.update_with_plan`` + ``HistoryLayerUpdater`` style write-back and
   ``Route.forward`` forward/backward over a 2-rank gloo group
   (starrygl/cache/cache_route.py:211-277, starrygl/route/route.py:427-466).
+* ``plan.npz``        -- ``_compute_layer_route`` (prepare_sample.py:266-310) for every partition of a 4-way split.
 * ``nodestate.npz``   -- ``DistNodeState.update`` / ``__getitem__`` with ``node_mode='map'``
   (starrygl/cache/NodeState.py:36-61, starrygl/utils/partition_book.py:98-133).
 """
@@ -293,6 +294,63 @@ def gen_ids(ref, out):
     dist.destroy_process_group()
 
 
+def gen_plan(ref, out):
+    """``_compute_layer_route`` (prepare_sample.py:266-310) on sorted unique (id, ts) layer lists.  ``torch_scatter`` is
+    absent here, so its ``scatter_max`` is supplied as a torch restatement (max per group, index of the first
+    maximum); on these inputs every (id, ts) pair is unique, so no tie can occur and the choice does not matter."""
+    import torch
+    sys.path.insert(0, ref)
+    het = _stub("dgl.heterograph", DGLBlock=object)
+    _stub("dgl", heterograph=het)
+    comm = _stub("starrygl.lib.libstarrygl_comm", DistContext=object, init_p2p=lambda *a: None)
+    _stub("starrygl.lib", libstarrygl_comm=comm)
+
+    def scatter_max(src, index, dim=0):
+        n = int(index.max()) + 1 if index.numel() else 0
+        mx = torch.full((n,), torch.iinfo(src.dtype).min, dtype=src.dtype).scatter_reduce(0, index, src, "amax")
+        is_max = src == mx[index]
+        pos = torch.where(is_max, torch.arange(len(src)), torch.full((len(src),), len(src)))
+        arg = torch.full((n,), len(src), dtype=torch.long).scatter_reduce(0, index, pos, "amin")
+        return mx, arg
+    _stub("torch_scatter", scatter_max=scatter_max)
+    spec = importlib.util.spec_from_file_location("ref_prepare_sample2", os.path.join(ref, "prepare_sample.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    from starrygl.cache.cache_route import CommPlan
+    from starrygl.cache.replica_table import build_replica_table
+    mod.CommPlan = CommPlan
+    rng = np.random.default_rng(21)
+    N, P = 500, 4
+    node_parts = torch.from_numpy(rng.integers(0, P, N))
+    book = []
+    for p in range(P):
+        owned = torch.nonzero(node_parts == p)[:, 0].numpy()
+        halo = rng.choice(np.setdiff1d(np.arange(N), owned), 120, replace=False)
+        book.append(torch.from_numpy(np.concatenate([owned, halo])))
+    rt = build_replica_table(N, book, P)
+    rec = {"N": np.int64(N), "P": np.int64(P), "node_parts": node_parts.numpy(), "rt_indptr": rt.indptr.numpy(),
+           "rt_ranks": rt.indices.numpy(), "rt_locs": rt.locs.numpy()}
+    e = np.zeros(1, np.int64)
+    for case in range(3):
+        n_pairs = [400, 40, 1500][case]
+        ids = rng.integers(0, N, n_pairs)
+        ts = rng.integers(0, 1000, n_pairs)
+        pairs = np.unique(np.stack([ids, ts], 1), axis=0)          # sorted by id, then ts
+        for pid in range(P):
+            b = mod.MaterializedMultiLayerBuilder({'src': e, 'dst': e, 'ts': e}, N, node_parts, rt, pid, P)
+            plan = b._compute_layer_route(pairs[:, 0].copy(), pairs[:, 1].copy())
+            tag = f"c{case}_p{pid}"
+            rec[f"{tag}_ids"], rec[f"{tag}_ts"] = pairs[:, 0], pairs[:, 1]
+            if plan is None:
+                rec[f"{tag}_none"] = np.int64(1)
+                continue
+            rec[f"{tag}_send_ranks"] = plan.send_ranks.numpy()
+            rec[f"{tag}_send_sizes"] = plan.send_sizes.numpy()
+            rec[f"{tag}_send_indices"] = plan.send_indices.numpy()
+            rec[f"{tag}_send_remote"] = plan.send_remote_indices.numpy()
+    np.savez_compressed(os.path.join(out, "plan.npz"), **rec)
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
@@ -306,4 +364,6 @@ if __name__ == "__main__":
         gen_batches(mod, HERE)
     if a.only in ("all", "ids"):
         gen_ids(a.reference, HERE)
+    if a.only in ("all", "plan"):
+        gen_plan(a.reference, HERE)
     print("golden vectors written to", HERE)

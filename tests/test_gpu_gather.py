@@ -164,3 +164,30 @@ def test_ids_and_replica_lookup_match_reference():
     assert np.array_equal(npy(rt.indptr), z["rt_indptr"]) and np.array_equal(npy(rt.indices), z["rt_ranks"])
     s, r, l = rt.to("cuda").lookup(cu(z["lk_ids"]))
     assert np.array_equal(npy(s), z["lk_src"]) and np.array_equal(npy(r), z["lk_ranks"]) and np.array_equal(npy(l), z["lk_locs"])
+
+
+def test_route_plan_matches_reference():
+    """compute_layer_route on the GPU against plans produced by the reference's _compute_layer_route."""
+    from starrygl.cache.cache_route import compute_layer_route
+    from starrygl.cache.replica_table import CSRReplicaTable
+    z = load("plan.npz")
+    P = int(z["P"])
+    rt = CSRReplicaTable(cu(z["rt_indptr"]), cu(z["rt_ranks"]), cu(z["rt_locs"]))
+    parts = cu(z["node_parts"])
+    for case in range(3):
+        for pid in range(P):
+            tag = f"c{case}_p{pid}"
+            plan = compute_layer_route(cu(z[f"{tag}_ids"]), parts, pid, rt, P)
+            ref = O.compute_layer_route(z[f"{tag}_ids"], z[f"{tag}_ts"], z["node_parts"], pid, z["rt_indptr"], z["rt_ranks"],
+                                        z["rt_locs"], P)
+            if ref is None:
+                assert plan is None and f"{tag}_none" in z.files
+                continue
+            # bit-exact against the oracle (same stable order) ...
+            assert np.array_equal(npy(plan.send_ranks), ref[0]) and np.array_equal(npy(plan.send_sizes), ref[1])
+            assert np.array_equal(npy(plan.send_indices), ref[2]) and np.array_equal(npy(plan.send_remote_indices), ref[3])
+            # ... and, per destination segment, the same (row, slot) multiset as the reference's own plan
+            assert np.array_equal(npy(plan.send_sizes), z[f"{tag}_send_sizes"])
+            got = sorted(zip(npy(plan.send_ranks).tolist(), npy(plan.send_indices).tolist(), npy(plan.send_remote_indices).tolist()))
+            want = sorted(zip(z[f"{tag}_send_ranks"].tolist(), z[f"{tag}_send_indices"].tolist(), z[f"{tag}_send_remote"].tolist()))
+            assert got == want, tag

@@ -175,3 +175,30 @@ def test_c_oracle_gather():
     out, mp, mi = OC.cache_gather(table[hot].copy(), hitmap, table, ids)
     ref, hit, rp, ri = O.cache_gather(table[hot], hitmap, table, ids)
     assert np.array_equal(out, ref) and np.array_equal(mp, rp) and np.array_equal(mi, ri)
+
+
+def plan_cases():
+    z = load("plan.npz")
+    for case in range(3):
+        for pid in range(int(z["P"])):
+            yield z, f"c{case}_p{pid}", pid
+
+
+def same_plan_up_to_segment_order(got, z, tag):
+    """Equal split sizes and, inside every destination-rank segment, the same multiset of (list row, receiver slot)."""
+    if got is None:
+        return f"{tag}_none" in z.files
+    ranks, sizes, rows, locs = got
+    if f"{tag}_none" in z.files or not np.array_equal(sizes, z[f"{tag}_send_sizes"]):
+        return False
+    if not np.array_equal(ranks, np.sort(z[f"{tag}_send_ranks"])):
+        return False
+    ref = sorted(zip(z[f"{tag}_send_ranks"].tolist(), z[f"{tag}_send_indices"].tolist(), z[f"{tag}_send_remote"].tolist()))
+    return sorted(zip(ranks.tolist(), rows.tolist(), locs.tolist())) == ref
+
+
+def test_route_plan_matches_reference():
+    for z, tag, pid in plan_cases():
+        got = O.compute_layer_route(z[f"{tag}_ids"], z[f"{tag}_ts"], z["node_parts"], pid, z["rt_indptr"], z["rt_ranks"],
+                                    z["rt_locs"], int(z["P"]))
+        assert same_plan_up_to_segment_order(got, z, tag), tag
