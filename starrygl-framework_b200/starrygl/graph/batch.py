@@ -28,7 +28,7 @@ class DeviceBatch:
 
     def finish(self) -> List[dict]:
         """One host synchronisation: read every count, check the device status word, trim the arrays."""
-        host = self._host = torch.cat(self.counts).tolist()
+        host = self._host = torch.cat(self.counts).tolist()      # one read-back (synchronises the current stream)
         self.status.check("build_batch")
         n_list = host[0]
         out = [{"gids": self.layers[0]["gids"][:n_list], "ts": self.layers[0]["ts"][:n_list],
@@ -109,3 +109,50 @@ def build_batch_async(g: ops.TCSR, roots: torch.Tensor, root_ts: torch.Tensor, f
 def build_batch(g, roots, root_ts, fanouts, policy="recent", **kw) -> List[dict]:
     """Synchronous form of :func:`build_batch_async`."""
     return build_batch_async(g, roots, root_ts, fanouts, policy, **kw).finish()
+
+
+class BatchGraph:
+    """The whole multi-hop batch construction of :func:`build_batch_async` captured once as a CUDA graph for a fixed
+    number of roots, and replayed per mini-batch: one launch instead of about a hundred small ones (the pipeline is a
+    chain of short sort / scan / emit kernels, so at mini-batch sizes it is bound by launch overhead, not by the GPU).
+
+    The result tensors are the same objects for every batch: consume (or copy) a result before the next ``run``.
+    """
+
+    def __init__(self, g: ops.TCSR, num_roots: int, fanouts: Sequence[int], policy: str = "recent", *,
+                 ts_range: Sequence[int], equal_root_time=False, allowed_offset=-1, seed=0,
+                 stream: Optional[torch.cuda.Stream] = None):
+        from .. import _C
+        dev = g.device
+        self.g, self.num_roots = g, int(num_roots)
+        self.stream = stream or torch.cuda.Stream(dev)
+        self.roots = torch.zeros(self.num_roots, dtype=torch.int64, device=dev)
+        self.root_ts = torch.full((self.num_roots,), int(ts_range[0]), dtype=torch.int64, device=dev)
+        self.status = ops.StatusWord(dev)
+        kw = dict(ts_range=ts_range, equal_root_time=equal_root_time, allowed_offset=allowed_offset, seed=seed,
+                  status=self.status)
+        # scratch used inside the graph must not be shared with eager calls: the capture gets its own workspace
+        saved = _C.WORKSPACE
+        _C.WORKSPACE = self._workspace = _C.Workspace()
+        try:
+            torch.cuda.synchronize(dev)
+            with torch.cuda.stream(self.stream):
+                build_batch_async(g, self.roots, self.root_ts, fanouts, policy, **kw)     # warm-up: sizes the scratch
+            self.stream.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=self.stream):
+                self.batch = build_batch_async(g, self.roots, self.root_ts, fanouts, policy, **kw)
+        finally:
+            _C.WORKSPACE = saved
+        self.stream.synchronize()
+
+    def run(self, roots: torch.Tensor, root_ts: torch.Tensor) -> DeviceBatch:
+        """Enqueue one batch (exactly ``num_roots`` roots, already on the GPU); returns the un-trimmed device batch,
+        whose ``finish()`` synchronises and trims."""
+        if roots.numel() != self.num_roots:
+            raise ValueError(f"this graph was captured for {self.num_roots} roots, got {roots.numel()}")
+        with torch.cuda.stream(self.stream):
+            self.roots.copy_(roots, non_blocking=True)
+            self.root_ts.copy_(root_ts, non_blocking=True)
+            self.graph.replay()
+        return self.batch

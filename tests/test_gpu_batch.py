@@ -91,3 +91,26 @@ def test_node_relabel_matches_oracle():
     loc, new_ids, d_new = rl.insert(cu(lists[0]))
     r2, m2 = O.relabel_nodes([lists[0]])
     assert np.array_equal(npy(loc), r2[0]) and np.array_equal(npy(new_ids[:int(d_new.item())]), m2)
+
+
+def test_batch_graph_replay_matches_eager():
+    """The CUDA-graph form of the batch builder gives the same layers as the call-by-call form, batch after batch."""
+    from starrygl.graph.batch import BatchGraph, build_batch
+    rng = np.random.default_rng(12)
+    n, m = 2000, 60000
+    z = {"n": n, "dst": rng.integers(0, n, m).astype(np.int64), "src": rng.integers(0, n, m).astype(np.int64),
+         "ts": np.sort(rng.integers(0, 10 ** 5, m)).astype(np.int64), "eid": np.arange(m, dtype=np.int64)}
+    g = build_graph(z)
+    bg = BatchGraph(g, 256, [5, 5], "uniform", ts_range=(0, 10 ** 5), seed=9)
+    for trial in range(3):
+        pick = rng.integers(0, m, 256)
+        roots, rts = cu(z["dst"][pick]), cu(z["ts"][pick])
+        torch.cuda.synchronize()
+        dev_batch = bg.run(roots, rts)
+        with torch.cuda.stream(bg.stream):
+            got = [{k: v.clone() for k, v in d.items()} for d in dev_batch.finish()]
+        ref = build_batch(g, roots, rts, [5, 5], "uniform", ts_range=(0, 10 ** 5), seed=9)
+        assert len(got) == len(ref)
+        for d, r in zip(got, ref):
+            for k in r:
+                assert torch.equal(d[k], r[k]), (trial, k)
