@@ -30,6 +30,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "starrygl-framework_b200"))
 sys.path.insert(0, ROOT)
 
+# more hardware work queues than the default 8: the benchmark drives up to 10 streams per GPU, and streams that share a
+# queue serialise behind each other's kernels (must be set before CUDA is initialised)
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
 import numpy as np
 import torch
 
@@ -105,7 +109,9 @@ def make_graph(dev, seed):
 
 def make_batches(src, ts, gen, dev):
     pick = torch.randint(0, NUM_EDGES, (NUM_BATCHES, BATCH), device=dev, generator=gen)
-    return src[pick].contiguous(), ts[pick].contiguous()       # query time = the drawn edge's own timestamp
+    # [batch, 2, BATCH]: roots and query times of one batch are contiguous; query time = the drawn edge's own timestamp
+    both = torch.stack([src[pick], ts[pick]], 1).contiguous()
+    return both[:, 0], both[:, 1]
 
 
 def run_reference(args, rank, out_stream):
@@ -287,6 +293,8 @@ def main():
                          "the host-buffer loop always replays a graph that includes its copies)")
     ap.add_argument("--route", default="p2p", choices=["p2p", "nccl", "none"],
                     help="transport of the cache route at N > 1: peer-memory kernels (default) or grouped NCCL send/recv")
+    ap.add_argument("--no-step-graph", action="store_true",
+                    help="issue sample+gather as one fused foreign call (three kernel launches) instead of one graph launch")
     ap.add_argument("--num-nodes", type=int, default=NUM_NODES, help="smaller graphs are for profiler captures only")
     ap.add_argument("--num-edges", type=int, default=NUM_EDGES)
     args = ap.parse_args()
@@ -329,6 +337,8 @@ def main():
     use_graph = args.graph_value
     for p_ in pipes:
         p_.capture()
+        if not args.no_step_graph:
+            p_.capture_native()
     main_stream = torch.cuda.Stream(dev)
     route_stream = torch.cuda.Stream(dev, priority=-1)     # its few CTAs must not queue behind the persistent gather CTAs
     route_recv_stream = torch.cuda.Stream(dev, priority=-1)
@@ -382,6 +392,8 @@ def main():
             pipes[i % S].run_device(b_roots[b], b_ts[b], 0, ev)
         elif use_graph:
             pipes[i % S].replay_device(b_roots[b], b_ts[b])
+        elif not args.no_step_graph:
+            pipes[i % S].replay_ptr(batch_ptrs[b][0])       # one call: copy the batch's roots in + one graph launch
         else:
             pipes[i % S].run_device_ptr(batch_ptrs[b][0], batch_ptrs[b][1], BATCH)
         if route is not None and route_inline:
@@ -433,8 +445,10 @@ def main():
         # issue loops run side by side, the device-side ring bounds how far a rank can run ahead of its peers
         def route_loop():
             torch.cuda.set_device(dev)
+            t_r = time.perf_counter()
             for i in range(args.steps):
                 route_steps[(args.warmup + i) % NUM_BATCHES]()
+            issue_t["route_thread_total"] = time.perf_counter() - t_r
         route_thread = threading.Thread(target=route_loop)
         route_thread.start()
     t_issue = time.perf_counter()
@@ -443,6 +457,15 @@ def main():
     t_issue = time.perf_counter() - t_issue
     if route_thread is not None:
         route_thread.join()
+    # where the device time goes: end of the sampler/gather streams and end of the two route chains, each against e0
+    e_pipe = torch.cuda.Event(enable_timing=True)
+    e_rs, e_rr = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    join_stream = torch.cuda.Stream(dev)
+    for st in streams:
+        join_stream.wait_stream(st)
+    e_pipe.record(join_stream)
+    e_rs.record(route_stream)
+    e_rr.record(route_recv_stream)
     for st in streams + [route_stream, route_recv_stream]:
         main_stream.wait_stream(st)
     e1.record(main_stream)
@@ -450,6 +473,16 @@ def main():
     ms = e0.elapsed_time(e1)
     for p_ in pipes:
         p_.status.check("bench")
+    if os.environ.get("SGL_P2P_DBG", "0") == "2" and route_steps is not None and rank == 0:
+        import ctypes as C_
+        n_tl = min(args.steps + 2 * args.warmup, 4096)
+        buf = (C_.c_uint64 * (n_tl * 8))()
+        _C.lib().sgl_p2p_route_timeline(p2p.ctx, buf, n_tl)
+        tl = np.array(buf, dtype=np.uint64).reshape(n_tl, 8).astype(np.float64)[args.warmup + 50:args.warmup + args.steps - 10] / 1e3
+        sys.stderr.write("P2P timeline (us): send dur %.1f | send start->next start %.1f | apply launch->flags %.1f | flags->end %.1f | "
+                         "apply start->next start %.1f | send end -> apply(flags seen) %.1f\n" % (
+                             np.median(tl[:, 1] - tl[:, 0]), np.median(np.diff(tl[:, 0])), np.median(tl[:, 3] - tl[:, 2]),
+                             np.median(tl[:, 4] - tl[:, 3]), np.median(np.diff(tl[:, 2])), np.median(tl[:, 3] - tl[:, 1])))
     if True:
         # the step is one foreign call (or one graph replay), so its kernels cannot be bracketed individually:
         # the dominant kernel is timed in a second pass over the same K batches, kernel by kernel on one stream
@@ -506,6 +539,9 @@ def main():
                 "unit": "events/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms / args.steps, "host_issue_ms_per_step": t_issue * 1e3 / args.steps,
                 "host_issue_breakdown_ms": {k: v * 1e3 / args.steps for k, v in issue_t.items()},
+                "device_ms_per_step": {"sample_gather_streams": e0.elapsed_time(e_pipe) / args.steps,
+                                       "route_send_chain": e0.elapsed_time(e_rs) / args.steps,
+                                       "route_apply_chain": e0.elapsed_time(e_rr) / args.steps},
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "int64", "data": "synthetic", "config": workload_config(world),
                 "e2e": {"value": world * BATCH * e2e_steps / (e2e_ms / 1e3), "unit": "events/s",

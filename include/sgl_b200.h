@@ -311,6 +311,9 @@ int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows, int64_t di
                        int32_t* d_status, void* stream);
 int sgl_p2p_route_recv(void* ctx, const int64_t* h_recv_rows, float* data, int64_t data_rows, int64_t dim, int has_ts,
                        float* ts_table, uint64_t step, int32_t* d_status, void* stream);
+/* Diagnostics: with SGL_P2P_DBG=2 in the environment at context creation the kernels stamp %globaltimer per step
+ * (send start, send end, apply start, flags seen, apply end; 8 uint64 per step, first 4096 steps); this copies them out. */
+int sgl_p2p_route_timeline(void* ctx, unsigned long long* h_out, int64_t steps);
 /* send + recv of one step in one call (for callers that apply the received rows right away) */
 int sgl_p2p_route_step(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
                        const int64_t* send_idx, const int64_t* remote_idx, const int64_t* h_send_rows,
@@ -383,6 +386,19 @@ int sgl_seeds_in_window(const int64_t* ev_src, const int64_t* ev_ts, const int64
 /* out[i] = first position p with sorted[p] >= values[i] (n when none); k values.  Used to find the slice of the
  * time-ordered event arrays that a window [t_begin, t_end) covers. */
 int sgl_lower_bound_i64(const int64_t* sorted, int64_t n, const int64_t* values, int k, int64_t* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * CUDA-graph helpers for launch-bound steps.  Between sgl_graph_capture_begin(stream) and
+ * sgl_graph_capture_end(stream, &exec) every asynchronous call of this library on `stream` is recorded instead
+ * of executed (thread-local capture mode; sgl_tcsr_build synchronises and cannot be captured).  sgl_graph_launch
+ * optionally copies copy_bytes from copy_src to copy_dst on the stream first (the step's varying input, e.g. the
+ * batch's roots, into the buffer the captured kernels read) and then replays the recorded sequence with one
+ * launch.  (No counterpart in the reference, which issues every kernel from the host.)
+ * ---------------------------------------------------------------------------------------------- */
+int sgl_graph_capture_begin(void* stream);
+int sgl_graph_capture_end(void* stream, void** out_exec);
+int sgl_graph_launch(void* exec, const void* copy_src, void* copy_dst, size_t copy_bytes, void* stream);
+int sgl_graph_destroy(void* exec);
 
 #ifdef __cplusplus
 }

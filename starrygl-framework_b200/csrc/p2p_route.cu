@@ -16,6 +16,7 @@
 // wait is bounded by a wall-clock limit; on expiry the kernel raises SGL_DEV_TIMEOUT in the status word, publishes
 // nothing and returns, so the context stays usable.  Every rank must run send and recv for every step (zero rows are
 // fine): the handshake is per step, not per row.
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -24,10 +25,13 @@ namespace sgl {
 namespace {
 
 constexpr int kMaxWorld = 16;
-constexpr int kThreads = 256;
+constexpr int kThreads = 64;    // small CTAs: they fit into the register/thread gaps a busy GPU has left, so they start promptly
+constexpr int kUnroll = 4;   // lanes in flight per thread in the route kernels
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct P2PCfg {
+  int dbg;
+  unsigned long long* tl;   // optional timeline buffer [steps][8] (diagnostics)
   int rank, world, ring;
   int64_t cap_rows;
   uint32_t pitch;
@@ -89,6 +93,7 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
   __shared__ int s_ok;
   __shared__ bool s_last;
   if (threadIdx.x == 0) s_ok = 1;
+  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 0] = now_ns();
   __syncthreads();
   // flow control: the ring slot may be overwritten once every receiver has applied the step that used it last
   if (threadIdx.x < c.world && step >= (unsigned long long)c.ring) {
@@ -103,52 +108,83 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
     const int64_t n_send = seg.off[c.world];
     const int64_t total = n_send * lanes;
     const int64_t stride = (int64_t)gridDim.x * kThreads;
-    for (int64_t q = (int64_t)blockIdx.x * kThreads + threadIdx.x; q < total; q += stride) {
-      int64_t i = q / lanes;
-      uint32_t l = (uint32_t)(q - i * lanes);
-      int64_t r = __ldg(send_idx + i);
-      if (r < 0) r += n_rows;
-      if (r < 0 || r >= n_rows) {
-        dev_flag(d_status, SGL_DEV_BAD_INDEX);
-        continue;
-      }
-      const int p = segment_of(seg, c.world, i);
-      float* dst_row = c.peer_stage[p] + (((int64_t)c.rank * c.ring + slot) * c.cap_rows + (i - seg.off[p])) * c.pitch;
-      const float* frow = feats + r * dim;
-      uint64_t slotv = (uint64_t)__ldg(remote_idx + i);
-      if (VEC == 4) {
-        uint4 v;
-        if ((l + 1) * 4 <= dim) {
-          v = __ldg((const uint4*)frow + l);
-        } else {
-          v.x = wire_word2(4 * l + 0, dim, payload, frow, ts, r, slotv);
-          v.y = wire_word2(4 * l + 1, dim, payload, frow, ts, r, slotv);
-          v.z = wire_word2(4 * l + 2, dim, payload, frow, ts, r, slotv);
-          v.w = wire_word2(4 * l + 3, dim, payload, frow, ts, r, slotv);
+    // kUnroll lanes per thread and iteration, in three phases (indices, rows, stores), so that the two dependent
+    // loads of every lane overlap with those of the other lanes: a small grid then moves a small message in about
+    // two memory latencies, and few CTAs have to find a free slot on a busy GPU
+    for (int64_t q0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; q0 < total; q0 += stride * kUnroll) {
+      int64_t row_i[kUnroll], src_r[kUnroll];
+      uint64_t slotv[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t q = q0 + u * stride;
+        row_i[u] = -1;
+        if (q < total) {
+          row_i[u] = q / lanes;
+          src_r[u] = __ldg(send_idx + row_i[u]);
+          slotv[u] = (uint64_t)__ldg(remote_idx + row_i[u]);
         }
-        ((uint4*)dst_row)[l] = v;
-      } else {
-        ((uint32_t*)dst_row)[l] = wire_word2(l, dim, payload, frow, ts, r, slotv);
+      }
+      uint4 v[kUnroll];
+      void* dst[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        dst[u] = nullptr;
+        if (row_i[u] < 0) continue;
+        const int64_t i = row_i[u];
+        const uint32_t l = (uint32_t)(q0 + u * stride - i * lanes);
+        int64_t r = src_r[u];
+        if (r < 0) r += n_rows;
+        if (r < 0 || r >= n_rows) {
+          dev_flag(d_status, SGL_DEV_BAD_INDEX);
+          continue;
+        }
+        const int p = segment_of(seg, c.world, i);
+        float* dst_row = c.peer_stage[p] + (((int64_t)c.rank * c.ring + slot) * c.cap_rows + (i - seg.off[p])) * c.pitch;
+        const float* frow = feats + r * dim;
+        if (VEC == 4) {
+          if ((l + 1) * 4 <= dim) {
+            v[u] = __ldg((const uint4*)frow + l);
+          } else {
+            v[u].x = wire_word2(4 * l + 0, dim, payload, frow, ts, r, slotv[u]);
+            v[u].y = wire_word2(4 * l + 1, dim, payload, frow, ts, r, slotv[u]);
+            v[u].z = wire_word2(4 * l + 2, dim, payload, frow, ts, r, slotv[u]);
+            v[u].w = wire_word2(4 * l + 3, dim, payload, frow, ts, r, slotv[u]);
+          }
+          dst[u] = (uint4*)dst_row + l;
+        } else {
+          v[u].x = wire_word2(l, dim, payload, frow, ts, r, slotv[u]);
+          dst[u] = (uint32_t*)dst_row + l;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (!dst[u]) continue;
+        if (VEC == 4) *(uint4*)dst[u] = v[u];
+        else *(uint32_t*)dst[u] = v[u].x;
       }
     }
   } else if (threadIdx.x == 0) {
     dev_flag(d_status, SGL_DEV_TIMEOUT);
   }
-  // publish: all rows of all CTAs are ordered before the flag by a system-scope fence on both sides of the counter
-  __threadfence_system();
+  // publish.  One system-scope fence per CTA instead of one per thread: the CTA barrier makes every thread's stores
+  // happen-before thread 0's fence, and fences are cumulative, so thread 0's fence + counter increment orders the whole
+  // CTA's rows before anything the last CTA does after it has seen all increments.  (A system fence is expensive
+  // while the GPU streams other data; 20,000 of them per launch dominated this kernel's latency.)
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     unsigned prev = atomicAdd(done_counter, 1u);
     s_last = prev == gridDim.x - 1;
+    if (s_last) __threadfence_system();
   }
   __syncthreads();
   if (!s_last) return;
-  __threadfence_system();
   const bool failed = d_status && (*(volatile int32_t*)d_status & SGL_DEV_TIMEOUT);
   if (threadIdx.x < c.world && !failed) {
     volatile unsigned long long* f = c.peer_flags[threadIdx.x] + (int64_t)c.rank * c.ring + (step % c.ring);
     *f = step + 1;
   }
+  if (c.tl && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 1] = now_ns();
   if (threadIdx.x == 0) *done_counter = 0;
 }
 
@@ -161,55 +197,75 @@ p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, 
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   const int slot = (int)(step % c.ring);
+  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 2] = now_ns();
   if (threadIdx.x < c.world) {
     if (!wait_at_least(c.flags + (int64_t)threadIdx.x * c.ring + slot, step + 1)) s_ok = 0;
+    __threadfence_system();   // acquire side: the rows written before the flag are visible after this fence ...
   }
-  __threadfence_system();   // rows written before the flag are visible to the loads below
-  __syncthreads();
+  __syncthreads();            // ... and, through the barrier, to every thread of the CTA
+  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 3] = now_ns();
   const bool ok = s_ok != 0;
   if (ok) {
     const uint32_t lanes = (width + VEC - 1) / VEC;
     const int64_t n_recv = seg.off[c.world];
     const int64_t total = n_recv * lanes;
     const int64_t stride = (int64_t)gridDim.x * kThreads;
-    for (int64_t q = (int64_t)blockIdx.x * kThreads + threadIdx.x; q < total; q += stride) {
-      int64_t i = q / lanes;
-      uint32_t l = (uint32_t)(q - i * lanes);
-      const int s = segment_of(seg, c.world, i);
-      const uint32_t* row = (const uint32_t*)(c.stage + (((int64_t)s * c.ring + slot) * c.cap_rows + (i - seg.off[s])) * c.pitch);
-      // plain loads: the stage was written by another GPU, the read-only cache must not be used for it
-      int64_t dslot = (int64_t)((uint64_t)row[width] | ((uint64_t)row[width + 1] << 32));
-      if (dslot < 0 || dslot >= data_rows) {
-        dev_flag(d_status, SGL_DEV_BAD_INDEX);
-        continue;
+    for (int64_t q0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; q0 < total; q0 += stride * kUnroll) {
+      // plain loads throughout: the stage was written by another GPU, the read-only cache must not be used for it
+      uint4 v[kUnroll];
+      int64_t dslot[kUnroll];
+      uint32_t lane_l[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t q = q0 + u * stride;
+        dslot[u] = -1;
+        if (q >= total) continue;
+        const int64_t i = q / lanes;
+        const uint32_t l = (uint32_t)(q - i * lanes);
+        const int sdr = segment_of(seg, c.world, i);
+        const uint32_t* row = (const uint32_t*)(c.stage + (((int64_t)sdr * c.ring + slot) * c.cap_rows + (i - seg.off[sdr])) * c.pitch);
+        dslot[u] = (int64_t)((uint64_t)row[width] | ((uint64_t)row[width + 1] << 32));
+        lane_l[u] = l;
+        if (VEC == 4) v[u] = ((const uint4*)row)[l];
+        else v[u].x = row[l];
+        if (dslot[u] < 0 || dslot[u] >= data_rows) {
+          dev_flag(d_status, SGL_DEV_BAD_INDEX);
+          dslot[u] = -1;
+        }
       }
-      if (VEC == 4) {
-        uint4 v = ((const uint4*)row)[l];
-        if ((l + 1) * 4 <= dim) ((uint4*)(data + dslot * dim))[l] = v;
-        else if (ts_table) ts_table[dslot] = __uint_as_float(v.x);
-      } else {
-        float v = __uint_as_float(row[l]);
-        if (l < dim) data[dslot * dim + l] = v;
-        else if (ts_table) ts_table[dslot] = v;
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (dslot[u] < 0) continue;
+        const uint32_t l = lane_l[u];
+        if (VEC == 4) {
+          if ((l + 1) * 4 <= dim) ((uint4*)(data + dslot[u] * dim))[l] = v[u];
+          else if (ts_table) ts_table[dslot[u]] = __uint_as_float(v[u].x);
+        } else {
+          if (l < dim) data[dslot[u] * dim + l] = __uint_as_float(v[u].x);
+          else if (ts_table) ts_table[dslot[u]] = __uint_as_float(v[u].x);
+        }
       }
     }
   } else if (threadIdx.x == 0) {
     dev_flag(d_status, SGL_DEV_TIMEOUT);
   }
-  __threadfence_system();
+  // all reads of the staging slot are done before the senders are told they may overwrite it (same one-fence-per-CTA
+  // pattern as in the send kernel)
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     unsigned prev = atomicAdd(done_counter, 1u);
     s_last = prev == gridDim.x - 1;
+    if (s_last) __threadfence_system();
   }
   __syncthreads();
   if (!s_last) return;
-  __threadfence_system();
   const bool failed = d_status && (*(volatile int32_t*)d_status & SGL_DEV_TIMEOUT);
   if (threadIdx.x < c.world && !failed) {
     volatile unsigned long long* a = c.peer_acks[threadIdx.x] + c.rank;   // "rank has applied your step"
     *a = step + 1;
   }
+  if (c.tl && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 4] = now_ns();
   if (threadIdx.x == 0) *done_counter = 0;
 }
 
@@ -263,6 +319,7 @@ extern "C" int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_r
               SGL_ERR_ARG, "p2p_route_create: bad argument (world <= %d, ring >= 2)", kMaxWorld);
   Ctx* x = new Ctx();
   P2PCfg& c = x->cfg;
+  c.dbg = getenv("SGL_P2P_DBG") ? atoi(getenv("SGL_P2P_DBG")) : 0;   // 2 = record a per-step kernel timeline (diagnostics)
   c.rank = rank; c.world = world; c.ring = ring; c.cap_rows = cap_rows; c.pitch = (uint32_t)pitch_floats;
   const size_t hb = header_bytes(world, ring);
   for (int p = 0; p < world; ++p) {
@@ -277,6 +334,11 @@ extern "C" int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_r
   c.stage = c.peer_stage[rank];
   SGL_CUDA_CHECK(cudaMalloc(&x->counters, 256));
   SGL_CUDA_CHECK(cudaMemset(x->counters, 0, 256));
+  c.tl = nullptr;
+  if (c.dbg & 2) {
+    SGL_CUDA_CHECK(cudaMalloc(&c.tl, 4096 * 8 * 8));
+    SGL_CUDA_CHECK(cudaMemset(c.tl, 0, 4096 * 8 * 8));
+  }
   *out_ctx = x;
   return SGL_OK;
 }
@@ -287,6 +349,19 @@ extern "C" int sgl_p2p_route_destroy(void* ctx) {
   cudaFree(x->counters);
   delete x;
   return SGL_OK;
+}
+
+// number of CTAs of a route kernel: enough for the rows, capped (SGL_P2P_MAX_CTAS, tuning aid) -- small messages are
+// latency-bound and every extra CTA adds fence traffic and a longer wait for the last one
+static int p2p_grid(int64_t lanes_total) {
+  static int cap = -1;
+  if (cap < 0) {
+    const char* e = getenv("SGL_P2P_MAX_CTAS");
+    cap = e ? atoi(e) : kNumSM * 8;
+    if (cap < 1) cap = 1;
+  }
+  int g = stream_grid(lanes_total, kThreads * kUnroll, 8);
+  return g < cap ? g : cap;
 }
 
 static int make_splits(const Ctx* x, const int64_t* h_rows, Splits* s, const char* what) {
@@ -316,11 +391,11 @@ extern "C" int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows,
   cudaStream_t stream = (cudaStream_t)stream_;
   const bool vec = dim % 4 == 0 && ((uintptr_t)feats & 15) == 0;
   if (vec) {
-    const int grid = stream_grid(n_send * (pitch / 4), kThreads, 8);
+    const int grid = p2p_grid(n_send * (pitch / 4));
     p2p_send_kernel<4><<<grid, kThreads, 0, stream>>>(x->cfg, feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, seg, step,
                                                      x->counters, d_status);
   } else {
-    const int grid = stream_grid(n_send * pitch, kThreads, 8);
+    const int grid = p2p_grid(n_send * pitch);
     p2p_send_kernel<1><<<grid, kThreads, 0, stream>>>(x->cfg, feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, seg, step,
                                                      x->counters, d_status);
   }
@@ -343,11 +418,11 @@ extern "C" int sgl_p2p_route_recv(void* ctx, const int64_t* h_recv_rows, float* 
   cudaStream_t stream = (cudaStream_t)stream_;
   const bool vec = dim % 4 == 0 && ((uintptr_t)data & 15) == 0;
   if (vec) {
-    const int grid = stream_grid(n_recv * ((width + 3) / 4), kThreads, 8);
+    const int grid = p2p_grid(n_recv * ((width + 3) / 4));
     p2p_recv_kernel<4><<<grid, kThreads, 0, stream>>>(x->cfg, seg, (uint32_t)width, data, data_rows, (uint32_t)dim, ts_table,
                                                      step, x->counters + 32, d_status);
   } else {
-    const int grid = stream_grid(n_recv * width, kThreads, 8);
+    const int grid = p2p_grid(n_recv * width);
     p2p_recv_kernel<1><<<grid, kThreads, 0, stream>>>(x->cfg, seg, (uint32_t)width, data, data_rows, (uint32_t)dim, ts_table,
                                                      step, x->counters + 32, d_status);
   }
@@ -362,4 +437,12 @@ extern "C" int sgl_p2p_route_step(void* ctx, const float* feats, int64_t n_rows,
   int rc = sgl_p2p_route_send(ctx, feats, n_rows, dim, ts, send_idx, remote_idx, h_send_rows, step, d_status, stream);
   if (rc) return rc;
   return sgl_p2p_route_recv(ctx, h_recv_rows, data, data_rows, dim, ts != nullptr, ts_table, step, d_status, stream);
+}
+
+// diagnostics: copies the per-step kernel timeline (ns; send start/end, apply start/flags seen/end) to the host
+extern "C" int sgl_p2p_route_timeline(void* ctx, unsigned long long* h_out, int64_t steps) {
+  Ctx* x = (Ctx*)ctx;
+  SGL_REQUIRE(x && x->cfg.tl && h_out && steps <= 4096, SGL_ERR_ARG, "p2p_route_timeline: not enabled (SGL_P2P_DBG=2)");
+  SGL_CUDA_CHECK(cudaMemcpy(h_out, x->cfg.tl, (size_t)steps * 8 * 8, cudaMemcpyDeviceToHost));
+  return SGL_OK;
 }

@@ -68,6 +68,7 @@ _SIGNATURES = {
     "sgl_p2p_route_destroy": (_i32, [_vp]),
     "sgl_p2p_route_send": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, C.POINTER(C.c_int64), _u64, _vp, _vp]),
     "sgl_p2p_route_recv": (_i32, [_vp, C.POINTER(C.c_int64), _vp, _i64, _i64, _i32, _vp, _u64, _vp, _vp]),
+    "sgl_p2p_route_timeline": (_i32, [_vp, _vp, _i64]),
     "sgl_p2p_route_step": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), _vp, _i64,
                                   _vp, _u64, _vp, _vp]),
     "sgl_route_add_rows": (_i32, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),
@@ -80,6 +81,10 @@ _SIGNATURES = {
     "sgl_plan_route_ws_bytes": (_sz, [_i64, _i64]),
     "sgl_plan_route": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                               _sz, _vp]),
+    "sgl_graph_capture_begin": (_i32, [_vp]),
+    "sgl_graph_capture_end": (_i32, [_vp, C.POINTER(C.c_void_p)]),
+    "sgl_graph_launch": (_i32, [_vp, _vp, _vp, _sz, _vp]),
+    "sgl_graph_destroy": (_i32, [_vp]),
     "sgl_replica_lookup_ws_bytes": (_sz, [_i64]),
     "sgl_replica_lookup": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
 }

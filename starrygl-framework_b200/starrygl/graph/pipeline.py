@@ -31,8 +31,9 @@ class SampleGatherPipeline:
         self.L = _C.lib()
         cap = self.max_roots * self.k
         self.cap = cap
-        self.roots = torch.empty(self.max_roots, dtype=I64, device=dev)
-        self.root_ts = torch.empty(self.max_roots, dtype=I64, device=dev)
+        # roots and query times of the current batch, contiguous ([2, max_roots]) so that one copy fills both
+        self.roots_ts = torch.empty(2, self.max_roots, dtype=I64, device=dev)
+        self.roots, self.root_ts = self.roots_ts[0], self.roots_ts[1]
         # one int64 block for the index outputs so that the block structure goes back to the host in ONE copy:
         # [offsets (max_roots+1) | nbr | ts | eid] each of capacity cap, then dt (float32) separately.  The target
         # slot of every edge (dst) stays on the device: on the host it is implied by the offsets.
@@ -109,6 +110,37 @@ class SampleGatherPipeline:
             self.h_dt.copy_(self.dt, non_blocking=True)
         self.stream.synchronize()
         return self
+
+    def capture_native(self):
+        """Record the full-batch device step (``sgl_sample_gather`` on this object's root buffers) with the library's
+        own graph helpers; :meth:`replay_ptr` then costs one foreign call = one copy + one graph launch."""
+        sp = self.stream.cuda_stream
+        self.roots_ts.zero_()
+        torch.cuda.synchronize(self.dev)
+        self.run_device_ptr(self.roots.data_ptr(), self.root_ts.data_ptr(), self.max_roots)   # warm-up
+        self.stream.synchronize()
+        _C.check(self.L.sgl_graph_capture_begin(sp))
+        try:
+            self.run_device_ptr(self.roots.data_ptr(), self.root_ts.data_ptr(), self.max_roots)
+        finally:
+            ex = C.c_void_p()
+            rc = self.L.sgl_graph_capture_end(sp, C.byref(ex))
+        _C.check(rc)
+        self._exec = ex
+        v = C.c_void_p
+        self._a_src = v(0)
+        self._launch_args = [ex, self._a_src, v(self.roots_ts.data_ptr()), C.c_size_t(self.roots_ts.numel() * 8), v(sp)]
+        self._launch = self.L.sgl_graph_launch
+        self.stream.synchronize()
+        return self
+
+    def replay_ptr(self, roots_ts_ptr: int):
+        """Run the captured step for a batch whose roots and query times lie contiguously ([2, max_roots] int64) at the
+        given device (or pinned host) address."""
+        self._a_src.value = roots_ts_ptr
+        rc = self._launch(*self._launch_args)
+        if rc:
+            _C.check(rc)
 
     def replay_device(self, roots: torch.Tensor, root_ts: torch.Tensor):
         """Graph form of :meth:`run_device` for a full batch: copy the roots into the captured input buffers
