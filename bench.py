@@ -473,6 +473,12 @@ def main():
     ms = e0.elapsed_time(e1)
     for p_ in pipes:
         p_.status.check("bench")
+    if os.environ.get("SGL_P2P_DBG", "0") == "2" and route_steps is not None and os.environ.get("SGL_P2P_TL_OUT"):
+        import ctypes as C_
+        n_tl = min(args.steps + 2 * args.warmup, 4096)
+        buf = (C_.c_uint64 * (n_tl * 8))()
+        _C.lib().sgl_p2p_route_timeline(p2p.ctx, buf, n_tl)
+        np.save(os.environ["SGL_P2P_TL_OUT"] + f".rank{rank}.npy", np.array(buf, dtype=np.uint64).reshape(n_tl, 8))
     if os.environ.get("SGL_P2P_DBG", "0") == "2" and route_steps is not None and rank == 0:
         import ctypes as C_
         n_tl = min(args.steps + 2 * args.warmup, 4096)
@@ -480,9 +486,10 @@ def main():
         _C.lib().sgl_p2p_route_timeline(p2p.ctx, buf, n_tl)
         tl = np.array(buf, dtype=np.uint64).reshape(n_tl, 8).astype(np.float64)[args.warmup + 50:args.warmup + args.steps - 10] / 1e3
         sys.stderr.write("P2P timeline (us): send dur %.1f | send start->next start %.1f | apply launch->flags %.1f | flags->end %.1f | "
-                         "apply start->next start %.1f | send end -> apply(flags seen) %.1f\n" % (
+                         "apply start->next start %.1f | send end -> apply(flags seen) %.1f | resident before start: send %.1f apply %.1f\n" % (
                              np.median(tl[:, 1] - tl[:, 0]), np.median(np.diff(tl[:, 0])), np.median(tl[:, 3] - tl[:, 2]),
-                             np.median(tl[:, 4] - tl[:, 3]), np.median(np.diff(tl[:, 2])), np.median(tl[:, 3] - tl[:, 1])))
+                             np.median(tl[:, 4] - tl[:, 3]), np.median(np.diff(tl[:, 2])), np.median(tl[:, 3] - tl[:, 1]),
+                             np.median(tl[:, 0] - tl[:, 5]), np.median(tl[:, 2] - tl[:, 6])))
     if True:
         # the step is one foreign call (or one graph replay), so its kernels cannot be bracketed individually:
         # the dominant kernel is timed in a second pass over the same K batches, kernel by kernel on one stream

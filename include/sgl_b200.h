@@ -284,8 +284,11 @@ int sgl_cache_route_step(void* comm, const float* feats, int64_t n_rows, int64_t
 
 /* ------------------------------------------------------------------------------------------------
  * Cache route over NVLink peer memory (one node): the pack and the transfer are ONE kernel that stores the wire
- * rows straight into the receivers' staging buffers; a second kernel on the receiver applies them.  No
- * collective-library call per step.  Set-up (not on the batch path, allocates): every rank allocates one buffer
+ * rows straight into the receivers' staging buffers, as 16-byte lines that carry the step's tag next to the data
+ * (the receiver polls the lines themselves; there is no separate flag and no fence); a second kernel on the
+ * receiver applies them and acknowledges the step.  No collective-library call per step.  Consecutive route
+ * kernels of a stream are launched with programmatic stream serialization: they may become resident early but
+ * touch nothing before the previous kernel of the stream has completed.  Set-up (not on the batch path, allocates): every rank allocates one buffer
  * of sgl_p2p_buffer_bytes() with sgl_p2p_alloc (zeroed, returns a 64-byte inter-process handle), the handles
  * are exchanged out of band, every rank maps the others with sgl_p2p_open and builds a context from the
  * world-sized array of base pointers (its own entry = its own buffer).
@@ -312,7 +315,8 @@ int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows, int64_t di
 int sgl_p2p_route_recv(void* ctx, const int64_t* h_recv_rows, float* data, int64_t data_rows, int64_t dim, int has_ts,
                        float* ts_table, uint64_t step, int32_t* d_status, void* stream);
 /* Diagnostics: with SGL_P2P_DBG=2 in the environment at context creation the kernels stamp %globaltimer per step
- * (send start, send end, apply start, flags seen, apply end; 8 uint64 per step, first 4096 steps); this copies them out. */
+ * (send start, send end, apply start, first CTA applied, apply end, send resident, apply resident; 8 uint64 per step,
+ * first 4096 steps); this copies them out. */
 int sgl_p2p_route_timeline(void* ctx, unsigned long long* h_out, int64_t steps);
 /* send + recv of one step in one call (for callers that apply the received rows right away) */
 int sgl_p2p_route_step(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,

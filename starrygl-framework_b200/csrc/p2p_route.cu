@@ -1,16 +1,22 @@
 // Cache route over NVLink peer memory: pack + transfer in ONE kernel, no collective library call per step.
 //
 // Every rank owns a buffer that all ranks of the node map (CUDA IPC):
-//     flags[world][ring]   flags[q][slot] = step + 1 once sender q's rows of that step have landed here
 //     acks [world]         acks[p] = number of this rank's steps that receiver p has applied (written by p)
-//     stage[world][ring][cap_rows][pitch]   wire rows from sender q, ring slot = step % ring
+//     stage[world][ring][cap_rows][pitch / 2]   16-byte lines from sender q, ring slot = step % ring
+//
+// The wire row of a node is [features | ts | slot lo | slot hi | pad] (pitch 32-bit words, a multiple of 4), the same
+// row route_pack_kernel builds.  On the staging buffer every 16-byte line carries two data words and two copies of
+// the step's tag:  { w0, tag, w1, tag },  tag = (uint32)(step + 1).  The receiver polls the lines themselves until
+// both tags match, so the data needs no separate "rows have landed" flag: no fence, no arrival counter and no last
+// CTA on the sender, and the receiver starts on the first lines while the rest are still in flight.  (A line is
+// written with one 16-byte store; only 8-byte halves are assumed to arrive atomically, hence one tag per half.)  A
+// ring slot is reused every `ring` steps, and a line left from an earlier use carries that step's tag, never the
+// current one.
 //
 // send kernel (rank r, step s):  waits until every receiver has applied step s - ring (so the slot is free), builds
-//     the wire rows [features | ts | slot | pad] exactly like route_pack_kernel and stores them with 128-bit stores
-//     straight into the receivers' stage[r][s % ring] over NVLink; the last CTA to finish (fence + counter) publishes
-//     flags[r][s % ring] = s + 1 on every receiver.
-// recv kernel (rank p, step s):  waits for the flags of all senders, scatters the rows from its own stage into the
-//     node-state table (same work as route_unpack_kernel), then the last CTA acknowledges to every sender.
+//     the wire rows and stores the tagged lines straight into the receivers' stage[r][s % ring] over NVLink.
+// recv kernel (rank p, step s):  polls the lines of all senders, scatters the rows into the node-state table (same
+//     work as route_unpack_kernel); the last CTA to finish acknowledges the step to every sender.
 //
 // The two kernels of a step run on DIFFERENT GPUs (one process per GPU), never as two launches on one GPU.  Every
 // wait is bounded by a wall-clock limit; on expiry the kernel raises SGL_DEV_TIMEOUT in the status word, publishes
@@ -25,8 +31,7 @@ namespace sgl {
 namespace {
 
 constexpr int kMaxWorld = 16;
-constexpr int kThreads = 64;    // small CTAs: they fit into the register/thread gaps a busy GPU has left, so they start promptly
-constexpr int kUnroll = 4;   // lanes in flight per thread in the route kernels
+constexpr int kThreads = 128;   // 4 rows per CTA
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct P2PCfg {
@@ -34,13 +39,11 @@ struct P2PCfg {
   unsigned long long* tl;   // optional timeline buffer [steps][8] (diagnostics)
   int rank, world, ring;
   int64_t cap_rows;
-  uint32_t pitch;
-  unsigned long long* flags;
+  uint32_t pitch;           // 32-bit words per wire row; a row occupies pitch / 2 lines
   unsigned long long* acks;
-  float* stage;
-  unsigned long long* peer_flags[kMaxWorld];
+  uint4* stage;
   unsigned long long* peer_acks[kMaxWorld];
-  float* peer_stage[kMaxWorld];
+  uint4* peer_stage[kMaxWorld];
 };
 
 struct Splits {
@@ -49,7 +52,7 @@ struct Splits {
 
 struct Ctx {
   P2PCfg cfg;
-  unsigned int* counters;   // [2] device: arrival counters of the send / recv kernels
+  unsigned int* counters;   // device: arrival counter of the recv kernel
 };
 
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -57,6 +60,15 @@ __device__ __forceinline__ unsigned long long now_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+
+// Programmatic dependent launch: the route kernels of consecutive steps sit back to back in one stream.  A kernel
+// launched with the programmatic-serialization attribute may become resident while its predecessor still runs; it
+// blocks in pdl_wait() until the predecessor has completed and its writes are visible, so nothing below that call can
+// overtake the previous step.  pdl_release() (issued right after the wait) lets the NEXT kernel of the stream become
+// resident in turn -- at most one successor is ever waiting.  This takes the launch + CTA placement latency of a busy
+// GPU off the per-step chain.  Without a programmatic predecessor both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // spin until *p >= want; false when the limit expires
 __device__ __forceinline__ bool wait_at_least(const unsigned long long* p, unsigned long long want) {
@@ -67,6 +79,27 @@ __device__ __forceinline__ bool wait_at_least(const unsigned long long* p, unsig
     if (*vp >= want) return true;
     __nanosleep(200);
   }
+  return false;
+}
+
+__device__ __forceinline__ void store_line(uint4* p, uint32_t w0, uint32_t w1, uint32_t tag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(w0), "r"(tag), "r"(w1), "r"(tag) : "memory");
+}
+
+__device__ __forceinline__ uint4 load_line(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// re-reads a line until both halves carry the tag; false when the limit expires
+__device__ __noinline__ bool poll_line(const uint4* p, uint32_t tag, uint4* v) {
+  const unsigned long long t0 = now_ns();
+  do {
+    *v = load_line(p);
+    if (v->y == tag && v->w == tag) return true;
+    __nanosleep(100);
+  } while (now_ns() - t0 < kWaitLimitNs);
   return false;
 }
 
@@ -85,13 +118,19 @@ __device__ __forceinline__ int segment_of(const Splits& s, int world, int64_t i)
   return p;
 }
 
-template <int VEC>
+// A route kernel competes for issue slots with whatever else runs on its SM (warps are scheduled round robin, stream
+// priority only decides which CTA is placed first), so on a busy GPU its duration is set by its instruction count per
+// warp, not by memory latency.  Hence one WARP per row: the row's index, destination and segment are computed once
+// per row with no division, a lane handles a quad (4 consecutive wire words = 2 lines), and many small warps rather
+// than few long-running ones share the work.
 __global__ void __launch_bounds__(kThreads)
 p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint32_t dim, const float* __restrict__ ts,
                 const int64_t* __restrict__ send_idx, const int64_t* __restrict__ remote_idx, Splits seg,
-                unsigned long long step, unsigned int* done_counter, int32_t* d_status) {
+                unsigned long long step, int vec_ok, int32_t* d_status) {
   __shared__ int s_ok;
-  __shared__ bool s_last;
+  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 5] = now_ns();
+  pdl_wait();
+  pdl_release();
   if (threadIdx.x == 0) s_ok = 1;
   if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 0] = now_ns();
   __syncthreads();
@@ -100,176 +139,140 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
     if (!wait_at_least(c.acks + threadIdx.x, step - c.ring + 1)) s_ok = 0;
   }
   __syncthreads();
-  const bool ok = s_ok != 0;
-  if (ok) {
-    const int slot = (int)(step % c.ring);
-    const uint32_t payload = dim + (ts ? 1u : 0u);
-    const uint32_t lanes = c.pitch / VEC;
-    const int64_t n_send = seg.off[c.world];
-    const int64_t total = n_send * lanes;
-    const int64_t stride = (int64_t)gridDim.x * kThreads;
-    // kUnroll lanes per thread and iteration, in three phases (indices, rows, stores), so that the two dependent
-    // loads of every lane overlap with those of the other lanes: a small grid then moves a small message in about
-    // two memory latencies, and few CTAs have to find a free slot on a busy GPU
-    for (int64_t q0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; q0 < total; q0 += stride * kUnroll) {
-      int64_t row_i[kUnroll], src_r[kUnroll];
-      uint64_t slotv[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t q = q0 + u * stride;
-        row_i[u] = -1;
-        if (q < total) {
-          row_i[u] = q / lanes;
-          src_r[u] = __ldg(send_idx + row_i[u]);
-          slotv[u] = (uint64_t)__ldg(remote_idx + row_i[u]);
-        }
+  if (s_ok == 0) {
+    if (threadIdx.x == 0) dev_flag(d_status, SGL_DEV_TIMEOUT);
+    return;
+  }
+  const uint32_t tag = (uint32_t)(step + 1);
+  const uint32_t payload = dim + (ts ? 1u : 0u);
+  const uint32_t quads = c.pitch / 4;
+  const uint32_t lane = threadIdx.x & 31u;
+  const int64_t n_send = seg.off[c.world];
+  const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
+  const int64_t slot_base = ((int64_t)c.rank * c.ring + (int64_t)(step % c.ring)) * c.cap_rows;
+  for (int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i < n_send; i += n_warps) {
+    int64_t r = __ldg(send_idx + i);                       // one address per warp: a single broadcast load
+    const uint64_t slotv = (uint64_t)__ldg(remote_idx + i);
+    if (r < 0) r += n_rows;
+    const bool bad = r < 0 || r >= n_rows;
+    if (bad && lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
+    const int p = segment_of(seg, c.world, i);
+    uint4* dst = c.peer_stage[p] + (slot_base + (i - seg.off[p])) * (c.pitch / 2);
+    const float* frow = feats + r * dim;
+    for (uint32_t l = lane; l < quads; l += 32) {
+      uint4 v;
+      if (bad) {
+        // a row that cannot be read is sent as zeros with slot -1, which the receiver skips (and reports as well)
+        const uint32_t e = 4 * l;
+        v.x = (e + 0 == payload || e + 0 == payload + 1) ? 0xffffffffu : 0u;
+        v.y = (e + 1 == payload || e + 1 == payload + 1) ? 0xffffffffu : 0u;
+        v.z = (e + 2 == payload || e + 2 == payload + 1) ? 0xffffffffu : 0u;
+        v.w = (e + 3 == payload || e + 3 == payload + 1) ? 0xffffffffu : 0u;
+      } else if (vec_ok && (l + 1) * 4 <= dim) {
+        v = __ldg((const uint4*)frow + l);
+      } else {
+        v.x = wire_word2(4 * l + 0, dim, payload, frow, ts, r, slotv);
+        v.y = wire_word2(4 * l + 1, dim, payload, frow, ts, r, slotv);
+        v.z = wire_word2(4 * l + 2, dim, payload, frow, ts, r, slotv);
+        v.w = wire_word2(4 * l + 3, dim, payload, frow, ts, r, slotv);
       }
-      uint4 v[kUnroll];
-      void* dst[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        dst[u] = nullptr;
-        if (row_i[u] < 0) continue;
-        const int64_t i = row_i[u];
-        const uint32_t l = (uint32_t)(q0 + u * stride - i * lanes);
-        int64_t r = src_r[u];
-        if (r < 0) r += n_rows;
-        if (r < 0 || r >= n_rows) {
-          dev_flag(d_status, SGL_DEV_BAD_INDEX);
-          continue;
-        }
-        const int p = segment_of(seg, c.world, i);
-        float* dst_row = c.peer_stage[p] + (((int64_t)c.rank * c.ring + slot) * c.cap_rows + (i - seg.off[p])) * c.pitch;
-        const float* frow = feats + r * dim;
-        if (VEC == 4) {
-          if ((l + 1) * 4 <= dim) {
-            v[u] = __ldg((const uint4*)frow + l);
-          } else {
-            v[u].x = wire_word2(4 * l + 0, dim, payload, frow, ts, r, slotv[u]);
-            v[u].y = wire_word2(4 * l + 1, dim, payload, frow, ts, r, slotv[u]);
-            v[u].z = wire_word2(4 * l + 2, dim, payload, frow, ts, r, slotv[u]);
-            v[u].w = wire_word2(4 * l + 3, dim, payload, frow, ts, r, slotv[u]);
-          }
-          dst[u] = (uint4*)dst_row + l;
-        } else {
-          v[u].x = wire_word2(l, dim, payload, frow, ts, r, slotv[u]);
-          dst[u] = (uint32_t*)dst_row + l;
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (!dst[u]) continue;
-        if (VEC == 4) *(uint4*)dst[u] = v[u];
-        else *(uint32_t*)dst[u] = v[u].x;
-      }
+      store_line(dst + 2 * l, v.x, v.y, tag);
+      store_line(dst + 2 * l + 1, v.z, v.w, tag);
     }
-  } else if (threadIdx.x == 0) {
-    dev_flag(d_status, SGL_DEV_TIMEOUT);
   }
-  // publish.  One system-scope fence per CTA instead of one per thread: the CTA barrier makes every thread's stores
-  // happen-before thread 0's fence, and fences are cumulative, so thread 0's fence + counter increment orders the whole
-  // CTA's rows before anything the last CTA does after it has seen all increments.  (A system fence is expensive
-  // while the GPU streams other data; 20,000 of them per launch dominated this kernel's latency.)
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    unsigned prev = atomicAdd(done_counter, 1u);
-    s_last = prev == gridDim.x - 1;
-    if (s_last) __threadfence_system();
-  }
-  __syncthreads();
-  if (!s_last) return;
-  const bool failed = d_status && (*(volatile int32_t*)d_status & SGL_DEV_TIMEOUT);
-  if (threadIdx.x < c.world && !failed) {
-    volatile unsigned long long* f = c.peer_flags[threadIdx.x] + (int64_t)c.rank * c.ring + (step % c.ring);
-    *f = step + 1;
-  }
-  if (c.tl && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 1] = now_ns();
-  if (threadIdx.x == 0) *done_counter = 0;
+  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 1] = now_ns();
 }
 
-template <int VEC>
+// One warp per incoming row: every lane reads the line(s) holding the row's slot (one broadcast load per line) and
+// the 2 lines of its own quad, and re-polls (bounded) only what has not landed yet.
 __global__ void __launch_bounds__(kThreads)
 p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, int64_t data_rows, uint32_t dim,
-                float* __restrict__ ts_table, unsigned long long step, unsigned int* done_counter, int32_t* d_status) {
+                float* __restrict__ ts_table, unsigned long long step, int vec_ok, unsigned int* done_counter, int32_t* d_status) {
   __shared__ int s_ok;
   __shared__ bool s_last;
+  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 6] = now_ns();
+  pdl_wait();
+  pdl_release();
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
-  const int slot = (int)(step % c.ring);
   if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 2] = now_ns();
-  if (threadIdx.x < c.world) {
-    if (!wait_at_least(c.flags + (int64_t)threadIdx.x * c.ring + slot, step + 1)) s_ok = 0;
-    __threadfence_system();   // acquire side: the rows written before the flag are visible after this fence ...
-  }
-  __syncthreads();            // ... and, through the barrier, to every thread of the CTA
-  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 3] = now_ns();
-  const bool ok = s_ok != 0;
-  if (ok) {
-    const uint32_t lanes = (width + VEC - 1) / VEC;
-    const int64_t n_recv = seg.off[c.world];
-    const int64_t total = n_recv * lanes;
-    const int64_t stride = (int64_t)gridDim.x * kThreads;
-    for (int64_t q0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; q0 < total; q0 += stride * kUnroll) {
-      // plain loads throughout: the stage was written by another GPU, the read-only cache must not be used for it
-      uint4 v[kUnroll];
-      int64_t dslot[kUnroll];
-      uint32_t lane_l[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t q = q0 + u * stride;
-        dslot[u] = -1;
-        if (q >= total) continue;
-        const int64_t i = q / lanes;
-        const uint32_t l = (uint32_t)(q - i * lanes);
-        const int sdr = segment_of(seg, c.world, i);
-        const uint32_t* row = (const uint32_t*)(c.stage + (((int64_t)sdr * c.ring + slot) * c.cap_rows + (i - seg.off[sdr])) * c.pitch);
-        dslot[u] = (int64_t)((uint64_t)row[width] | ((uint64_t)row[width + 1] << 32));
-        lane_l[u] = l;
-        if (VEC == 4) v[u] = ((const uint4*)row)[l];
-        else v[u].x = row[l];
-        if (dslot[u] < 0 || dslot[u] >= data_rows) {
-          dev_flag(d_status, SGL_DEV_BAD_INDEX);
-          dslot[u] = -1;
-        }
+  if (c.tl && threadIdx.x == 0 && step < 4096) atomicMax(c.tl + step * 8 + 7, now_ns());   // start of the latest CTA
+  const uint32_t tag = (uint32_t)(step + 1);
+  const uint32_t quads = (width + 3) / 4;                // quads that hold features / ts
+  const uint32_t la = width / 2, lb = (width + 1) / 2;   // lines of the slot's low and high word
+  const uint32_t lane = threadIdx.x & 31u;
+  const int64_t n_recv = seg.off[c.world];
+  const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
+  const int64_t ring_slot = (int64_t)(step % c.ring);
+  bool ok = true;
+  for (int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i < n_recv && ok; i += n_warps) {
+    const int sdr = segment_of(seg, c.world, i);
+    const uint4* row = c.stage + (((int64_t)sdr * c.ring + ring_slot) * c.cap_rows + (i - seg.off[sdr])) * (c.pitch / 2);
+    // all loads in flight first; the rows have normally landed long ago
+    uint4 sa = load_line(row + la);
+    uint4 sb = la == lb ? sa : load_line(row + lb);
+    uint4 a = make_uint4(0, tag, 0, tag), b = a;
+    if (lane < quads) {
+      a = load_line(row + 2 * lane);
+      b = load_line(row + 2 * lane + 1);
+    }
+    if (sa.y != tag || sa.w != tag) ok = ok && poll_line(row + la, tag, &sa);
+    if (la == lb) sb = sa;
+    else if (sb.y != tag || sb.w != tag) ok = ok && poll_line(row + lb, tag, &sb);
+    if (!ok) break;
+    const uint32_t lo = (width & 1) ? sa.z : sa.x;
+    const uint32_t hi = ((width + 1) & 1) ? sb.z : sb.x;
+    const int64_t dslot = (int64_t)((uint64_t)lo | ((uint64_t)hi << 32));
+    const bool bad = dslot < 0 || dslot >= data_rows;
+    if (bad && lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
+    for (uint32_t l = lane; l < quads; l += 32) {
+      if (l != lane) {
+        a = load_line(row + 2 * l);
+        b = load_line(row + 2 * l + 1);
       }
+      if (a.y != tag || a.w != tag) ok = ok && poll_line(row + 2 * l, tag, &a);
+      if (b.y != tag || b.w != tag) ok = ok && poll_line(row + 2 * l + 1, tag, &b);
+      if (!ok || bad) break;
+      if (vec_ok && (l + 1) * 4 <= dim) {
+        ((uint4*)(data + dslot * dim))[l] = make_uint4(a.x, a.z, b.x, b.z);
+      } else {
+        const uint32_t w[4] = {a.x, a.z, b.x, b.z};
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (dslot[u] < 0) continue;
-        const uint32_t l = lane_l[u];
-        if (VEC == 4) {
-          if ((l + 1) * 4 <= dim) ((uint4*)(data + dslot[u] * dim))[l] = v[u];
-          else if (ts_table) ts_table[dslot[u]] = __uint_as_float(v[u].x);
-        } else {
-          if (l < dim) data[dslot[u] * dim + l] = __uint_as_float(v[u].x);
-          else if (ts_table) ts_table[dslot[u]] = __uint_as_float(v[u].x);
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t e = 4 * l + k;
+          if (e < dim) data[dslot * dim + e] = __uint_as_float(w[k]);
+          else if (e < width && ts_table) ts_table[dslot] = __uint_as_float(w[k]);
         }
       }
     }
-  } else if (threadIdx.x == 0) {
+  }
+  if (!ok) {
+    s_ok = 0;
     dev_flag(d_status, SGL_DEV_TIMEOUT);
   }
-  // all reads of the staging slot are done before the senders are told they may overwrite it (same one-fence-per-CTA
-  // pattern as in the send kernel)
+  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 3] = now_ns();
+  // Acknowledge once every CTA has read its lines.  A thread reaches the barrier only after the values of its polls
+  // have been examined, so its loads of the slot are complete by then; the counter is incremented after the CTA's
+  // barrier and the acknowledgement is stored after the last increment, so no load of this step can still be in
+  // flight when a sender sees the acknowledgement.  No fence is needed for that: nothing this kernel WRITES has to
+  // be visible to the senders (the table it writes is read by later kernels of this stream only).
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
     unsigned prev = atomicAdd(done_counter, 1u);
     s_last = prev == gridDim.x - 1;
-    if (s_last) __threadfence_system();
   }
   __syncthreads();
   if (!s_last) return;
-  const bool failed = d_status && (*(volatile int32_t*)d_status & SGL_DEV_TIMEOUT);
+  const bool failed = s_ok == 0 || (d_status && (*(volatile int32_t*)d_status & SGL_DEV_TIMEOUT));
   if (threadIdx.x < c.world && !failed) {
-    volatile unsigned long long* a = c.peer_acks[threadIdx.x] + c.rank;   // "rank has applied your step"
-    *a = step + 1;
+    volatile unsigned long long* ak = c.peer_acks[threadIdx.x] + c.rank;   // "rank has applied your step"
+    *ak = step + 1;
   }
   if (c.tl && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 4] = now_ns();
   if (threadIdx.x == 0) *done_counter = 0;
 }
 
-inline size_t header_bytes(int world, int ring) { return align_up((size_t)world * ring * 8 + (size_t)world * 8, 256); }
+inline size_t header_bytes(int world) { return align_up((size_t)world * 8, 256); }
 
 }  // namespace
 }  // namespace sgl
@@ -278,7 +281,9 @@ using namespace sgl;
 
 extern "C" size_t sgl_p2p_buffer_bytes(int world, int ring, int64_t cap_rows, int64_t pitch_floats) {
   if (world < 1 || ring < 1 || cap_rows < 0 || pitch_floats < 1) return 0;
-  return header_bytes(world, ring) + (size_t)world * ring * (size_t)cap_rows * (size_t)pitch_floats * 4;
+  if (pitch_floats % 4) return 0;
+  // every 16-byte line holds two wire words and two tags: twice the bytes of the plain wire rows
+  return header_bytes(world) + (size_t)world * ring * (size_t)cap_rows * (size_t)pitch_floats * 8;
 }
 
 extern "C" int sgl_p2p_alloc(size_t bytes, void** out_ptr, char* out_handle, size_t handle_bytes) {
@@ -315,21 +320,19 @@ extern "C" int sgl_p2p_free(void* ptr) {
 extern "C" int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_rows, int64_t pitch_floats,
                                     void* const* h_bases, void** out_ctx) {
   SGL_REQUIRE(out_ctx && h_bases && world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world && ring >= 2 &&
-                  cap_rows >= 1 && pitch_floats >= 1,
-              SGL_ERR_ARG, "p2p_route_create: bad argument (world <= %d, ring >= 2)", kMaxWorld);
+                  cap_rows >= 1 && pitch_floats >= 4 && pitch_floats % 4 == 0,
+              SGL_ERR_ARG, "p2p_route_create: bad argument (world <= %d, ring >= 2, pitch a multiple of 4)", kMaxWorld);
   Ctx* x = new Ctx();
   P2PCfg& c = x->cfg;
   c.dbg = getenv("SGL_P2P_DBG") ? atoi(getenv("SGL_P2P_DBG")) : 0;   // 2 = record a per-step kernel timeline (diagnostics)
   c.rank = rank; c.world = world; c.ring = ring; c.cap_rows = cap_rows; c.pitch = (uint32_t)pitch_floats;
-  const size_t hb = header_bytes(world, ring);
+  const size_t hb = header_bytes(world);
   for (int p = 0; p < world; ++p) {
     SGL_REQUIRE(h_bases[p], SGL_ERR_ARG, "p2p_route_create: base pointer of rank %d is null", p);
     char* b = (char*)h_bases[p];
-    c.peer_flags[p] = (unsigned long long*)b;
-    c.peer_acks[p] = (unsigned long long*)b + (size_t)world * ring;
-    c.peer_stage[p] = (float*)(b + hb);
+    c.peer_acks[p] = (unsigned long long*)b;
+    c.peer_stage[p] = (uint4*)(b + hb);
   }
-  c.flags = c.peer_flags[rank];
   c.acks = c.peer_acks[rank];
   c.stage = c.peer_stage[rank];
   SGL_CUDA_CHECK(cudaMalloc(&x->counters, 256));
@@ -353,15 +356,36 @@ extern "C" int sgl_p2p_route_destroy(void* ctx) {
 
 // number of CTAs of a route kernel: enough for the rows, capped (SGL_P2P_MAX_CTAS, tuning aid) -- small messages are
 // latency-bound and every extra CTA adds fence traffic and a longer wait for the last one
-static int p2p_grid(int64_t lanes_total) {
+static int p2p_grid(int64_t rows) {
   static int cap = -1;
   if (cap < 0) {
     const char* e = getenv("SGL_P2P_MAX_CTAS");
     cap = e ? atoi(e) : kNumSM * 8;
     if (cap < 1) cap = 1;
   }
-  int g = stream_grid(lanes_total, kThreads * kUnroll, 8);
+  int g = stream_grid(rows, kThreads / 32, 8);
   return g < cap ? g : cap;
+}
+
+// launch with the programmatic-serialization attribute (see pdl_wait); SGL_P2P_PDL=0 turns it off (tuning aid)
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, cudaStream_t stream, Args... args) {
+  static int pdl = -1;
+  if (pdl < 0) {
+    const char* e = getenv("SGL_P2P_PDL");
+    pdl = e ? atoi(e) : 1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 static int make_splits(const Ctx* x, const int64_t* h_rows, Splits* s, const char* what) {
@@ -389,16 +413,10 @@ extern "C" int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows,
               (long long)pitch, x->cfg.pitch);
   SGL_REQUIRE(n_send == 0 || (feats && send_idx && remote_idx), SGL_ERR_ARG, "p2p_route_send: null array");
   cudaStream_t stream = (cudaStream_t)stream_;
-  const bool vec = dim % 4 == 0 && ((uintptr_t)feats & 15) == 0;
-  if (vec) {
-    const int grid = p2p_grid(n_send * (pitch / 4));
-    p2p_send_kernel<4><<<grid, kThreads, 0, stream>>>(x->cfg, feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, seg, step,
-                                                     x->counters, d_status);
-  } else {
-    const int grid = p2p_grid(n_send * pitch);
-    p2p_send_kernel<1><<<grid, kThreads, 0, stream>>>(x->cfg, feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, seg, step,
-                                                     x->counters, d_status);
-  }
+  const int vec_ok = dim % 4 == 0 && ((uintptr_t)feats & 15) == 0;
+  const int grid = p2p_grid(n_send);
+  SGL_CUDA_CHECK(launch_pdl(p2p_send_kernel, grid, stream, x->cfg, feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, seg,
+                            (unsigned long long)step, vec_ok, d_status));
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }
@@ -416,16 +434,10 @@ extern "C" int sgl_p2p_route_recv(void* ctx, const int64_t* h_recv_rows, float* 
   SGL_REQUIRE(sgl_wire_pitch(dim, has_ts, 1) == x->cfg.pitch, SGL_ERR_ARG, "p2p_route_recv: wire pitch differs from the context's");
   SGL_REQUIRE(n_recv == 0 || data, SGL_ERR_ARG, "p2p_route_recv: null table");
   cudaStream_t stream = (cudaStream_t)stream_;
-  const bool vec = dim % 4 == 0 && ((uintptr_t)data & 15) == 0;
-  if (vec) {
-    const int grid = p2p_grid(n_recv * ((width + 3) / 4));
-    p2p_recv_kernel<4><<<grid, kThreads, 0, stream>>>(x->cfg, seg, (uint32_t)width, data, data_rows, (uint32_t)dim, ts_table,
-                                                     step, x->counters + 32, d_status);
-  } else {
-    const int grid = p2p_grid(n_recv * width);
-    p2p_recv_kernel<1><<<grid, kThreads, 0, stream>>>(x->cfg, seg, (uint32_t)width, data, data_rows, (uint32_t)dim, ts_table,
-                                                     step, x->counters + 32, d_status);
-  }
+  const int vec_ok = dim % 4 == 0 && ((uintptr_t)data & 15) == 0;
+  const int grid = p2p_grid(n_recv);
+  SGL_CUDA_CHECK(launch_pdl(p2p_recv_kernel, grid, stream, x->cfg, seg, (uint32_t)width, data, data_rows, (uint32_t)dim,
+                            has_ts ? ts_table : (float*)nullptr, (unsigned long long)step, vec_ok, x->counters, d_status));
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }
@@ -439,7 +451,8 @@ extern "C" int sgl_p2p_route_step(void* ctx, const float* feats, int64_t n_rows,
   return sgl_p2p_route_recv(ctx, h_recv_rows, data, data_rows, dim, ts != nullptr, ts_table, step, d_status, stream);
 }
 
-// diagnostics: copies the per-step kernel timeline (ns; send start/end, apply start/flags seen/end) to the host
+// diagnostics: copies the per-step kernel timeline to the host (ns; words 0/1 send start/end, 2/3/4 apply start / CTA 0's
+// rows applied / end, 5/6 send / apply kernel resident)
 extern "C" int sgl_p2p_route_timeline(void* ctx, unsigned long long* h_out, int64_t steps) {
   Ctx* x = (Ctx*)ctx;
   SGL_REQUIRE(x && x->cfg.tl && h_out && steps <= 4096, SGL_ERR_ARG, "p2p_route_timeline: not enabled (SGL_P2P_DBG=2)");

@@ -158,6 +158,31 @@ def _worker_p2p(rank, world, port, q):
         route.status.check("p2p route ring")
         ok_ring = torch.equal(state2.data.cpu(), ref_d) and torch.equal(state2.ts.cpu(), ref_t)
         route.close()
+
+        # (3) row widths whose slot words fall on every position of a 16-byte staging line, with and without timestamps
+        for D3, has_ts in ((7, True), (6, True), (5, False), (8, False), (1, True)):
+            route = P2PCacheRoute(D3, has_ts, cap_rows=K, ring=2)
+            st3 = DistNodeState(ps2, D3, device=dev)
+            f3 = [torch.randn(N, D3, generator=torch.Generator().manual_seed(90 + r + D3)) for r in range(world)]
+            t3 = [torch.rand(N, generator=torch.Generator().manual_seed(95 + r + D3)) for r in range(world)]
+            r_d, r_t = torch.zeros(N, D3), torch.zeros(N)
+            for step in range(5):
+                sizes, idx, slots = plan_of(step + 100 * D3, rank)
+                pl = CommPlan(send_ranks=torch.repeat_interleave(torch.arange(world), sizes), send_sizes=sizes, send_indices=idx,
+                              send_remote_indices=slots)
+                pl.recv_sizes = [int(plan_of(step + 100 * D3, s)[0][rank]) for s in range(world)]
+                route.push(f3[rank].to(dev), pl, st3, t3[rank].to(dev) if has_ts else None).wait()
+                for s in range(world):
+                    sz, ix, sl = plan_of(step + 100 * D3, s)
+                    off = int(sz[:rank].sum())
+                    seg = slice(off, off + int(sz[rank]))
+                    r_d[sl[seg]] = f3[s][ix[seg]]
+                    if has_ts:
+                        r_t[sl[seg]] = t3[s][ix[seg]]
+            torch.cuda.synchronize()
+            route.status.check("p2p route widths")
+            ok_ring = ok_ring and torch.equal(st3.data.cpu(), r_d) and torch.equal(st3.ts.cpu(), r_t)
+            route.close()
         q.put((rank, ok_golden, ok_ring, True, None))
         dist.barrier()
         DistributedContext.shutdown()
