@@ -354,6 +354,36 @@ int sgl_replica_lookup(const int64_t* indptr, const int64_t* ranks, const int64_
                        void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Mailbox update of a mini-batch: latest message per node + row assembly, and the write into the mailbox.
+ *
+ * sgl_mail_reduce: entries = ids_a[n_a] followed by ids_b[n_b] (the batch's source nodes, then its destination
+ * nodes); entry j has timestamp ts[j] (ts_len == n_a + n_b) or ts[j mod ts_len] (ts_len == n_a == n_b: one value
+ * per event, used for both ends); ts is int64 (ts_is_i64) or fp32 and is compared as fp32.  For every distinct
+ * node id (ascending in out_index) the entry with the largest timestamp wins, the first such entry on ties.
+ * Outputs (capacity n_a + n_b, valid length *d_num_unique): out_index, out_pos (winning entry, optional), out_ts
+ * (optional), out_mail (optional): row u = concatenation of n_seg segments (at most 4), segment s read from
+ * seg_a[s][pos * seg_dim[s] ...] when the winner pos is an entry of the first list, else from
+ * seg_b[s][(pos - n_a) * seg_dim[s] ...]; the seg_* arrays are HOST arrays of device pointers / sizes.
+ * The per-entry mail matrix of the reference is never built.
+ * Replaces: mailbox.get_update_mail (starrygl/nn/memory/mailbox.py:56-84: cat, unique, torch_scatter.scatter_max,
+ * index) and the 'max' reduce at the head of mailbox.set_mailbox_local (:41-47).
+ *
+ * sgl_mailbox_write: mailbox[index[u], next_mail_pos[index[u]], :] = mail[u, :], mailbox_ts likewise, and (advance
+ * != 0, mailbox_size > 1) next_mail_pos[index[u]] = (pos + 1) mod mailbox_size.  index must hold distinct nodes
+ * (the output of the reduce).  mailbox is [num_nodes, mailbox_size, width] fp32, mailbox_ts [num_nodes,
+ * mailbox_size] fp32, next_mail_pos [num_nodes] int64 (may be null when mailbox_size == 1).
+ * Replaces: the writes of mailbox.set_mailbox_local (starrygl/nn/memory/mailbox.py:49-54).
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_mail_reduce_ws_bytes(int64_t n_entries);
+int sgl_mail_reduce(const int64_t* ids_a, int64_t n_a, const int64_t* ids_b, int64_t n_b, int64_t num_nodes, const void* ts,
+                    int64_t ts_len, int ts_is_i64, int n_seg, const float* const* seg_a, const float* const* seg_b,
+                    const int64_t* seg_dim, int64_t* out_index, int64_t* out_pos, float* out_ts, float* out_mail,
+                    int64_t* d_num_unique, int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
+int sgl_mailbox_write(const int64_t* index, int64_t n, const int64_t* d_n, const float* mail, const float* mail_ts,
+                      int64_t width, float* mailbox, float* mailbox_ts, int64_t* next_mail_pos, int64_t num_nodes,
+                      int64_t mailbox_size, int advance, int32_t* d_status, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Route plan of one layer: which rows of the layer's node list this partition pushes to which other ranks.
  * layer_ids[n] = node ids of the layer list, sorted (rows of one node adjacent, latest timestamp last -- the
  * (id, ts) order of sgl_unique_pairs).  For every node owned here (node_parts[id] == pid) the LAST row of its run

@@ -21,6 +21,7 @@ Reference locations restated (paths inside the reference project):
 * replica lookup                   starrygl/cache/replica_table.py:16-82, :178-215
 * cache route                      starrygl/cache/cache_route.py:211-277, starrygl/cache/NodeState.py:245-282
 * halo route                       starrygl/route/route.py:427-466
+* mailbox update                   starrygl/nn/memory/mailbox.py:41-84
 """
 import numpy as np
 
@@ -407,3 +408,63 @@ def compute_layer_route(layer_ids, layer_ts, node_parts, pid, rep_indptr, rep_ra
     order = np.lexsort((rows, ranks))          # by rank, then list row (stable, ascending)
     sizes = np.bincount(ranks, minlength=num_parts).astype(I64)
     return ranks[order], sizes, rows[order], locs[order]
+
+
+# ----------------------------------------------------------------------------------------------
+# mailbox update
+# ----------------------------------------------------------------------------------------------
+
+
+def scatter_max_first(values, groups, n_groups):
+    """Per group the maximum and the position of its FIRST occurrence (the sequential strict-greater update of a CPU
+    scatter-max; the reference calls ``torch_scatter.scatter_max``, whose GPU kernel leaves ties unordered)."""
+    best = np.full(n_groups, -np.inf, dtype=np.float64)
+    arg = np.full(n_groups, -1, dtype=I64)
+    for j in range(len(values)):
+        g = groups[j]
+        if arg[g] < 0 or values[j] > best[g]:
+            best[g], arg[g] = values[j], j
+    return arg
+
+
+def get_update_mail(src, dst, ts, edge_feats, mem_src, mem_dst, embedding=None, use_src_emb=False, use_dst_emb=False):
+    """starrygl/nn/memory/mailbox.py:56-84: index = cat(src, dst); one mail row per entry
+    ``[own | other | edge feature]``; timestamps cat(ts, ts) as fp32; per distinct node (ascending) the entry with the
+    largest timestamp.  Returns (index, mail, mail_ts)."""
+    src, dst = np.asarray(src, I64), np.asarray(dst, I64)
+    n = len(src)
+    emb_src = emb_dst = None
+    if embedding is not None:
+        emb_src, emb_dst = embedding[:n], embedding[n:]
+    src_mail = np.concatenate([emb_src if use_src_emb else mem_src, emb_dst if use_dst_emb else mem_dst], 1)
+    dst_mail = np.concatenate([emb_dst if use_src_emb else mem_dst, emb_src if use_dst_emb else mem_src], 1)
+    if edge_feats is not None:
+        src_mail = np.concatenate([src_mail, edge_feats], 1)
+        dst_mail = np.concatenate([dst_mail, edge_feats], 1)
+    mail = np.concatenate([src_mail, dst_mail], 0).astype(np.float32)
+    mail_ts = np.concatenate([ts, ts]).astype(np.float32)
+    index = np.concatenate([src, dst])
+    uniq, inv = np.unique(index, return_inverse=True)
+    arg = scatter_max_first(mail_ts, inv.reshape(-1), len(uniq))
+    return uniq.astype(I64), mail[arg], mail_ts[arg]
+
+
+def reduce_max_rows(index, rows, ts):
+    """Head of mailbox.set_mailbox_local with Reduce_Op == 'max' (starrygl/nn/memory/mailbox.py:41-47)."""
+    index = np.asarray(index, I64)
+    ts32 = np.asarray(ts).astype(np.float32)
+    uniq, inv = np.unique(index, return_inverse=True)
+    arg = scatter_max_first(ts32, inv.reshape(-1), len(uniq))
+    return uniq.astype(I64), rows[arg], ts32[arg]
+
+
+def mailbox_write(mailbox, mailbox_ts, next_pos, index, rows, ts):
+    """starrygl/nn/memory/mailbox.py:49-54 (in place): slot = next_mail_pos[index]; the position advances modulo the
+    slot count when there is more than one slot."""
+    index = np.asarray(index, I64)
+    slots = mailbox.shape[1]
+    p = next_pos[index]
+    mailbox_ts[index, p] = np.asarray(ts).astype(np.float32)
+    mailbox[index, p] = rows
+    if slots > 1:
+        next_pos[index] = (p + 1) % slots

@@ -81,6 +81,10 @@ _SIGNATURES = {
     "sgl_plan_route_ws_bytes": (_sz, [_i64, _i64]),
     "sgl_plan_route": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                               _sz, _vp]),
+    "sgl_mail_reduce_ws_bytes": (_sz, [_i64]),
+    "sgl_mail_reduce": (_i32, [_vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                               _sz, _vp]),
+    "sgl_mailbox_write": (_i32, [_vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp]),
     "sgl_graph_capture_begin": (_i32, [_vp]),
     "sgl_graph_capture_end": (_i32, [_vp, C.POINTER(C.c_void_p)]),
     "sgl_graph_launch": (_i32, [_vp, _vp, _vp, _sz, _vp]),

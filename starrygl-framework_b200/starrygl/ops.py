@@ -467,3 +467,72 @@ def plan_route(layer_ids, node_parts, pid: int, rep_indptr, rep_ranks, rep_locs,
                               _C.ptr(rows), _C.ptr(locs), _C.ptr(sizes), _C.ptr(total), status.ptr() if status else None, wp, wn,
                               _C.stream_ptr()))
     return ranks, rows, locs, sizes, total
+
+
+# --------------------------------------------------------------------------------------------------------------
+# mailbox update
+# --------------------------------------------------------------------------------------------------------------
+
+def mail_reduce(ids_a, ids_b, ts, num_nodes: int, segments=(), *, want_pos: bool = False,
+                status: Optional[StatusWord] = None):
+    """Latest message per node (see ``sgl_mail_reduce``).  ``ids_a`` / ``ids_b``: int64 node ids of the two entry lists
+    (``ids_b`` may be None); ``ts``: int64 or fp32, one value per entry or one per event; ``segments``: list of
+    ``(table_a, table_b)`` fp32 row tables whose rows are concatenated into the mail of the winning entry.
+    Returns ``(index, mail, mail_ts, pos, d_num_unique)`` with capacity ``len(ids_a) + len(ids_b)``; the valid
+    length is the device scalar ``d_num_unique`` (no synchronisation here).  ``mail`` is None without segments."""
+    L = _C.lib()
+    ids_a = _i64(ids_a)
+    dev = ids_a.device
+    n_a = ids_a.numel()
+    ids_b = _i64(ids_b) if ids_b is not None else None
+    n_b = ids_b.numel() if ids_b is not None else 0
+    n = n_a + n_b
+    if ts.dtype not in (torch.int64, torch.float32):
+        raise _C.SglError(f"mail_reduce: timestamps must be int64 or float32, got {ts.dtype}")
+    ts = ts.contiguous()
+    segs = []
+    for ta, tb in segments:
+        ta = ta.contiguous()
+        tb = ta if tb is None else tb.contiguous()
+        if ta.dtype != torch.float32 or tb.dtype != torch.float32 or ta.dim() != 2 or tb.shape[1:] != ta.shape[1:]:
+            raise _C.SglError("mail_reduce: segments are pairs of fp32 [rows, dim] tables of equal width")
+        if ta.shape[0] < n_a or (n_b and tb.shape[0] < n_b):
+            raise _C.SglError("mail_reduce: a segment table has fewer rows than its entry list")
+        segs.append((ta, tb))
+    width = sum(int(a.shape[1]) for a, _ in segs)
+    cap = max(n, 1)
+    index = torch.empty(cap, dtype=I64, device=dev)
+    pos = torch.empty(cap, dtype=I64, device=dev) if want_pos else None
+    out_ts = torch.empty(cap, dtype=torch.float32, device=dev)
+    mail = torch.empty((cap, width), dtype=torch.float32, device=dev) if segs else None
+    d_u = torch.zeros(1, dtype=I64, device=dev)
+    k = len(segs)
+    arr_a = (C.c_void_p * max(k, 1))(*[a.data_ptr() for a, _ in segs])
+    arr_b = (C.c_void_p * max(k, 1))(*[b.data_ptr() for _, b in segs])
+    arr_d = (C.c_int64 * max(k, 1))(*[int(a.shape[1]) for a, _ in segs])
+    _, wp, wn = _C.workspace(L.sgl_mail_reduce_ws_bytes(n), dev)
+    _C.check(L.sgl_mail_reduce(_C.ptr(ids_a), n_a, _C.ptr(ids_b) if n_b else None, n_b, int(num_nodes), _C.ptr(ts), ts.numel(),
+                               1 if ts.dtype == torch.int64 else 0, k, C.cast(arr_a, C.c_void_p), C.cast(arr_b, C.c_void_p),
+                               C.cast(arr_d, C.c_void_p), _C.ptr(index), _C.ptr(pos) if want_pos else None, _C.ptr(out_ts),
+                               _C.ptr(mail) if mail is not None else None, _C.ptr(d_u), status.ptr() if status else None,
+                               wp, wn, _C.stream_ptr()))
+    return index, mail, out_ts, pos, d_u
+
+
+def mailbox_write(index, mail, mail_ts, mailbox, mailbox_ts, next_mail_pos, *, d_n=None, advance: bool = True,
+                  status: Optional[StatusWord] = None):
+    """``mailbox[index, next_mail_pos[index]] = mail`` (+ timestamps, + ring position), see ``sgl_mailbox_write``.
+    ``index`` must hold distinct nodes.  With ``d_n`` (device int64) only the first ``*d_n`` rows are written."""
+    L = _C.lib()
+    index = _i64(index)
+    if mailbox.dim() != 3 or not mailbox.is_contiguous() or not mailbox_ts.is_contiguous():
+        raise _C.SglError("mailbox_write: mailbox must be a contiguous [nodes, slots, width] tensor")
+    nodes, slots, width = mailbox.shape
+    if mail.dim() != 2 or mail.shape[1] != width or mail.dtype != torch.float32 or mail_ts.dtype != torch.float32:
+        raise _C.SglError("mailbox_write: mail rows must be fp32 of the mailbox's width")
+    if next_mail_pos is not None:
+        next_mail_pos = _i64(next_mail_pos)
+    n = min(index.numel(), mail.shape[0])
+    _C.check(L.sgl_mailbox_write(_C.ptr(index), n, _C.ptr(d_n), _C.ptr(mail.contiguous()), _C.ptr(mail_ts.contiguous()), width,
+                                 _C.ptr(mailbox), _C.ptr(mailbox_ts), _C.ptr(next_mail_pos) if next_mail_pos is not None else None,
+                                 nodes, slots, 1 if advance else 0, status.ptr() if status else None, _C.stream_ptr()))

@@ -20,6 +20,9 @@ What is pinned, and the reference code that produced it:
   ``Route.forward`` forward/backward over a 2-rank gloo group
   (starrygl/cache/cache_route.py:211-277, starrygl/route/route.py:427-466).
 * ``plan.npz``        -- ``_compute_layer_route`` (prepare_sample.py:266-310) for every partition of a 4-way split.
+* ``mail.npz``        -- ``mailbox.get_update_mail`` (starrygl/nn/memory/mailbox.py:56-84) on batches with distinct
+  timestamps per node entry (``torch_scatter`` is absent: its ``scatter_max`` is a torch restatement, so the tie case
+  stored beside them is defined by that restatement, not by the reference).
 * ``nodestate.npz``   -- ``DistNodeState.update`` / ``__getitem__`` with ``node_mode='map'``
   (starrygl/cache/NodeState.py:36-61, starrygl/utils/partition_book.py:98-133).
 """
@@ -351,6 +354,60 @@ def gen_plan(ref, out):
     np.savez_compressed(os.path.join(out, "plan.npz"), **rec)
 
 
+def gen_mail(ref, out):
+    """Runs the reference's ``mailbox.get_update_mail`` on CPU tensors."""
+    import torch
+    sys.path.insert(0, ref)
+
+    def scatter_max(src, index, dim=0):
+        n = int(index.max()) + 1 if index.numel() else 0
+        mx = torch.full((n,), -float("inf"), dtype=src.dtype).scatter_reduce(0, index, src, "amax")
+        is_max = src == mx[index]
+        pos = torch.where(is_max, torch.arange(len(src)), torch.full((len(src),), len(src)))
+        arg = torch.full((n,), len(src), dtype=torch.long).scatter_reduce(0, index, pos, "amin")
+        return mx, arg
+    _stub("torch_scatter", scatter_max=scatter_max)
+    ctx = _stub("starrygl.utils.context", DistributedContext=object)
+    _stub("starrygl.utils", context=ctx)
+    _stub("starrygl", utils=sys.modules["starrygl.utils"])
+    spec = importlib.util.spec_from_file_location("ref_mailbox", os.path.join(ref, "starrygl", "nn", "memory", "mailbox.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    rng = np.random.default_rng(31)
+    rec = {}
+    for case, (n_nodes, B, D, E, ties, emb) in enumerate([(50, 40, 8, 5, False, 0), (2000, 300, 32, 172, False, 0),
+                                                         (300, 200, 16, 0, False, 1), (300, 200, 16, 7, False, 2),
+                                                         (30, 120, 4, 3, True, 0)]):
+        mb = mod.mailbox(n_nodes, 1, D, E)
+        half = n_nodes // 2
+        src = rng.integers(0, half, B)
+        dst = rng.integers(half, n_nodes, B)           # bipartite: an event never has the same node at both ends
+        ts = rng.integers(0, 50, B) if ties else rng.permutation(100000)[:B]
+        ts = np.sort(ts).astype(np.int64)
+        mem_src = rng.standard_normal((B, D)).astype(np.float32)
+        mem_dst = rng.standard_normal((B, D)).astype(np.float32)
+        ef = rng.standard_normal((B, E)).astype(np.float32) if E else None
+        embedding = rng.standard_normal((2 * B, D)).astype(np.float32) if emb else None
+        kw = {}
+        if emb:
+            kw = dict(embedding=torch.from_numpy(embedding), use_src_emb=emb >= 1, use_dst_emb=emb >= 2)
+        index, mail, mail_ts = mb.get_update_mail(torch.from_numpy(src), torch.from_numpy(dst), torch.from_numpy(ts),
+                                                  torch.from_numpy(ef) if E else None, torch.from_numpy(mem_src),
+                                                  torch.from_numpy(mem_dst), **kw)
+        t = f"c{case}"
+        rec.update({f"{t}_n_nodes": np.int64(n_nodes), f"{t}_src": src, f"{t}_dst": dst, f"{t}_ts": ts, f"{t}_mem_src": mem_src,
+                    f"{t}_mem_dst": mem_dst, f"{t}_ties": np.int64(ties), f"{t}_emb": np.int64(emb),
+                    f"{t}_index": index.numpy(), f"{t}_mail": mail.numpy(), f"{t}_mail_ts": mail_ts.numpy()})
+        if E:
+            rec[f"{t}_ef"] = ef
+        if emb:
+            rec[f"{t}_embedding"] = embedding
+    rec["n_cases"] = np.int64(5)
+    np.savez_compressed(os.path.join(out, "mail.npz"), **rec)
+    for k in [k for k in sys.modules if k == "starrygl" or k.startswith("starrygl.")]:
+        del sys.modules[k]
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
@@ -366,4 +423,6 @@ if __name__ == "__main__":
         gen_ids(a.reference, HERE)
     if a.only in ("all", "plan"):
         gen_plan(a.reference, HERE)
+    if a.only in ("all", "mail"):
+        gen_mail(a.reference, HERE)
     print("golden vectors written to", HERE)

@@ -202,3 +202,35 @@ def test_route_plan_matches_reference():
         got = O.compute_layer_route(z[f"{tag}_ids"], z[f"{tag}_ts"], z["node_parts"], pid, z["rt_indptr"], z["rt_ranks"],
                                     z["rt_locs"], int(z["P"]))
         assert same_plan_up_to_segment_order(got, z, tag), tag
+
+
+def _mail_case(z, c):
+    t = f"c{c}"
+    ef = z[f"{t}_ef"] if f"{t}_ef" in z else None
+    emb = int(z[f"{t}_emb"])
+    kw = dict(embedding=z[f"{t}_embedding"], use_src_emb=emb >= 1, use_dst_emb=emb >= 2) if emb else {}
+    return (z[f"{t}_src"], z[f"{t}_dst"], z[f"{t}_ts"], ef, z[f"{t}_mem_src"], z[f"{t}_mem_dst"]), kw
+
+
+def test_mail_reduce_matches_reference():
+    """``mailbox.get_update_mail`` run by the reference (the last case has equal timestamps inside a node's entries: its
+    expected rows follow the first-occurrence rule of the scatter-max restatement used to generate it)."""
+    z = load("mail.npz")
+    for c in range(int(z["n_cases"])):
+        args, kw = _mail_case(z, c)
+        index, mail, mail_ts = O.get_update_mail(*args, **kw)
+        assert np.array_equal(index, z[f"c{c}_index"]), c
+        assert np.array_equal(mail_ts, z[f"c{c}_mail_ts"]), c
+        assert np.array_equal(mail, z[f"c{c}_mail"]), c
+
+
+def test_mailbox_write_ring():
+    rng = np.random.default_rng(3)
+    mb, mts, pos = np.zeros((10, 3, 4), np.float32), np.zeros((10, 3), np.float32), np.zeros(10, np.int64)
+    for step in range(5):
+        idx = rng.permutation(10)[:6]
+        rows, ts = rng.standard_normal((6, 4)).astype(np.float32), rng.random(6).astype(np.float32)
+        before = pos.copy()
+        O.mailbox_write(mb, mts, pos, idx, rows, ts)
+        assert np.array_equal(mb[idx, before[idx]], rows) and np.array_equal(mts[idx, before[idx]], ts)
+        assert np.array_equal(pos[idx], (before[idx] + 1) % 3)
