@@ -293,6 +293,10 @@ def main():
                          "the host-buffer loop always replays a graph that includes its copies)")
     ap.add_argument("--route", default="p2p", choices=["p2p", "nccl", "none"],
                     help="transport of the cache route at N > 1: peer-memory kernels (default) or grouped NCCL send/recv")
+    ap.add_argument("--e2e-mode", default="native", choices=["native", "torch"],
+                    help="host-buffer step as one library call (copy + captured graph) or as a torch CUDA-graph replay")
+    ap.add_argument("--e2e-export", default="prefix", choices=["prefix", "full"],
+                    help="result copy to the host: device-counted prefix (exact bytes) or whole-capacity copies")
     ap.add_argument("--no-step-graph", action="store_true",
                     help="issue sample+gather as one fused foreign call (three kernel launches) instead of one graph launch")
     ap.add_argument("--num-nodes", type=int, default=NUM_NODES, help="smaller graphs are for profiler captures only")
@@ -326,19 +330,22 @@ def main():
     feats = torch.empty(NUM_EDGES, EDGE_DIM, dtype=torch.float32, device=dev)
     for s in range(0, NUM_EDGES, 5_000_000):
         feats[s:s + 5_000_000].normal_(generator=gen)
-    h_roots = b_roots.cpu().pin_memory()
-    h_ts = b_ts.cpu().pin_memory()
+    h_both = b_roots._base.cpu().pin_memory()           # [batch, 2, BATCH]: one contiguous host block per batch
+    h_roots, h_ts = h_both[:, 0], h_both[:, 1]
+    h_ptrs = [h_both[b].data_ptr() for b in range(NUM_BATCHES)]
 
     S = max(1, args.streams)
     streams = [torch.cuda.Stream(dev) for _ in range(S)]
-    pipes = [SampleGatherPipeline(g, feats, FANOUT, "recent", BATCH, gather_mode=args.gather_mode, stream=st)
-             for st in streams]
+    pipes = [SampleGatherPipeline(g, feats, FANOUT, "recent", BATCH, gather_mode=args.gather_mode, stream=st,
+                                  export=args.e2e_export) for st in streams]
     pipe, stream = pipes[0], streams[0]
     use_graph = args.graph_value
     for p_ in pipes:
         p_.capture()
         if not args.no_step_graph:
             p_.capture_native()
+        if args.e2e_mode == "native":
+            p_.capture_native_host()
     main_stream = torch.cuda.Stream(dev)
     route_stream = torch.cuda.Stream(dev, priority=-1)     # its few CTAs must not queue behind the persistent gather CTAs
     route_recv_stream = torch.cuda.Stream(dev, priority=-1)
@@ -512,8 +519,13 @@ def main():
             if i >= S:                          # retire the batch that used this pipeline object before reusing it
                 tot += p_.result()[0]
             b = (first + i) % NUM_BATCHES
-            p_.submit_host(h_roots[b], h_ts[b])
-            if route is not None:
+            if args.e2e_mode == "native":
+                p_.submit_host_ptr(h_ptrs[b])   # one call: roots from the pinned block + the captured step with its export
+            else:
+                p_.submit_host(h_roots[b], h_ts[b])
+            if route_steps is not None:
+                route_steps[b]()                # peer-memory route: send + apply of this step
+            elif route is not None:
                 cr, plans, mem, mem_ts, cb = route
                 with torch.cuda.stream(route_stream):
                     for f in cr.update_with_plan(mem, plans[b], cb, local_ts=mem_ts):
@@ -552,7 +564,7 @@ def main():
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "int64", "data": "synthetic", "config": workload_config(world),
                 "e2e": {"value": world * BATCH * e2e_steps / (e2e_ms / 1e3), "unit": "events/s",
-                        "h2d_bytes_per_step": pipe.h2d_bytes(BATCH), "d2h_bytes_per_step": pipe.d2h_bytes(),
+                        "h2d_bytes_per_step": pipe.h2d_bytes(BATCH), "d2h_bytes_per_step": pipe.d2h_bytes(e2e_edges / max(e2e_steps, 1)),
                         "note": "pinned host roots/times in; offsets, neighbour ids, timestamps, edge ids and dt out; "
                                 "gathered feature rows stay on the GPU for the model", "edges_per_step": e2e_edges / e2e_steps},
                 "gpu_launches": args.steps * (pipe.kernel_launches_per_step + (2 if multi else 0)),

@@ -219,6 +219,18 @@ int sgl_cache_gather(const void* cache_rows, int64_t cache_slots, const int32_t*
                      size_t ws_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Device-counted prefix copy: dst[a][0 .. *d_count * elem_bytes[a]) = src[a][...] for up to 8 arrays in one
+ * launch (*d_count clamped to [0, cap]); an array with elem_bytes[a] < 0 is copied whole (-elem_bytes[a] bytes,
+ * for fixed-size companions such as the offsets).  src / dst / elem_bytes are HOST arrays; the pointers in them are device
+ * pointers or pinned host pointers, 16-byte aligned.  With dst in pinned host memory a result whose length only
+ * the device knows (the sampled edges of a batch) crosses PCIe with exactly its bytes and without a host round trip.
+ * No reference counterpart (the reference's CUDA sampler sizes its result arrays on the host,
+ * csrc/include/starrygl/sample.cu.hpp:898-903).
+ * ---------------------------------------------------------------------------------------------- */
+int sgl_copy_prefix(int n_arrays, const void* const* src, void* const* dst, const int64_t* elem_bytes,
+                    const int64_t* d_count, int64_t cap, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Row scatter: table[row(i), :] = rows[i, :] for rows with row(i) >= 0 (row(i) = map ? map[idx[i]] :
  * idx[i]); optional ts_table[row(i)] = ts[i].  With split_last_col the source rows carry one extra
  * trailing float32 column that goes to ts_table instead of `ts` (the embedding||ts wire rows).

@@ -488,6 +488,34 @@ replica_expand_kernel(const int64_t* __restrict__ indptr, const int64_t* __restr
 
 inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
+
+// ---- device-counted prefix copy ------------------------------------------------------------------------------
+// Copies the first *d_count elements of up to 8 arrays in one launch (an array with a negative element size is
+// copied whole: that many bytes).  The destination may be pinned host memory: a batch's result then crosses PCIe with
+// exactly the bytes it has, although its size is only known on the device.
+struct PrefixCopy {
+  const char* src[8];
+  char* dst[8];
+  int64_t elem_bytes[8];
+  int n;
+};
+
+__global__ void __launch_bounds__(256)
+copy_prefix_kernel(PrefixCopy pc, const int64_t* __restrict__ d_count, int64_t cap) {
+  int64_t cnt = *d_count;
+  cnt = cnt < 0 ? 0 : (cnt > cap ? cap : cnt);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int a = 0; a < pc.n; ++a) {
+    const int64_t bytes = pc.elem_bytes[a] < 0 ? -pc.elem_bytes[a] : cnt * pc.elem_bytes[a];
+    const int64_t vec = bytes >> 4;
+    const uint4* s = (const uint4*)pc.src[a];
+    uint4* d = (uint4*)pc.dst[a];
+    for (int64_t u = tid; u < vec; u += stride) d[u] = s[u];
+    for (int64_t b = (vec << 4) + tid; b < bytes; b += stride) pc.dst[a][b] = pc.src[a][b];
+  }
+}
+
 }  // namespace
 }  // namespace sgl
 
@@ -569,6 +597,29 @@ extern "C" int sgl_gather_rows(const void* table, int64_t table_rows, int64_t ro
                                                                     idx, map, map_len, n, d_n, (char*)out, dst_pitch,
                                                                     ts_table, out_ts, d_status);
   }
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" int sgl_copy_prefix(int n_arrays, const void* const* src, void* const* dst, const int64_t* elem_bytes,
+                               const int64_t* d_count, int64_t cap, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(n_arrays >= 0 && n_arrays <= 8 && cap >= 0 && d_count, SGL_ERR_ARG, "copy_prefix: at most 8 arrays, non-null count");
+  if (n_arrays == 0) return SGL_OK;
+  PrefixCopy pc;
+  memset(&pc, 0, sizeof(pc));
+  pc.n = n_arrays;
+  int64_t most = 0;
+  for (int a = 0; a < n_arrays; ++a) {
+    SGL_REQUIRE(src && dst && elem_bytes && src[a] && dst[a] && elem_bytes[a] != 0, SGL_ERR_ARG, "copy_prefix: bad array %d", a);
+    SGL_REQUIRE((((uintptr_t)src[a] | (uintptr_t)dst[a]) & 15) == 0, SGL_ERR_ARG, "copy_prefix: array %d is not 16-byte aligned", a);
+    pc.src[a] = (const char*)src[a];
+    pc.dst[a] = (char*)dst[a];
+    pc.elem_bytes[a] = elem_bytes[a];
+    const int64_t b = elem_bytes[a] < 0 ? -elem_bytes[a] : cap * elem_bytes[a];
+    most = most > b ? most : b;
+  }
+  copy_prefix_kernel<<<stream_grid(most / 16 + 1, 256 * 4, 2), 256, 0, stream>>>(pc, d_count, cap);
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }

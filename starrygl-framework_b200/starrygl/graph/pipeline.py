@@ -20,10 +20,41 @@ from .. import _C, ops
 I64 = torch.int64
 
 
+class HostBlock:
+    """Host views of one batch's block structure (``offsets``, ``nbr``, ``ts``, ``eid``, ``dt``), sliced out of the
+    pipeline's pinned buffers on first use.  They alias those buffers: copy what must outlive the next batch."""
+
+    _KEYS = ("offsets", "nbr", "ts", "eid", "dt")
+
+    def __init__(self, pipe, n, tot):
+        self._p, self._n, self._tot = pipe, n, tot
+
+    def __getitem__(self, k):
+        p, n, tot = self._p, self._n, self._tot
+        o, cs = p._o, p._cs
+        if k == "offsets":
+            return p.h_blk[:n + 1]
+        if k == "dt":
+            return p.h_dt[:tot]
+        if k in ("nbr", "ts", "eid"):
+            b = o + ("nbr", "ts", "eid").index(k) * cs
+            return p.h_blk[b:b + tot]
+        raise KeyError(k)
+
+    def keys(self):
+        return self._KEYS
+
+    def items(self):
+        return [(k, self[k]) for k in self._KEYS]
+
+
 class SampleGatherPipeline:
     def __init__(self, g: ops.TCSR, edge_feats: Optional[torch.Tensor], fanout: int, policy: str = "recent",
                  max_roots: int = 4096, *, equal_root_time=False, allowed_offset=-1, keep_root_time=False, seed=0,
-                 gather_mode="auto", stream: Optional[torch.cuda.Stream] = None):
+                 gather_mode="auto", stream: Optional[torch.cuda.Stream] = None, export: str = "prefix"):
+        if export not in ("prefix", "full"):
+            raise _C.SglError("export must be 'prefix' (device-counted copy of the sampled edges) or 'full' (capacity)")
+        self.export = export
         self.g, self.feats, self.k, self.max_roots = g, edge_feats, int(fanout), int(max_roots)
         dev = g.device
         self.dev = dev
@@ -37,10 +68,12 @@ class SampleGatherPipeline:
         # one int64 block for the index outputs so that the block structure goes back to the host in ONE copy:
         # [offsets (max_roots+1) | nbr | ts | eid] each of capacity cap, then dt (float32) separately.  The target
         # slot of every edge (dst) stays on the device: on the host it is implied by the offsets.
-        self.blk = torch.empty(self.max_roots + 1 + 3 * cap, dtype=I64, device=dev)
-        o = self.max_roots + 1
-        self.offsets = self.blk[:o]
-        self.nbr, self.ts, self.eid = (self.blk[o + i * cap:o + (i + 1) * cap] for i in range(3))
+        # (section starts are kept 16-byte aligned for the vectorised export copy: even element counts)
+        o, cs = (self.max_roots + 2) & ~1, (cap + 1) & ~1
+        self._o, self._cs = o, cs
+        self.blk = torch.empty(o + 3 * cs, dtype=I64, device=dev)
+        self.offsets = self.blk[:self.max_roots + 1]
+        self.nbr, self.ts, self.eid = (self.blk[o + i * cs:o + i * cs + cap] for i in range(3))
         self.dst = torch.empty(cap, dtype=I64, device=dev)
         self.dt = torch.empty(cap, dtype=torch.float32, device=dev)
         self.done = torch.cuda.Event()
@@ -58,6 +91,16 @@ class SampleGatherPipeline:
         self.h_root_ts = torch.empty(self.max_roots, dtype=I64).pin_memory()
         self.h_blk = torch.empty(self.blk.numel(), dtype=I64).pin_memory()
         self.h_dt = torch.empty(cap, dtype=torch.float32).pin_memory()
+        # device-counted copy of the sampled edges (neighbour ids, timestamps, edge ids, dt) to the pinned mirrors
+        v = C.c_void_p
+        # (+ the offsets, copied whole: negative element size)
+        self._exp_src = (v * 5)(self.nbr.data_ptr(), self.ts.data_ptr(), self.eid.data_ptr(), self.dt.data_ptr(),
+                                self.offsets.data_ptr())
+        self._exp_dst = (v * 5)(*[self.h_blk.data_ptr() + 8 * (o + i * cs) for i in range(3)], self.h_dt.data_ptr(),
+                                self.h_blk.data_ptr())
+        self._exp_elem = (C.c_int64 * 5)(8, 8, 8, 4, -8 * (self.max_roots + 1))
+        self._exp_ok = all(p % 16 == 0 for p in list(self._exp_src) + list(self._exp_dst))
+        self._h_blk_np, self._exec_host = self.h_blk.numpy(), None
         self.kernel_launches_per_step = 2 + (1 if edge_feats is not None else 0)
         self._g_dev = self._g_host = None
         # pre-converted argument list of the fused C call; per batch only the two input pointers and n change
@@ -106,8 +149,7 @@ class SampleGatherPipeline:
             self.roots.copy_(self.h_roots, non_blocking=True)
             self.root_ts.copy_(self.h_root_ts, non_blocking=True)
             self.run_device(self.roots, self.root_ts)
-            self.h_blk.copy_(self.blk, non_blocking=True)
-            self.h_dt.copy_(self.dt, non_blocking=True)
+            self._export(n)
         self.stream.synchronize()
         return self
 
@@ -133,6 +175,44 @@ class SampleGatherPipeline:
         self._launch = self.L.sgl_graph_launch
         self.stream.synchronize()
         return self
+
+    def capture_native_host(self):
+        """Record the full-batch host step -- ``sgl_sample_gather`` on this object's root buffers followed by the
+        export of the block structure to the pinned mirrors -- with the library's graph helpers.
+        :meth:`submit_host_ptr` then costs one foreign call: the copy of the roots from the caller's pinned buffer
+        plus one graph launch."""
+        if not (self._exp_ok and self.export == "prefix"):
+            raise _C.SglError("capture_native_host needs the device-counted export (16-byte aligned buffers)")
+        sp = self.stream.cuda_stream
+        self.roots_ts.zero_()
+        torch.cuda.synchronize(self.dev)
+        self.run_device_ptr(self.roots.data_ptr(), self.root_ts.data_ptr(), self.max_roots)   # warm-up
+        self._export(self.max_roots)
+        self.stream.synchronize()
+        _C.check(self.L.sgl_graph_capture_begin(sp))
+        try:
+            self.run_device_ptr(self.roots.data_ptr(), self.root_ts.data_ptr(), self.max_roots)
+            self._export(self.max_roots)
+        finally:
+            ex = C.c_void_p()
+            rc = self.L.sgl_graph_capture_end(sp, C.byref(ex))
+        _C.check(rc)
+        v = C.c_void_p
+        self._exec_host, self._a_hsrc = ex, v(0)
+        self._hlaunch_args = [ex, self._a_hsrc, v(self.roots_ts.data_ptr()), C.c_size_t(self.roots_ts.numel() * 8), v(sp)]
+        self._launch = self.L.sgl_graph_launch
+        self.stream.synchronize()
+        return self
+
+    def submit_host_ptr(self, roots_ts_host_ptr: int):
+        """:meth:`submit_host` for a full batch whose roots and query times lie contiguously ([2, max_roots] int64) in
+        PINNED host memory at the given address: H2D copy + the captured step, one foreign call."""
+        self._n = self.max_roots
+        self._a_hsrc.value = roots_ts_host_ptr
+        rc = self._launch(*self._hlaunch_args)
+        if rc:
+            _C.check(rc)
+        self.done.record(self.stream)
 
     def replay_ptr(self, roots_ts_ptr: int):
         """Run the captured step for a batch whose roots and query times lie contiguously ([2, max_roots] int64) at the
@@ -197,20 +277,25 @@ class SampleGatherPipeline:
             self.roots[:n].copy_(h_roots, non_blocking=True)
             self.root_ts[:n].copy_(h_root_ts, non_blocking=True)
             self.run_device(self.roots[:n], self.root_ts[:n], rng_stream)
-            # one fixed-size copy of the whole block: copying only the used prefix would need the edge count on
-            # the host first, i.e. an extra round trip
+            self._export(n)
+            self.done.record(self.stream)
+
+    def _export(self, n):
+        """Block structure of the batch on this pipeline's stream -> pinned host mirrors: the offsets as one fixed-size
+        copy, the per-edge arrays with a device-counted prefix copy (only the edges the batch really has cross PCIe,
+        and the host never has to learn the count first)."""
+        if self._exp_ok and self.export == "prefix":
+            _C.check(self.L.sgl_copy_prefix(5, self._exp_src, self._exp_dst, self._exp_elem, self.offsets.data_ptr() + 8 * n,
+                                            self.cap, self.stream.cuda_stream))
+        else:   # whole-capacity copies (also when torch did not align the buffers to 16 bytes)
             self.h_blk.copy_(self.blk, non_blocking=True)
             self.h_dt.copy_(self.dt, non_blocking=True)
-            self.done.record(self.stream)
 
     def result(self):
         """(n_edges, dict of host views) of the batch submitted last; blocks until its copies have landed."""
         self.done.synchronize()
-        n, cap, o = self._n, self.cap, self.max_roots + 1
-        tot = int(self.h_blk[n])
-        views = {"offsets": self.h_blk[:n + 1], "nbr": self.h_blk[o:o + tot], "ts": self.h_blk[o + cap:o + cap + tot],
-                 "eid": self.h_blk[o + 2 * cap:o + 2 * cap + tot], "dt": self.h_dt[:tot]}
-        return tot, views
+        tot = int(self._h_blk_np[self._n])
+        return tot, HostBlock(self, self._n, tot)
 
     def run_host(self, h_roots: torch.Tensor, h_root_ts: torch.Tensor, rng_stream: int = 0):
         """Synchronous form: :meth:`submit_host` followed by :meth:`result`."""
@@ -220,5 +305,9 @@ class SampleGatherPipeline:
     def h2d_bytes(self, n):
         return 16 * n
 
-    def d2h_bytes(self):
-        return self.blk.numel() * 8 + self.dt.numel() * 4
+    def d2h_bytes(self, n_edges=None):
+        """Bytes of one batch's result copy: the offsets plus 28 bytes per sampled edge (capacity when the count is
+        not given)."""
+        if n_edges is None or not self._exp_ok or self.export == "full":
+            return self.blk.numel() * 8 + self.dt.numel() * 4
+        return (self.max_roots + 1) * 8 + int(n_edges * 28)
