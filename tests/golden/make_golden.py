@@ -23,6 +23,8 @@ What is pinned, and the reference code that produced it:
 * ``mail.npz``        -- ``mailbox.get_update_mail`` (starrygl/nn/memory/mailbox.py:56-84) on batches with distinct
   timestamps per node entry (``torch_scatter`` is absent: its ``scatter_max`` is a torch restatement, so the tie case
   stored beside them is defined by that restatement, not by the reference).
+* ``slots.npz``       -- complete slot files of ``build_aligned_batch`` INCLUDING the per-layer ``comm_plan``
+  (prepare_sample.py:313-406) for every partition of a 3-way split, read back from the ``.pt`` file the reference wrote.
 * ``nodestate.npz``   -- ``DistNodeState.update`` / ``__getitem__`` with ``node_mode='map'``
   (starrygl/cache/NodeState.py:36-61, starrygl/utils/partition_book.py:98-133).
 """
@@ -354,6 +356,83 @@ def gen_plan(ref, out):
     np.savez_compressed(os.path.join(out, "plan.npz"), **rec)
 
 
+def gen_slots(ref, out):
+    """``build_aligned_batch`` with route planning ON, written by the reference with ``torch.save`` and read back."""
+    import tempfile
+    import torch
+    sys.path.insert(0, ref)
+    het = _stub("dgl.heterograph", DGLBlock=object)
+    _stub("dgl", heterograph=het)
+    comm = _stub("starrygl.lib.libstarrygl_comm", DistContext=object, init_p2p=lambda *a: None)
+    _stub("starrygl.lib", libstarrygl_comm=comm)
+
+    def scatter_max(src, index, dim=0):
+        n = int(index.max()) + 1 if index.numel() else 0
+        mx = torch.full((n,), torch.iinfo(src.dtype).min, dtype=src.dtype).scatter_reduce(0, index, src, "amax")
+        is_max = src == mx[index]
+        pos = torch.where(is_max, torch.arange(len(src)), torch.full((len(src),), len(src)))
+        arg = torch.full((n,), len(src), dtype=torch.long).scatter_reduce(0, index, pos, "amin")
+        return mx, arg
+    _stub("torch_scatter", scatter_max=scatter_max)
+    spec = importlib.util.spec_from_file_location("ref_prepare_sample3", os.path.join(ref, "prepare_sample.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    from starrygl.cache.cache_route import CommPlan
+    from starrygl.cache.replica_table import build_replica_table
+    mod.CommPlan = CommPlan
+    rng = np.random.default_rng(41)
+    N, P, M = 300, 3, 6000
+    node_parts = torch.from_numpy(rng.integers(0, P, N))
+    book = []
+    for p in range(P):
+        owned = torch.nonzero(node_parts == p)[:, 0].numpy()
+        halo = rng.choice(np.setdiff1d(np.arange(N), owned), 90, replace=False)
+        book.append(torch.from_numpy(np.concatenate([owned, halo])))
+    rt = build_replica_table(N, book, P)
+    src, dst = rng.integers(0, N, M), rng.integers(0, N, M)
+    ts = np.sort(rng.integers(0, 50000, M)).astype(np.int64)
+    eid = rng.permutation(M).astype(np.int64)
+    rec = {"N": np.int64(N), "P": np.int64(P), "node_parts": node_parts.numpy(), "rt_indptr": rt.indptr.numpy(),
+           "rt_ranks": rt.indices.numpy(), "rt_locs": rt.locs.numpy(), "src": src, "dst": dst, "ts": ts, "eid": eid}
+    pick = np.sort(rng.choice(M, 60, replace=False))
+    cases = [("link", [3, 2], 0), ("node", [5], 1), ("link", [4, 4], 1)]
+    rec["n_cases"] = np.int64(len(cases))
+    for c, (kind, fanouts, end_offset) in enumerate(cases):
+        cfg = {'meta': {'start_offset': -1, 'end_offset': end_offset, 'graph_type': 'c'},
+               'layer': [{'type': 'recent', 'fanout': f} for f in fanouts]}
+        if kind == "link":
+            task = ('link', (src[pick], dst[pick], ts[pick], np.ones(len(pick), np.int64), eid[pick]))
+        else:
+            task = ('node', (dst[pick], ts[pick], np.zeros(len(pick), np.int64)))
+        rec[f"c{c}_kind"], rec[f"c{c}_fanouts"], rec[f"c{c}_end_offset"] = np.array(kind), np.array(fanouts), np.int64(end_offset)
+        rec[f"c{c}_pick"] = pick
+        for pid in range(P):
+            b = mod.MaterializedMultiLayerBuilder({'src': src, 'dst': dst, 'ts': ts, 'eid': eid}, N, node_parts, rt, pid, P)
+            with tempfile.TemporaryDirectory() as d:
+                path = os.path.join(d, "slot_0000_sub_0000.pt")
+                b.build_aligned_batch(task, path, cfg, 1, None, None)
+                data = torch.load(path, weights_only=False)
+            tag = f"c{c}_p{pid}"
+            rec[f"{tag}_num_layers"] = np.int64(len(data))
+            for i, dct in enumerate(data):
+                for k, v in dct.items():
+                    if isinstance(v, torch.Tensor):
+                        rec[f"{tag}_L{i}_{k}"] = v.numpy()
+                    elif isinstance(v, (int, np.integer)):
+                        rec[f"{tag}_L{i}_{k}"] = np.int64(v)
+            plans = data[0]["comm_plan"]
+            rec[f"{tag}_num_plans"] = np.int64(len(plans))
+            for i, pl in enumerate(plans):
+                if pl is None:
+                    rec[f"{tag}_plan{i}_none"] = np.int64(1)
+                    continue
+                rec[f"{tag}_plan{i}_send_ranks"] = pl.send_ranks.numpy()
+                rec[f"{tag}_plan{i}_send_sizes"] = pl.send_sizes.numpy()
+                rec[f"{tag}_plan{i}_send_indices"] = pl.send_indices.numpy()
+                rec[f"{tag}_plan{i}_send_remote"] = pl.send_remote_indices.numpy()
+    np.savez_compressed(os.path.join(out, "slots.npz"), **rec)
+
+
 def gen_mail(ref, out):
     """Runs the reference's ``mailbox.get_update_mail`` on CPU tensors."""
     import torch
@@ -423,6 +502,8 @@ if __name__ == "__main__":
         gen_ids(a.reference, HERE)
     if a.only in ("all", "plan"):
         gen_plan(a.reference, HERE)
+    if a.only in ("all", "slots"):
+        gen_slots(a.reference, HERE)
     if a.only in ("all", "mail"):
         gen_mail(a.reference, HERE)
     print("golden vectors written to", HERE)

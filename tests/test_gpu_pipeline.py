@@ -130,3 +130,31 @@ def test_copy_prefix_edges():
         assert torch.equal(oa[:m], a[:m].cpu()) and (oa[m:] == -1).all()
         assert torch.equal(ob[:m], b[:m].cpu()) and (ob[m:] == -1).all()
         assert torch.equal(oc[:37], c[:37].cpu()) and (oc[37:] == 0).all()
+
+
+def test_prefetcher_yields_every_batch_in_order(world):
+    """Batches from a loader (device tensors and pinned host tensors mixed) through 3 pipeline slots; a consumer kernel
+    per batch copies what it reads, the copies are checked after the loop (so a slot overwritten too early would show)."""
+    from starrygl.data.prefetcher import HostToDevicePrefetcher
+    g, feats, feats_np, batches = world
+
+    def loader():
+        for i in range(12):
+            q, qt, _ = batches[i % len(batches)]
+            if i % 2:
+                yield torch.from_numpy(q).pin_memory(), torch.from_numpy(qt).pin_memory()
+            else:
+                yield cu(q), cu(qt)
+    pf = HostToDevicePrefetcher(loader(), g, feats, K, "recent", B, depth=3)
+    kept = []
+    for b in pf:
+        kept.append((b.offsets.clone(), b.nbr.clone(), b.eid.clone(), b.dt.clone(), b.edge_feats.clone()))
+    torch.cuda.synchronize()
+    pf.check()
+    assert len(kept) == 12
+    for i, (offs, nbr, eid, dt, ef) in enumerate(kept):
+        src, dst, ts, rdt, reid, counts = batches[i % len(batches)][2][:6]
+        tot = len(src)
+        assert np.array_equal(np.diff(npy(offs)), counts)
+        assert np.array_equal(npy(nbr[:tot]), src) and np.array_equal(npy(eid[:tot]), reid) and np.array_equal(npy(dt[:tot]), rdt)
+        assert np.array_equal(npy(ef[:tot]), feats_np[reid])

@@ -234,3 +234,38 @@ def test_mailbox_write_ring():
         O.mailbox_write(mb, mts, pos, idx, rows, ts)
         assert np.array_equal(mb[idx, before[idx]], rows) and np.array_equal(mts[idx, before[idx]], ts)
         assert np.array_equal(pos[idx], (before[idx] + 1) % 3)
+
+
+LAYER_KEYS = ("indptr", "indices", "eid", "edge_ts", "edge_dt", "gids", "ts")
+
+
+def slot_cases():
+    z = load("slots.npz")
+    for c in range(int(z["n_cases"])):
+        pick = z[f"c{c}_pick"]
+        if str(z[f"c{c}_kind"]) == "link":
+            roots, rts = np.concatenate([z["src"][pick], z["dst"][pick]]), np.concatenate([z["ts"][pick], z["ts"][pick]])
+        else:
+            roots, rts = z["dst"][pick], z["ts"][pick]
+        for pid in range(int(z["P"])):
+            yield z, c, pid, roots, rts
+
+
+def test_slot_files_match_reference():
+    """Whole slot files written by the reference's ``build_aligned_batch`` (route planning on): layer dictionaries and
+    the per-layer plans, restated as oracle ``build_batch`` + ``compute_layer_route``."""
+    for z, c, pid, roots, rts in slot_cases():
+        csr = O.tcsr_build(z["dst"], z["src"], z["ts"], z["eid"], int(z["N"]))[:4]
+        layers = O.build_batch(*csr, roots, rts, [int(f) for f in z[f"c{c}_fanouts"]],
+                               equal_root_time=bool(int(z[f"c{c}_end_offset"])))
+        tag = f"c{c}_p{pid}"
+        assert len(layers) == int(z[f"{tag}_num_layers"]) == int(z[f"{tag}_num_plans"])
+        for k in ("gids", "ts", "inv_map"):
+            assert np.array_equal(layers[0][k], z[f"{tag}_L0_{k}"]), (tag, k)
+        for i in range(1, len(layers)):
+            for k in LAYER_KEYS:
+                assert np.array_equal(layers[i][k], z[f"{tag}_L{i}_{k}"]), (tag, i, k)
+        for i, L in enumerate(layers):
+            got = O.compute_layer_route(L["gids"], L["ts"], z["node_parts"], pid, z["rt_indptr"], z["rt_ranks"], z["rt_locs"],
+                                        int(z["P"]))
+            assert same_plan_up_to_segment_order(got, z, f"{tag}_plan{i}"), (tag, i)
