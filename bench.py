@@ -297,6 +297,8 @@ def main():
                     help="host-buffer step as one library call (copy + captured graph) or as a torch CUDA-graph replay")
     ap.add_argument("--e2e-export", default="prefix", choices=["prefix", "full"],
                     help="result copy to the host: device-counted prefix (exact bytes) or whole-capacity copies")
+    ap.add_argument("--no-numa-bind", action="store_true", help="N > 1: do not bind the rank to the CPUs of its GPU's NUMA node")
+    ap.add_argument("--row-align", type=int, default=0, help="pad the feature table's rows in HBM to this many bytes (0 = dense)")
     ap.add_argument("--no-step-graph", action="store_true",
                     help="issue sample+gather as one fused foreign call (three kernel launches) instead of one graph launch")
     ap.add_argument("--num-nodes", type=int, default=NUM_NODES, help="smaller graphs are for profiler captures only")
@@ -318,6 +320,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     multi = world > 1
+    from starrygl.utils.affinity import bind_to_gpu_numa_node
+    host_info = bind_to_gpu_numa_node(local) if (multi and not args.no_numa_bind) else {"numa_node": None, "cpus": len(os.sched_getaffinity(0))}
     if multi:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -327,7 +331,10 @@ def main():
     g = ops.tcsr_build(src, dst, ts, None, NUM_NODES)
     b_roots, b_ts = make_batches(src, ts, gen, dev)
     del src, dst, ts
-    feats = torch.empty(NUM_EDGES, EDGE_DIM, dtype=torch.float32, device=dev)
+    # rows padded in HBM to a multiple of --row-align bytes (0 = dense): a 688-byte row that starts on a 64-byte boundary
+    # touches 11 DRAM atoms instead of 11-12 and 22 sectors instead of 22-23
+    pitch_f = EDGE_DIM if args.row_align <= 0 else ((EDGE_DIM * 4 + args.row_align - 1) // args.row_align) * args.row_align // 4
+    feats = torch.empty(NUM_EDGES, pitch_f, dtype=torch.float32, device=dev)[:, :EDGE_DIM]
     for s in range(0, NUM_EDGES, 5_000_000):
         feats[s:s + 5_000_000].normal_(generator=gen)
     h_both = b_roots._base.cpu().pin_memory()           # [batch, 2, BATCH]: one contiguous host block per batch
@@ -556,7 +563,7 @@ def main():
         achieved = alg / g_ms / 1e6
         line = {"metric": "sampled+gathered events/sec", "value": world * BATCH * args.steps / (ms / 1e3),
                 "unit": "events/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms / args.steps, "host_issue_ms_per_step": t_issue * 1e3 / args.steps,
+                "ms_per_step": ms / args.steps, "host": host_info, "host_issue_ms_per_step": t_issue * 1e3 / args.steps,
                 "host_issue_breakdown_ms": {k: v * 1e3 / args.steps for k, v in issue_t.items()},
                 "device_ms_per_step": {"sample_gather_streams": e0.elapsed_time(e_pipe) / args.steps,
                                        "route_send_chain": e0.elapsed_time(e_rs) / args.steps,
