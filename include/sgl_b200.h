@@ -366,6 +366,25 @@ int sgl_replica_lookup(const int64_t* indptr, const int64_t* ranks, const int64_
                        void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Sub-graph of a chunk set and a time window as a two-level CSR (node -> distinct timestamps -> edges).
+ * Kept edges: source node in a selected chunk (chunk_mask[node_chunk[src]] != 0; null mask = all), t_begin <= ts <
+ * t_end, neighbour in a selected chunk too.  Outputs: out_nodes[U] (ascending ids of nodes that keep an edge),
+ * out_node_ptr[U+1] into the groups, out_group_ts[G], out_group_ptr[G+1] into the edges, out_nbr / out_ts /
+ * out_eid[E] in T-CSR order; d_counts = {U, G, E}.  Capacities: out_nodes and out_node_ptr num_nodes (+1), the group
+ * and edge arrays cap_edges (+1); more kept edges than cap_edges raise SGL_DEV_OVERFLOW and nothing is written.
+ * Replaces: Graph::slice_by_chunk_ts + count_edges_kernel / write_edges_kernel
+ * (csrc/include/starrygl/sample.cu.hpp:1189-1291, :300-520).  The reference's version indexes its chunk table by
+ * block number instead of chunk id and drops the first timestamp group of every node; the contract here is the
+ * one stated above (window half open like the root extraction).
+ * ---------------------------------------------------------------------------------------------- */
+size_t sgl_slice_window_ws_bytes(int64_t num_nodes);
+int sgl_slice_window(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid, int64_t num_nodes,
+                     const int64_t* node_chunk, const uint8_t* chunk_mask, int64_t num_chunks, int64_t t_begin,
+                     int64_t t_end, int64_t cap_edges, int64_t* out_nodes, int64_t* out_node_ptr, int64_t* out_group_ts,
+                     int64_t* out_group_ptr, int64_t* out_nbr, int64_t* out_ts, int64_t* out_eid, int64_t* d_counts,
+                     int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Mailbox update of a mini-batch: latest message per node + row assembly, and the write into the mailbox.
  *
  * sgl_mail_reduce: entries = ids_a[n_a] followed by ids_b[n_b] (the batch's source nodes, then its destination

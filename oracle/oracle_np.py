@@ -468,3 +468,33 @@ def mailbox_write(mailbox, mailbox_ts, next_pos, index, rows, ts):
     mailbox[index, p] = rows
     if slots > 1:
         next_pos[index] = (p + 1) % slots
+
+
+# ----------------------------------------------------------------------------------------------
+# chunk / time-window slice
+# ----------------------------------------------------------------------------------------------
+
+
+def slice_window(indptr, nbr, ts, eid, node_chunk, chunk_mask, t_begin, t_end):
+    """Intended result of Graph::slice_by_chunk_ts (csrc/include/starrygl/sample.cu.hpp:1189-1291): edges whose two
+    end nodes lie in selected chunks and whose timestamp lies in [t_begin, t_end), as node -> distinct timestamps ->
+    edges.  Returns (nodes, node_ptr, group_ts, group_ptr, nbr, ts, eid)."""
+    n = len(indptr) - 1
+    src = np.repeat(np.arange(n, dtype=I64), np.diff(indptr))
+    sel_node = np.ones(n, bool) if chunk_mask is None else np.asarray(chunk_mask, bool)[
+        node_chunk if node_chunk is not None else np.zeros(n, I64)]
+    keep = sel_node[src] & sel_node[nbr] & (ts >= t_begin) & (ts < t_end)
+    k_src, k_nbr, k_ts, k_eid = src[keep], nbr[keep], ts[keep], eid[keep]
+    e = len(k_src)
+    if e == 0:
+        z = np.zeros(0, I64)
+        return z, np.zeros(1, I64), z, np.zeros(1, I64), z, z, z
+    head = np.ones(e, bool)
+    head[1:] = (k_src[1:] != k_src[:-1]) | (k_ts[1:] != k_ts[:-1])
+    group_start = np.nonzero(head)[0].astype(I64)
+    g_src, g_ts = k_src[group_start], k_ts[group_start]
+    node_head = np.ones(len(g_src), bool)
+    node_head[1:] = g_src[1:] != g_src[:-1]
+    node_start = np.nonzero(node_head)[0].astype(I64)
+    return (g_src[node_start], np.append(node_start, len(g_src)).astype(I64), g_ts, np.append(group_start, e).astype(I64),
+            k_nbr, k_ts, k_eid)

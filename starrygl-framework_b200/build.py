@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "lib")
 OUT = os.path.join(OUT_DIR, "libsgl_b200.so")
-SOURCES = ["api.cu", "sort.cu", "tcsr.cu", "sampler.cu", "relabel.cu", "gather.cu", "comm.cu", "p2p_route.cu", "plan.cu", "mail.cu"]
+SOURCES = ["api.cu", "sort.cu", "tcsr.cu", "sampler.cu", "relabel.cu", "gather.cu", "comm.cu", "p2p_route.cu", "plan.cu", "mail.cu", "slice.cu"]
 FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "--expt-relaxed-constexpr",
          "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared"]
 

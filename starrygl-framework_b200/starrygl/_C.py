@@ -81,6 +81,9 @@ _SIGNATURES = {
     "sgl_plan_route_ws_bytes": (_sz, [_i64, _i64]),
     "sgl_plan_route": (_i32, [_vp, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                               _sz, _vp]),
+    "sgl_slice_window_ws_bytes": (_sz, [_i64]),
+    "sgl_slice_window": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                _vp, _vp, _vp, _sz, _vp]),
     "sgl_copy_prefix": (_i32, [_i32, _vp, _vp, _vp, _vp, _i64, _vp]),
     "sgl_mail_reduce_ws_bytes": (_sz, [_i64]),
     "sgl_mail_reduce": (_i32, [_vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,

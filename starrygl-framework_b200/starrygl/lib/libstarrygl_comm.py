@@ -75,6 +75,17 @@ class TemporalNeighbor:
         self.neighbors_dt = hop.dt_i64[:n]
         self.neighbor_num = n
 
+    @classmethod
+    def from_arrays(cls, start_ptr, neighbors, neighbors_ts, neighbors_eid):
+        """Layer given directly by its CSR arrays (``start_ptr`` with one extra entry)."""
+        self = cls.__new__(cls)
+        self.root_start_ptr = start_ptr
+        self.root_end_ptr = torch.cat([start_ptr[1:], start_ptr[-1:]])
+        self.neighbors, self.neighbors_ts, self.neighbors_eid = neighbors, neighbors_ts, neighbors_eid
+        self.neighbors_dt = torch.zeros_like(neighbors_ts)
+        self.neighbor_num = neighbors.numel()
+        return self
+
     @property
     def start_ptr(self):   # name used by the reference's block builder (starrygl/graph/graph.py:174)
         return self.root_start_ptr
@@ -154,8 +165,21 @@ class CUDAGraph:
             self.status.check("sample_src_in_chunks_khop")
         return out
 
-    def slice_by_chunk_ts(self, chunks, time_begin, time_end, using_full_timestamp=False, stream=0):
-        raise NotImplementedError("chunk/time-window sub-graph slices are not part of the sampling data path")
+    def slice_by_chunk_ts(self, chunks, time_begin, time_end, using_full_timestamp=False, stream=0) -> "TemporalResult":
+        """Sub-graph of the chunks' nodes inside ``[time_begin, time_end)``: ``roots`` = the nodes that keep an edge with
+        their distinct timestamps (``ts_ptr`` / ``ts``), one neighbour layer whose ``root_start_ptr`` has one entry per
+        (node, timestamp) group (reference: csrc/include/starrygl/sample.cu.hpp:1189-1291)."""
+        if using_full_timestamp:
+            raise NotImplementedError("dense per-timestep groups (using_full_timestamp) are not provided")
+        ev_ts = self.ev[1]
+        with torch.cuda.stream(self.stream):
+            lo, hi = ops.lower_bound(ev_ts, torch.tensor([int(time_begin), int(time_end)], dtype=torch.int64,
+                                                         device=ev_ts.device)).tolist()
+            nodes, node_ptr, group_ts, group_ptr, nbr, ts, eid = ops.slice_window(
+                self.g, chunks, self.mapper, int(time_begin), int(time_end), max(hi - lo, 0), status=self.status)
+        out = TemporalResult(TemporalRoot(nodes, node_ptr, group_ts))
+        out.neighbors_list.append(TemporalNeighbor.from_arrays(group_ptr, nbr, ts, eid))
+        return out
 
     def _remap(self, result: TemporalResult, reset: bool):
         """Node-level relabel: roots first, then every hop; local ids in ascending global id among the new ids."""

@@ -211,6 +211,38 @@ def seeds_in_window(ev, g: TCSR, chunks, node_chunk, t_begin: int, t_end: int, *
     return roots[:n_roots], ts_ptr[:n_roots + 1], tsv[:n_pairs], q_ptr[:n_pairs + 1], q_eid[:n_ev]
 
 
+def slice_window(g: TCSR, chunks, node_chunk, t_begin: int, t_end: int, cap_edges: int, *,
+                 status: Optional[StatusWord] = None):
+    """Two-level CSR of the edges with ``t_begin <= ts < t_end`` whose two end nodes lie in ``chunks`` (see
+    ``sgl_slice_window``; ``chunks`` None = every chunk).  Returns (nodes, node_ptr, group_ts, group_ptr, nbr, ts, eid)
+    trimmed to size (one read-back of the three counts).  ``cap_edges`` bounds the kept edges, e.g. the number of events
+    in the window."""
+    L = _C.lib()
+    dev = g.device
+    chunk_mask, d_node_chunk, num_chunks = None, None, 0
+    if chunks is not None and node_chunk is not None and node_chunk.numel():
+        if not hasattr(g, "_node_chunk_dev"):
+            g._node_chunk_dev = node_chunk.to(dev, I64).contiguous()
+            g._num_chunks = int(node_chunk.max().item()) + 1
+        d_node_chunk, num_chunks = g._node_chunk_dev, g._num_chunks
+        chunk_mask = torch.zeros(num_chunks, dtype=torch.uint8, device=dev)
+        chunk_mask[chunks.to(dev, I64)] = 1
+    n, cap = g.num_nodes, max(int(cap_edges), 1)
+    nodes, node_ptr = torch.empty(max(n, 1), dtype=I64, device=dev), torch.empty(n + 1, dtype=I64, device=dev)
+    group_ts, nbr, ts, eid = (torch.empty(cap, dtype=I64, device=dev) for _ in range(4))
+    group_ptr = torch.empty(cap + 1, dtype=I64, device=dev)
+    counts = torch.zeros(3, dtype=I64, device=dev)
+    _, wp, wn = _C.workspace(L.sgl_slice_window_ws_bytes(n), dev)
+    _C.check(L.sgl_slice_window(_C.ptr(g.indptr), _C.ptr(g.nbr), _C.ptr(g.ts), _C.ptr(g.eid), n, _C.ptr(d_node_chunk),
+                                _C.ptr(chunk_mask), num_chunks, int(t_begin), int(t_end), int(cap_edges), _C.ptr(nodes),
+                                _C.ptr(node_ptr), _C.ptr(group_ts), _C.ptr(group_ptr), _C.ptr(nbr), _C.ptr(ts), _C.ptr(eid),
+                                _C.ptr(counts), status.ptr() if status else None, wp, wn, _C.stream_ptr()))
+    u, gcnt, e = counts.tolist()
+    if status is not None:
+        status.check("slice_window")
+    return nodes[:u], node_ptr[:u + 1], group_ts[:gcnt], group_ptr[:gcnt + 1], nbr[:e], ts[:e], eid[:e]
+
+
 # --------------------------------------------------------------------------------------------------------------
 # relabel
 # --------------------------------------------------------------------------------------------------------------

@@ -100,3 +100,40 @@ def test_chunk_filter():
     assert np.array_equal(npy(r.roots), roots) and np.array_equal(npy(r.ts_ptr), ts_ptr) and np.array_equal(npy(r.ts), rts)
     assert np.array_equal(npy(r.q_ptr), q_ptr) and np.array_equal(npy(r.q_eid), q_eid)
     g.close()
+
+
+@pytest.mark.parametrize("chunks,t0,t1", [([1, 3], 500, 900), ([0, 1, 2, 3], 0, 10000), (None, 2000, 2001), ([2], 9000, 9000),
+                                          ([0], -50, 20000)])
+def test_slice_by_chunk_ts(chunks, t0, t1):
+    """Chunk/time-window sub-graph (node -> distinct timestamps -> edges) against the oracle, through the graph API."""
+    from starrygl.lib import libstarrygl_comm as L
+    n, src, dst, ts, eid = make_events(seed=3, n=400, m=30000, tmax=3000)      # 10 events per timestamp: real groups
+    src[:5000] = 7                                                             # one hub row spanning many ballots
+    node_chunk = (np.arange(n) // 100).astype(np.int64)
+    g = L.from_edge_index(n, 100, cu(src), cu(dst), cu(ts), cu(eid), torch.from_numpy(node_chunk))
+    r = g.slice_by_chunk_ts(None if chunks is None else torch.tensor(chunks).cuda(), t0, t1)
+    g.status.check("slice")
+    indptr, s_nbr, s_ts, s_eid, _ = O.tcsr_build(src, dst, ts, eid, n)
+    mask = None if chunks is None else np.isin(np.arange(4), chunks)
+    nodes, node_ptr, group_ts, group_ptr, k_nbr, k_ts, k_eid = O.slice_window(indptr, s_nbr, s_ts, s_eid, node_chunk, mask, t0, t1)
+    nb = r.neighbors[0]
+    assert np.array_equal(npy(r.roots.roots), nodes) and np.array_equal(npy(r.roots.ts_ptr), node_ptr)
+    assert np.array_equal(npy(r.roots.ts), group_ts) and np.array_equal(npy(nb.root_start_ptr), group_ptr)
+    assert np.array_equal(npy(nb.neighbors), k_nbr) and np.array_equal(npy(nb.neighbors_ts), k_ts)
+    assert np.array_equal(npy(nb.neighbors_eid), k_eid)
+    # structure: groups partition the edges, one timestamp per group, ascending inside a node
+    if len(k_ts):
+        gp = npy(nb.root_start_ptr)
+        assert all(len(set(k_ts[gp[i]:gp[i + 1]])) == 1 for i in range(0, len(gp) - 1, max(1, (len(gp) - 1) // 50)))
+    g.close()
+
+
+def test_slice_window_capacity_overflow_is_reported():
+    from starrygl import _C, ops
+    n, src, dst, ts, eid = make_events(seed=4, n=50, m=2000, tmax=100)
+    g = ops.tcsr_build(cu(src), cu(dst), cu(ts), cu(eid), n)
+    st = ops.StatusWord(g.device)
+    with pytest.raises(_C.SglError):
+        ops.slice_window(g, None, None, 0, 100, 10, status=st)
+    out = ops.slice_window(g, None, None, 0, 100, 2000, status=st)
+    assert out[4].numel() == 2000

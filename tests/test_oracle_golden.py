@@ -269,3 +269,28 @@ def test_slot_files_match_reference():
             got = O.compute_layer_route(L["gids"], L["ts"], z["node_parts"], pid, z["rt_indptr"], z["rt_ranks"], z["rt_locs"],
                                         int(z["P"]))
             assert same_plan_up_to_segment_order(got, z, f"{tag}_plan{i}"), (tag, i)
+
+
+def test_slice_window_structure():
+    """The chunk/time-window slice has no runnable reference (its kernels index the chunk table by block number); the
+    oracle is checked against a brute-force enumeration on a small graph."""
+    rng = np.random.default_rng(5)
+    n, m = 30, 600
+    src, dst = rng.integers(0, n, m), rng.integers(0, n, m)
+    ts = rng.integers(0, 40, m).astype(np.int64)
+    indptr, nbr, sts, eid, _ = O.tcsr_build(src, dst, ts, np.arange(m, dtype=np.int64), n)
+    chunk = (np.arange(n) // 10).astype(np.int64)
+    mask = np.array([1, 0, 1], bool)
+    nodes, node_ptr, group_ts, group_ptr, k_nbr, k_ts, k_eid = O.slice_window(indptr, nbr, sts, eid, chunk, mask, 5, 25)
+    want = {}
+    for v in range(n):
+        for e in range(indptr[v], indptr[v + 1]):
+            if mask[chunk[v]] and mask[chunk[nbr[e]]] and 5 <= sts[e] < 25:
+                want.setdefault(v, {}).setdefault(int(sts[e]), []).append((int(nbr[e]), int(eid[e])))
+    assert nodes.tolist() == sorted(want)
+    for u, v in enumerate(nodes):
+        groups = range(node_ptr[u], node_ptr[u + 1])
+        assert [int(group_ts[g]) for g in groups] == sorted(want[v])
+        for g in groups:
+            got = list(zip(k_nbr[group_ptr[g]:group_ptr[g + 1]].tolist(), k_eid[group_ptr[g]:group_ptr[g + 1]].tolist()))
+            assert got == want[v][int(group_ts[g])]
