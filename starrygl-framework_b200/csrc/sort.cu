@@ -1,8 +1,9 @@
 // Stable LSD radix sort, 8 bits per pass, three kernels per pass:
 //   1. sort_hist_kernel    per-CTA digit histogram of its tile (4096 keys)          -> block_hist[digit][cta]
 //   2. sort_scan_kernel    one CTA per digit: exclusive scan over CTAs + digit total
-//   3. sort_scatter_kernel re-reads the tile, ranks keys stably (warp match + per-warp running counters)
-//                          and writes key/payload to their final place for this digit
+//   3. sort_scatter_kernel re-reads the tile, ranks keys stably (warp match + per-warp running counters), lays the
+//                          tile out in digit order in shared memory and writes every digit's run with consecutive
+//                          threads (coalesced runs instead of scattered 8- and 4-byte stores)
 // HBM traffic per pass and key: 8 B (histogram read) + 12 B read + 12 B write.
 #include "sort.cuh"
 
@@ -65,18 +66,29 @@ sort_scan_kernel(uint32_t* __restrict__ block_hist, int num_blocks, uint32_t* __
   if (threadIdx.x == 0) digit_total[blockIdx.x] = carry_s;
 }
 
-__global__ void __launch_bounds__(kSortThreads)
+// Shared memory of the scatter kernel: the tile's keys and payloads in digit order, the per-warp digit counters and
+// two per-digit tables.
+constexpr size_t kScatterSmem = (size_t)kSortTile * 12 + (size_t)(kSortThreads / 32) * kSortRadix * 4 + 2 * kSortRadix * 4;
+
+__global__ void __launch_bounds__(kSortThreads, 3)   // three tiles per SM: their load / rank / write phases overlap
 sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ vals, int64_t n_cap,
                     const int64_t* d_n, int shift, const uint32_t* __restrict__ block_hist, int num_blocks,
                     const uint32_t* __restrict__ digit_total, uint64_t* __restrict__ out_keys,
                     uint32_t* __restrict__ out_vals) {
-  __shared__ uint32_t digit_base[kSortRadix];
-  __shared__ uint32_t warp_cnt[kSortThreads / 32][kSortRadix];
+  extern __shared__ __align__(16) unsigned char smem[];
+  uint64_t* s_keys = (uint64_t*)smem;                                             // [kSortTile]
+  uint32_t* s_vals = (uint32_t*)(s_keys + kSortTile);                             // [kSortTile]
+  uint32_t(*warp_cnt)[kSortRadix] = (uint32_t(*)[kSortRadix])(s_vals + kSortTile);  // [warps][radix]
+  uint32_t* glob_base = (uint32_t*)(warp_cnt + kSortThreads / 32);                // [radix] where this tile's run of a digit starts
+  uint32_t* tile_start = glob_base + kSortRadix;                                  // [radix] start of the digit inside the tile
   __shared__ uint32_t scan_tmp[8];
   const int64_t n = eff_count(n_cap, d_n);
+  const int64_t tile_base = (int64_t)blockIdx.x * kSortTile;
+  if (tile_base >= n) return;                                   // nothing in this tile (device-side count below capacity)
+  const int tile_n = (int)(n - tile_base < kSortTile ? n - tile_base : kSortTile);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // exclusive scan of the 256 digit totals (global start of every digit) + this CTA's offset inside the digit
+  // global start of every digit (exclusive scan of the 256 totals) + this tile's offset inside the digit
   {
     uint32_t v = digit_total[threadIdx.x];
     uint32_t x = v;
@@ -91,49 +103,79 @@ sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
 #pragma unroll
     for (int w = 0; w < 8; ++w)
       if (w < warp) woff += scan_tmp[w];
-    digit_base[threadIdx.x] = woff + x - v + block_hist[(size_t)threadIdx.x * num_blocks + blockIdx.x];
+    glob_base[threadIdx.x] = woff + x - v + block_hist[(size_t)threadIdx.x * num_blocks + blockIdx.x];
   }
 #pragma unroll
   for (int w = 0; w < kSortThreads / 32; ++w) warp_cnt[w][threadIdx.x] = 0;
   __syncthreads();
 
-  const int64_t base = (int64_t)blockIdx.x * kSortTile + (int64_t)warp * (kSortItems * 32) + lane;
+  // warp w owns items [w * 512, (w + 1) * 512) of the tile, 32 at a time: (warp, round, lane) order = key order
+  const int64_t base = tile_base + (int64_t)warp * (kSortItems * 32) + lane;
   uint64_t k[kSortItems];
+  uint32_t v[kSortItems];
 #pragma unroll
   for (int c = 0; c < kSortItems; ++c) {
-    int64_t i = base + c * 32;
+    const int64_t i = base + c * 32;
     k[c] = i < n ? keys[i] : 0;
+    v[c] = i < n ? (vals ? vals[i] : (uint32_t)i) : 0u;
     if (i < n) atomicAdd(&warp_cnt[warp][digit_of(k[c], shift)], 1u);
   }
   __syncthreads();
-  // per digit: turn the per-warp counts into per-warp start positions (warp order = key order)
+  // per digit: counts of the warps -> start of every warp's keys inside the tile (digit-major, then warp order)
   {
-    uint32_t run = digit_base[threadIdx.x];
+    uint32_t run = 0;
 #pragma unroll
     for (int w = 0; w < kSortThreads / 32; ++w) {
-      uint32_t c = warp_cnt[w][threadIdx.x];
+      const uint32_t c = warp_cnt[w][threadIdx.x];
       warp_cnt[w][threadIdx.x] = run;
       run += c;
     }
+    uint32_t x = run;   // keys of this digit in the tile
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    __syncthreads();    // scan_tmp is free again
+    if (lane == 31) scan_tmp[warp] = x;
+    __syncthreads();
+    uint32_t woff = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w)
+      if (w < warp) woff += scan_tmp[w];
+    const uint32_t start = woff + x - run;
+    tile_start[threadIdx.x] = start;
+#pragma unroll
+    for (int w = 0; w < kSortThreads / 32; ++w) warp_cnt[w][threadIdx.x] += start;
   }
   __syncthreads();
+  // stable rank of every key inside the tile; the tile is laid out in digit order in shared memory
   const uint32_t lt_mask = (1u << lane) - 1u;
 #pragma unroll
   for (int c = 0; c < kSortItems; ++c) {
-    int64_t i = base + c * 32;
-    bool valid = i < n;
-    uint32_t d = valid ? digit_of(k[c], shift) : (uint32_t)kSortRadix;
-    uint32_t peers = __match_any_sync(0xffffffffu, d);
-    uint32_t rank = __popc(peers & lt_mask);
+    const int64_t i = base + c * 32;
+    const bool valid = i < n;
+    const uint32_t d = valid ? digit_of(k[c], shift) : (uint32_t)kSortRadix;
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    const uint32_t rank = __popc(peers & lt_mask);
     uint32_t pos = 0;
     if (valid) pos = warp_cnt[warp][d] + rank;
     __syncwarp();
     if (valid && rank == 0) warp_cnt[warp][d] += __popc(peers);
     __syncwarp();
     if (valid) {
-      out_keys[pos] = k[c];
-      out_vals[pos] = vals ? vals[i] : (uint32_t)i;
+      s_keys[pos] = k[c];
+      s_vals[pos] = v[c];
     }
+  }
+  __syncthreads();
+  // write-out: consecutive threads take consecutive tile positions, i.e. runs of one digit -> consecutive addresses
+  for (int j = threadIdx.x; j < tile_n; j += kSortThreads) {
+    const uint64_t key = s_keys[j];
+    const uint32_t d = digit_of(key, shift);
+    const uint32_t g = glob_base[d] + ((uint32_t)j - tile_start[d]);
+    out_keys[g] = key;
+    out_vals[g] = s_vals[j];
   }
 }
 
@@ -162,11 +204,20 @@ int radix_sort_pairs(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_
   if (passes == 0 && iota_vals) passes = 1;  // still has to materialise the payload
   uint64_t *kin = keys, *kout = keys_alt;
   uint32_t *vin = vals, *vout = vals_alt;
+  static bool smem_set = false;   // the attribute is per device function and context: set it once per process and device
+  static int smem_dev = -1;
+  int dev = 0;
+  SGL_CUDA_CHECK(cudaGetDevice(&dev));
+  if (!smem_set || smem_dev != dev) {
+    SGL_CUDA_CHECK(cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScatterSmem));
+    smem_set = true;
+    smem_dev = dev;
+  }
   for (int p = 0; p < passes; ++p) {
     int shift = p * kSortRadixBits;
     sort_hist_kernel<<<num_blocks, kSortThreads, 0, stream>>>(kin, n, d_n, shift, block_hist, num_blocks);
     sort_scan_kernel<<<kSortRadix, 256, 0, stream>>>(block_hist, num_blocks, digit_total);
-    sort_scatter_kernel<<<num_blocks, kSortThreads, 0, stream>>>(kin, (p == 0 && iota_vals) ? nullptr : vin, n, d_n,
+    sort_scatter_kernel<<<num_blocks, kSortThreads, kScatterSmem, stream>>>(kin, (p == 0 && iota_vals) ? nullptr : vin, n, d_n,
                                                                  shift, block_hist, num_blocks, digit_total, kout, vout);
     SGL_LAUNCH_CHECK();
     uint64_t* tk = kin; kin = kout; kout = tk;

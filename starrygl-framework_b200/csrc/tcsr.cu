@@ -4,8 +4,9 @@
 //   2. tcsr_pack_kernel         64-bit sort key = (node << ts_bits) | (ts - ts_min)
 //   3. stable LSD radix sort    on the populated key bits, payload = input position
 //      (when node bits + timestamp bits exceed 64: sort by timestamp first, then stably by node)
-//   4. tcsr_emit_kernel         gathers nbr/ts/eid through the permutation and writes indptr from the
-//                               row boundaries of the sorted keys (no atomics, no separate prefix sum)
+//   4. tcsr_emit_kernel         reads the sorted keys sequentially (row and timestamp of every edge), gathers only the
+//                               neighbour / edge id through the permutation and writes indptr from the row
+//                               boundaries of the sorted keys (no atomics, no separate prefix sum)
 #include "sort.cuh"
 
 namespace sgl {
@@ -69,20 +70,31 @@ tcsr_pack_kernel(const int64_t* __restrict__ key, const int64_t* __restrict__ ts
   }
 }
 
+// The sorted keys are read sequentially and already hold the row of every edge (and, when node and timestamp share one
+// key, its timestamp): only the neighbour (and the edge id, when given) are gathered through the permutation.
+// combined != 0: key = (node << ts_bits) | (ts - ts_min); else key = node and the timestamp is gathered too.
 __global__ void __launch_bounds__(256)
-tcsr_emit_kernel(const uint32_t* __restrict__ perm, const int64_t* __restrict__ key, const int64_t* __restrict__ nbr,
-                 const int64_t* __restrict__ ts, const int64_t* __restrict__ eid, int64_t m, int64_t num_nodes,
-                 int64_t* __restrict__ indptr, int64_t* __restrict__ out_nbr, int64_t* __restrict__ out_ts,
-                 int64_t* __restrict__ out_eid, int64_t* __restrict__ out_perm) {
+tcsr_emit_kernel(const uint64_t* __restrict__ sorted_keys, const uint32_t* __restrict__ perm, int combined, int ts_bits,
+                 long long ts_min, const int64_t* __restrict__ nbr, const int64_t* __restrict__ ts,
+                 const int64_t* __restrict__ eid, int64_t m, int64_t num_nodes, int64_t* __restrict__ indptr,
+                 int64_t* __restrict__ out_nbr, int64_t* __restrict__ out_ts, int64_t* __restrict__ out_eid,
+                 int64_t* __restrict__ out_perm) {
+  const bool split = combined && ts_bits < 64;
+  const uint64_t ts_mask = ts_bits >= 64 ? ~0ull : ((1ull << ts_bits) - 1ull);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < m; i += (int64_t)gridDim.x * blockDim.x) {
-    uint32_t p = perm[i];
+    const uint32_t p = perm[i];
+    const uint64_t k = sorted_keys[i];
     out_nbr[i] = nbr[p];
-    out_ts[i] = ts[p];
+    out_ts[i] = combined ? (int64_t)((k & ts_mask) + (uint64_t)ts_min) : ts[p];
     out_eid[i] = eid ? eid[p] : (int64_t)p;
     if (out_perm) out_perm[i] = (int64_t)p;
     // row boundaries: every node id in (prev_node, this_node] starts at position i
-    int64_t node = key[p];
-    int64_t prev = i == 0 ? -1 : key[perm[i - 1]];
+    const int64_t node = combined ? (split ? (int64_t)(k >> ts_bits) : 0) : (int64_t)k;
+    int64_t prev = -1;
+    if (i > 0) {
+      const uint64_t kp = sorted_keys[i - 1];
+      prev = combined ? (split ? (int64_t)(kp >> ts_bits) : 0) : (int64_t)kp;
+    }
     for (int64_t v = prev + 1; v <= node; ++v) indptr[v] = i;
     if (i == m - 1)
       for (int64_t v = node + 1; v <= num_nodes; ++v) indptr[v] = m;
@@ -145,11 +157,14 @@ extern "C" int sgl_tcsr_build(int64_t num_nodes, int64_t m, const int64_t* key, 
   const int ts_bits = bits_for((uint64_t)h.ts_max - (uint64_t)h.ts_min);
   const int id_bits = bits_for(num_nodes > 0 ? (uint64_t)(num_nodes - 1) : 0);
   int in_alt = 0;
-  if (ts_bits + id_bits <= 64) {
+  const uint64_t* sorted_keys = nullptr;
+  const bool combined = ts_bits + id_bits <= 64;
+  if (combined) {
     tcsr_pack_kernel<<<grid, 256, 0, stream>>>(key, ts, nullptr, m, h.ts_min, ts_bits, 0, k0);
     SGL_LAUNCH_CHECK();
     int rc = radix_sort_pairs(k0, v0, k1, v1, m, nullptr, ts_bits + id_bits, true, &in_alt, sort_ws, sort_bytes, stream);
     if (rc) return rc;
+    sorted_keys = in_alt ? k1 : k0;
   } else {
     // two stable rounds: by timestamp, then by node id
     tcsr_pack_kernel<<<grid, 256, 0, stream>>>(key, ts, nullptr, m, h.ts_min, ts_bits, 1, k0);
@@ -165,11 +180,12 @@ extern "C" int sgl_tcsr_build(int64_t num_nodes, int64_t m, const int64_t* key, 
     int in_alt2 = 0;
     rc = radix_sort_pairs(kk, perm1, kk_alt, vv_alt, m, nullptr, id_bits, false, &in_alt2, sort_ws, sort_bytes, stream);
     if (rc) return rc;
+    sorted_keys = in_alt2 ? kk_alt : kk;
     in_alt = in_alt2 ? !in_alt : in_alt;
   }
   const uint32_t* perm = in_alt ? v1 : v0;
-  tcsr_emit_kernel<<<grid, 256, 0, stream>>>(perm, key, nbr, ts, eid, m, num_nodes, indptr, out_nbr, out_ts, out_eid,
-                                             out_perm);
+  tcsr_emit_kernel<<<grid, 256, 0, stream>>>(sorted_keys, perm, combined ? 1 : 0, ts_bits, h.ts_min, nbr, ts, eid, m, num_nodes,
+                                             indptr, out_nbr, out_ts, out_eid, out_perm);
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }
