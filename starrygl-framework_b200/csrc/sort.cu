@@ -1,4 +1,4 @@
-// Stable LSD radix sort, 8 bits per pass, three kernels per pass:
+// Stable LSD radix sort, 8 or 9 bits per pass (whichever needs fewer passes for the key width), three kernels per pass:
 //   1. sort_hist_kernel    per-CTA digit histogram of its tile (4096 keys)          -> block_hist[digit][cta]
 //   2. sort_scan_kernel    one CTA per digit: exclusive scan over CTAs + digit total
 //   3. sort_scatter_kernel re-reads the tile, ranks keys stably (warp match + per-warp running counters), lays the
@@ -11,26 +11,58 @@ namespace sgl {
 
 namespace {
 
+constexpr int kMaxRadixBits = 9;
+constexpr int kMaxRadix = 1 << kMaxRadixBits;
+constexpr int kWarps = kSortThreads / 32;
+
+template <int BITS>
 __device__ __forceinline__ uint32_t digit_of(uint64_t key, int shift) {
-  return (uint32_t)(key >> shift) & (kSortRadix - 1);
+  return (uint32_t)(key >> shift) & ((1u << BITS) - 1u);
 }
 
+// exclusive scan of one value per thread across the CTA (256 threads); tmp = 8 words of shared memory
+__device__ __forceinline__ uint32_t cta_scan_u32(uint32_t v, uint32_t* tmp) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  __syncthreads();   // tmp may still be read from an earlier call
+  if (lane == 31) tmp[warp] = x;
+  __syncthreads();
+  uint32_t woff = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w)
+    if (w < warp) woff += tmp[w];
+  return woff + x - v;
+}
+
+// Thread t owns the digits [t * DPT, (t + 1) * DPT), DPT = radix / 256.
+template <int BITS>
 __global__ void __launch_bounds__(kSortThreads)
 sort_hist_kernel(const uint64_t* __restrict__ keys, int64_t n_cap, const int64_t* d_n, int shift,
                  uint32_t* __restrict__ block_hist, int num_blocks) {
-  __shared__ uint32_t hist[kSortRadix];
+  constexpr int RADIX = 1 << BITS, DPT = RADIX / kSortThreads;
+  __shared__ uint32_t hist[RADIX];
   const int64_t n = eff_count(n_cap, d_n);
-  hist[threadIdx.x] = 0;
+#pragma unroll
+  for (int q = 0; q < DPT; ++q) hist[threadIdx.x * DPT + q] = 0;
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t base = (int64_t)blockIdx.x * kSortTile + (int64_t)warp * (kSortItems * 32) + lane;
 #pragma unroll
   for (int c = 0; c < kSortItems; ++c) {
     int64_t i = base + c * 32;
-    if (i < n) atomicAdd(&hist[digit_of(keys[i], shift)], 1u);
+    if (i < n) atomicAdd(&hist[digit_of<BITS>(keys[i], shift)], 1u);
   }
   __syncthreads();
-  block_hist[(size_t)threadIdx.x * num_blocks + blockIdx.x] = hist[threadIdx.x];
+#pragma unroll
+  for (int q = 0; q < DPT; ++q) {
+    const int d = threadIdx.x * DPT + q;
+    block_hist[(size_t)d * num_blocks + blockIdx.x] = hist[d];
+  }
 }
 
 // one CTA per digit: exclusive scan of block_hist[digit][0..num_blocks) in place, total -> digit_total[digit]
@@ -68,45 +100,48 @@ sort_scan_kernel(uint32_t* __restrict__ block_hist, int num_blocks, uint32_t* __
 
 // Shared memory of the scatter kernel: the tile's keys and payloads in digit order, the per-warp digit counters and
 // two per-digit tables.
-constexpr size_t kScatterSmem = (size_t)kSortTile * 12 + (size_t)(kSortThreads / 32) * kSortRadix * 4 + 2 * kSortRadix * 4;
+constexpr size_t scatter_smem(int bits) { return (size_t)kSortTile * 12 + (size_t)(kWarps + 2) * ((size_t)1 << bits) * 4; }
 
+template <int BITS>
 __global__ void __launch_bounds__(kSortThreads, 3)   // three tiles per SM: their load / rank / write phases overlap
 sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ vals, int64_t n_cap,
                     const int64_t* d_n, int shift, const uint32_t* __restrict__ block_hist, int num_blocks,
                     const uint32_t* __restrict__ digit_total, uint64_t* __restrict__ out_keys,
                     uint32_t* __restrict__ out_vals) {
+  constexpr int RADIX = 1 << BITS, DPT = RADIX / kSortThreads;
   extern __shared__ __align__(16) unsigned char smem[];
-  uint64_t* s_keys = (uint64_t*)smem;                                             // [kSortTile]
-  uint32_t* s_vals = (uint32_t*)(s_keys + kSortTile);                             // [kSortTile]
-  uint32_t(*warp_cnt)[kSortRadix] = (uint32_t(*)[kSortRadix])(s_vals + kSortTile);  // [warps][radix]
-  uint32_t* glob_base = (uint32_t*)(warp_cnt + kSortThreads / 32);                // [radix] where this tile's run of a digit starts
-  uint32_t* tile_start = glob_base + kSortRadix;                                  // [radix] start of the digit inside the tile
-  __shared__ uint32_t scan_tmp[8];
+  uint64_t* s_keys = (uint64_t*)smem;                                 // [kSortTile]
+  uint32_t* s_vals = (uint32_t*)(s_keys + kSortTile);                 // [kSortTile]
+  uint32_t(*warp_cnt)[RADIX] = (uint32_t(*)[RADIX])(s_vals + kSortTile);  // [warps][radix]
+  uint32_t* glob_base = (uint32_t*)(warp_cnt + kWarps);               // [radix] where this tile's run of a digit starts
+  uint32_t* tile_start = glob_base + RADIX;                           // [radix] start of the digit inside the tile
+  __shared__ uint32_t scan_tmp[kWarps];
   const int64_t n = eff_count(n_cap, d_n);
   const int64_t tile_base = (int64_t)blockIdx.x * kSortTile;
   if (tile_base >= n) return;                                   // nothing in this tile (device-side count below capacity)
   const int tile_n = (int)(n - tile_base < kSortTile ? n - tile_base : kSortTile);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int d0 = threadIdx.x * DPT;
 
-  // global start of every digit (exclusive scan of the 256 totals) + this tile's offset inside the digit
+  // global start of every digit (exclusive scan of the totals) + this tile's offset inside the digit
   {
-    uint32_t v = digit_total[threadIdx.x];
-    uint32_t x = v;
+    uint32_t t[DPT], sum = 0;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
-      if (lane >= o) x += y;
+    for (int q = 0; q < DPT; ++q) {
+      t[q] = digit_total[d0 + q];
+      sum += t[q];
     }
-    if (lane == 31) scan_tmp[warp] = x;
-    __syncthreads();
-    uint32_t woff = 0;
+    uint32_t start = cta_scan_u32(sum, scan_tmp);
 #pragma unroll
-    for (int w = 0; w < 8; ++w)
-      if (w < warp) woff += scan_tmp[w];
-    glob_base[threadIdx.x] = woff + x - v + block_hist[(size_t)threadIdx.x * num_blocks + blockIdx.x];
+    for (int q = 0; q < DPT; ++q) {
+      glob_base[d0 + q] = start + block_hist[(size_t)(d0 + q) * num_blocks + blockIdx.x];
+      start += t[q];
+    }
   }
 #pragma unroll
-  for (int w = 0; w < kSortThreads / 32; ++w) warp_cnt[w][threadIdx.x] = 0;
+  for (int w = 0; w < kWarps; ++w)
+#pragma unroll
+    for (int q = 0; q < DPT; ++q) warp_cnt[w][d0 + q] = 0;
   __syncthreads();
 
   // warp w owns items [w * 512, (w + 1) * 512) of the tile, 32 at a time: (warp, round, lane) order = key order
@@ -118,35 +153,32 @@ sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
     const int64_t i = base + c * 32;
     k[c] = i < n ? keys[i] : 0;
     v[c] = i < n ? (vals ? vals[i] : (uint32_t)i) : 0u;
-    if (i < n) atomicAdd(&warp_cnt[warp][digit_of(k[c], shift)], 1u);
+    if (i < n) atomicAdd(&warp_cnt[warp][digit_of<BITS>(k[c], shift)], 1u);
   }
   __syncthreads();
   // per digit: counts of the warps -> start of every warp's keys inside the tile (digit-major, then warp order)
   {
-    uint32_t run = 0;
+    uint32_t cnt[DPT], sum = 0;
 #pragma unroll
-    for (int w = 0; w < kSortThreads / 32; ++w) {
-      const uint32_t c = warp_cnt[w][threadIdx.x];
-      warp_cnt[w][threadIdx.x] = run;
-      run += c;
+    for (int q = 0; q < DPT; ++q) {
+      uint32_t run = 0;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const uint32_t c = warp_cnt[w][d0 + q];
+        warp_cnt[w][d0 + q] = run;
+        run += c;
+      }
+      cnt[q] = run;   // keys of this digit in the tile
+      sum += run;
     }
-    uint32_t x = run;   // keys of this digit in the tile
+    uint32_t start = cta_scan_u32(sum, scan_tmp);
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
-      if (lane >= o) x += y;
+    for (int q = 0; q < DPT; ++q) {
+      tile_start[d0 + q] = start;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) warp_cnt[w][d0 + q] += start;
+      start += cnt[q];
     }
-    __syncthreads();    // scan_tmp is free again
-    if (lane == 31) scan_tmp[warp] = x;
-    __syncthreads();
-    uint32_t woff = 0;
-#pragma unroll
-    for (int w = 0; w < 8; ++w)
-      if (w < warp) woff += scan_tmp[w];
-    const uint32_t start = woff + x - run;
-    tile_start[threadIdx.x] = start;
-#pragma unroll
-    for (int w = 0; w < kSortThreads / 32; ++w) warp_cnt[w][threadIdx.x] += start;
   }
   __syncthreads();
   // stable rank of every key inside the tile; the tile is laid out in digit order in shared memory
@@ -155,7 +187,7 @@ sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
   for (int c = 0; c < kSortItems; ++c) {
     const int64_t i = base + c * 32;
     const bool valid = i < n;
-    const uint32_t d = valid ? digit_of(k[c], shift) : (uint32_t)kSortRadix;
+    const uint32_t d = valid ? digit_of<BITS>(k[c], shift) : (uint32_t)RADIX;
     const uint32_t peers = __match_any_sync(0xffffffffu, d);
     const uint32_t rank = __popc(peers & lt_mask);
     uint32_t pos = 0;
@@ -172,11 +204,37 @@ sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
   // write-out: consecutive threads take consecutive tile positions, i.e. runs of one digit -> consecutive addresses
   for (int j = threadIdx.x; j < tile_n; j += kSortThreads) {
     const uint64_t key = s_keys[j];
-    const uint32_t d = digit_of(key, shift);
+    const uint32_t d = digit_of<BITS>(key, shift);
     const uint32_t g = glob_base[d] + ((uint32_t)j - tile_start[d]);
     out_keys[g] = key;
     out_vals[g] = s_vals[j];
   }
+}
+
+template <int BITS>
+int run_passes(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_t* vals_alt, int64_t n, const int64_t* d_n,
+               int passes, bool iota_vals, uint32_t* block_hist, uint32_t* digit_total, int num_blocks, cudaStream_t stream) {
+  static int smem_dev = -1;   // the attribute is per device function and context: set it once per process and device
+  int dev = 0;
+  SGL_CUDA_CHECK(cudaGetDevice(&dev));
+  if (smem_dev != dev) {
+    SGL_CUDA_CHECK(cudaFuncSetAttribute(sort_scatter_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)scatter_smem(BITS)));
+    smem_dev = dev;
+  }
+  uint64_t *kin = keys, *kout = keys_alt;
+  uint32_t *vin = vals, *vout = vals_alt;
+  for (int p = 0; p < passes; ++p) {
+    const int shift = p * BITS;
+    sort_hist_kernel<BITS><<<num_blocks, kSortThreads, 0, stream>>>(kin, n, d_n, shift, block_hist, num_blocks);
+    sort_scan_kernel<<<1 << BITS, 256, 0, stream>>>(block_hist, num_blocks, digit_total);
+    sort_scatter_kernel<BITS><<<num_blocks, kSortThreads, scatter_smem(BITS), stream>>>(
+        kin, (p == 0 && iota_vals) ? nullptr : vin, n, d_n, shift, block_hist, num_blocks, digit_total, kout, vout);
+    SGL_LAUNCH_CHECK();
+    uint64_t* tk = kin; kin = kout; kout = tk;
+    uint32_t* tv = vin; vin = vout; vout = tv;
+  }
+  return SGL_OK;
 }
 
 }  // namespace
@@ -184,7 +242,7 @@ sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
 size_t radix_sort_ws_bytes(int64_t n) {
   int64_t nb = (n + kSortTile - 1) / kSortTile;
   if (nb < 1) nb = 1;
-  return align_up((size_t)nb * kSortRadix * sizeof(uint32_t)) + align_up(kSortRadix * sizeof(uint32_t));
+  return align_up((size_t)nb * kMaxRadix * sizeof(uint32_t)) + align_up(kMaxRadix * sizeof(uint32_t));
 }
 
 int radix_sort_pairs(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_t* vals_alt, int64_t n,
@@ -197,32 +255,17 @@ int radix_sort_pairs(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_
   SGL_REQUIRE(keys && vals && keys_alt && vals_alt, SGL_ERR_ARG, "radix sort: null buffer");
   const int num_blocks = (int)((n + kSortTile - 1) / kSortTile);
   WsCarver c(ws, ws_bytes);
-  uint32_t* block_hist = c.take<uint32_t>((size_t)num_blocks * kSortRadix);
-  uint32_t* digit_total = c.take<uint32_t>(kSortRadix);
+  uint32_t* block_hist = c.take<uint32_t>((size_t)num_blocks * kMaxRadix);
+  uint32_t* digit_total = c.take<uint32_t>(kMaxRadix);
   SGL_REQUIRE(c.ok(), SGL_ERR_WORKSPACE, "radix sort: workspace %zu < %zu bytes", ws_bytes, radix_sort_ws_bytes(n));
-  int passes = (num_bits + kSortRadixBits - 1) / kSortRadixBits;
-  if (passes == 0 && iota_vals) passes = 1;  // still has to materialise the payload
-  uint64_t *kin = keys, *kout = keys_alt;
-  uint32_t *vin = vals, *vout = vals_alt;
-  static bool smem_set = false;   // the attribute is per device function and context: set it once per process and device
-  static int smem_dev = -1;
-  int dev = 0;
-  SGL_CUDA_CHECK(cudaGetDevice(&dev));
-  if (!smem_set || smem_dev != dev) {
-    SGL_CUDA_CHECK(cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScatterSmem));
-    smem_set = true;
-    smem_dev = dev;
-  }
-  for (int p = 0; p < passes; ++p) {
-    int shift = p * kSortRadixBits;
-    sort_hist_kernel<<<num_blocks, kSortThreads, 0, stream>>>(kin, n, d_n, shift, block_hist, num_blocks);
-    sort_scan_kernel<<<kSortRadix, 256, 0, stream>>>(block_hist, num_blocks, digit_total);
-    sort_scatter_kernel<<<num_blocks, kSortThreads, kScatterSmem, stream>>>(kin, (p == 0 && iota_vals) ? nullptr : vin, n, d_n,
-                                                                 shift, block_hist, num_blocks, digit_total, kout, vout);
-    SGL_LAUNCH_CHECK();
-    uint64_t* tk = kin; kin = kout; kout = tk;
-    uint32_t* tv = vin; vin = vout; vout = tv;
-  }
+  // 9-bit digits when they save a pass (e.g. 44 key bits: 5 passes instead of 6); their runs per tile are half as long
+  int passes8 = (num_bits + 7) / 8, passes9 = (num_bits + 8) / 9;
+  if (passes8 == 0 && iota_vals) passes8 = passes9 = 1;  // still has to materialise the payload
+  const bool wide = passes9 < passes8;
+  const int passes = wide ? passes9 : passes8;
+  int rc = wide ? run_passes<9>(keys, vals, keys_alt, vals_alt, n, d_n, passes, iota_vals, block_hist, digit_total, num_blocks, stream)
+                : run_passes<8>(keys, vals, keys_alt, vals_alt, n, d_n, passes, iota_vals, block_hist, digit_total, num_blocks, stream);
+  if (rc) return rc;
   *result_in_alt = (passes & 1);
   return SGL_OK;
 }

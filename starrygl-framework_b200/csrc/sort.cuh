@@ -4,8 +4,6 @@
 
 namespace sgl {
 
-constexpr int kSortRadixBits = 8;
-constexpr int kSortRadix = 1 << kSortRadixBits;
 constexpr int kSortThreads = 256;
 constexpr int kSortItems = 16;
 constexpr int kSortTile = kSortThreads * kSortItems;  // keys per CTA

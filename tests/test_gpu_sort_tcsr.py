@@ -9,7 +9,9 @@ from gpu_util import cu, load, npy, build_graph
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("n,bits", [(0, 64), (1, 64), (33, 8), (4096, 16), (4097, 40), (100003, 64), (1 << 20, 24)])
+# key widths for which 8-bit digits are used, and widths where 9-bit digits save a pass (9, 17, 27, 44, 63)
+@pytest.mark.parametrize("n,bits", [(0, 64), (1, 64), (33, 8), (4096, 16), (4097, 40), (100003, 64), (1 << 20, 24),
+                                    (5000, 9), (70001, 17), (12345, 27), (300000, 44), (9999, 63), (40, 1)])
 def test_radix_sort_stable(n, bits):
     from starrygl import ops
     rng = np.random.default_rng(n + bits)
