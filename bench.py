@@ -324,6 +324,7 @@ def main():
                     help="result copy to the host: device-counted prefix (exact bytes) or whole-capacity copies")
     ap.add_argument("--no-numa-bind", action="store_true", help="N > 1: do not bind the rank to the CPUs of its GPU's NUMA node")
     ap.add_argument("--row-align", type=int, default=0, help="pad the feature table's rows in HBM to this many bytes (0 = dense)")
+    ap.add_argument("--tcsr-only", action="store_true", help="time the T-CSR construction of the benchmark graph and exit")
     ap.add_argument("--no-step-graph", action="store_true",
                     help="issue sample+gather as one fused foreign call (three kernel launches) instead of one graph launch")
     ap.add_argument("--num-nodes", type=int, default=NUM_NODES, help="smaller graphs are for profiler captures only")
@@ -353,6 +354,22 @@ def main():
 
     # ---- set-up (untimed): graph, T-CSR, feature table, batches -------------------------------------------
     src, dst, ts, gen = make_graph(dev, seed=rank)
+    if args.tcsr_only:
+        # side measurement (not the benchmark line): T-CSR construction of the benchmark graph, CUDA-event timed
+        ops.tcsr_build(src, dst, ts, None, NUM_NODES)
+        e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        e0_.record()
+        for _ in range(reps):
+            ops.tcsr_build(src, dst, ts, None, NUM_NODES)
+        e1_.record()
+        torch.cuda.synchronize(dev)
+        ms_ = e0_.elapsed_time(e1_) / reps
+        alg_ = NUM_EDGES * 56 + (NUM_NODES + 1) * 8 + 6 * 2 * NUM_EDGES * 12
+        if rank == 0:
+            print(json.dumps({"tcsr_build_ms": ms_, "edges": NUM_EDGES, "nodes": NUM_NODES, "algorithmic_bytes": alg_,
+                              "algorithmic_GBps": alg_ / ms_ / 1e6}), file=out_stream, flush=True)
+        return
     g = ops.tcsr_build(src, dst, ts, None, NUM_NODES)
     b_roots, b_ts = make_batches(src, ts, gen, dev)
     del src, dst, ts
