@@ -541,8 +541,8 @@ def main():
         buf = (C_.c_uint64 * (n_tl * 8))()
         _C.lib().sgl_p2p_route_timeline(p2p.ctx, buf, n_tl)
         tl = np.array(buf, dtype=np.uint64).reshape(n_tl, 8).astype(np.float64)[args.warmup + 50:args.warmup + args.steps - 10] / 1e3
-        sys.stderr.write("P2P timeline (us): send dur %.1f | send start->next start %.1f | apply launch->flags %.1f | flags->end %.1f | "
-                         "apply start->next start %.1f | send end -> apply(flags seen) %.1f | resident before start: send %.1f apply %.1f\n" % (
+        sys.stderr.write("P2P timeline (us): send dur %.1f | send start->next start %.1f | apply start->first CTA done %.1f | first CTA done->end %.1f | "
+                         "apply start->next start %.1f | send end -> apply first CTA done %.1f | resident before start: send %.1f apply %.1f\n" % (
                              np.median(tl[:, 1] - tl[:, 0]), np.median(np.diff(tl[:, 0])), np.median(tl[:, 3] - tl[:, 2]),
                              np.median(tl[:, 4] - tl[:, 3]), np.median(np.diff(tl[:, 2])), np.median(tl[:, 3] - tl[:, 1]),
                              np.median(tl[:, 0] - tl[:, 5]), np.median(tl[:, 2] - tl[:, 6])))

@@ -32,10 +32,11 @@ namespace {
 
 constexpr int kMaxWorld = 16;
 constexpr int kThreads = 128;   // 4 rows per CTA
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // default bound of every device-side wait (SGL_P2P_WAIT_MS overrides)
 
 struct P2PCfg {
   int dbg;
+  unsigned long long wait_ns;   // bound of every device-side wait
   unsigned long long* tl;   // optional timeline buffer [steps][8] (diagnostics)
   int rank, world, ring;
   int64_t cap_rows;
@@ -71,11 +72,11 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // spin until *p >= want; false when the limit expires
-__device__ __forceinline__ bool wait_at_least(const unsigned long long* p, unsigned long long want) {
+__device__ __forceinline__ bool wait_at_least(const unsigned long long* p, unsigned long long want, unsigned long long limit_ns) {
   const volatile unsigned long long* vp = p;
   if (*vp >= want) return true;
   const unsigned long long t0 = now_ns();
-  while (now_ns() - t0 < kWaitLimitNs) {
+  while (now_ns() - t0 < limit_ns) {
     if (*vp >= want) return true;
     __nanosleep(200);
   }
@@ -93,13 +94,13 @@ __device__ __forceinline__ uint4 load_line(const uint4* p) {
 }
 
 // re-reads a line until both halves carry the tag; false when the limit expires
-__device__ __noinline__ bool poll_line(const uint4* p, uint32_t tag, uint4* v) {
+__device__ __noinline__ bool poll_line(const uint4* p, uint32_t tag, uint4* v, unsigned long long limit_ns) {
   const unsigned long long t0 = now_ns();
   do {
     *v = load_line(p);
     if (v->y == tag && v->w == tag) return true;
     __nanosleep(100);
-  } while (now_ns() - t0 < kWaitLimitNs);
+  } while (now_ns() - t0 < limit_ns);
   return false;
 }
 
@@ -136,7 +137,7 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
   __syncthreads();
   // flow control: the ring slot may be overwritten once every receiver has applied the step that used it last
   if (threadIdx.x < c.world && step >= (unsigned long long)c.ring) {
-    if (!wait_at_least(c.acks + threadIdx.x, step - c.ring + 1)) s_ok = 0;
+    if (!wait_at_least(c.acks + threadIdx.x, step - c.ring + 1, c.wait_ns)) s_ok = 0;
   }
   __syncthreads();
   if (s_ok == 0) {
@@ -216,9 +217,9 @@ p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, 
       a = load_line(row + 2 * lane);
       b = load_line(row + 2 * lane + 1);
     }
-    if (sa.y != tag || sa.w != tag) ok = ok && poll_line(row + la, tag, &sa);
+    if (sa.y != tag || sa.w != tag) ok = ok && poll_line(row + la, tag, &sa, c.wait_ns);
     if (la == lb) sb = sa;
-    else if (sb.y != tag || sb.w != tag) ok = ok && poll_line(row + lb, tag, &sb);
+    else if (sb.y != tag || sb.w != tag) ok = ok && poll_line(row + lb, tag, &sb, c.wait_ns);
     if (!ok) break;
     const uint32_t lo = (width & 1) ? sa.z : sa.x;
     const uint32_t hi = ((width + 1) & 1) ? sb.z : sb.x;
@@ -230,8 +231,8 @@ p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, 
         a = load_line(row + 2 * l);
         b = load_line(row + 2 * l + 1);
       }
-      if (a.y != tag || a.w != tag) ok = ok && poll_line(row + 2 * l, tag, &a);
-      if (b.y != tag || b.w != tag) ok = ok && poll_line(row + 2 * l + 1, tag, &b);
+      if (a.y != tag || a.w != tag) ok = ok && poll_line(row + 2 * l, tag, &a, c.wait_ns);
+      if (b.y != tag || b.w != tag) ok = ok && poll_line(row + 2 * l + 1, tag, &b, c.wait_ns);
       if (!ok || bad) break;
       if (vec_ok && (l + 1) * 4 <= dim) {
         ((uint4*)(data + dslot * dim))[l] = make_uint4(a.x, a.z, b.x, b.z);
@@ -324,6 +325,11 @@ extern "C" int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_r
               SGL_ERR_ARG, "p2p_route_create: bad argument (world <= %d, ring >= 2, pitch a multiple of 4)", kMaxWorld);
   Ctx* x = new Ctx();
   P2PCfg& c = x->cfg;
+  c.wait_ns = kWaitLimitNs;
+  if (const char* w = getenv("SGL_P2P_WAIT_MS")) {
+    const long ms = atol(w);
+    if (ms >= 1 && ms <= 60000) c.wait_ns = (unsigned long long)ms * 1000000ull;
+  }
   c.dbg = getenv("SGL_P2P_DBG") ? atoi(getenv("SGL_P2P_DBG")) : 0;   // 2 = record a per-step kernel timeline (diagnostics)
   c.rank = rank; c.world = world; c.ring = ring; c.cap_rows = cap_rows; c.pitch = (uint32_t)pitch_floats;
   const size_t hb = header_bytes(world);

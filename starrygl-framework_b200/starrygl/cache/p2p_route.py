@@ -113,7 +113,7 @@ class P2PCacheRoute:
         """Pre-convert every argument of ``push`` + ``wait`` for one (table, plan, state) combination and return a
         callable that runs the step (the step number is filled in per call).  With one stream the step is ONE foreign
         call; with a separate ``recv_stream`` the send kernels and the apply kernels form two independent chains
-        (the apply kernel of a step only depends on the senders' flags, not on this rank's stream order), which
+        (the apply kernel of a step only depends on the senders' tagged staging lines, not on this rank's stream order), which
         halves the per-step latency of the route."""
         send_idx, remote, h_send, h_recv = self._bind(plan)
         v = C.c_void_p

@@ -1,0 +1,67 @@
+"""Failure handling of the peer-memory route on ONE GPU (world size 1, the rank is its own peer): an apply kernel whose
+rows never arrive gives up after its (shortened) bound, reports SGL_DEV_TIMEOUT through the status word, publishes
+nothing -- and the process keeps working: a fresh route context moves rows normally afterwards.  Nothing here hangs or
+faults the GPU: the wait that runs out is the kernel's own bounded poll."""
+import ctypes as C
+import time
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DIM, ROWS, SLOTS = 8, 5, 100
+
+
+def make_ctx(L, _C):
+    pitch = L.sgl_wire_pitch(DIM, 1, 1)
+    nbytes = L.sgl_p2p_buffer_bytes(1, 2, 64, pitch)
+    base, handle = C.c_void_p(), C.create_string_buffer(64)
+    _C.check(L.sgl_p2p_alloc(nbytes, C.byref(base), handle, 64))
+    bases = (C.c_void_p * 1)(base.value)
+    ctx = C.c_void_p()
+    _C.check(L.sgl_p2p_route_create(0, 1, 2, 64, pitch, bases, C.byref(ctx)))
+    return ctx, base
+
+
+def test_apply_gives_up_with_a_status_and_the_context_stays_usable(monkeypatch):
+    from starrygl import _C, ops
+    monkeypatch.setenv("SGL_P2P_WAIT_MS", "200")
+    L = _C.lib()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    data, ts = torch.zeros(SLOTS, DIM, device=dev), torch.zeros(SLOTS, device=dev)
+    status = ops.StatusWord(dev)
+    n_rows = (C.c_int64 * 1)(ROWS)
+    sp = _C.stream_ptr()
+
+    # (1) nothing was sent for step 0: the poll of the staging lines runs out
+    ctx, base = make_ctx(L, _C)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    _C.check(L.sgl_p2p_route_recv(ctx, n_rows, data.data_ptr(), SLOTS, DIM, 1, ts.data_ptr(), 0, status.ptr(), sp))
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 0.15 < waited < 10.0, waited
+    with pytest.raises(_C.SglError, match="(?i)timeout|wait"):
+        status.check("apply without rows")
+    assert not data.any() and not ts.any()                      # nothing was applied
+    _C.check(L.sgl_p2p_route_destroy(ctx))
+    _C.check(L.sgl_p2p_free(base))
+
+    # (2) same process, fresh context: send + apply of real rows
+    ctx, base = make_ctx(L, _C)
+    feats = torch.randn(50, DIM, device=dev)
+    fts = torch.rand(50, device=dev)
+    send_idx = torch.tensor([3, 7, 7, 49, 0], device=dev)
+    slots = torch.tensor([10, 11, 99, 0, 42], device=dev)
+    _C.check(L.sgl_p2p_route_send(ctx, feats.data_ptr(), 50, DIM, fts.data_ptr(), send_idx.data_ptr(), slots.data_ptr(), n_rows,
+                                  0, status.ptr(), sp))
+    _C.check(L.sgl_p2p_route_recv(ctx, n_rows, data.data_ptr(), SLOTS, DIM, 1, ts.data_ptr(), 0, status.ptr(), sp))
+    torch.cuda.synchronize()
+    status.check("send + apply")
+    want_d, want_t = np.zeros((SLOTS, DIM), np.float32), np.zeros(SLOTS, np.float32)
+    want_d[slots.cpu().numpy()] = feats.cpu().numpy()[send_idx.cpu().numpy()]
+    want_t[slots.cpu().numpy()] = fts.cpu().numpy()[send_idx.cpu().numpy()]
+    assert np.array_equal(data.cpu().numpy(), want_d) and np.array_equal(ts.cpu().numpy(), want_t)
+    _C.check(L.sgl_p2p_route_destroy(ctx))
+    _C.check(L.sgl_p2p_free(base))
