@@ -249,6 +249,75 @@ def secondary_measurements(g, dev, peak):
     return out
 
 
+def route_bandwidth(args, rank, world, dev, out_stream):
+    """Side measurement (not the benchmark line): the cache route alone at a message size where NVLink bandwidth, not
+    latency, bounds it.  Every rank pushes ``--route-bw-rows`` rows of 100 x fp32 + ts per step, split evenly over the
+    other ranks, through (a) the peer-memory kernels and (b) the grouped NCCL send/recv path.  GB/s = payload bytes a
+    rank sends per step / step time (device time, max over ranks); every rank receives as much as it sends."""
+    import torch.distributed as dist
+    from starrygl.cache.cache_route import CacheRoute, CommPlan
+    from starrygl.cache.p2p_route import P2PCacheRoute
+    from starrygl.cache.NodeState import DistNodeState
+    from starrygl.utils.partition_book import PartitionState
+    N, D, rows = 2_000_000, MEM_DIM, int(args.route_bw_rows)
+    per = rows // (world - 1)
+    ranks = torch.cat([torch.full((per,), p, dtype=torch.long) for p in range(world) if p != rank])
+    sizes = torch.bincount(ranks, minlength=world)
+    g = torch.Generator().manual_seed(rank)
+    plan = CommPlan(ranks, sizes, torch.randint(0, N, (ranks.numel(),), generator=g),
+                    torch.randperm(N, generator=g)[:ranks.numel()]).to(dev)
+    mem, mts = torch.randn(N, D, device=dev), torch.rand(N, device=dev)
+    ps = PartitionState(loc_ids=torch.arange(N, device=dev), num_master_nums=N, node_mode='identity', num_nodes=N)
+    state = DistNodeState(ps, D, device=dev)
+    payload = ranks.numel() * (D + 1) * 4
+    K = 50
+    res = {"rows_per_step": int(ranks.numel()), "payload_MB_per_rank_and_step": payload / 1e6, "peers": world - 1}
+
+    def timed(step_fn, streams):
+        for _ in range(5):
+            step_fn()
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(streams[0])
+        for st in streams[1:]:
+            st.wait_stream(streams[0])
+        for _ in range(K):
+            step_fn()
+        for st in streams[1:]:
+            streams[0].wait_stream(st)
+        e1.record(streams[0])
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([e0.elapsed_time(e1) / K], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    st_a, st_b = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    p2p = P2PCacheRoute(D, True, cap_rows=max(1024, per), ring=4)
+    step = p2p.bind_step(mem, mts, plan, state, st_a, st_b)
+    ms = timed(step, [st_a, st_b])
+    p2p.status.check("route bandwidth (peer memory)")
+    res["p2p"] = {"ms_per_step": ms, "GBps_per_direction": payload / ms / 1e6}
+    p2p.close()
+
+    cr = CacheRoute()
+
+    def cb(idx, rows_, mode):
+        state.write_packed(idx, rows_)
+    cb.fused_state = state
+    cr._exchange_counts(plan, dev)
+
+    def nccl_step():
+        with torch.cuda.stream(st_a):
+            for f in cr.update_with_plan(mem, plan, cb, local_ts=mts):
+                f.wait()
+    ms = timed(nccl_step, [st_a])
+    res["nccl"] = {"ms_per_step": ms, "GBps_per_direction": payload / ms / 1e6}
+    if rank == 0:
+        print(json.dumps({"route_bandwidth": res, "n_gpus": world, "nvlink_peak_GBps_per_direction": 900,
+                          "measured_peer_copy_GBps": 770}), file=out_stream, flush=True)
+
+
 def cpu_baseline_measure(dev, steps, warmup, budget_s):
     """Times the C oracle on the same graph and batches.  The graph is generated with the same seeded generator
     (on the GPU when there is one, and copied to the host); the feature table is a 1 M-row host sample
@@ -324,6 +393,8 @@ def main():
                     help="result copy to the host: device-counted prefix (exact bytes) or whole-capacity copies")
     ap.add_argument("--no-numa-bind", action="store_true", help="N > 1: do not bind the rank to the CPUs of its GPU's NUMA node")
     ap.add_argument("--row-align", type=int, default=0, help="pad the feature table's rows in HBM to this many bytes (0 = dense)")
+    ap.add_argument("--route-bw-rows", type=int, default=0,
+                    help="N > 1: measure the route alone with this many rows per rank and step (bandwidth-bound sizes) and exit")
     ap.add_argument("--tcsr-only", action="store_true", help="time the T-CSR construction of the benchmark graph and exit")
     ap.add_argument("--no-step-graph", action="store_true",
                     help="issue sample+gather as one fused foreign call (three kernel launches) instead of one graph launch")
@@ -351,6 +422,11 @@ def main():
     if multi:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    if args.route_bw_rows > 0:
+        if not multi:
+            raise SystemExit("--route-bw-rows needs at least two ranks")
+        return route_bandwidth(args, rank, world, dev, out_stream)
 
     # ---- set-up (untimed): graph, T-CSR, feature table, batches -------------------------------------------
     src, dst, ts, gen = make_graph(dev, seed=rank)

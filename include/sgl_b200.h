@@ -298,7 +298,9 @@ int sgl_cache_route_step(void* comm, const float* feats, int64_t n_rows, int64_t
  * Cache route over NVLink peer memory (one node): the pack and the transfer are ONE kernel that stores the wire
  * rows straight into the receivers' staging buffers, as 16-byte lines that carry the step's tag next to the data
  * (the receiver polls the lines themselves; there is no separate flag and no fence); a second kernel on the
- * receiver applies them and acknowledges the step.  No collective-library call per step.  Consecutive route
+ * receiver applies them and acknowledges the step.  A pair's message of 2 MiB and more (SGL_P2P_BULK_BYTES
+ * overrides the limit) is bandwidth-bound and travels as plain rows followed by a fence and a per-pair flag instead.
+ * No collective-library call per step.  Consecutive route
  * kernels of a stream are launched with programmatic stream serialization: they may become resident early but
  * touch nothing before the previous kernel of the stream has completed.  Set-up (not on the batch path, allocates): every rank allocates one buffer
  * of sgl_p2p_buffer_bytes() with sgl_p2p_alloc (zeroed, returns a 64-byte inter-process handle), the handles

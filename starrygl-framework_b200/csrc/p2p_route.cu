@@ -18,6 +18,14 @@
 // recv kernel (rank p, step s):  polls the lines of all senders, scatters the rows into the node-state table (same
 //     work as route_unpack_kernel); the last CTA to finish acknowledges the step to every sender.
 //
+// Large messages: tagging doubles the bytes on the wire, which is the wrong trade once a message is bandwidth-bound.
+// A (sender, receiver) pair whose message of a step has at least `bulk_rows` rows (both ends know that count) uses
+// plain wire rows instead -- 128-bit stores into the first half of the same staging region -- followed by one
+// system-scope fence per CTA, an arrival counter, and a per-pair flag
+//     flags[world][ring]   flags[q][slot] = step + 1 once sender q's plain rows of that step have landed here
+// written by the last CTA of the send kernel; the receiver waits (bounded) for the flags of its bulk senders before
+// it reads their rows.  Small and large pairs can be mixed inside one step.
+//
 // The two kernels of a step run on DIFFERENT GPUs (one process per GPU), never as two launches on one GPU.  Every
 // wait is bounded by a wall-clock limit; on expiry the kernel raises SGL_DEV_TIMEOUT in the status word, publishes
 // nothing and returns, so the context stays usable.  Every rank must run send and recv for every step (zero rows are
@@ -31,7 +39,8 @@ namespace sgl {
 namespace {
 
 constexpr int kMaxWorld = 16;
-constexpr int kThreads = 128;   // 4 rows per CTA
+constexpr int kThreads = 128;   // 4 warps per CTA, one row per warp at a time
+constexpr int kRowsInFlight = 1;   // rows per warp and iteration; more in flight measured slower (299 vs 371 GB/s at 40 MB)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // default bound of every device-side wait (SGL_P2P_WAIT_MS overrides)
 
 struct P2PCfg {
@@ -41,9 +50,12 @@ struct P2PCfg {
   int rank, world, ring;
   int64_t cap_rows;
   uint32_t pitch;           // 32-bit words per wire row; a row occupies pitch / 2 lines
+  int64_t bulk_rows;        // a pair's message with at least this many rows travels as plain rows + flag
   unsigned long long* acks;
+  unsigned long long* flags;
   uint4* stage;
   unsigned long long* peer_acks[kMaxWorld];
+  unsigned long long* peer_flags[kMaxWorld];
   uint4* peer_stage[kMaxWorld];
 };
 
@@ -53,7 +65,7 @@ struct Splits {
 
 struct Ctx {
   P2PCfg cfg;
-  unsigned int* counters;   // device: arrival counter of the recv kernel
+  unsigned int* counters;   // device: arrival counters of the send ([0]) and recv ([32]) kernels
 };
 
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -113,6 +125,27 @@ __device__ __forceinline__ uint32_t wire_word2(uint32_t e, uint32_t dim, uint32_
   return 0u;
 }
 
+// quad l (wire words 4l .. 4l+3) of the row built from table row r; r == -2 marks a row that could not be read
+__device__ __forceinline__ uint4 wire_quad(uint32_t l, uint32_t dim, uint32_t payload, int vec_ok, const float* __restrict__ feats,
+                                           const float* __restrict__ ts, int64_t r, uint64_t slot) {
+  uint4 v;
+  if (r < 0) {
+    const uint32_t e = 4 * l;
+    v.x = (e + 0 == payload || e + 0 == payload + 1) ? 0xffffffffu : 0u;
+    v.y = (e + 1 == payload || e + 1 == payload + 1) ? 0xffffffffu : 0u;
+    v.z = (e + 2 == payload || e + 2 == payload + 1) ? 0xffffffffu : 0u;
+    v.w = (e + 3 == payload || e + 3 == payload + 1) ? 0xffffffffu : 0u;
+    return v;
+  }
+  const float* frow = feats + r * dim;
+  if (vec_ok && (l + 1) * 4 <= dim) return __ldg((const uint4*)frow + l);
+  v.x = wire_word2(4 * l + 0, dim, payload, frow, ts, r, slot);
+  v.y = wire_word2(4 * l + 1, dim, payload, frow, ts, r, slot);
+  v.z = wire_word2(4 * l + 2, dim, payload, frow, ts, r, slot);
+  v.w = wire_word2(4 * l + 3, dim, payload, frow, ts, r, slot);
+  return v;
+}
+
 __device__ __forceinline__ int segment_of(const Splits& s, int world, int64_t i) {
   int p = 0;
   while (p + 1 < world && i >= s.off[p + 1]) ++p;
@@ -127,8 +160,9 @@ __device__ __forceinline__ int segment_of(const Splits& s, int world, int64_t i)
 __global__ void __launch_bounds__(kThreads)
 p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint32_t dim, const float* __restrict__ ts,
                 const int64_t* __restrict__ send_idx, const int64_t* __restrict__ remote_idx, Splits seg,
-                unsigned long long step, int vec_ok, int32_t* d_status) {
+                unsigned long long step, int vec_ok, int any_bulk, unsigned int* done_counter, int32_t* d_status) {
   __shared__ int s_ok;
+  __shared__ bool s_last;
   if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 5] = now_ns();
   pdl_wait();
   pdl_release();
@@ -140,55 +174,86 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
     if (!wait_at_least(c.acks + threadIdx.x, step - c.ring + 1, c.wait_ns)) s_ok = 0;
   }
   __syncthreads();
-  if (s_ok == 0) {
-    if (threadIdx.x == 0) dev_flag(d_status, SGL_DEV_TIMEOUT);
-    return;
-  }
+  const bool ok = s_ok != 0;
+  if (!ok && threadIdx.x == 0) dev_flag(d_status, SGL_DEV_TIMEOUT);
   const uint32_t tag = (uint32_t)(step + 1);
   const uint32_t payload = dim + (ts ? 1u : 0u);
   const uint32_t quads = c.pitch / 4;
   const uint32_t lane = threadIdx.x & 31u;
-  const int64_t n_send = seg.off[c.world];
+  const int64_t n_send = ok ? seg.off[c.world] : 0;
   const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
   const int64_t slot_base = ((int64_t)c.rank * c.ring + (int64_t)(step % c.ring)) * c.cap_rows;
-  for (int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i < n_send; i += n_warps) {
-    int64_t r = __ldg(send_idx + i);                       // one address per warp: a single broadcast load
-    const uint64_t slotv = (uint64_t)__ldg(remote_idx + i);
-    if (r < 0) r += n_rows;
-    const bool bad = r < 0 || r >= n_rows;
-    if (bad && lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
-    const int p = segment_of(seg, c.world, i);
-    uint4* dst = c.peer_stage[p] + (slot_base + (i - seg.off[p])) * (c.pitch / 2);
-    const float* frow = feats + r * dim;
-    for (uint32_t l = lane; l < quads; l += 32) {
-      uint4 v;
-      if (bad) {
-        // a row that cannot be read is sent as zeros with slot -1, which the receiver skips (and reports as well)
-        const uint32_t e = 4 * l;
-        v.x = (e + 0 == payload || e + 0 == payload + 1) ? 0xffffffffu : 0u;
-        v.y = (e + 1 == payload || e + 1 == payload + 1) ? 0xffffffffu : 0u;
-        v.z = (e + 2 == payload || e + 2 == payload + 1) ? 0xffffffffu : 0u;
-        v.w = (e + 3 == payload || e + 3 == payload + 1) ? 0xffffffffu : 0u;
-      } else if (vec_ok && (l + 1) * 4 <= dim) {
-        v = __ldg((const uint4*)frow + l);
-      } else {
-        v.x = wire_word2(4 * l + 0, dim, payload, frow, ts, r, slotv);
-        v.y = wire_word2(4 * l + 1, dim, payload, frow, ts, r, slotv);
-        v.z = wire_word2(4 * l + 2, dim, payload, frow, ts, r, slotv);
-        v.w = wire_word2(4 * l + 3, dim, payload, frow, ts, r, slotv);
+  // kRowsInFlight rows per warp and iteration, in three phases (indices, rows, stores)
+  for (int64_t i0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i0 < n_send; i0 += n_warps * kRowsInFlight) {
+    int64_t r[kRowsInFlight];
+    uint64_t slotv[kRowsInFlight];
+#pragma unroll
+    for (int u = 0; u < kRowsInFlight; ++u) {
+      const int64_t i = i0 + u * n_warps;
+      r[u] = -1;
+      slotv[u] = 0;
+      if (i < n_send) {
+        r[u] = __ldg(send_idx + i);                       // one address per warp: a single broadcast load
+        slotv[u] = (uint64_t)__ldg(remote_idx + i);
+        if (r[u] < 0) r[u] += n_rows;
+        if (r[u] < 0 || r[u] >= n_rows) {
+          if (lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
+          r[u] = -2;                                      // sent as zeros with slot -1, which the receiver skips
+        }
       }
-      store_line(dst + 2 * l, v.x, v.y, tag);
-      store_line(dst + 2 * l + 1, v.z, v.w, tag);
+    }
+    uint4 v[kRowsInFlight];
+#pragma unroll
+    for (int u = 0; u < kRowsInFlight; ++u)
+      if (r[u] != -1 && lane < quads) v[u] = wire_quad(lane, dim, payload, vec_ok, feats, ts, r[u], slotv[u]);
+#pragma unroll
+    for (int u = 0; u < kRowsInFlight; ++u) {
+      if (r[u] == -1) continue;
+      const int64_t i = i0 + u * n_warps;
+      const int p = segment_of(seg, c.world, i);
+      const bool bulk = seg.off[p + 1] - seg.off[p] >= c.bulk_rows;
+      // the pair's region starts at the same place in both layouts; a plain row takes pitch / 4 lines, a tagged one pitch / 2
+      uint4* region = c.peer_stage[p] + slot_base * (c.pitch / 2);
+      uint4* dst = region + (i - seg.off[p]) * (bulk ? c.pitch / 4 : c.pitch / 2);
+      for (uint32_t l = lane; l < quads; l += 32) {
+        const uint4 q = l == lane ? v[u] : wire_quad(l, dim, payload, vec_ok, feats, ts, r[u], slotv[u]);
+        if (bulk) {
+          dst[l] = q;
+        } else {
+          store_line(dst + 2 * l, q.x, q.y, tag);
+          store_line(dst + 2 * l + 1, q.z, q.w, tag);
+        }
+      }
     }
   }
   if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 1] = now_ns();
+  if (!any_bulk) return;
+  // plain rows are published with a flag.  One system-scope fence per CTA: the CTA barrier makes every thread's stores
+  // happen-before thread 0's fence, and fences are cumulative, so thread 0's fence + counter increment orders the whole
+  // CTA's rows before anything the last CTA does after it has seen all increments.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(done_counter, 1u);
+    s_last = prev == gridDim.x - 1;
+    if (s_last) __threadfence_system();
+  }
+  __syncthreads();
+  if (!s_last) return;
+  const bool failed = !ok || (d_status && (*(volatile int32_t*)d_status & SGL_DEV_TIMEOUT));
+  if (threadIdx.x < c.world && !failed && seg.off[threadIdx.x + 1] - seg.off[threadIdx.x] >= c.bulk_rows) {
+    volatile unsigned long long* f = c.peer_flags[threadIdx.x] + (int64_t)c.rank * c.ring + (step % c.ring);
+    *f = step + 1;
+  }
+  if (threadIdx.x == 0) *done_counter = 0;
 }
 
 // One warp per incoming row: every lane reads the line(s) holding the row's slot (one broadcast load per line) and
 // the 2 lines of its own quad, and re-polls (bounded) only what has not landed yet.
 __global__ void __launch_bounds__(kThreads)
 p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, int64_t data_rows, uint32_t dim,
-                float* __restrict__ ts_table, unsigned long long step, int vec_ok, unsigned int* done_counter, int32_t* d_status) {
+                float* __restrict__ ts_table, unsigned long long step, int vec_ok, int any_bulk, unsigned int* done_counter,
+                int32_t* d_status) {
   __shared__ int s_ok;
   __shared__ bool s_last;
   if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 6] = now_ns();
@@ -205,10 +270,43 @@ p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, 
   const int64_t n_recv = seg.off[c.world];
   const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
   const int64_t ring_slot = (int64_t)(step % c.ring);
-  bool ok = true;
+  if (any_bulk) {
+    // plain rows of a large pair are complete once its sender's flag says so
+    if (threadIdx.x < c.world && seg.off[threadIdx.x + 1] - seg.off[threadIdx.x] >= c.bulk_rows) {
+      if (!wait_at_least(c.flags + (int64_t)threadIdx.x * c.ring + ring_slot, step + 1, c.wait_ns)) s_ok = 0;
+      __threadfence_system();   // acquire side: the rows written before the flag are visible after this fence ...
+    }
+    __syncthreads();            // ... and, through the barrier, to every thread of the CTA
+  }
+  bool ok = s_ok != 0;
   for (int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i < n_recv && ok; i += n_warps) {
     const int sdr = segment_of(seg, c.world, i);
-    const uint4* row = c.stage + (((int64_t)sdr * c.ring + ring_slot) * c.cap_rows + (i - seg.off[sdr])) * (c.pitch / 2);
+    const uint4* region = c.stage + ((int64_t)sdr * c.ring + ring_slot) * c.cap_rows * (c.pitch / 2);
+    if (seg.off[sdr + 1] - seg.off[sdr] >= c.bulk_rows) {
+      // plain wire row (pitch / 4 quads); volatile loads: the row was written by another GPU
+      const uint4* prow = region + (i - seg.off[sdr]) * (c.pitch / 4);
+      const uint4 qa = load_line(prow + width / 4), qb = load_line(prow + (width + 1) / 4);
+      const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
+      const int64_t dslot = (int64_t)((uint64_t)wa[width & 3] | ((uint64_t)wb[(width + 1) & 3] << 32));
+      const bool bad = dslot < 0 || dslot >= data_rows;
+      if (bad && lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
+      for (uint32_t l = lane; l < quads && !bad; l += 32) {
+        const uint4 q = load_line(prow + l);
+        if (vec_ok && (l + 1) * 4 <= dim) {
+          ((uint4*)(data + dslot * dim))[l] = q;
+        } else {
+          const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t e = 4 * l + k;
+            if (e < dim) data[dslot * dim + e] = __uint_as_float(w[k]);
+            else if (e < width && ts_table) ts_table[dslot] = __uint_as_float(w[k]);
+          }
+        }
+      }
+      continue;
+    }
+    const uint4* row = region + (i - seg.off[sdr]) * (c.pitch / 2);
     // all loads in flight first; the rows have normally landed long ago
     uint4 sa = load_line(row + la);
     uint4 sb = la == lb ? sa : load_line(row + lb);
@@ -273,7 +371,7 @@ p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, 
   if (threadIdx.x == 0) *done_counter = 0;
 }
 
-inline size_t header_bytes(int world) { return align_up((size_t)world * 8, 256); }
+inline size_t header_bytes(int world, int ring) { return align_up((size_t)world * 8 + (size_t)world * ring * 8, 256); }
 
 }  // namespace
 }  // namespace sgl
@@ -284,7 +382,7 @@ extern "C" size_t sgl_p2p_buffer_bytes(int world, int ring, int64_t cap_rows, in
   if (world < 1 || ring < 1 || cap_rows < 0 || pitch_floats < 1) return 0;
   if (pitch_floats % 4) return 0;
   // every 16-byte line holds two wire words and two tags: twice the bytes of the plain wire rows
-  return header_bytes(world) + (size_t)world * ring * (size_t)cap_rows * (size_t)pitch_floats * 8;
+  return header_bytes(world, ring) + (size_t)world * ring * (size_t)cap_rows * (size_t)pitch_floats * 8;
 }
 
 extern "C" int sgl_p2p_alloc(size_t bytes, void** out_ptr, char* out_handle, size_t handle_bytes) {
@@ -332,14 +430,20 @@ extern "C" int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_r
   }
   c.dbg = getenv("SGL_P2P_DBG") ? atoi(getenv("SGL_P2P_DBG")) : 0;   // 2 = record a per-step kernel timeline (diagnostics)
   c.rank = rank; c.world = world; c.ring = ring; c.cap_rows = cap_rows; c.pitch = (uint32_t)pitch_floats;
-  const size_t hb = header_bytes(world);
+  const size_t hb = header_bytes(world, ring);
   for (int p = 0; p < world; ++p) {
     SGL_REQUIRE(h_bases[p], SGL_ERR_ARG, "p2p_route_create: base pointer of rank %d is null", p);
     char* b = (char*)h_bases[p];
     c.peer_acks[p] = (unsigned long long*)b;
+    c.peer_flags[p] = (unsigned long long*)b + world;
     c.peer_stage[p] = (uint4*)(b + hb);
   }
   c.acks = c.peer_acks[rank];
+  c.flags = c.peer_flags[rank];
+  // pairs whose message is at least this large travel as plain rows (SGL_P2P_BULK_BYTES overrides; 0 = always)
+  long long bulk_bytes = 2 << 20;
+  if (const char* e = getenv("SGL_P2P_BULK_BYTES")) bulk_bytes = atoll(e);
+  c.bulk_rows = bulk_bytes <= 0 ? 1 : (bulk_bytes + pitch_floats * 4 - 1) / (pitch_floats * 4);
   c.stage = c.peer_stage[rank];
   SGL_CUDA_CHECK(cudaMalloc(&x->counters, 256));
   SGL_CUDA_CHECK(cudaMemset(x->counters, 0, 256));
@@ -421,8 +525,10 @@ extern "C" int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows,
   cudaStream_t stream = (cudaStream_t)stream_;
   const int vec_ok = dim % 4 == 0 && ((uintptr_t)feats & 15) == 0;
   const int grid = p2p_grid(n_send);
+  int any_bulk = 0;
+  for (int p = 0; p < x->cfg.world; ++p) any_bulk |= h_send_rows[p] >= x->cfg.bulk_rows;
   SGL_CUDA_CHECK(launch_pdl(p2p_send_kernel, grid, stream, x->cfg, feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, seg,
-                            (unsigned long long)step, vec_ok, d_status));
+                            (unsigned long long)step, vec_ok, any_bulk, x->counters, d_status));
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }
@@ -442,8 +548,11 @@ extern "C" int sgl_p2p_route_recv(void* ctx, const int64_t* h_recv_rows, float* 
   cudaStream_t stream = (cudaStream_t)stream_;
   const int vec_ok = dim % 4 == 0 && ((uintptr_t)data & 15) == 0;
   const int grid = p2p_grid(n_recv);
+  int any_bulk = 0;
+  for (int p = 0; p < x->cfg.world; ++p) any_bulk |= h_recv_rows[p] >= x->cfg.bulk_rows;
   SGL_CUDA_CHECK(launch_pdl(p2p_recv_kernel, grid, stream, x->cfg, seg, (uint32_t)width, data, data_rows, (uint32_t)dim,
-                            has_ts ? ts_table : (float*)nullptr, (unsigned long long)step, vec_ok, x->counters, d_status));
+                            has_ts ? ts_table : (float*)nullptr, (unsigned long long)step, vec_ok, any_bulk, x->counters + 32,
+                            d_status));
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }

@@ -65,3 +65,38 @@ def test_apply_gives_up_with_a_status_and_the_context_stays_usable(monkeypatch):
     assert np.array_equal(data.cpu().numpy(), want_d) and np.array_equal(ts.cpu().numpy(), want_t)
     _C.check(L.sgl_p2p_route_destroy(ctx))
     _C.check(L.sgl_p2p_free(base))
+
+
+@pytest.mark.parametrize("bulk_bytes", ["1", "1000000000"])
+def test_world1_roundtrip_plain_rows_and_tagged_lines(monkeypatch, bulk_bytes):
+    """Both wire forms of a pair's message (plain rows + flag for large messages, tagged lines for small ones), several
+    steps through a ring of 2, rank 0 sending to itself."""
+    from starrygl import _C, ops
+    monkeypatch.setenv("SGL_P2P_BULK_BYTES", bulk_bytes)
+    L = _C.lib()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ctx, base = make_ctx(L, _C)
+    data, ts = torch.zeros(SLOTS, DIM, device=dev), torch.zeros(SLOTS, device=dev)
+    want_d, want_t = np.zeros((SLOTS, DIM), np.float32), np.zeros(SLOTS, np.float32)
+    status = ops.StatusWord(dev)
+    sp = _C.stream_ptr()
+    g = torch.Generator().manual_seed(int(bulk_bytes) % 97)
+    keep = []
+    for step in range(7):
+        n = int(torch.randint(0, 40, (1,), generator=g))
+        feats = torch.randn(50, DIM, generator=g).to(dev)
+        fts = torch.rand(50, generator=g).to(dev)
+        send_idx = torch.randint(0, 50, (n,), generator=g).to(dev)
+        slots = torch.randperm(SLOTS, generator=g)[:n].to(dev)
+        rows = (C.c_int64 * 1)(n)
+        _C.check(L.sgl_p2p_route_send(ctx, feats.data_ptr(), 50, DIM, fts.data_ptr(), send_idx.data_ptr(), slots.data_ptr(), rows,
+                                      step, status.ptr(), sp))
+        _C.check(L.sgl_p2p_route_recv(ctx, rows, data.data_ptr(), SLOTS, DIM, 1, ts.data_ptr(), step, status.ptr(), sp))
+        keep.append((feats, fts, send_idx, slots))
+        want_d[slots.cpu().numpy()] = feats.cpu().numpy()[send_idx.cpu().numpy()]
+        want_t[slots.cpu().numpy()] = fts.cpu().numpy()[send_idx.cpu().numpy()]
+    torch.cuda.synchronize()
+    status.check("world-1 route")
+    assert np.array_equal(data.cpu().numpy(), want_d) and np.array_equal(ts.cpu().numpy(), want_t)
+    _C.check(L.sgl_p2p_route_destroy(ctx))
+    _C.check(L.sgl_p2p_free(base))

@@ -115,9 +115,13 @@ def _worker_p2p(rank, world, port, q):
         ok_golden = torch.equal(state.data, t("data")) and torch.equal(state.ts, t("ts"))
         route.close()
 
-        # (2) 40 steps through a ring of 4 with changing sizes (including empty ones); dim 100 -> 128-bit lanes
+        # (2) 40 steps through a ring of 4 with changing sizes (including empty ones); dim 100 -> 128-bit lanes.
+        # Messages of 40 rows and more (16 KB) travel as plain rows + flag, smaller ones as tagged lines: both forms
+        # and their mixture inside one step are exercised.
         D2, N, K = 100, 4096, 512
+        os.environ["SGL_P2P_BULK_BYTES"] = "16384"
         route = P2PCacheRoute(D2, True, cap_rows=K, ring=4)
+        del os.environ["SGL_P2P_BULK_BYTES"]
         ps2 = PartitionState(loc_ids=torch.arange(N, device=dev), num_master_nums=N, node_mode='identity', num_nodes=N)
         state2 = DistNodeState(ps2, D2, device=dev)
         all_feats = [torch.randn(N, D2, generator=torch.Generator().manual_seed(50 + r)) for r in range(world)]
