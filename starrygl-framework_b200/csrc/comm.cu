@@ -147,8 +147,9 @@ extern "C" int sgl_cache_route_step(void* comm, const float* feats, int64_t n_ro
     n_recv += h_recv_rows[p];
   }
   const int64_t width = dim + (ts ? 1 : 0);
-  SGL_REQUIRE(remote_idx, SGL_ERR_ARG, "cache_route_step: remote_idx is null");
-  int rc = sgl_route_pack(feats, n_rows, dim, ts, send_idx, remote_idx, n_send, send_buf, d_status, stream);
+  // a rank with nothing to send still takes part in the exchange (its peers may send to it)
+  SGL_REQUIRE(n_send == 0 || remote_idx, SGL_ERR_ARG, "cache_route_step: remote_idx is null");
+  int rc = n_send ? sgl_route_pack(feats, n_rows, dim, ts, send_idx, remote_idx, n_send, send_buf, d_status, stream) : SGL_OK;
   if (rc) return rc;
   rc = exchange(c, send_buf, h_send_rows, recv_buf, h_recv_rows, sgl_wire_pitch(dim, ts != nullptr, 1), (cudaStream_t)stream);
   if (rc) return rc;
