@@ -135,7 +135,7 @@ def workload_config(n_gpus):
     return {"workload": "1xB200 sampler microbench + sampled edge-feature gather (BASELINE configs[1] graph, configs[2] rows)",
             "graph": f"{NUM_NODES} nodes, {NUM_EDGES} edges, out-degree power law alpha 2.1, int64 ids, ts U[0,1e7)",
             "batch_roots": BATCH, "policy": f"recent-{FANOUT}, 1 hop", "edge_feat": f"{EDGE_DIM} x fp32",
-            "edge_feat_rows": NUM_EDGES, "event": "one root query",
+            "edge_feat_rows": NUM_EDGES, "event": "one root query (a link-prediction interaction = three of them: source, destination, negative destination)",
             "l2": "inputs larger than L2: 64 distinct batches over a 34 GB feature table and a 1.2 GB adjacency",
             "batches_in_flight": STREAMS, "parallelism": f"{n_gpus} partition(s), one process per GPU" +
                            (f", cache route ({ROUTE}) of {ROUTE_ROWS} memory rows per step" if n_gpus > 1 else "")}
