@@ -25,6 +25,8 @@
 //     flags[world][ring]   flags[q][slot] = step + 1 once sender q's plain rows of that step have landed here
 // written by the last CTA of the send kernel; the receiver waits (bounded) for the flags of its bulk senders before
 // it reads their rows.  Small and large pairs can be mixed inside one step.
+// (A region that held plain rows and is reused for tagged lines contains arbitrary words, not old tags: a stale line
+// passes for a fresh one only if two of its words both equal the new 32-bit tag, a 2^-64 event per line.)
 //
 // The two kernels of a step run on DIFFERENT GPUs (one process per GPU), never as two launches on one GPU.  Every
 // wait is bounded by a wall-clock limit; on expiry the kernel raises SGL_DEV_TIMEOUT in the status word, publishes
