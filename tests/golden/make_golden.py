@@ -25,6 +25,8 @@ What is pinned, and the reference code that produced it:
   stored beside them is defined by that restatement, not by the reference).
 * ``slots.npz``       -- complete slot files of ``build_aligned_batch`` INCLUDING the per-layer ``comm_plan``
   (prepare_sample.py:313-406) for every partition of a 3-way split, read back from the ``.pt`` file the reference wrote.
+  (``uniform_hist.npz`` is statistical: the reference draws from unseeded generators, a regenerated file differs
+  in its counts and the chi-square test compares distributions, not bytes.)
 * ``nodestate.npz``   -- ``DistNodeState.update`` / ``__getitem__`` with ``node_mode='map'``
   (starrygl/cache/NodeState.py:36-61, starrygl/utils/partition_book.py:98-133).
 """
@@ -140,6 +142,7 @@ def gen_batches(mod, out):
     B = mod.MaterializedMultiLayerBuilder
     B._compute_layer_route = lambda self, n, t: None
     cap = {}
+    real_save = mod.torch.save               # ``mod.torch`` is the torch module itself: put it back when done
     mod.torch.save = lambda obj, path: cap.__setitem__('obj', obj)
     cases = {
         "tiny": (graph_tiny(), (np.array([1, 0]), np.array([0, 7]), np.array([30, 40])), [2, 2]),
@@ -164,6 +167,7 @@ def gen_batches(mod, out):
                 if isinstance(v, torch.Tensor):
                     rec[f"L{i}_{k}"] = v.numpy()
         np.savez_compressed(os.path.join(out, f"batch_{name}.npz"), **rec)
+    mod.torch.save = real_save
 
 
 def _route_worker(rank, world, ref, port, q):
