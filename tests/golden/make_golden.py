@@ -10,7 +10,9 @@ What is pinned, and the reference code that produced it:
   ``_sample_layer`` / ``_jit_sample_kernel`` for the ``recent`` policy
   (prepare_sample.py:32-172, :179-203, :248-265).
 * ``uniform_hist.npz`` -- position histogram of the ``uniform`` policy (prepare_sample.py:120-134),
-  the distribution the chi-square test compares against.
+  the distribution the chi-square test compares against.  This one file is statistical: the reference draws from
+  unseeded generators, so a regenerated file differs in its counts (the test compares distributions, not bytes);
+  every other file regenerates bit for bit.
 * ``batch_*.npz``     -- ``build_aligned_batch`` per-layer dicts (prepare_sample.py:313-406)
   with route planning disabled (it needs ``torch_scatter``, which is absent).
 * ``ids.npz``         -- ``DistRouteIndex`` packing, ``build_replica_table`` +
@@ -25,8 +27,6 @@ What is pinned, and the reference code that produced it:
   stored beside them is defined by that restatement, not by the reference).
 * ``slots.npz``       -- complete slot files of ``build_aligned_batch`` INCLUDING the per-layer ``comm_plan``
   (prepare_sample.py:313-406) for every partition of a 3-way split, read back from the ``.pt`` file the reference wrote.
-  (``uniform_hist.npz`` is statistical: the reference draws from unseeded generators, a regenerated file differs
-  in its counts and the chi-square test compares distributions, not bytes.)
 * ``nodestate.npz``   -- ``DistNodeState.update`` / ``__getitem__`` with ``node_mode='map'``
   (starrygl/cache/NodeState.py:36-61, starrygl/utils/partition_book.py:98-133).
 """
