@@ -16,6 +16,9 @@ larger than L2.  An "event" is one root query.  Prints ONE JSON line (rank 0).
              host cores, on a bounded sample of the same batches
 With --gpus N > 1 (under torchrun) every rank owns one partition of equal size (weak scaling) and every step
 additionally pushes node-memory rows (100 x fp32 + ts) to the other partitions through the cache route.
+
+Side measurements (their own one-line JSON, not the benchmark line): ``--tcsr-only`` times the T-CSR construction of
+the benchmark graph; ``--route-bw-rows R`` (N > 1) times the route alone with R rows per rank and step.
 """
 import argparse
 import json
