@@ -12,6 +12,19 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 
 
+def _collect(q, procs, timeout=180):
+    """Results of the two ranks; the children this test started are ended (by their own pids) whatever happens, so
+    that a rank that waits for ever cannot keep its GPU after the test has failed."""
+    try:
+        return sorted(q.get(timeout=timeout) for _ in procs)
+    finally:
+        for p in procs:
+            p.join(30)
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+
+
 def _worker(rank, world, port, q):
     try:
         import torch.distributed as dist
@@ -72,9 +85,7 @@ def test_routes_on_two_gpus():
     procs = [ctx.Process(target=_worker, args=(r, 2, 29651, q)) for r in range(2)]
     for p in procs:
         p.start()
-    out = sorted(q.get(timeout=300) for _ in range(2))
-    for p in procs:
-        p.join(60)
+    out = _collect(q, procs)
     for rank, a, b, c, err in out:
         assert err is None, err
         assert a, f"rank {rank}: remote writes differ from the reference"
@@ -203,9 +214,7 @@ def test_p2p_cache_route_on_two_gpus():
     procs = [ctx.Process(target=_worker_p2p, args=(r, 2, 29652, q)) for r in range(2)]
     for p in procs:
         p.start()
-    out = sorted(q.get(timeout=300) for _ in range(2))
-    for p in procs:
-        p.join(60)
+    out = _collect(q, procs)
     for rank, a, b, _, err in out:
         assert err is None, err
         assert a, f"rank {rank}: peer-memory route differs from the reference's result"
