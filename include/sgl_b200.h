@@ -43,7 +43,8 @@ extern "C" {
 #define SGL_DEV_BAD_TS 2     /* timestamp outside the declared [ts_base, ts_base + 2^ts_bits) window */
 #define SGL_DEV_BAD_INDEX 4  /* row index outside the table */
 #define SGL_DEV_OVERFLOW 8   /* an output capacity was exceeded */
-#define SGL_DEV_TIMEOUT 16   /* a bounded device-side wait gave up (copy engine did not signal in time) */
+#define SGL_DEV_TIMEOUT 16   /* a bounded device-side wait gave up (copy engine or peer did not signal in time) */
+#define SGL_DEV_MISMATCH 32  /* a peer's message size differs from the size the receiver was told to expect */
 
 #define SGL_POLICY_RECENT 0
 #define SGL_POLICY_UNIFORM 1
@@ -275,6 +276,12 @@ int sgl_route_unpack(const float* packed, int64_t n, int64_t width, float* data,
 int sgl_comm_unique_id(char* out_id, size_t id_bytes);
 int sgl_comm_init(void** out_comm, int rank, int world, const char* id_bytes);
 int sgl_comm_destroy(void* comm);
+/* rank / size of a communicator (DistContext::get_rank / get_size, csrc/include/starrygl/commContext.cu.hpp:54-60). */
+int sgl_comm_info(void* comm, int* out_rank, int* out_world);
+/* Enable peer access from the current device to the listed devices that this process can see; *out_accessible =
+ * how many of them (the current one included) are now reachable.  Replaces: init_p2p
+ * (csrc/include/starrygl/feature.cu.hpp:30-40 as exported at :715). */
+int sgl_init_p2p(const int* devices, int n, int* out_accessible);
 
 /* Rows of row_floats float32: segment p of `send` (h_send_rows[p] rows, host array of world entries) goes to rank
  * p; segment p of `recv` (h_recv_rows[p] rows) arrives from rank p.  Enqueued on `stream`, no synchronisation.
@@ -298,8 +305,11 @@ int sgl_cache_route_step(void* comm, const float* feats, int64_t n_rows, int64_t
  * Cache route over NVLink peer memory (one node): the pack and the transfer are ONE kernel that stores the wire
  * rows straight into the receivers' staging buffers, as 16-byte lines that carry the step's tag next to the data
  * (the receiver polls the lines themselves; there is no separate flag and no fence); a second kernel on the
- * receiver applies them and acknowledges the step.  A pair's message of 2 MiB and more (SGL_P2P_BULK_BYTES
- * overrides the limit) is bandwidth-bound and travels as plain rows followed by a fence and a per-pair flag instead.
+ * receiver applies them and acknowledges the step.  A pair's message of 2 MiB and more (sgl_p2p_route_configure
+ * changes the limit) is bandwidth-bound and travels as plain rows followed by a fence and a per-pair word instead.
+ * Every sender also tells every receiver how many rows it pushed (one 8-byte word per pair and step), so the
+ * receiver needs no count exchange: a plan whose sizes exist only in device memory (sgl_plan_route's d_send_sizes)
+ * is routed without a host synchronisation (sgl_p2p_route_send_dev / sgl_p2p_route_recv_dev).
  * No collective-library call per step.  Consecutive route
  * kernels of a stream are launched with programmatic stream serialization: they may become resident early but
  * touch nothing before the previous kernel of the stream has completed.  Set-up (not on the batch path, allocates): every rank allocates one buffer
@@ -308,9 +318,12 @@ int sgl_cache_route_step(void* comm, const float* feats, int64_t n_rows, int64_t
  * world-sized array of base pointers (its own entry = its own buffer).
  * Per step, on every rank, with the same `step` number (0, 1, 2, ...): sgl_p2p_route_send (rows for rank p =
  * h_send_rows[p], grouped by destination like the plan's send_indices), later sgl_p2p_route_recv
- * (h_recv_rows[q] rows from rank q) which writes data[slot] / ts_table[slot].  Both are asynchronous on the
- * stream.  A rank may run ahead of a peer by at most `ring` steps; device-side waits are bounded (2 s) and end
- * in SGL_DEV_TIMEOUT in *d_status instead of hanging.  At most cap_rows rows per (sender, receiver, step).
+ * (h_recv_rows[q] rows expected from rank q; a different count on the wire raises SGL_DEV_MISMATCH) which writes
+ * data[slot] / ts_table[slot].  Both are asynchronous on the
+ * stream.  A rank may run ahead of a peer by at most `ring` steps; device-side waits are bounded (2 s unless
+ * configured) and end in SGL_DEV_TIMEOUT in *d_status instead of hanging.  At most cap_rows rows per (sender,
+ * receiver, step); a device-side count above that is cut and raises SGL_DEV_OVERFLOW.
+ * The *_dev forms size their launch for rows_hint rows (any value works; it only sets the number of CTAs).
  * Replaces: the same reference code as sgl_cache_route_step; ShardTensor's peer-memory design
  * (csrc/include/starrygl/feature.cu.hpp:142-422) is the closest reference counterpart.
  * ---------------------------------------------------------------------------------------------- */
@@ -322,16 +335,20 @@ int sgl_p2p_close(void* peer_ptr);
 int sgl_p2p_free(void* ptr);
 int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_rows, int64_t pitch_floats, void* const* h_bases,
                          void** out_ctx);
+/* wait_ms: bound of every device-side wait (1..60000); bulk_bytes: message size from which a pair uses plain rows
+ * (0 = always).  A negative value leaves the setting as it is.  All ranks must use the same bulk_bytes. */
+int sgl_p2p_route_configure(void* ctx, int64_t wait_ms, int64_t bulk_bytes);
 int sgl_p2p_route_destroy(void* ctx);
 int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
                        const int64_t* send_idx, const int64_t* remote_idx, const int64_t* h_send_rows, uint64_t step,
                        int32_t* d_status, void* stream);
+int sgl_p2p_route_send_dev(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
+                           const int64_t* send_idx, const int64_t* remote_idx, const int64_t* d_send_rows,
+                           int64_t rows_hint, uint64_t step, int32_t* d_status, void* stream);
 int sgl_p2p_route_recv(void* ctx, const int64_t* h_recv_rows, float* data, int64_t data_rows, int64_t dim, int has_ts,
                        float* ts_table, uint64_t step, int32_t* d_status, void* stream);
-/* Diagnostics: with SGL_P2P_DBG=2 in the environment at context creation the kernels stamp %globaltimer per step
- * (send start, send end, apply start, first CTA applied, apply end, send resident, apply resident; 8 uint64 per step,
- * first 4096 steps); this copies them out. */
-int sgl_p2p_route_timeline(void* ctx, unsigned long long* h_out, int64_t steps);
+int sgl_p2p_route_recv_dev(void* ctx, int64_t rows_hint, float* data, int64_t data_rows, int64_t dim, int has_ts,
+                           float* ts_table, uint64_t step, int32_t* d_status, void* stream);
 /* send + recv of one step in one call (for callers that apply the received rows right away) */
 int sgl_p2p_route_step(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
                        const int64_t* send_idx, const int64_t* remote_idx, const int64_t* h_send_rows,
@@ -345,6 +362,26 @@ int sgl_p2p_route_step(void* ctx, const float* feats, int64_t n_rows, int64_t di
  * ---------------------------------------------------------------------------------------------- */
 int sgl_route_add_rows(float* x, int64_t n_rows, int64_t dim, const int64_t* send_idx, const float* outs,
                        int64_t seg_len, int32_t* d_status, void* stream);
+
+/* All peer segments of the reverse route in one launch.  The received rows `outs` are grouped by destination:
+ * group u adds outs[pos[j], :] for j in [row_ptr[u], row_ptr[u+1]) -- positions ascending, i.e. in peer order -- to
+ * x[rows[u], :], one contribution after the other, which gives the float32 result of the per-peer loop bit for bit.
+ * The grouping (a stable sort of the route's send_index) is built once per route.
+ * Replaces: the whole loop of RouteContext._recv_post (starrygl/route/route.py:456-466). */
+int sgl_route_add_grouped(float* x, int64_t n_rows, int64_t dim, const int64_t* rows, const int64_t* row_ptr,
+                          const int64_t* pos, int64_t n_groups, const float* outs, int64_t n_outs, int32_t* d_status,
+                          void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Gather from a row table sharded over the GPUs of one node: out[i, :] = shard[part(i)][loc(i), :] with
+ * dist_idx[i] = (part << 48) | loc (sgl_dist_pack).  d_bases[world] (DEVICE array) holds every shard's base address as
+ * seen from this GPU -- its own memory or a peer mapping (sgl_p2p_open) -- d_shard_rows[world] the shards' row counts.
+ * Rows are read from their owner directly over NVLink: no id exchange, no row exchange, no reorder pass.
+ * Replaces: ShardTensor::operator[] (csrc/include/starrygl/feature.cu.hpp:298-422: split ids by owner, exchange ids,
+ * owner-side tensor_gather :42-88, exchange rows, scatter to the original order).
+ * ---------------------------------------------------------------------------------------------- */
+int sgl_shard_gather(const void* const* d_bases, const int64_t* d_shard_rows, int world, int64_t row_bytes,
+                     const int64_t* dist_idx, int64_t n, const int64_t* d_n, void* out, int32_t* d_status, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * DistRouteIndex packing: dist = (loc & (2^48-1)) | ((part & 0x3FFF) << 48) | (shared << 62).

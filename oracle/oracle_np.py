@@ -21,6 +21,8 @@ Reference locations restated (paths inside the reference project):
 * replica lookup                   starrygl/cache/replica_table.py:16-82, :178-215
 * cache route                      starrygl/cache/cache_route.py:211-277, starrygl/cache/NodeState.py:245-282
 * halo route                       starrygl/route/route.py:427-466
+* distributed gather (intent)      csrc/include/starrygl/feature.cu.hpp:298-422 (parity unpinned: the reference
+                                   code cannot run; this restates the steps its comments and calls name)
 * mailbox update                   starrygl/nn/memory/mailbox.py:41-84
 """
 import numpy as np
@@ -377,6 +379,24 @@ def route_reverse(gs, send_sizes, recv_sizes, send_index):
 # ----------------------------------------------------------------------------------------------
 # route plan of one layer
 # ----------------------------------------------------------------------------------------------
+
+
+def shard_gather(shards, dist_idx, me=0):
+    """Distributed row gather as rank ``me`` would run it, step by step as ShardTensor::operator[] lays it out
+    (csrc/include/starrygl/feature.cu.hpp:298-422): split the packed ids by owner partition (copy_if per partition, in
+    partition order :353-357), send every owner its list of local rows (:367), the owner gathers them from its shard
+    (tensor_gather :377-380), the rows travel back (:387) and are scattered to the positions the ids came from
+    (:389-392).  ``shards[p]`` = rows owned by partition p; ``dist_idx`` = (part << 48) | loc."""
+    dist_idx = np.asarray(dist_idx, I64)
+    part = (dist_idx >> 48) & 0x3FFF
+    loc = dist_idx & ((1 << 48) - 1)
+    out = np.empty((len(dist_idx),) + shards[0].shape[1:], shards[0].dtype)
+    for p in range(len(shards)):
+        pos = np.nonzero(part == p)[0]          # original positions of the ids partition p owns, ascending
+        asked = loc[pos]                        # id message to owner p
+        rows = shards[p][asked]                 # owner-side gather, row message back
+        out[pos] = rows                         # scatter to the original order
+    return out
 
 
 def compute_layer_route(layer_ids, layer_ts, node_parts, pid, rep_indptr, rep_ranks, rep_locs, num_parts):

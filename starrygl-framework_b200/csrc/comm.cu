@@ -25,18 +25,13 @@ struct NcclApi {
   ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
   ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
   const char* (*GetErrorString)(ncclResult_t);
-  bool ok = false;
 };
 
-static NcclApi* nccl_api() {
-  static NcclApi api;
-  static bool tried = false;
-  if (tried) return api.ok ? &api : nullptr;
-  tried = true;
+static bool load_nccl(NcclApi* api) {
   void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);   // the copy the process already uses, if any
   if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-  if (!h) return nullptr;
-#define SGL_SYM(field, name) *(void**)(&api.field) = dlsym(h, name); if (!api.field) return nullptr
+  if (!h) return false;
+#define SGL_SYM(field, name) *(void**)(&api->field) = dlsym(h, name); if (!api->field) return false
   SGL_SYM(GetUniqueId, "ncclGetUniqueId");
   SGL_SYM(CommInitRank, "ncclCommInitRank");
   SGL_SYM(CommDestroy, "ncclCommDestroy");
@@ -46,8 +41,15 @@ static NcclApi* nccl_api() {
   SGL_SYM(Recv, "ncclRecv");
   SGL_SYM(GetErrorString, "ncclGetErrorString");
 #undef SGL_SYM
-  api.ok = true;
-  return &api;
+  return true;
+}
+
+// Resolved once per process; a function-local static is initialised under the language's own lock, so host threads
+// that race here all wait for the one dlopen / dlsym sequence and see its result.
+static NcclApi* nccl_api() {
+  static NcclApi api;
+  static const bool ok = load_nccl(&api);
+  return ok ? &api : nullptr;
 }
 }  // namespace sgl
 
@@ -115,16 +117,24 @@ static int exchange(Comm* c, const float* send, const int64_t* h_send_rows, floa
                     int64_t row_floats, cudaStream_t stream) {
   SGL_NEED_NCCL();
   SGL_NCCL_CHECK(ncclGroupStart());
+  // a failing send / recv must not leave the group open for the next call of this thread: remember the first error,
+  // close the group, then report
+  ncclResult_t first = ncclSuccess;
   int64_t so = 0, ro = 0;
-  for (int p = 0; p < c->world; ++p) {
+  for (int p = 0; p < c->world && first == ncclSuccess; ++p) {
     if (h_send_rows[p] > 0)
-      SGL_NCCL_CHECK(ncclSend(send + so * row_floats, (size_t)(h_send_rows[p] * row_floats), ncclFloat, p, c->nccl, stream));
-    if (h_recv_rows[p] > 0)
-      SGL_NCCL_CHECK(ncclRecv(recv + ro * row_floats, (size_t)(h_recv_rows[p] * row_floats), ncclFloat, p, c->nccl, stream));
+      first = ncclSend(send + so * row_floats, (size_t)(h_send_rows[p] * row_floats), ncclFloat, p, c->nccl, stream);
+    if (first == ncclSuccess && h_recv_rows[p] > 0)
+      first = ncclRecv(recv + ro * row_floats, (size_t)(h_recv_rows[p] * row_floats), ncclFloat, p, c->nccl, stream);
     so += h_send_rows[p];
     ro += h_recv_rows[p];
   }
-  SGL_NCCL_CHECK(ncclGroupEnd());
+  const ncclResult_t end = ncclGroupEnd();
+  if (first == ncclSuccess) first = end;
+  if (first != ncclSuccess) {
+    sgl::set_error("route exchange failed: %s", ncclGetErrorString(first));
+    return SGL_ERR_CUDA;
+  }
   return SGL_OK;
 }
 
@@ -155,4 +165,35 @@ extern "C" int sgl_cache_route_step(void* comm, const float* feats, int64_t n_ro
   if (rc) return rc;
   if (apply) rc = sgl_route_unpack(recv_buf, n_recv, width, data, data_rows, dim, ts_table, d_status, stream);
   return rc;
+}
+
+extern "C" int sgl_comm_info(void* comm, int* out_rank, int* out_world) {
+  SGL_REQUIRE(comm, SGL_ERR_ARG, "comm_info: null communicator");
+  Comm* c = (Comm*)comm;
+  if (out_rank) *out_rank = c->rank;
+  if (out_world) *out_world = c->world;
+  return SGL_OK;
+}
+
+// Peer access from the current device to the listed devices of this process (needed only when one process drives
+// several GPUs; mappings of other processes' memory enable it themselves when they are opened).
+extern "C" int sgl_init_p2p(const int* devices, int n, int* out_accessible) {
+  SGL_REQUIRE(n >= 0 && (n == 0 || devices), SGL_ERR_ARG, "init_p2p: bad device list");
+  int cur = 0, count = 0, ok = 0;
+  SGL_CUDA_CHECK(cudaGetDevice(&cur));
+  SGL_CUDA_CHECK(cudaGetDeviceCount(&count));
+  for (int i = 0; i < n; ++i) {
+    const int d = devices[i];
+    if (d == cur) { ++ok; continue; }
+    if (d < 0 || d >= count) continue;     // a device of another process: nothing to enable from here
+    int can = 0;
+    SGL_CUDA_CHECK(cudaDeviceCanAccessPeer(&can, cur, d));
+    if (!can) continue;
+    cudaError_t e = cudaDeviceEnablePeerAccess(d, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); e = cudaSuccess; }
+    SGL_CUDA_CHECK(e);
+    ++ok;
+  }
+  if (out_accessible) *out_accessible = ok;
+  return SGL_OK;
 }

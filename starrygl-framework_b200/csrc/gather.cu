@@ -12,8 +12,6 @@
 //   scatter_lanes_kernel    the reverse of the gather, optionally splitting a trailing timestamp column.
 //
 // Algorithmic HBM bytes: rows * (2 * row_bytes + 8) (+4 per id for the hit-map, +16 per miss for the miss list).
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "scan.cuh"
 
@@ -101,7 +99,7 @@ gather_lanes_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t
 // ---------------------------------------------------------------------------------------------------------------
 // bulk asynchronous copy path
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kBulkWarps = 4;     // default configuration; the kernel is templated for tuning
+constexpr int kBulkWarps = 4;
 constexpr int kBulkStages = 3;
 constexpr unsigned long long kBulkWaitLimitNs = 2000000000ull;  // a wait gives up after two seconds
 
@@ -149,35 +147,35 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Output rows must be contiguous (dst_pitch == row_bytes); row_bytes multiple of 16; rows_per_stage <= 32.
-template <int kBulkWarps, int kBulkStages>
-__global__ void __launch_bounds__(kBulkWarps * 32)
+template <int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32)
 gather_bulk_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t row_bytes, int64_t src_pitch,
                    const int64_t* __restrict__ idx, const int64_t* __restrict__ map, int64_t map_len, int64_t n_cap,
                    const int64_t* d_n, char* __restrict__ out, const float* __restrict__ ts_table,
                    float* __restrict__ out_ts, int rows_per_stage, int32_t* d_status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t bars[kBulkWarps][kBulkStages];
+  __shared__ __align__(8) uint64_t bars[WARPS][STAGES];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t n = eff_count(n_cap, d_n);
   const uint32_t stage_bytes = (uint32_t)rows_per_stage * row_bytes;
-  unsigned char* my_smem = smem_raw + (size_t)warp * kBulkStages * stage_bytes;
+  unsigned char* my_smem = smem_raw + (size_t)warp * STAGES * stage_bytes;
   const int64_t num_chunks = (n + rows_per_stage - 1) / rows_per_stage;
-  const int64_t warps_total = (int64_t)gridDim.x * kBulkWarps;
-  const int64_t gwarp = (int64_t)blockIdx.x * kBulkWarps + warp;
+  const int64_t warps_total = (int64_t)gridDim.x * WARPS;
+  const int64_t gwarp = (int64_t)blockIdx.x * WARPS + warp;
 
   if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < kBulkStages; ++s) mbar_init(smem_u32(&bars[warp][s]), 1);
+    for (int s = 0; s < STAGES; ++s) mbar_init(smem_u32(&bars[warp][s]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
   }
   __syncwarp();
 
-  // issue the loads of this warp's k-th chunk into stage k % kBulkStages
+  // issue the loads of this warp's k-th chunk into stage k % STAGES
   auto issue = [&](int64_t k) {
     const int64_t chunk = gwarp + k * warps_total;
     if (chunk >= num_chunks) return;
-    const int s = (int)(k % kBulkStages);
+    const int s = (int)(k % STAGES);
     const int64_t row0 = chunk * rows_per_stage;
     const int rows = (int)((n - row0) < rows_per_stage ? (n - row0) : rows_per_stage);
     const uint32_t bar = smem_u32(&bars[warp][s]);
@@ -192,13 +190,13 @@ gather_bulk_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t 
     }
   };
 
-  for (int k = 0; k < kBulkStages; ++k) issue(k);
+  for (int k = 0; k < STAGES; ++k) issue(k);
   bool failed = false;
   for (int64_t k = 0;; ++k) {
     const int64_t chunk = gwarp + k * warps_total;
     if (chunk >= num_chunks) break;
-    const int s = (int)(k % kBulkStages);
-    const uint32_t parity = (uint32_t)((k / kBulkStages) & 1);
+    const int s = (int)(k % STAGES);
+    const uint32_t parity = (uint32_t)((k / STAGES) & 1);
     const int64_t row0 = chunk * rows_per_stage;
     const int rows = (int)((n - row0) < rows_per_stage ? (n - row0) : rows_per_stage);
     bool ok = mbar_wait_bounded(smem_u32(&bars[warp][s]), parity);
@@ -214,13 +212,13 @@ gather_bulk_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t 
       bulk_wait_read<1>();
     }
     __syncwarp();
-    if (k >= 1) issue(k - 1 + kBulkStages);
+    if (k >= 1) issue(k - 1 + STAGES);
   }
   if (lane == 0) bulk_wait_all();
   if (failed) {
     if (lane == 0) dev_flag(d_status, SGL_DEV_TIMEOUT);
     // give copies still in flight a bounded chance to land before the CTA's shared memory is released
-    for (int s = 0; s < kBulkStages; ++s) mbar_wait_bounded(smem_u32(&bars[warp][s]), 0);
+    for (int s = 0; s < STAGES; ++s) mbar_wait_bounded(smem_u32(&bars[warp][s]), 0);
   }
   __syncwarp();
 }
@@ -424,6 +422,73 @@ route_add_kernel(float* __restrict__ x, int64_t n_rows, uint32_t dim, const int6
   }
 }
 
+// Reverse-route accumulate over ALL peer segments in one launch.  The received rows are grouped by the row of x they
+// add to (row_ptr / pos: for destination row rows[u] the positions pos[row_ptr[u] .. row_ptr[u+1]) of `outs`, ascending,
+// i.e. in peer order); one warp owns one destination row and adds its contributions one after the other, which is
+// the summation order of a per-peer loop -- the float32 result is the same bit for bit.
+__global__ void __launch_bounds__(kLaneThreads)
+route_add_grouped_kernel(float* __restrict__ x, int64_t n_rows, uint32_t dim, const int64_t* __restrict__ rows,
+                         const int64_t* __restrict__ row_ptr, const int64_t* __restrict__ pos, int64_t n_groups,
+                         const float* __restrict__ outs, int64_t n_outs, int32_t* d_status) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (kLaneThreads / 32);
+  for (int64_t u = ((int64_t)blockIdx.x * kLaneThreads + threadIdx.x) >> 5; u < n_groups; u += warps) {
+    int64_t r = __ldg(rows + u);
+    if (r < 0) r += n_rows;
+    if (r < 0 || r >= n_rows) {
+      if (lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
+      continue;
+    }
+    const int64_t a = __ldg(row_ptr + u), b = __ldg(row_ptr + u + 1);
+    for (uint32_t l = lane; l < dim; l += 32) {
+      float acc = x[r * dim + l];
+      for (int64_t j = a; j < b; ++j) {
+        const int64_t p = __ldg(pos + j);
+        if (p >= 0 && p < n_outs) acc += __ldg(outs + p * dim + l);
+        else dev_flag(d_status, SGL_DEV_BAD_INDEX);
+      }
+      x[r * dim + l] = acc;
+    }
+  }
+}
+
+// Gather from a table whose rows live on several GPUs of one node: id = (partition << 48) | local row (the packed
+// route index); the row is read straight from its owner's memory over NVLink (plain 128-bit / 32-bit loads of a peer
+// mapping), so every row crosses the link once and no id or row exchange is needed.
+template <typename V>
+__global__ void __launch_bounds__(kLaneThreads)
+shard_gather_kernel(const char* const* __restrict__ bases, const int64_t* __restrict__ shard_rows, int world,
+                    uint32_t lanes_per_row, int64_t row_bytes, const int64_t* __restrict__ dist_idx, int64_t n_cap,
+                    const int64_t* d_n, char* __restrict__ out, int32_t* d_status) {
+  const int64_t n = eff_count(n_cap, d_n);
+  const int64_t total = n * lanes_per_row;
+  const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
+  for (int64_t q0 = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q0 < total; q0 += stride * kLaneUnroll) {
+    V v[kLaneUnroll];
+    V* dst[kLaneUnroll];
+#pragma unroll
+    for (int u = 0; u < kLaneUnroll; ++u) {
+      const int64_t q = q0 + u * stride;
+      dst[u] = nullptr;
+      if (q < total) {
+        const int64_t i = q / lanes_per_row;
+        const uint32_t l = (uint32_t)(q - i * lanes_per_row);
+        const int64_t id = __ldg(dist_idx + i);
+        const int64_t part = (id >> 48) & 0x3FFF, loc = id & 0xFFFFFFFFFFFFll;
+        if (part >= world || loc >= __ldg(shard_rows + part)) {
+          dev_flag(d_status, SGL_DEV_BAD_INDEX);
+        } else {
+          v[u] = ld_stream((const V*)(bases[part] + loc * row_bytes) + l);
+          dst[u] = (V*)(out + i * row_bytes) + l;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kLaneUnroll; ++u)
+      if (dst[u]) st_stream(dst[u], v[u]);
+  }
+}
+
 __global__ void dist_pack_kernel(const int64_t* __restrict__ loc, const int64_t* __restrict__ part,
                                  const uint8_t* __restrict__ shared, int64_t n, int64_t* __restrict__ dist) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
@@ -535,51 +600,34 @@ extern "C" int sgl_gather_rows(const void* table, int64_t table_rows, int64_t ro
   SGL_REQUIRE(table && idx && out, SGL_ERR_ARG, "gather_rows: null array");
   SGL_REQUIRE(map == nullptr || map_len > 0, SGL_ERR_ARG, "gather_rows: empty map");
   const bool vec_ok = row_bytes % 16 == 0 && src_pitch % 16 == 0 && dst_pitch % 16 == 0 && aligned16(table) && aligned16(out);
+  // bulk configuration: 4 warps x 3 stages per CTA, two CTAs per SM, about 5.5 KB per stage (8 rows of 688 bytes)
+  constexpr int64_t kBulkBudget = 200 * 1024 / 2;
+  int rows_per_stage = (int)(kBulkBudget / ((int64_t)kBulkWarps * kBulkStages * row_bytes));
+  {
+    const int want_rows = (int)((5632 + row_bytes - 1) / row_bytes);
+    if (rows_per_stage > want_rows) rows_per_stage = want_rows;
+    if (rows_per_stage > 32) rows_per_stage = 32;
+  }
   if (mode == SGL_GATHER_AUTO) {
-    // measured on B200: the bulk-copy pipeline beats 128-bit lanes from 512-byte rows up; below that they tie
-    const bool bulk_ok = vec_ok && dst_pitch == row_bytes && row_bytes >= 512 && row_bytes <= 8192 && n >= 1024;
+    // measured on B200: the bulk-copy pipeline beats 128-bit lanes from 512-byte rows up; below that they tie.  Rows
+    // of which fewer than two fit a stage (above about 4 KB) go through the lanes kernel.
+    const bool bulk_ok = vec_ok && dst_pitch == row_bytes && row_bytes >= 512 && rows_per_stage >= 2 && n >= 1024;
     mode = bulk_ok ? SGL_GATHER_BULK : (vec_ok ? SGL_GATHER_VEC : 0);
   }
   if (mode == SGL_GATHER_BULK) {
     SGL_REQUIRE(vec_ok && dst_pitch == row_bytes, SGL_ERR_UNSUPPORTED,
                 "gather_rows: bulk mode needs 16-byte rows and a dense output");
-    // configuration: warps per CTA, stages per warp, rows per stage, CTAs per SM (SGL_BULK_CFG="w,s,r,c" overrides)
-    static int cfg[4] = {-1, 0, 0, 0};
-    if (cfg[0] < 0) {
-      cfg[0] = kBulkWarps; cfg[1] = kBulkStages; cfg[2] = 0; cfg[3] = 2;   // measured best on B200 (two CTAs per SM)
-      const char* e = getenv("SGL_BULK_CFG");
-      if (e) sscanf(e, "%d,%d,%d,%d", &cfg[0], &cfg[1], &cfg[2], &cfg[3]);
-    }
-    const int warps = cfg[0], stages = cfg[1], ctas_per_sm = cfg[3] < 1 ? 1 : cfg[3];
-    const int64_t budget = 200 * 1024 / ctas_per_sm;
-    int rows_per_stage = (int)(budget / ((int64_t)warps * stages * row_bytes));
-    // about 5.5 KB per stage (8 rows of 688 bytes) unless overridden
-    const int want_rows = cfg[2] > 0 ? cfg[2] : (int)((5632 + row_bytes - 1) / row_bytes);
-    if (rows_per_stage > want_rows) rows_per_stage = want_rows;
-    if (rows_per_stage > 32) rows_per_stage = 32;
     SGL_REQUIRE(rows_per_stage >= 2, SGL_ERR_UNSUPPORTED, "gather_rows: row of %lld bytes too large for bulk mode",
                 (long long)row_bytes);
-    const size_t smem = (size_t)warps * stages * rows_per_stage * row_bytes;
+    const size_t smem = (size_t)kBulkWarps * kBulkStages * rows_per_stage * row_bytes;
     const int64_t chunks = (n + rows_per_stage - 1) / rows_per_stage;
-    int64_t ctas = (chunks + warps - 1) / warps;
-    if (ctas > (int64_t)kNumSM * ctas_per_sm) ctas = (int64_t)kNumSM * ctas_per_sm;  // persistent CTAs
-#define SGL_BULK_LAUNCH(W, S)                                                                                          \
-  do {                                                                                                                 \
-    SGL_CUDA_CHECK(cudaFuncSetAttribute(gather_bulk_kernel<W, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); \
-    gather_bulk_kernel<W, S><<<(unsigned)ctas, W * 32, smem, stream>>>(                                                \
-        (const char*)table, table_rows, (uint32_t)row_bytes, src_pitch, idx, map, map_len, n, d_n, (char*)out, ts_table, \
-        out_ts, rows_per_stage, d_status);                                                                             \
-  } while (0)
-    if (warps == 4 && stages == 3) SGL_BULK_LAUNCH(4, 3);
-    else if (warps == 4 && stages == 2) SGL_BULK_LAUNCH(4, 2);
-    else if (warps == 4 && stages == 4) SGL_BULK_LAUNCH(4, 4);
-    else if (warps == 8 && stages == 2) SGL_BULK_LAUNCH(8, 2);
-    else if (warps == 8 && stages == 3) SGL_BULK_LAUNCH(8, 3);
-    else if (warps == 8 && stages == 4) SGL_BULK_LAUNCH(8, 4);
-    else if (warps == 2 && stages == 4) SGL_BULK_LAUNCH(2, 4);
-    else if (warps == 16 && stages == 2) SGL_BULK_LAUNCH(16, 2);
-    else SGL_REQUIRE(false, SGL_ERR_ARG, "gather_rows: unsupported SGL_BULK_CFG %d,%d", warps, stages);
-#undef SGL_BULK_LAUNCH
+    int64_t ctas = (chunks + kBulkWarps - 1) / kBulkWarps;
+    if (ctas > (int64_t)kNumSM * 2) ctas = (int64_t)kNumSM * 2;  // persistent CTAs
+    SGL_CUDA_CHECK(cudaFuncSetAttribute(gather_bulk_kernel<kBulkWarps, kBulkStages>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    gather_bulk_kernel<kBulkWarps, kBulkStages><<<(unsigned)ctas, kBulkWarps * 32, smem, stream>>>(
+        (const char*)table, table_rows, (uint32_t)row_bytes, src_pitch, idx, map, map_len, n, d_n, (char*)out, ts_table,
+        out_ts, rows_per_stage, d_status);
     SGL_LAUNCH_CHECK();
     return SGL_OK;
   }
@@ -759,6 +807,42 @@ extern "C" int sgl_route_add_rows(float* x, int64_t n_rows, int64_t dim, const i
   SGL_REQUIRE(x && send_idx && outs, SGL_ERR_ARG, "route_add_rows: null array");
   const int grid = stream_grid(seg_len * dim, kLaneThreads, 16);
   route_add_kernel<<<grid, kLaneThreads, 0, stream>>>(x, n_rows, (uint32_t)dim, send_idx, outs, seg_len, d_status);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" int sgl_route_add_grouped(float* x, int64_t n_rows, int64_t dim, const int64_t* rows, const int64_t* row_ptr,
+                                     const int64_t* pos, int64_t n_groups, const float* outs, int64_t n_outs,
+                                     int32_t* d_status, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(n_groups >= 0 && n_rows >= 0 && n_outs >= 0 && dim > 0, SGL_ERR_ARG, "route_add_grouped: bad size");
+  if (n_groups == 0) return SGL_OK;
+  SGL_REQUIRE(x && rows && row_ptr && pos && outs, SGL_ERR_ARG, "route_add_grouped: null array");
+  const int grid = stream_grid(n_groups, kLaneThreads / 32, 16);
+  route_add_grouped_kernel<<<grid, kLaneThreads, 0, stream>>>(x, n_rows, (uint32_t)dim, rows, row_ptr, pos, n_groups, outs,
+                                                             n_outs, d_status);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" int sgl_shard_gather(const void* const* d_bases, const int64_t* d_shard_rows, int world, int64_t row_bytes,
+                                const int64_t* dist_idx, int64_t n, const int64_t* d_n, void* out, int32_t* d_status,
+                                void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  SGL_REQUIRE(n >= 0 && world >= 1 && world <= 0x3FFF && row_bytes > 0 && row_bytes % 4 == 0, SGL_ERR_ARG,
+              "shard_gather: bad size (rows must be multiples of 4 bytes)");
+  if (n == 0) return SGL_OK;
+  SGL_REQUIRE(d_bases && d_shard_rows && dist_idx && out, SGL_ERR_ARG, "shard_gather: null array");
+  // the shard base pointers are device values: their 16-byte alignment is the caller's contract (cudaMalloc gives 256)
+  if (row_bytes % 16 == 0 && aligned16(out)) {
+    const uint32_t lanes = (uint32_t)(row_bytes / 16);
+    shard_gather_kernel<uint4><<<stream_grid(n * lanes, kLaneThreads * kLaneUnroll, 8), kLaneThreads, 0, stream>>>(
+        (const char* const*)d_bases, d_shard_rows, world, lanes, row_bytes, dist_idx, n, d_n, (char*)out, d_status);
+  } else {
+    const uint32_t lanes = (uint32_t)(row_bytes / 4);
+    shard_gather_kernel<uint32_t><<<stream_grid(n * lanes, kLaneThreads * kLaneUnroll, 8), kLaneThreads, 0, stream>>>(
+        (const char* const*)d_bases, d_shard_rows, world, lanes, row_bytes, dist_idx, n, d_n, (char*)out, d_status);
+  }
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }

@@ -2,6 +2,9 @@
 //
 // Every rank owns a buffer that all ranks of the node map (CUDA IPC):
 //     acks [world]         acks[p] = number of this rank's steps that receiver p has applied (written by p)
+//     meta [world][ring]   meta[q][slot] = (rows << 32) | tag: how many rows sender q pushed here in the step that uses
+//                          the slot.  The receiver learns its row counts from these words, so a plan that was built on
+//                          the device (its sizes never visit the host) needs no count exchange and no host sync.
 //     stage[world][ring][cap_rows][pitch / 2]   16-byte lines from sender q, ring slot = step % ring
 //
 // The wire row of a node is [features | ts | slot lo | slot hi | pad] (pitch 32-bit words, a multiple of 4), the same
@@ -21,10 +24,9 @@
 // Large messages: tagging doubles the bytes on the wire, which is the wrong trade once a message is bandwidth-bound.
 // A (sender, receiver) pair whose message of a step has at least `bulk_rows` rows (both ends know that count) uses
 // plain wire rows instead -- 128-bit stores into the first half of the same staging region -- followed by one
-// system-scope fence per CTA, an arrival counter, and a per-pair flag
-//     flags[world][ring]   flags[q][slot] = step + 1 once sender q's plain rows of that step have landed here
-// written by the last CTA of the send kernel; the receiver waits (bounded) for the flags of its bulk senders before
-// it reads their rows.  Small and large pairs can be mixed inside one step.
+// system-scope fence per CTA and an arrival counter; the last CTA of the send kernel then writes the pair's meta word,
+// which for such a pair doubles as the "rows have landed" flag (for a small pair the meta word is written up front and
+// the lines validate themselves).  Small and large pairs can be mixed inside one step.
 // (A region that held plain rows and is reused for tagged lines contains arbitrary words, not old tags: a stale line
 // passes for a fresh one only if two of its words both equal the new 32-bit tag, a 2^-64 event per line.)
 //
@@ -32,7 +34,6 @@
 // wait is bounded by a wall-clock limit; on expiry the kernel raises SGL_DEV_TIMEOUT in the status word, publishes
 // nothing and returns, so the context stays usable.  Every rank must run send and recv for every step (zero rows are
 // fine): the handshake is per step, not per row.
-#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -43,21 +44,19 @@ namespace {
 constexpr int kMaxWorld = 16;
 constexpr int kThreads = 128;   // 4 warps per CTA, one row per warp at a time
 constexpr int kRowsInFlight = 1;   // rows per warp and iteration; more in flight measured slower (299 vs 371 GB/s at 40 MB)
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // default bound of every device-side wait (SGL_P2P_WAIT_MS overrides)
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // default bound of every device-side wait (sgl_p2p_route_configure changes it)
 
 struct P2PCfg {
-  int dbg;
   unsigned long long wait_ns;   // bound of every device-side wait
-  unsigned long long* tl;   // optional timeline buffer [steps][8] (diagnostics)
   int rank, world, ring;
   int64_t cap_rows;
   uint32_t pitch;           // 32-bit words per wire row; a row occupies pitch / 2 lines
   int64_t bulk_rows;        // a pair's message with at least this many rows travels as plain rows + flag
   unsigned long long* acks;
-  unsigned long long* flags;
+  unsigned long long* meta;
   uint4* stage;
   unsigned long long* peer_acks[kMaxWorld];
-  unsigned long long* peer_flags[kMaxWorld];
+  unsigned long long* peer_meta[kMaxWorld];
   uint4* peer_stage[kMaxWorld];
 };
 
@@ -148,10 +147,14 @@ __device__ __forceinline__ uint4 wire_quad(uint32_t l, uint32_t dim, uint32_t pa
   return v;
 }
 
-__device__ __forceinline__ int segment_of(const Splits& s, int world, int64_t i) {
+__device__ __forceinline__ int segment_of(const int64_t* off, int world, int64_t i) {
   int p = 0;
-  while (p + 1 < world && i >= s.off[p + 1]) ++p;
+  while (p + 1 < world && i >= off[p + 1]) ++p;
   return p;
+}
+
+__device__ __forceinline__ unsigned long long meta_word(int64_t rows, unsigned long long step) {
+  return ((unsigned long long)rows << 32) | (unsigned long long)(uint32_t)(step + 1);
 }
 
 // A route kernel competes for issue slots with whatever else runs on its SM (warps are scheduled round robin, stream
@@ -159,17 +162,35 @@ __device__ __forceinline__ int segment_of(const Splits& s, int world, int64_t i)
 // warp, not by memory latency.  Hence one WARP per row: the row's index, destination and segment are computed once
 // per row with no division, a lane handles a quad (4 consecutive wire words = 2 lines), and many small warps rather
 // than few long-running ones share the work.
+//
+// Row counts per destination come from the host (seg, d_sizes == nullptr) or from device memory (d_sizes[world], the
+// send sizes a device-built plan left there); counts above the staging capacity are cut and flagged.
 __global__ void __launch_bounds__(kThreads)
 p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint32_t dim, const float* __restrict__ ts,
                 const int64_t* __restrict__ send_idx, const int64_t* __restrict__ remote_idx, Splits seg,
-                unsigned long long step, int vec_ok, int any_bulk, unsigned int* done_counter, int32_t* d_status) {
+                const int64_t* __restrict__ d_sizes, unsigned long long step, int vec_ok, unsigned int* done_counter,
+                int32_t* d_status) {
   __shared__ int s_ok;
   __shared__ bool s_last;
-  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 5] = now_ns();
+  __shared__ int64_t s_off[kMaxWorld + 1];   // exclusive prefix of the row counts per destination (what is SENT)
+  __shared__ int64_t s_src[kMaxWorld + 1];   // the same prefix over the plan's own counts (where the rows sit in send_idx)
   pdl_wait();
   pdl_release();
-  if (threadIdx.x == 0) s_ok = 1;
-  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 0] = now_ns();
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    s_off[0] = s_src[0] = 0;
+    for (int p = 0; p < c.world; ++p) {
+      int64_t have = d_sizes ? d_sizes[p] : seg.off[p + 1] - seg.off[p];
+      if (have < 0) have = 0;
+      int64_t cnt = have;
+      if (cnt > c.cap_rows) {
+        dev_flag(d_status, SGL_DEV_OVERFLOW);
+        cnt = c.cap_rows;
+      }
+      s_off[p + 1] = s_off[p] + cnt;
+      s_src[p + 1] = s_src[p] + have;
+    }
+  }
   __syncthreads();
   // flow control: the ring slot may be overwritten once every receiver has applied the step that used it last
   if (threadIdx.x < c.world && step >= (unsigned long long)c.ring) {
@@ -182,57 +203,49 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
   const uint32_t payload = dim + (ts ? 1u : 0u);
   const uint32_t quads = c.pitch / 4;
   const uint32_t lane = threadIdx.x & 31u;
-  const int64_t n_send = ok ? seg.off[c.world] : 0;
-  const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
-  const int64_t slot_base = ((int64_t)c.rank * c.ring + (int64_t)(step % c.ring)) * c.cap_rows;
-  // kRowsInFlight rows per warp and iteration, in three phases (indices, rows, stores)
-  for (int64_t i0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i0 < n_send; i0 += n_warps * kRowsInFlight) {
-    int64_t r[kRowsInFlight];
-    uint64_t slotv[kRowsInFlight];
-#pragma unroll
-    for (int u = 0; u < kRowsInFlight; ++u) {
-      const int64_t i = i0 + u * n_warps;
-      r[u] = -1;
-      slotv[u] = 0;
-      if (i < n_send) {
-        r[u] = __ldg(send_idx + i);                       // one address per warp: a single broadcast load
-        slotv[u] = (uint64_t)__ldg(remote_idx + i);
-        if (r[u] < 0) r[u] += n_rows;
-        if (r[u] < 0 || r[u] >= n_rows) {
-          if (lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
-          r[u] = -2;                                      // sent as zeros with slot -1, which the receiver skips
-        }
-      }
+  const int64_t ring_slot = (int64_t)(step % c.ring);
+  bool any_bulk = false;
+  for (int p = 0; p < c.world; ++p) any_bulk |= s_off[p + 1] - s_off[p] >= c.bulk_rows;
+  // small pairs: the count goes out first, the tagged lines validate themselves
+  if (ok && blockIdx.x == 0 && threadIdx.x < c.world) {
+    const int64_t cnt = s_off[threadIdx.x + 1] - s_off[threadIdx.x];
+    if (cnt < c.bulk_rows) {
+      volatile unsigned long long* m = c.peer_meta[threadIdx.x] + (int64_t)c.rank * c.ring + ring_slot;
+      *m = meta_word(cnt, step);
     }
-    uint4 v[kRowsInFlight];
-#pragma unroll
-    for (int u = 0; u < kRowsInFlight; ++u)
-      if (r[u] != -1 && lane < quads) v[u] = wire_quad(lane, dim, payload, vec_ok, feats, ts, r[u], slotv[u]);
-#pragma unroll
-    for (int u = 0; u < kRowsInFlight; ++u) {
-      if (r[u] == -1) continue;
-      const int64_t i = i0 + u * n_warps;
-      const int p = segment_of(seg, c.world, i);
-      const bool bulk = seg.off[p + 1] - seg.off[p] >= c.bulk_rows;
-      // the pair's region starts at the same place in both layouts; a plain row takes pitch / 4 lines, a tagged one pitch / 2
-      uint4* region = c.peer_stage[p] + slot_base * (c.pitch / 2);
-      uint4* dst = region + (i - seg.off[p]) * (bulk ? c.pitch / 4 : c.pitch / 2);
-      for (uint32_t l = lane; l < quads; l += 32) {
-        const uint4 q = l == lane ? v[u] : wire_quad(l, dim, payload, vec_ok, feats, ts, r[u], slotv[u]);
-        if (bulk) {
-          dst[l] = q;
-        } else {
-          store_line(dst + 2 * l, q.x, q.y, tag);
-          store_line(dst + 2 * l + 1, q.z, q.w, tag);
-        }
+  }
+  const int64_t n_send = ok ? s_off[c.world] : 0;
+  const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
+  const int64_t slot_base = ((int64_t)c.rank * c.ring + ring_slot) * c.cap_rows;
+  for (int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i < n_send; i += n_warps) {
+    const int p = segment_of(s_off, c.world, i);
+    const int64_t in_seg = i - s_off[p];
+    const int64_t src = s_src[p] + in_seg;                // position in the plan's index arrays
+    int64_t r = __ldg(send_idx + src);                    // one address per warp: a single broadcast load
+    const uint64_t slotv = (uint64_t)__ldg(remote_idx + src);
+    if (r < 0) r += n_rows;
+    if (r < 0 || r >= n_rows) {
+      if (lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
+      r = -2;                                             // sent as zeros with slot -1, which the receiver skips
+    }
+    const bool bulk = s_off[p + 1] - s_off[p] >= c.bulk_rows;
+    // the pair's region starts at the same place in both layouts; a plain row takes pitch / 4 lines, a tagged one pitch / 2
+    uint4* region = c.peer_stage[p] + slot_base * (c.pitch / 2);
+    uint4* dst = region + in_seg * (bulk ? c.pitch / 4 : c.pitch / 2);
+    for (uint32_t l = lane; l < quads; l += 32) {
+      const uint4 q = wire_quad(l, dim, payload, vec_ok, feats, ts, r, slotv);
+      if (bulk) {
+        dst[l] = q;
+      } else {
+        store_line(dst + 2 * l, q.x, q.y, tag);
+        store_line(dst + 2 * l + 1, q.z, q.w, tag);
       }
     }
   }
-  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 1] = now_ns();
   if (!any_bulk) return;
-  // plain rows are published with a flag.  One system-scope fence per CTA: the CTA barrier makes every thread's stores
-  // happen-before thread 0's fence, and fences are cumulative, so thread 0's fence + counter increment orders the whole
-  // CTA's rows before anything the last CTA does after it has seen all increments.
+  // plain rows are published by the pair's meta word.  One system-scope fence per CTA: the CTA barrier makes every
+  // thread's stores happen-before thread 0's fence, and fences are cumulative, so thread 0's fence + counter increment
+  // orders the whole CTA's rows before anything the last CTA does after it has seen all increments.
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
@@ -243,50 +256,71 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
   __syncthreads();
   if (!s_last) return;
   const bool failed = !ok || (d_status && (*(volatile int32_t*)d_status & SGL_DEV_TIMEOUT));
-  if (threadIdx.x < c.world && !failed && seg.off[threadIdx.x + 1] - seg.off[threadIdx.x] >= c.bulk_rows) {
-    volatile unsigned long long* f = c.peer_flags[threadIdx.x] + (int64_t)c.rank * c.ring + (step % c.ring);
-    *f = step + 1;
+  if (threadIdx.x < c.world && !failed) {
+    const int64_t cnt = s_off[threadIdx.x + 1] - s_off[threadIdx.x];
+    if (cnt >= c.bulk_rows) {
+      volatile unsigned long long* m = c.peer_meta[threadIdx.x] + (int64_t)c.rank * c.ring + ring_slot;
+      *m = meta_word(cnt, step);
+    }
   }
   if (threadIdx.x == 0) *done_counter = 0;
 }
 
 // One warp per incoming row: every lane reads the line(s) holding the row's slot (one broadcast load per line) and
-// the 2 lines of its own quad, and re-polls (bounded) only what has not landed yet.
+// the 2 lines of its own quad, and re-polls (bounded) only what has not landed yet.  The number of rows per sender is
+// what the sender's meta word says; when the host also named a count (expect.off, check != 0) a difference is flagged.
 __global__ void __launch_bounds__(kThreads)
-p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, int64_t data_rows, uint32_t dim,
-                float* __restrict__ ts_table, unsigned long long step, int vec_ok, int any_bulk, unsigned int* done_counter,
+p2p_recv_kernel(P2PCfg c, Splits expect, int check, uint32_t width, float* __restrict__ data, int64_t data_rows, uint32_t dim,
+                float* __restrict__ ts_table, unsigned long long step, int vec_ok, unsigned int* done_counter,
                 int32_t* d_status) {
   __shared__ int s_ok;
   __shared__ bool s_last;
-  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 6] = now_ns();
+  __shared__ int64_t s_cnt[kMaxWorld];
+  __shared__ int64_t s_off[kMaxWorld + 1];
   pdl_wait();
   pdl_release();
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
-  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 2] = now_ns();
-  if (c.tl && threadIdx.x == 0 && step < 4096) atomicMax(c.tl + step * 8 + 7, now_ns());   // start of the latest CTA
   const uint32_t tag = (uint32_t)(step + 1);
   const uint32_t quads = (width + 3) / 4;                // quads that hold features / ts
   const uint32_t la = width / 2, lb = (width + 1) / 2;   // lines of the slot's low and high word
   const uint32_t lane = threadIdx.x & 31u;
-  const int64_t n_recv = seg.off[c.world];
   const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
   const int64_t ring_slot = (int64_t)(step % c.ring);
-  if (any_bulk) {
-    // plain rows of a large pair are complete once its sender's flag says so
-    if (threadIdx.x < c.world && seg.off[threadIdx.x + 1] - seg.off[threadIdx.x] >= c.bulk_rows) {
-      if (!wait_at_least(c.flags + (int64_t)threadIdx.x * c.ring + ring_slot, step + 1, c.wait_ns)) s_ok = 0;
-      __threadfence_system();   // acquire side: the rows written before the flag are visible after this fence ...
+  // every sender's meta word of this step: its row count; for a large pair also the sign that its plain rows landed
+  if (threadIdx.x < c.world) {
+    const volatile unsigned long long* m = c.meta + (int64_t)threadIdx.x * c.ring + ring_slot;
+    unsigned long long w = *m;
+    if ((uint32_t)w != tag) {
+      const unsigned long long t0 = now_ns();
+      bool got = false;
+      while (now_ns() - t0 < c.wait_ns) {
+        w = *m;
+        if ((uint32_t)w == tag) { got = true; break; }
+        __nanosleep(100);
+      }
+      if (!got) { s_ok = 0; w = 0; }
     }
-    __syncthreads();            // ... and, through the barrier, to every thread of the CTA
+    int64_t cnt = (int64_t)(w >> 32);
+    if (cnt > c.cap_rows) cnt = c.cap_rows;
+    if (check && s_ok && cnt != expect.off[threadIdx.x + 1] - expect.off[threadIdx.x]) dev_flag(d_status, SGL_DEV_MISMATCH);
+    s_cnt[threadIdx.x] = cnt;
+    __threadfence_system();   // acquire side: plain rows written before the meta word are visible after this fence ...
   }
+  __syncthreads();            // ... and, through the barrier, to every thread of the CTA
+  if (threadIdx.x == 0) {
+    s_off[0] = 0;
+    for (int p = 0; p < c.world; ++p) s_off[p + 1] = s_off[p] + s_cnt[p];
+  }
+  __syncthreads();
   bool ok = s_ok != 0;
+  const int64_t n_recv = ok ? s_off[c.world] : 0;
   for (int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i < n_recv && ok; i += n_warps) {
-    const int sdr = segment_of(seg, c.world, i);
+    const int sdr = segment_of(s_off, c.world, i);
     const uint4* region = c.stage + ((int64_t)sdr * c.ring + ring_slot) * c.cap_rows * (c.pitch / 2);
-    if (seg.off[sdr + 1] - seg.off[sdr] >= c.bulk_rows) {
+    if (s_cnt[sdr] >= c.bulk_rows) {
       // plain wire row (pitch / 4 quads); volatile loads: the row was written by another GPU
-      const uint4* prow = region + (i - seg.off[sdr]) * (c.pitch / 4);
+      const uint4* prow = region + (i - s_off[sdr]) * (c.pitch / 4);
       const uint4 qa = load_line(prow + width / 4), qb = load_line(prow + (width + 1) / 4);
       const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
       const int64_t dslot = (int64_t)((uint64_t)wa[width & 3] | ((uint64_t)wb[(width + 1) & 3] << 32));
@@ -308,7 +342,7 @@ p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, 
       }
       continue;
     }
-    const uint4* row = region + (i - seg.off[sdr]) * (c.pitch / 2);
+    const uint4* row = region + (i - s_off[sdr]) * (c.pitch / 2);
     // all loads in flight first; the rows have normally landed long ago
     uint4 sa = load_line(row + la);
     uint4 sb = la == lb ? sa : load_line(row + lb);
@@ -351,7 +385,6 @@ p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, 
     s_ok = 0;
     dev_flag(d_status, SGL_DEV_TIMEOUT);
   }
-  if (c.tl && blockIdx.x == 0 && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 3] = now_ns();
   // Acknowledge once every CTA has read its lines.  A thread reaches the barrier only after the values of its polls
   // have been examined, so its loads of the slot are complete by then; the counter is incremented after the CTA's
   // barrier and the acknowledgement is stored after the last increment, so no load of this step can still be in
@@ -369,7 +402,6 @@ p2p_recv_kernel(P2PCfg c, Splits seg, uint32_t width, float* __restrict__ data, 
     volatile unsigned long long* ak = c.peer_acks[threadIdx.x] + c.rank;   // "rank has applied your step"
     *ak = step + 1;
   }
-  if (c.tl && threadIdx.x == 0 && step < 4096) c.tl[step * 8 + 4] = now_ns();
   if (threadIdx.x == 0) *done_counter = 0;
 }
 
@@ -421,40 +453,47 @@ extern "C" int sgl_p2p_free(void* ptr) {
 extern "C" int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_rows, int64_t pitch_floats,
                                     void* const* h_bases, void** out_ctx) {
   SGL_REQUIRE(out_ctx && h_bases && world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world && ring >= 2 &&
-                  cap_rows >= 1 && pitch_floats >= 4 && pitch_floats % 4 == 0,
+                  cap_rows >= 1 && cap_rows < ((int64_t)1 << 31) && pitch_floats >= 4 && pitch_floats % 4 == 0,
               SGL_ERR_ARG, "p2p_route_create: bad argument (world <= %d, ring >= 2, pitch a multiple of 4)", kMaxWorld);
+  for (int p = 0; p < world; ++p)
+    SGL_REQUIRE(h_bases[p], SGL_ERR_ARG, "p2p_route_create: base pointer of rank %d is null", p);
+  unsigned int* counters = nullptr;
+  SGL_CUDA_CHECK(cudaMalloc(&counters, 256));
+  if (cudaMemset(counters, 0, 256) != cudaSuccess) {
+    cudaFree(counters);
+    set_error("p2p_route_create: cudaMemset of the arrival counters failed");
+    return SGL_ERR_CUDA;
+  }
   Ctx* x = new Ctx();
+  x->counters = counters;
   P2PCfg& c = x->cfg;
   c.wait_ns = kWaitLimitNs;
-  if (const char* w = getenv("SGL_P2P_WAIT_MS")) {
-    const long ms = atol(w);
-    if (ms >= 1 && ms <= 60000) c.wait_ns = (unsigned long long)ms * 1000000ull;
-  }
-  c.dbg = getenv("SGL_P2P_DBG") ? atoi(getenv("SGL_P2P_DBG")) : 0;   // 2 = record a per-step kernel timeline (diagnostics)
   c.rank = rank; c.world = world; c.ring = ring; c.cap_rows = cap_rows; c.pitch = (uint32_t)pitch_floats;
   const size_t hb = header_bytes(world, ring);
   for (int p = 0; p < world; ++p) {
-    SGL_REQUIRE(h_bases[p], SGL_ERR_ARG, "p2p_route_create: base pointer of rank %d is null", p);
     char* b = (char*)h_bases[p];
     c.peer_acks[p] = (unsigned long long*)b;
-    c.peer_flags[p] = (unsigned long long*)b + world;
+    c.peer_meta[p] = (unsigned long long*)b + world;
     c.peer_stage[p] = (uint4*)(b + hb);
   }
   c.acks = c.peer_acks[rank];
-  c.flags = c.peer_flags[rank];
-  // pairs whose message is at least this large travel as plain rows (SGL_P2P_BULK_BYTES overrides; 0 = always)
-  long long bulk_bytes = 2 << 20;
-  if (const char* e = getenv("SGL_P2P_BULK_BYTES")) bulk_bytes = atoll(e);
-  c.bulk_rows = bulk_bytes <= 0 ? 1 : (bulk_bytes + pitch_floats * 4 - 1) / (pitch_floats * 4);
+  c.meta = c.peer_meta[rank];
   c.stage = c.peer_stage[rank];
-  SGL_CUDA_CHECK(cudaMalloc(&x->counters, 256));
-  SGL_CUDA_CHECK(cudaMemset(x->counters, 0, 256));
-  c.tl = nullptr;
-  if (c.dbg & 2) {
-    SGL_CUDA_CHECK(cudaMalloc(&c.tl, 4096 * 8 * 8));
-    SGL_CUDA_CHECK(cudaMemset(c.tl, 0, 4096 * 8 * 8));
-  }
+  // pairs whose message is at least 2 MiB travel as plain rows (sgl_p2p_route_configure changes the limit)
+  c.bulk_rows = ((2 << 20) + pitch_floats * 4 - 1) / (pitch_floats * 4);
   *out_ctx = x;
+  return SGL_OK;
+}
+
+extern "C" int sgl_p2p_route_configure(void* ctx, int64_t wait_ms, int64_t bulk_bytes) {
+  SGL_REQUIRE(ctx, SGL_ERR_ARG, "p2p_route_configure: null context");
+  P2PCfg& c = ((Ctx*)ctx)->cfg;
+  if (wait_ms >= 0) {
+    SGL_REQUIRE(wait_ms >= 1 && wait_ms <= 60000, SGL_ERR_ARG, "p2p_route_configure: wait_ms %lld outside [1, 60000]",
+                (long long)wait_ms);
+    c.wait_ns = (unsigned long long)wait_ms * 1000000ull;
+  }
+  if (bulk_bytes >= 0) c.bulk_rows = bulk_bytes == 0 ? 0 : (bulk_bytes + c.pitch * 4 - 1) / ((int64_t)c.pitch * 4);
   return SGL_OK;
 }
 
@@ -466,27 +505,13 @@ extern "C" int sgl_p2p_route_destroy(void* ctx) {
   return SGL_OK;
 }
 
-// number of CTAs of a route kernel: enough for the rows, capped (SGL_P2P_MAX_CTAS, tuning aid) -- small messages are
-// latency-bound and every extra CTA adds fence traffic and a longer wait for the last one
-static int p2p_grid(int64_t rows) {
-  static int cap = -1;
-  if (cap < 0) {
-    const char* e = getenv("SGL_P2P_MAX_CTAS");
-    cap = e ? atoi(e) : kNumSM * 8;
-    if (cap < 1) cap = 1;
-  }
-  int g = stream_grid(rows, kThreads / 32, 8);
-  return g < cap ? g : cap;
-}
+// number of CTAs of a route kernel: enough for the rows, at most eight per SM -- small messages are latency-bound and
+// every extra CTA adds fence traffic and a longer wait for the last one
+static int p2p_grid(int64_t rows) { return stream_grid(rows, kThreads / 32, 8); }
 
-// launch with the programmatic-serialization attribute (see pdl_wait); SGL_P2P_PDL=0 turns it off (tuning aid)
+// Launch with the programmatic-serialization attribute (see pdl_wait).
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, cudaStream_t stream, Args... args) {
-  static int pdl = -1;
-  if (pdl < 0) {
-    const char* e = getenv("SGL_P2P_PDL");
-    pdl = e ? atoi(e) : 1;
-  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(kThreads);
@@ -496,7 +521,7 @@ static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, cudaStream_t s
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
@@ -511,52 +536,71 @@ static int make_splits(const Ctx* x, const int64_t* h_rows, Splits* s, const cha
   return SGL_OK;
 }
 
+static int send_impl(Ctx* x, const float* feats, int64_t n_rows, int64_t dim, const float* ts, const int64_t* send_idx,
+                     const int64_t* remote_idx, const Splits& seg, const int64_t* d_sizes, int64_t grid_rows, uint64_t step,
+                     int32_t* d_status, void* stream_) {
+  const int64_t pitch = sgl_wire_pitch(dim, ts != nullptr, 1);
+  SGL_REQUIRE(pitch == x->cfg.pitch, SGL_ERR_ARG, "p2p_route_send: wire pitch %lld differs from the context's %u",
+              (long long)pitch, x->cfg.pitch);
+  SGL_REQUIRE(grid_rows == 0 || (feats && send_idx && remote_idx), SGL_ERR_ARG, "p2p_route_send: null array");
+  const int vec_ok = dim % 4 == 0 && ((uintptr_t)feats & 15) == 0;
+  SGL_CUDA_CHECK(launch_pdl(p2p_send_kernel, p2p_grid(grid_rows), (cudaStream_t)stream_, x->cfg, feats, n_rows, (uint32_t)dim,
+                            ts, send_idx, remote_idx, seg, d_sizes, (unsigned long long)step, vec_ok, x->counters, d_status));
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
 extern "C" int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
                                   const int64_t* send_idx, const int64_t* remote_idx, const int64_t* h_send_rows,
-                                  uint64_t step, int32_t* d_status, void* stream_) {
+                                  uint64_t step, int32_t* d_status, void* stream) {
   SGL_REQUIRE(ctx && h_send_rows && dim > 0, SGL_ERR_ARG, "p2p_route_send: bad argument");
   Ctx* x = (Ctx*)ctx;
   Splits seg;
   int rc = make_splits(x, h_send_rows, &seg, "p2p_route_send");
   if (rc) return rc;
-  const int64_t n_send = seg.off[x->cfg.world];
-  const int64_t pitch = sgl_wire_pitch(dim, ts != nullptr, 1);
-  SGL_REQUIRE(pitch == x->cfg.pitch, SGL_ERR_ARG, "p2p_route_send: wire pitch %lld differs from the context's %u",
-              (long long)pitch, x->cfg.pitch);
-  SGL_REQUIRE(n_send == 0 || (feats && send_idx && remote_idx), SGL_ERR_ARG, "p2p_route_send: null array");
-  cudaStream_t stream = (cudaStream_t)stream_;
-  const int vec_ok = dim % 4 == 0 && ((uintptr_t)feats & 15) == 0;
-  const int grid = p2p_grid(n_send);
-  int any_bulk = 0;
-  for (int p = 0; p < x->cfg.world; ++p) any_bulk |= h_send_rows[p] >= x->cfg.bulk_rows;
-  SGL_CUDA_CHECK(launch_pdl(p2p_send_kernel, grid, stream, x->cfg, feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, seg,
-                            (unsigned long long)step, vec_ok, any_bulk, x->counters, d_status));
+  return send_impl(x, feats, n_rows, dim, ts, send_idx, remote_idx, seg, nullptr, seg.off[x->cfg.world], step, d_status, stream);
+}
+
+extern "C" int sgl_p2p_route_send_dev(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
+                                      const int64_t* send_idx, const int64_t* remote_idx, const int64_t* d_send_rows,
+                                      int64_t rows_hint, uint64_t step, int32_t* d_status, void* stream) {
+  SGL_REQUIRE(ctx && d_send_rows && dim > 0 && rows_hint >= 0, SGL_ERR_ARG, "p2p_route_send_dev: bad argument");
+  Splits seg;
+  memset(&seg, 0, sizeof(seg));
+  return send_impl((Ctx*)ctx, feats, n_rows, dim, ts, send_idx, remote_idx, seg, d_send_rows, rows_hint < 1 ? 1 : rows_hint, step,
+                   d_status, stream);
+}
+
+static int recv_impl(Ctx* x, const Splits& expect, int check, int64_t grid_rows, float* data, int64_t data_rows, int64_t dim,
+                     int has_ts, float* ts_table, uint64_t step, int32_t* d_status, void* stream_) {
+  SGL_REQUIRE(!has_ts || ts_table, SGL_ERR_ARG, "p2p_route_recv: rows carry a timestamp but ts_table is null");
+  const int64_t width = dim + (has_ts ? 1 : 0);
+  SGL_REQUIRE(sgl_wire_pitch(dim, has_ts, 1) == x->cfg.pitch, SGL_ERR_ARG, "p2p_route_recv: wire pitch differs from the context's");
+  SGL_REQUIRE(grid_rows == 0 || data, SGL_ERR_ARG, "p2p_route_recv: null table");
+  const int vec_ok = dim % 4 == 0 && ((uintptr_t)data & 15) == 0;
+  SGL_CUDA_CHECK(launch_pdl(p2p_recv_kernel, p2p_grid(grid_rows), (cudaStream_t)stream_, x->cfg, expect, check, (uint32_t)width,
+                            data, data_rows, (uint32_t)dim, has_ts ? ts_table : (float*)nullptr, (unsigned long long)step, vec_ok,
+                            x->counters + 32, d_status));
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }
 
 extern "C" int sgl_p2p_route_recv(void* ctx, const int64_t* h_recv_rows, float* data, int64_t data_rows, int64_t dim,
-                                  int has_ts, float* ts_table, uint64_t step, int32_t* d_status, void* stream_) {
+                                  int has_ts, float* ts_table, uint64_t step, int32_t* d_status, void* stream) {
   SGL_REQUIRE(ctx && h_recv_rows && dim > 0, SGL_ERR_ARG, "p2p_route_recv: bad argument");
-  SGL_REQUIRE(!has_ts || ts_table, SGL_ERR_ARG, "p2p_route_recv: rows carry a timestamp but ts_table is null");
   Ctx* x = (Ctx*)ctx;
   Splits seg;
   int rc = make_splits(x, h_recv_rows, &seg, "p2p_route_recv");
   if (rc) return rc;
-  const int64_t n_recv = seg.off[x->cfg.world];
-  const int64_t width = dim + (has_ts ? 1 : 0);
-  SGL_REQUIRE(sgl_wire_pitch(dim, has_ts, 1) == x->cfg.pitch, SGL_ERR_ARG, "p2p_route_recv: wire pitch differs from the context's");
-  SGL_REQUIRE(n_recv == 0 || data, SGL_ERR_ARG, "p2p_route_recv: null table");
-  cudaStream_t stream = (cudaStream_t)stream_;
-  const int vec_ok = dim % 4 == 0 && ((uintptr_t)data & 15) == 0;
-  const int grid = p2p_grid(n_recv);
-  int any_bulk = 0;
-  for (int p = 0; p < x->cfg.world; ++p) any_bulk |= h_recv_rows[p] >= x->cfg.bulk_rows;
-  SGL_CUDA_CHECK(launch_pdl(p2p_recv_kernel, grid, stream, x->cfg, seg, (uint32_t)width, data, data_rows, (uint32_t)dim,
-                            has_ts ? ts_table : (float*)nullptr, (unsigned long long)step, vec_ok, any_bulk, x->counters + 32,
-                            d_status));
-  SGL_LAUNCH_CHECK();
-  return SGL_OK;
+  return recv_impl(x, seg, 1, seg.off[x->cfg.world], data, data_rows, dim, has_ts, ts_table, step, d_status, stream);
+}
+
+extern "C" int sgl_p2p_route_recv_dev(void* ctx, int64_t rows_hint, float* data, int64_t data_rows, int64_t dim, int has_ts,
+                                      float* ts_table, uint64_t step, int32_t* d_status, void* stream) {
+  SGL_REQUIRE(ctx && dim > 0 && rows_hint >= 0 && data, SGL_ERR_ARG, "p2p_route_recv_dev: bad argument");
+  Splits seg;
+  memset(&seg, 0, sizeof(seg));
+  return recv_impl((Ctx*)ctx, seg, 0, rows_hint < 1 ? 1 : rows_hint, data, data_rows, dim, has_ts, ts_table, step, d_status, stream);
 }
 
 extern "C" int sgl_p2p_route_step(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
@@ -566,13 +610,4 @@ extern "C" int sgl_p2p_route_step(void* ctx, const float* feats, int64_t n_rows,
   int rc = sgl_p2p_route_send(ctx, feats, n_rows, dim, ts, send_idx, remote_idx, h_send_rows, step, d_status, stream);
   if (rc) return rc;
   return sgl_p2p_route_recv(ctx, h_recv_rows, data, data_rows, dim, ts != nullptr, ts_table, step, d_status, stream);
-}
-
-// diagnostics: copies the per-step kernel timeline to the host (ns; words 0/1 send start/end, 2/3/4 apply start / CTA 0's
-// rows applied / end, 5/6 send / apply kernel resident)
-extern "C" int sgl_p2p_route_timeline(void* ctx, unsigned long long* h_out, int64_t steps) {
-  Ctx* x = (Ctx*)ctx;
-  SGL_REQUIRE(x && x->cfg.tl && h_out && steps <= 4096, SGL_ERR_ARG, "p2p_route_timeline: not enabled (SGL_P2P_DBG=2)");
-  SGL_CUDA_CHECK(cudaMemcpy(h_out, x->cfg.tl, (size_t)steps * 8 * 8, cudaMemcpyDeviceToHost));
-  return SGL_OK;
 }

@@ -10,8 +10,6 @@
 //
 // Algorithmic HBM bytes per target: 16 (indptr pair) + 16 (target id, time) + 8*ceil(log2 deg) (search
 // probes) + k_eff*24 (nbr, ts, eid reads) + k_eff*36 (five output arrays) + 8 (offset).
-#include <stdlib.h>
-
 #include "common.cuh"
 #include "scan.cuh"
 
@@ -235,15 +233,7 @@ sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ 
 
 using namespace sgl;
 
-static inline int sample_tpw(int64_t n) {
-  static int forced = -1;   // SGL_SAMPLE_TPW=1|4|32 pins the variant (tuning aid)
-  if (forced < 0) {
-    const char* e = getenv("SGL_SAMPLE_TPW");
-    forced = e ? atoi(e) : 0;
-  }
-  if (forced == 1 || forced == 4 || forced == 32) return forced;
-  return n <= 16384 ? 1 : (n <= 262144 ? 4 : 32);
-}
+static inline int sample_tpw(int64_t n) { return n <= 16384 ? 1 : (n <= 262144 ? 4 : 32); }
 
 static inline int64_t sample_num_ctas(int64_t n, int tpw) {
   int64_t tpc = (int64_t)kWarpsPerCta * tpw;

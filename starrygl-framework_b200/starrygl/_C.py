@@ -15,7 +15,8 @@ _PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG_ROOT, "lib", "libsgl_b200.so")
 
 SGL_DEV_BITS = {1: "node id out of range", 2: "timestamp outside the declared window", 4: "row index out of range",
-                8: "output capacity exceeded", 16: "device-side wait timed out"}
+                8: "output capacity exceeded", 16: "device-side wait timed out",
+                32: "a peer sent a different number of rows than announced"}
 POLICY = {"recent": 0, "uniform": 1}
 GATHER_MODE = {"auto": 0, "vec": 1, "bulk": 2}
 
@@ -68,7 +69,13 @@ _SIGNATURES = {
     "sgl_p2p_route_destroy": (_i32, [_vp]),
     "sgl_p2p_route_send": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, C.POINTER(C.c_int64), _u64, _vp, _vp]),
     "sgl_p2p_route_recv": (_i32, [_vp, C.POINTER(C.c_int64), _vp, _i64, _i64, _i32, _vp, _u64, _vp, _vp]),
-    "sgl_p2p_route_timeline": (_i32, [_vp, _vp, _i64]),
+    "sgl_comm_info": (_i32, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "sgl_init_p2p": (_i32, [C.POINTER(C.c_int), _i32, C.POINTER(C.c_int)]),
+    "sgl_route_add_grouped": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp]),
+    "sgl_shard_gather": (_i32, [_vp, _vp, _i32, _i64, _vp, _i64, _vp, _vp, _vp, _vp]),
+    "sgl_p2p_route_configure": (_i32, [_vp, _i64, _i64]),
+    "sgl_p2p_route_send_dev": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _u64, _vp, _vp]),
+    "sgl_p2p_route_recv_dev": (_i32, [_vp, _i64, _vp, _i64, _i64, _i32, _vp, _u64, _vp, _vp]),
     "sgl_p2p_route_step": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), _vp, _i64,
                                   _vp, _u64, _vp, _vp]),
     "sgl_route_add_rows": (_i32, [_vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp]),

@@ -17,6 +17,7 @@ import torch.distributed as dist
 from torch import Tensor
 
 from .. import _C, ops
+from ..route.exchange import NativeComm, exchange_counts, exchange_rows, use_native
 
 __all__ = ['CommPlan', 'CacheUpdateFuture', 'CacheRoute', 'CacheRouteManager', 'compute_layer_route']
 
@@ -61,9 +62,12 @@ class CommPlan:
         return self
 
     @classmethod
-    def empty(cls, num_parts: int = 0):
-        return cls(send_ranks=torch.empty(0, dtype=torch.long),
-                   send_sizes=torch.zeros(num_parts, dtype=torch.long) if num_parts > 0 else torch.empty(0, dtype=torch.long),
+    def empty(cls, num_parts: int):
+        """A plan that sends nothing.  ``num_parts`` (the number of ranks) is required: the plan still takes part in
+        the exchange, and a ``send_sizes`` of another length than its peers' would never match their collective."""
+        if int(num_parts) < 1:
+            raise ValueError("CommPlan.empty needs the number of ranks (num_parts >= 1)")
+        return cls(send_ranks=torch.empty(0, dtype=torch.long), send_sizes=torch.zeros(int(num_parts), dtype=torch.long),
                    send_indices=torch.empty(0, dtype=torch.long), send_remote_indices=torch.empty(0, dtype=torch.long))
 
 
@@ -123,38 +127,6 @@ class CacheUpdateFuture:
         self.write_callback(self.recv_ids, self.recv_feats, self.mode)
 
 
-class NativeComm:
-    """The library's own NCCL communicator over all ranks of the default process group (the reference keeps a
-    private ``ncclComm_t`` next to torch.distributed too: starrygl/utils/context.py:109-122).  The unique id
-    travels through the process group that already exists."""
-    _instance = None
-
-    def __init__(self):
-        import ctypes as C
-        L = _C.lib()
-        rank, world = dist.get_rank(), dist.get_world_size()
-        buf = C.create_string_buffer(128)
-        if rank == 0:
-            _C.check(L.sgl_comm_unique_id(buf, 128))
-        box = [buf.raw]
-        dist.broadcast_object_list(box, src=0)
-        self.handle = C.c_void_p()
-        _C.check(L.sgl_comm_init(C.byref(self.handle), rank, world, box[0]))
-        self.rank, self.world = rank, world
-
-    @classmethod
-    def get(cls) -> "NativeComm":
-        if cls._instance is None:
-            cls._instance = cls()
-        return cls._instance
-
-    @classmethod
-    def shutdown(cls):
-        if cls._instance is not None:
-            _C.lib().sgl_comm_destroy(cls._instance.handle)
-            cls._instance = None
-
-
 class _NativeBinding:
     """Everything of one (plan, feature width) pair that does not change from call to call: device copies of the
     index arrays, host split arrays, send / receive buffers and the pre-converted argument list."""
@@ -183,8 +155,7 @@ class CacheRoute:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
 
     def _use_native(self, t: Tensor) -> bool:
-        return (t.is_cuda and dist.is_initialized() and self.group in (None, dist.GroupMember.WORLD)
-                and dist.get_backend() == "nccl")
+        return use_native(t, self.group)
 
     def _update_native(self, feats, plan, write_callback, local_ts):
         """GPU ranks on the default NCCL group: pack, grouped send/recv and (inside ``wait``) unpack are issued by the
@@ -208,10 +179,14 @@ class CacheRoute:
 
     def _exchange_counts(self, plan: CommPlan, device) -> List[int]:
         if plan.recv_sizes is None:
-            send = plan.send_sizes.to(device)
-            recv = torch.empty_like(send)
-            dist.all_to_all_single(recv, send, group=self.group)
-            plan.recv_sizes = [int(v) for v in recv.tolist()]
+            # checked on the host BEFORE the collective: ranks whose split arrays differ in length would wait for each
+            # other forever inside it
+            if plan.send_sizes.numel() != self.world_size:
+                raise ValueError(f"CommPlan.send_sizes has {plan.send_sizes.numel()} entries, the group has "
+                                 f"{self.world_size} ranks (an empty plan must be built with CommPlan.empty(world_size))")
+            if int(plan.send_sizes.sum()) != plan.send_indices.numel():
+                raise ValueError("CommPlan.send_sizes does not add up to the number of send_indices")
+            plan.recv_sizes = exchange_counts(plan.send_sizes.to(device), self.group)
         return plan.recv_sizes
 
     @torch.no_grad()
@@ -232,9 +207,10 @@ class CacheRoute:
         remote = plan.send_remote_indices.to(device)
         packed = ops.route_pack(feats, local_ts, send_idx, remote_idx=remote)          # [S, wire pitch]
         recv = torch.empty(sum(recv_list), ops.wire_pitch(width, False), dtype=torch.float32, device=device)
-        work = dist.all_to_all_single(recv, packed, output_split_sizes=recv_list, input_split_sizes=send_list,
-                                      group=self.group, async_op=True)
-        return [CacheUpdateFuture([work], None, recv, write_callback, 'cold', width)]
+        work = exchange_rows(packed, send_list, recv, recv_list, self.group)
+        fut = CacheUpdateFuture([work], None, recv, write_callback, 'cold', width)
+        fut._keep = packed
+        return [fut]
 
 
 class CacheRouteManager:

@@ -38,7 +38,9 @@ class P2PFuture:
 
 class P2PCacheRoute:
     def __init__(self, dim: int, has_ts: bool = True, cap_rows: int = 16384, ring: int = 4,
-                 device: Optional[torch.device] = None):
+                 device: Optional[torch.device] = None, wait_ms: int = -1, bulk_bytes: int = -1):
+        """``wait_ms`` bounds every device-side wait (default 2 s); a pair's message of ``bulk_bytes`` and more travels
+        as plain rows instead of tagged lines (default 2 MiB); every rank must pass the same values."""
         if not dist.is_initialized():
             raise RuntimeError("P2PCacheRoute needs an initialised process group (handles are exchanged through it)")
         self.L = _C.lib()
@@ -65,6 +67,7 @@ class P2PCacheRoute:
         self.ctx = C.c_void_p()
         _C.check(self.L.sgl_p2p_route_create(self.rank, self.world, self.ring, self.cap_rows, self.pitch, self.bases,
                                              C.byref(self.ctx)))
+        _C.check(self.L.sgl_p2p_route_configure(self.ctx, int(wait_ms), int(bulk_bytes)))
         self.status = ops.StatusWord(self.device)
         self.step = 0
         self._outstanding = 0
@@ -72,10 +75,10 @@ class P2PCacheRoute:
 
     def recv_sizes(self, plan: CommPlan) -> List[int]:
         if plan.recv_sizes is None:
-            send = plan.send_sizes.to(self.device)
-            recv = torch.empty_like(send)
-            dist.all_to_all_single(recv, send)
-            plan.recv_sizes = [int(v) for v in recv.tolist()]
+            if plan.send_sizes.numel() != self.world:
+                raise ValueError(f"CommPlan.send_sizes has {plan.send_sizes.numel()} entries, the group has {self.world} ranks")
+            from ..route.exchange import exchange_counts
+            plan.recv_sizes = exchange_counts(plan.send_sizes.to(self.device))
         return plan.recv_sizes
 
     @torch.no_grad()
@@ -150,12 +153,49 @@ class P2PCacheRoute:
             self.step += 1
         return run2
 
-    def close(self):
+    # ---- plans that exist only on the device -------------------------------------------------------------------
+    @torch.no_grad()
+    def push_dev(self, feats: torch.Tensor, send_idx: torch.Tensor, remote_idx: torch.Tensor, d_send_sizes: torch.Tensor,
+                 rows_hint: int, local_ts: Optional[torch.Tensor] = None, stream=None) -> int:
+        """Send ``feats[send_idx[:sum(d_send_sizes)]]`` according to a plan whose sizes are device values
+        (``ops.plan_route`` output): no host synchronisation, no count exchange.  ``rows_hint`` sizes the launch (the
+        expected number of rows; any value is correct).  Returns the step number to pass to :meth:`apply_dev`."""
+        if (local_ts is not None) != self.has_ts or feats.shape[1] != self.dim or feats.dtype != torch.float32:
+            raise _C.SglError("P2PCacheRoute.push_dev: row layout differs from the one the route was created for")
+        rc = self.L.sgl_p2p_route_send_dev(self.ctx, feats.data_ptr(), feats.shape[0], self.dim,
+                                           None if local_ts is None else local_ts.data_ptr(), send_idx.data_ptr(),
+                                           remote_idx.data_ptr(), d_send_sizes.data_ptr(), int(rows_hint), self.step,
+                                           self.status.ptr(), _C.stream_ptr(stream))
+        _C.check(rc)
+        self.step += 1
+        return self.step - 1
+
+    @torch.no_grad()
+    def apply_dev(self, step: int, state, rows_hint: int, stream=None):
+        """Receive side of :meth:`push_dev`: applies what the other ranks pushed in ``step`` to ``state``; the row
+        counts come from the senders."""
+        rc = self.L.sgl_p2p_route_recv_dev(self.ctx, int(rows_hint), state._d_data.data_ptr(), state._d_data.shape[0], self.dim,
+                                           int(self.has_ts), state._d_ts.data_ptr() if self.has_ts else None, int(step),
+                                           self.status.ptr(), _C.stream_ptr(stream))
+        _C.check(rc)
+
+    # ---- life cycle ---------------------------------------------------------------------------------------------
+    def close(self, collective: bool = True):
+        """Release the context, the peer mappings and the staging buffer.  ``collective=False`` skips the barrier (for
+        a process group that is already gone, e.g. inside ``__exit__`` after an error)."""
         if self.ctx:
             torch.cuda.synchronize(self.device)
-            dist.barrier()
+            if collective and dist.is_initialized():
+                dist.barrier()
             self.L.sgl_p2p_route_destroy(self.ctx)
             for p in self._opened:
                 self.L.sgl_p2p_close(p)
             self.L.sgl_p2p_free(self.base)
             self.ctx = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        self.close(collective=exc_type is None)
+        return False

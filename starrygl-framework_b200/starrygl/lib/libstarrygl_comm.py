@@ -3,7 +3,10 @@
 Same names and call signatures as the reference's pybind module ``libstarrygl_comm``
 (csrc/srcs/starrygl/export.cu:20-254): ``from_edge_index``, ``CUDAGraph`` with ``submit_query`` / ``get`` /
 ``get_seeds_in_chunks`` / ``get_negative_root`` / ``sample_src_in_chunks_khop``, and the result types
-``TemporalRoot``, ``NegativeRoot``, ``TemporalNeighbor``, ``TemporalResult``.  The work is done by libsgl_b200.so
+``TemporalRoot``, ``NegativeRoot``, ``TemporalNeighbor``, ``TemporalResult``; plus the communicator and the sharded
+feature table the same module exports (``create_nccl_id``, ``DistContext``,
+csrc/include/starrygl/commContext.cu.hpp:259-268; ``init_p2p``, ``ShardTensorItem``, ``ShardTensor``,
+csrc/include/starrygl/feature.cu.hpp:713-750).  The work is done by libsgl_b200.so
 through its C ABI; result attributes are the tensors the kernels wrote (no second device copy per attribute
 read, unlike export.cu:28-185).
 
@@ -281,3 +284,251 @@ def from_edge_index(n: int, chunk_size: int, src: torch.Tensor, dst: torch.Tenso
     except _C.SglError as e:
         raise RuntimeError(f"Graph construction failed: {e}") from e
     return CUDAGraph(g, ev, chunk_size, mapper, s, rank)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# communicator + sharded feature table
+# ---------------------------------------------------------------------------------------------------------------------
+
+def create_nccl_id() -> bytes:
+    """Unique id of a new communicator, to be handed to every rank out of band (the reference puts it into the
+    process group's store, starrygl/utils/context.py:111-117)."""
+    import ctypes as C
+    buf = C.create_string_buffer(128)
+    _C.check(_C.lib().sgl_comm_unique_id(buf, 128))
+    return buf.raw
+
+
+class DistContext:
+    """One rank of the library's own NCCL communicator: ``DistContext(rank, world_size, local_size, id)`` with
+    ``rank()``, ``size()``, ``device()`` (csrc/include/starrygl/commContext.cu.hpp:11-60, :259-268).  The device of the
+    rank is ``rank % local_size`` and is made current, as the reference's constructor does."""
+
+    def __init__(self, rank: int, world_size: int, local_size: int, id: bytes):
+        import ctypes as C
+        if not (isinstance(id, (bytes, bytearray)) and len(id) >= 128):
+            raise RuntimeError("DistContext: id must be the bytes create_nccl_id() returned")
+        if local_size < 1 or not (0 <= rank < world_size):
+            raise RuntimeError("DistContext: bad rank / size")
+        self._rank, self._world, self._local = int(rank), int(world_size), int(local_size)
+        self._device = self._rank % self._local
+        torch.cuda.set_device(self._device)
+        self.handle = C.c_void_p()
+        _C.check(_C.lib().sgl_comm_init(C.byref(self.handle), self._rank, self._world, bytes(id)))
+        from ..route.exchange import NativeComm
+        NativeComm.adopt(self.handle, self._rank, self._world)     # the routes of this process use this communicator
+
+    def rank(self) -> int:
+        return self._rank
+
+    def size(self) -> int:
+        return self._world
+
+    def device(self) -> int:
+        return self._device
+
+
+def init_p2p(devices: List[int]) -> int:
+    """Enable peer access from the current GPU to the listed ones where the hardware allows it; returns how many of
+    them are reachable.  With one process per GPU the mappings of other ranks' memory enable it when they are opened,
+    so this matters only for a process that drives several GPUs."""
+    import ctypes as C
+    arr = (C.c_int * max(len(devices), 1))(*[int(d) for d in devices])
+    ok = C.c_int(0)
+    _C.check(_C.lib().sgl_init_p2p(arr, len(devices), C.byref(ok)))
+    return ok.value
+
+
+class ShardTensorItem:
+    """Description of one shard that can travel between processes: owner rank and device, an inter-process handle of
+    its memory, its shape and element size (csrc/include/starrygl/feature.cu.hpp:94-140)."""
+
+    def __init__(self):
+        self.rank, self.group, self.device = 0, 0, -1
+        self.mem_handle, self.shape, self.element_size, self.dtype = b"", [], 4, "float32"
+
+    def share_ipc(self):
+        return (self.device, self.element_size, self.mem_handle, list(self.shape), self.rank, self.dtype)
+
+    def from_ipc(self, ipc_data):
+        self.device, self.element_size, self.mem_handle, shape = ipc_data[:4]
+        self.shape = list(shape)
+        if len(ipc_data) > 4:
+            self.rank = int(ipc_data[4])
+        if len(ipc_data) > 5:
+            self.dtype = ipc_data[5]
+        return self
+
+
+class ShardTensor:
+    """Row table sharded over the GPUs of one node; ``tensor[ids]`` with packed ids ``(partition << 48) | local row``
+    returns the rows in the order of the ids (csrc/include/starrygl/feature.cu.hpp:142-422).
+
+    Shard p belongs to rank p.  The owner appends its own CUDA tensor, every other rank appends the
+    ``ShardTensorItem`` the owner published (``share_ipc``) and thereby maps the owner's memory.  The gather is ONE
+    kernel that reads every row from its owner's memory over NVLink; the reference's plan -- split the ids by owner,
+    send the ids, gather at the owner, send the rows back, scatter to the original order -- is what
+    :meth:`gather_by_exchange` does for ranks without a mapping of each other's memory."""
+
+    def __init__(self, device: int, context: Optional[DistContext] = None):
+        self._device = int(device)
+        self.context = context
+        self._local = {}          # partition -> tensor owned here (kept alive)
+        self._bases, self._rows = [], []
+        self._opened = []
+        self._row_shape, self._dtype = None, None
+        self._tables = None
+
+    # ---- building ------------------------------------------------------------------------------------------------
+    def _check_layout(self, shape, dtype):
+        if self._row_shape is None:
+            self._row_shape, self._dtype = tuple(shape[1:]), dtype
+        elif tuple(shape[1:]) != self._row_shape or dtype != self._dtype:
+            raise RuntimeError("ShardTensor: all shards must have the same row shape and dtype")
+
+    def append(self, item, target_device: Optional[int] = None):
+        """Append the next partition's shard: a CUDA tensor of this process, or a ``ShardTensorItem`` of another."""
+        import ctypes as C
+        self._tables = None
+        if isinstance(item, torch.Tensor):
+            if not item.is_cuda or not item.is_contiguous():
+                raise RuntimeError("ShardTensor.append: a local shard must be a contiguous CUDA tensor")
+            self._check_layout(item.shape, item.dtype)
+            self._local[len(self._bases)] = item
+            self._bases.append(item.data_ptr())
+            self._rows.append(int(item.shape[0]))
+            return
+        dtype = getattr(torch, item.dtype)
+        self._check_layout(item.shape, dtype)
+        ptr = C.c_void_p()
+        _C.check(_C.lib().sgl_p2p_open(item.mem_handle, C.byref(ptr)))
+        self._opened.append(ptr)
+        self._bases.append(ptr.value)
+        self._rows.append(int(item.shape[0]))
+
+    def share_ipc(self) -> List[ShardTensorItem]:
+        """Items for the shards this process owns (the memory must come from ``cudaMalloc``, i.e. be a whole torch
+        allocation or one made with ``ShardTensor.alloc_shared``)."""
+        out = []
+        for part, t in self._local.items():
+            it = ShardTensorItem()
+            it.rank, it.device, it.shape, it.element_size = part, t.device.index, list(t.shape), t.element_size()
+            it.dtype = str(t.dtype).replace("torch.", "")
+            it.mem_handle = _ipc_handle(t)
+            out.append(it)
+        return out
+
+    @classmethod
+    def from_local(cls, local: torch.Tensor, context: Optional[DistContext] = None) -> "ShardTensor":
+        """Collective convenience: every rank of the default process group passes its own shard (allocated with
+        :func:`shared_empty`); the handles are exchanged through the group and every rank maps all shards."""
+        import torch.distributed as dist
+        rank, world = dist.get_rank(), dist.get_world_size()
+        me = cls(local.device.index, context)
+        mine = ShardTensorItem()
+        mine.rank, mine.device, mine.shape, mine.element_size = rank, local.device.index, list(local.shape), local.element_size()
+        mine.dtype = str(local.dtype).replace("torch.", "")
+        mine.mem_handle = _ipc_handle(local)
+        box = [None] * world
+        dist.all_gather_object(box, mine.share_ipc())
+        for p in range(world):
+            me.append(local if p == rank else ShardTensorItem().from_ipc(box[p]))
+        dist.barrier()
+        return me
+
+    # ---- queries ---------------------------------------------------------------------------------------------------
+    def shape(self):
+        return [sum(self._rows)] + list(self._row_shape or [])
+
+    def size(self, dim: int) -> int:
+        return self.shape()[dim]
+
+    def numel(self) -> int:
+        n = 1
+        for d in self.shape():
+            n *= d
+        return n
+
+    def stride(self, dim: int) -> int:
+        s = 1
+        for d in self.shape()[dim + 1:]:
+            s *= d
+        return s
+
+    def device(self) -> int:
+        return self._device
+
+    def device_count(self) -> int:
+        return len(self._bases)
+
+    # ---- gather ------------------------------------------------------------------------------------------------------
+    def _device_tables(self, dev):
+        if self._tables is None:
+            self._tables = (torch.tensor(self._bases, dtype=torch.int64, device=dev),
+                            torch.tensor(self._rows, dtype=torch.int64, device=dev), ops.StatusWord(dev))
+        return self._tables
+
+    def __getitem__(self, indices: torch.Tensor) -> torch.Tensor:
+        if not indices.is_cuda:
+            raise RuntimeError("ShardTensor: the ids must be on the GPU")
+        bases, rows, st = self._device_tables(indices.device)
+        return ops.shard_gather(bases, rows, len(self._bases), self._row_shape, self._dtype, indices, status=st)
+
+    def check(self):
+        """Raise if a gather since the last check met an id outside its shard (one synchronisation)."""
+        if self._tables is not None:
+            self._tables[2].check("ShardTensor gather")
+
+    def unregister(self):
+        for p in self._opened:
+            _C.lib().sgl_p2p_close(p)
+        self._opened, self._bases, self._rows, self._local, self._tables = [], [], [], {}, None
+
+    @staticmethod
+    def gather_by_exchange(local: torch.Tensor, indices: torch.Tensor, group=None) -> torch.Tensor:
+        """The same result without peer mappings, in the reference's five steps: ids ordered by owner, id exchange,
+        gather at the owner, row exchange, rows put back in the order of ``indices``.  Collective over ``group``."""
+        from ..route.exchange import exchange_rows
+        from ..route.route import Route
+        route, asked_rows, order = Route.all_to_all_ind2ptr(indices, group)
+        mine = ops.gather_rows(local, asked_rows)                                   # what the others asked me for
+        got = torch.empty((indices.numel(),) + tuple(local.shape[1:]), dtype=local.dtype, device=indices.device)
+        exchange_rows(mine, route.recv_sizes, got, route.send_sizes, group).wait()  # rows arrive in owner order
+        out = torch.empty_like(got)
+        ops.scatter_rows(out, order, got)                                           # back to the order of the ids
+        return out
+
+
+def shared_empty(rows: int, row_shape, dtype=torch.float32):
+    """A zero-filled CUDA tensor in memory of its own allocation, as inter-process handles need (a slice of torch's caching
+    allocator cannot be exported on its own).  Returns the tensor; its memory is released with the tensor."""
+    import ctypes as C
+    n = int(rows)
+    per = torch.empty(0, dtype=dtype).element_size()
+    for d in row_shape:
+        per *= int(d)
+    nbytes = max(n * per, 256)
+    base, handle = C.c_void_p(), C.create_string_buffer(64)
+    _C.check(_C.lib().sgl_p2p_alloc(nbytes, C.byref(base), handle, 64))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    t = _tensor_over(base.value, nbytes, dev).view(dtype)[: n * per // torch.empty(0, dtype=dtype).element_size()]
+    t = t.view((n,) + tuple(int(d) for d in row_shape))
+    _SHARED[t.data_ptr()] = (handle.raw, base)
+    return t
+
+
+_SHARED = {}   # data_ptr -> (ipc handle, base pointer) of tensors made by shared_empty
+
+
+def _ipc_handle(t: torch.Tensor) -> bytes:
+    hit = _SHARED.get(t.data_ptr())
+    if hit is None:
+        raise RuntimeError("ShardTensor: a shard that other processes map must be allocated with shared_empty()")
+    return hit[0]
+
+
+def _tensor_over(ptr: int, nbytes: int, dev) -> torch.Tensor:
+    """uint8 tensor viewing foreign device memory through the CUDA array interface."""
+    class _Mem:
+        __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+    return torch.as_tensor(_Mem(), device=dev)

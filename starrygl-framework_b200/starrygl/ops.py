@@ -449,6 +449,56 @@ def route_add_rows(x, send_idx, outs, *, status: Optional[StatusWord] = None):
                                   status.ptr() if status else None, _C.stream_ptr()))
 
 
+def route_groups(send_index):
+    """Grouping of a route's ``send_index`` by destination row for :func:`route_add_grouped` (built once per route):
+    ``(rows[U], row_ptr[U+1], pos[S])`` -- the distinct rows, and for each the positions in ``send_index`` that name it,
+    ascending (= peer order).  A stable sort by row; the small amount of bookkeeping around it is torch."""
+    send_index = _i64(send_index)
+    n = send_index.numel()
+    dev = send_index.device
+    if n == 0:
+        z = torch.zeros(0, dtype=I64, device=dev)
+        return z, torch.zeros(1, dtype=I64, device=dev), z
+    if (send_index < 0).any():
+        raise _C.SglError("route_groups: negative rows are not supported in a route's send_index")
+    keys, pos = radix_sort_pairs(send_index, torch.arange(n, dtype=torch.int32, device=dev),
+                                 num_bits=bits_for(int(send_index.max().item())))
+    rows, counts = torch.unique_consecutive(keys, return_counts=True)
+    row_ptr = torch.zeros(rows.numel() + 1, dtype=I64, device=dev)
+    row_ptr[1:] = torch.cumsum(counts, 0)
+    return rows.contiguous(), row_ptr, pos.to(I64).contiguous()
+
+
+def route_add_grouped(x, groups, outs, *, status: Optional[StatusWord] = None):
+    """``x[rows[u]] += outs[pos[j]]`` for every group, contributions added in ascending position: all peer segments of
+    the reverse route in one launch, same float32 result as the per-peer loop."""
+    L = _C.lib()
+    rows, row_ptr, pos = groups
+    if rows.numel() == 0:
+        return
+    if x.dtype != torch.float32 or outs.dtype != torch.float32:
+        raise _C.SglError("route_add_grouped accumulates float32 rows")
+    x2, o2 = x.view(x.shape[0], -1), outs.contiguous().view(outs.shape[0], -1)
+    _C.check(L.sgl_route_add_grouped(_C.ptr(x2), x2.shape[0], x2.shape[1], _C.ptr(rows), _C.ptr(row_ptr), _C.ptr(pos),
+                                     rows.numel(), _C.ptr(o2), o2.shape[0], status.ptr() if status else None, _C.stream_ptr()))
+
+
+def shard_gather(d_bases, d_shard_rows, world: int, row_shape, dtype, dist_idx, *, d_n=None,
+                 status: Optional[StatusWord] = None):
+    """Rows of a table sharded over the GPUs of one node, read from their owners' memory (see ``sgl_shard_gather``).
+    ``d_bases`` / ``d_shard_rows``: device int64 arrays of the shards' base addresses and row counts."""
+    L = _C.lib()
+    dist_idx = _i64(dist_idx)
+    n = dist_idx.numel()
+    out = torch.empty((n,) + tuple(row_shape), dtype=dtype, device=dist_idx.device)
+    row_bytes = out.element_size()
+    for d in row_shape:
+        row_bytes *= int(d)
+    _C.check(L.sgl_shard_gather(_C.ptr(d_bases), _C.ptr(d_shard_rows), int(world), row_bytes, _C.ptr(dist_idx), n, _C.ptr(d_n),
+                                out.data_ptr() if n else None, status.ptr() if status else None, _C.stream_ptr()))
+    return out
+
+
 def dist_pack(loc, part, shared=None):
     L = _C.lib()
     loc, part = _i64(loc), _i64(part)

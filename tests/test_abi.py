@@ -86,13 +86,3 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_C, "LIB_PATH", "/nonexistent/libsgl_b200.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _C.lib()
-
-
-def test_numa_affinity_helper_parses_cpu_lists_and_never_fails_without_a_gpu():
-    import os
-    from starrygl.utils import affinity
-    assert affinity._cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
-    assert affinity._cpulist("") == set()
-    before = os.sched_getaffinity(0)
-    info = affinity.bind_to_gpu_numa_node(0)          # no GPU here: nothing to bind to, nothing changed
-    assert info["numa_node"] is None and os.sched_getaffinity(0) == before and info["cpus"] == len(before)

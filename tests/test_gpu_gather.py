@@ -12,9 +12,12 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("mode", ["auto", "vec", "bulk"])
 @pytest.mark.parametrize("rows,dim,dtype,n", [(1000, 172, torch.float32, 5000), (1000, 128, torch.float32, 4097),
                                               (777, 128, torch.bfloat16, 3000), (50, 100, torch.float32, 1),
-                                              (64, 4, torch.float32, 100), (3000, 256, torch.float32, 70000)])
+                                              (64, 4, torch.float32, 100), (3000, 256, torch.float32, 70000),
+                                              (400, 1280, torch.float32, 2000), (300, 1116, torch.float32, 1500)])
 def test_gather_rows(mode, rows, dim, dtype, n):
     from starrygl import ops
+    if mode == "bulk" and dim * 4 > 4096:
+        pytest.skip("rows above 4 KB do not fit two to a pipeline stage: 'auto' routes them to the 128-bit lanes")
     g = torch.Generator().manual_seed(rows + dim)
     table = torch.randn(rows, dim, generator=g).to(dtype).cuda()
     idx = torch.randint(0, rows, (n,), generator=g).cuda()
@@ -33,6 +36,24 @@ def test_gather_rows_unaligned_rows_use_narrow_lanes():
         ops.gather_rows(table, idx, mode="bulk")
     t1 = torch.arange(1000, dtype=torch.int64).cuda() * 3      # 1-D tables (8-byte rows)
     assert torch.equal(ops.gather_rows(t1, idx), t1[idx])
+
+
+def test_wide_rows_in_auto_mode_and_explicit_bulk_refusal():
+    """Rows of 5,120 bytes (1280 x fp32) and the 4,464-byte rows of a three-slot mailbox with 1,024 and more ids: the
+    automatic mode must pick a kernel that takes them; only an explicitly requested bulk mode may refuse."""
+    from starrygl import ops, _C
+    from starrygl.nn.memory.mailbox import mailbox as MailBox
+    table = torch.randn(300, 1280).cuda()
+    idx = torch.randint(0, 300, (4096,)).cuda()
+    assert torch.equal(ops.gather_rows(table, idx, mode="auto"), table[idx])
+    with pytest.raises(_C.SglError, match="too large for bulk"):
+        ops.gather_rows(table, idx, mode="bulk")
+    mb = MailBox(500, 3, 100, 172, device=torch.device("cuda"))
+    mb.mailbox.copy_(torch.randn_like(mb.mailbox))
+    mb.mailbox_ts.copy_(torch.rand_like(mb.mailbox_ts))
+    ids = torch.randint(0, 500, (2048,)).cuda()
+    rows, ts = mb.get_message(ids)
+    assert torch.equal(rows, mb.mailbox[ids]) and torch.equal(ts, mb.mailbox_ts[ids])
 
 
 def test_gather_negative_wrap_map_and_status():

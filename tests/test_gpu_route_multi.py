@@ -130,9 +130,7 @@ def _worker_p2p(rank, world, port, q):
         # Messages of 40 rows and more (16 KB) travel as plain rows + flag, smaller ones as tagged lines: both forms
         # and their mixture inside one step are exercised.
         D2, N, K = 100, 4096, 512
-        os.environ["SGL_P2P_BULK_BYTES"] = "16384"
-        route = P2PCacheRoute(D2, True, cap_rows=K, ring=4)
-        del os.environ["SGL_P2P_BULK_BYTES"]
+        route = P2PCacheRoute(D2, True, cap_rows=K, ring=4, bulk_bytes=16384)
         ps2 = PartitionState(loc_ids=torch.arange(N, device=dev), num_master_nums=N, node_mode='identity', num_nodes=N)
         state2 = DistNodeState(ps2, D2, device=dev)
         all_feats = [torch.randn(N, D2, generator=torch.Generator().manual_seed(50 + r)) for r in range(world)]
@@ -219,3 +217,71 @@ def test_p2p_cache_route_on_two_gpus():
         assert err is None, err
         assert a, f"rank {rank}: peer-memory route differs from the reference's result"
         assert b, f"rank {rank}: 40 steps through the staging ring differ from the expected state"
+
+
+def _worker_world1(rank, world, port, q):
+    """A group of ONE NCCL rank: the native exchange (grouped send/recv to itself), the halo route with its gradient, the
+    native cache route step, and the sharded table built through the process group -- the code paths of the two-GPU
+    tests, on a box with a single GPU."""
+    try:
+        import torch.distributed as dist
+        for p in (ROOT, os.path.join(ROOT, "starrygl-framework_b200"), HERE):
+            if p not in sys.path:
+                sys.path.insert(0, p)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", RANK="0", WORLD_SIZE="1",
+                          LOCAL_RANK="0")
+        from oracle import oracle_np as O
+        from starrygl.utils.context import DistributedContext
+        ctx = DistributedContext.init("nccl")
+        dev = ctx.device
+        from starrygl.route.route import Route
+        from starrygl.lib.libstarrygl_comm import ShardTensor, shared_empty
+        from starrygl.utils.partition_book import DistRouteIndex
+        g = torch.Generator().manual_seed(5)
+        n, k, F = 40, 25, 12
+        send_index = torch.randperm(n, generator=g)[:k]
+        x_h = torch.randn(n, F, generator=g)
+        w_h = torch.randn(n + k, F, generator=g)
+        r = Route(send_sizes=[k], recv_sizes=[k], send_index=send_index.to(dev))
+        x = x_h.clone().to(dev).requires_grad_()
+        y = r.forward(x)
+        (y * w_h.to(dev)).sum().backward()
+        y_ref = O.route_forward([x_h.numpy()], [[k]], [[k]], [send_index.numpy()])[0]
+        g_ref = O.route_reverse([w_h.numpy()], [[k]], [[k]], [send_index.numpy()])[0]
+        ok_route = np.array_equal(y.detach().cpu().numpy(), y_ref) and np.array_equal(x.grad.cpu().numpy(), g_ref)
+        # split-phase form and the reversed direction
+        t = r.send(x_h.to(dev))
+        ok_route = ok_route and np.array_equal(r.recv(t).cpu().numpy(), y_ref)
+        ok_route = ok_route and np.array_equal(r.forward(w_h.to(dev), reverse=True).cpu().numpy(), g_ref)
+        # ids -> route: every id is owned by partition 0 here
+        ids = torch.randint(0, n, (60,), generator=g)
+        route2, asked, order = Route.all_to_all_ind2ptr(DistRouteIndex(ids.to(dev), torch.zeros(60, dtype=torch.long, device=dev)))
+        ok_ind = torch.equal(asked.cpu(), ids[order.cpu()]) and route2.send_sizes == [60] and route2.recv_sizes == [60]
+        # sharded table through the group + the exchange form of the gather
+        local = shared_empty(n, (F,))
+        local.copy_(x_h)
+        st = ShardTensor.from_local(local)
+        got = st[ids.to(dev)]
+        st.check()
+        ok_shard = torch.equal(got.cpu(), x_h[ids])
+        ok_shard = ok_shard and torch.equal(ShardTensor.gather_by_exchange(local, ids.to(dev)).cpu(), x_h[ids])
+        st.unregister()
+        q.put((rank, ok_route, ok_ind, ok_shard, None))
+        dist.barrier()
+        DistributedContext.shutdown()
+    except Exception:  # pragma: no cover
+        import traceback
+        q.put((rank, False, False, False, traceback.format_exc()))
+
+
+def test_native_exchange_route_and_shard_tensor_in_a_group_of_one():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_world1, args=(0, 1, 29653, q))]
+    procs[0].start()
+    for rank, a, b, c, err in _collect(q, procs):
+        assert err is None, err
+        assert a, "halo route forward / backward / split phase / reverse differs from the oracle"
+        assert b, "route built from packed ids"
+        assert c, "sharded table gather (peer form or exchange form)"

@@ -78,6 +78,25 @@ def _worker_golden(rank, world, port, q):
         for f in CacheRoute().update_with_plan(feats, e, cb3):
             f.wait()
         ok4 = (rank == 1 and not got) or (rank == 0 and got["idx"].tolist() == [5])
+        # (5) a plan whose split array does not have one entry per rank is refused on the host, before any collective
+        bad = CommPlan(send_ranks=torch.empty(0, dtype=torch.long), send_sizes=torch.empty(0, dtype=torch.long),
+                       send_indices=torch.empty(0, dtype=torch.long), send_remote_indices=torch.empty(0, dtype=torch.long))
+        try:
+            CacheRoute().update_with_plan(feats, bad, cb3)
+            ok4 = False
+        except ValueError:
+            pass
+        # (6) distributed gather in the reference's five steps (ids by owner, id exchange, owner gather, row exchange,
+        # original order) against the oracle's restatement
+        from oracle import oracle_np as O
+        from starrygl.lib.libstarrygl_comm import ShardTensor
+        shards = [np.random.default_rng(40 + r).standard_normal((30 + 7 * r, 5)).astype(np.float32) for r in range(world)]
+        rg = np.random.default_rng(60 + rank)
+        part = rg.integers(0, world, 50)
+        loc = np.array([rg.integers(0, shards[p].shape[0]) for p in part])
+        ids = O.dist_pack(loc, part)
+        got_rows = ShardTensor.gather_by_exchange(torch.from_numpy(shards[rank]), torch.from_numpy(ids))
+        ok4 = ok4 and np.array_equal(got_rows.numpy(), O.shard_gather(shards, ids, rank))
         q.put((rank, ok1, ok2, ok3, ok4, None))
     except Exception as ex:  # pragma: no cover
         import traceback
@@ -105,7 +124,7 @@ def test_route_two_ranks_matches_reference():
         assert ok1, f"rank {rank}: drop-in cache route differs from the reference"
         assert ok2, f"rank {rank}: fused cache route differs from the reference"
         assert ok3, f"rank {rank}: halo exchange forward/backward differs from the reference"
-        assert ok4, f"rank {rank}: empty-plan exchange"
+        assert ok4, f"rank {rank}: empty-plan exchange / plan validation / distributed gather"
 
 
 def _worker_failure(rank, world, port, q):
@@ -148,6 +167,8 @@ def test_commplan_api():
     sys.path.insert(0, os.path.join(ROOT, "starrygl-framework_b200"))
     from starrygl.cache.cache_route import CommPlan
     e = CommPlan.empty(4)
+    with pytest.raises(ValueError):
+        CommPlan.empty(0)
     assert e.is_empty() and repr(e) == "CommPlan(Empty)" and e.send_sizes.tolist() == [0, 0, 0, 0]
     p = CommPlan(send_ranks=torch.tensor([0, 2, 2]), send_sizes=torch.tensor([1, 0, 2]), send_indices=torch.tensor([4, 5, 6]),
                  send_remote_indices=torch.tensor([1, 2, 3]))
