@@ -3,19 +3,24 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-A step = one mini-batch of 4,096 roots on a synthetic temporal graph of 1 M nodes / 50 M edges (out-degree
+N = 1: a step = one mini-batch of 4,096 roots on a synthetic temporal graph of 1 M nodes / 50 M edges (out-degree
 power law, alpha 2.1; int64 ids; timestamps uniform in [0, 1e7)): most-recent-20 sampling of every root before
 its query time, then the gather of the sampled edges' feature rows (172 x fp32) from a table that is much
 larger than L2.  An "event" is one root query.  Prints ONE JSON line (rank 0).
 
-  value      events/s with the batch's roots already in HBM (CUDA-event time of K steps, max over ranks)
+  value      events/s with the batch's roots already in HBM: the K-step region (CUDA events, batches in flight on
+             several streams) is repeated many times and the MEDIAN region time is reported, with its spread
   e2e        the same through the host-facing call: pinned host roots -> H2D -> sample -> gather -> block
              structure back to pinned host memory (the gathered rows stay on the GPU for the model)
-  roofline   the dominant kernel (the edge-feature gather): algorithmic bytes / its CUDA-event time
+  roofline   the dominant kernel (the edge-feature gather): algorithmic bytes / its CUDA-event time;
+  roofline_sampler  the sampler's two kernels the same way, alone and with several batches in flight
   cpu_baseline  the CPU oracle (C/OpenMP restatement of the reference's CPU sampler + row gather) on the
              host cores, on a bounded sample of the same batches
-With --gpus N > 1 (under torchrun) every rank owns one partition of equal size (weak scaling) and every step
-additionally pushes node-memory rows (100 x fp32 + ts) to the other partitions through the cache route.
+  secondary  the other single-GPU configurations: uniform [10,10] two-hop batches with dedup / relabel (with their own
+             CPU baseline and roofline) and the node-feature gather through a 10 % cache
+N > 1 (under torchrun): the partitioned workload of ``bench_c4.py`` -- planted-community graph, one partition per
+rank, 4,000 events per rank and step, recent-10, memory rows and mails pushed owner -> replica with plans built on the
+device every step.
 
 Side measurements (their own one-line JSON, not the benchmark line): ``--tcsr-only`` times the T-CSR construction of
 the benchmark graph; ``--route-bw-rows R`` (N > 1) times the route alone with R rows per rank and step.
@@ -49,12 +54,10 @@ MEM_DIM = 100
 TS_MAX = 10_000_000
 NUM_BATCHES = 64          # distinct pre-generated batches cycled through the steps
 STREAMS = 6
-ROUTE = "p2p"
-GRAPHS = True
-# DRAM bytes per gathered row measured with ncu on the small case (profiles/gather_bulk_kernel_172xfp32_small_case.txt:
-# 57.1 MB for 65,160 rows); roofline.traffic scales it by the rows of a full-size launch
+REGION_REPEATS = 200      # the K-step timed region is repeated this often; the median is reported
+# DRAM bytes per gathered row measured with ncu on a small case (57.1 MB for 65,160 rows of 688 bytes);
+# roofline.traffic scales it by the rows of a full-size launch
 GATHER_TRAFFIC_BYTES_PER_ROW = 876.0
-ROUTE_ROWS = 800          # rows per step a partition pushes to its peers (20 % cut edges of a 4,096-root batch)
 
 
 def peaks():
@@ -119,16 +122,20 @@ def make_batches(src, ts, gen, dev):
 
 def run_reference(args, rank, out_stream):
     """The reference's CPU path (its C/OpenMP restatement: the reference is numba/Python and cannot travel) on
-    the host cores, same batches, bounded sample."""
+    the host cores, on the workload the other arm runs with the same --gpus: bounded sample."""
     if rank != 0:
         return
-    from oracle import oracle_c as OC
-    dev = torch.device("cuda", 0) if torch.cuda.is_available() else None
-    out = cpu_baseline_measure(dev, steps=args.steps, warmup=args.warmup, budget_s=60.0)
+    if args.gpus > 1:
+        out = cpu_c4_reference(args)
+        cfg = out["config"]
+    else:
+        dev = torch.device("cuda", 0) if torch.cuda.is_available() else None
+        out = cpu_baseline_measure(dev, steps=args.steps, warmup=args.warmup, budget_s=60.0, two_hop=False)
+        cfg = workload_config(1)
     line = {"metric": "sampled+gathered events/sec", "value": out["value"], "unit": "events/s", "n_gpus": args.gpus,
             "steps": out["steps"], "warmup": args.warmup, "ms_per_step": out["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic", "impl": "reference",
-            "config": workload_config(1), "cpu_baseline": out["cpu_baseline"],
+            "config": cfg, "cpu_baseline": out["cpu_baseline"],
             "e2e": {"value": out["value"], "unit": "events/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), file=out_stream, flush=True)
@@ -140,8 +147,8 @@ def workload_config(n_gpus):
             "batch_roots": BATCH, "policy": f"recent-{FANOUT}, 1 hop", "edge_feat": f"{EDGE_DIM} x fp32",
             "edge_feat_rows": NUM_EDGES, "event": "one root query (a link-prediction interaction = three of them: source, destination, negative destination)",
             "l2": "inputs larger than L2: 64 distinct batches over a 34 GB feature table and a 1.2 GB adjacency",
-            "batches_in_flight": STREAMS, "parallelism": f"{n_gpus} partition(s), one process per GPU" +
-                           (f", cache route ({ROUTE}) of {ROUTE_ROWS} memory rows per step" if n_gpus > 1 else "")}
+            "batches_in_flight": STREAMS, "parallelism": f"{n_gpus} partition(s), one process per GPU",
+            "timing": f"median of {REGION_REPEATS} repeats of the K-step region (CUDA events)"}
 
 
 def _time_ms(fn, stream, iters, warm=3):
@@ -215,13 +222,23 @@ def secondary_measurements(g, dev, peak):
     for b_ in bgs:
         b_.status.check("two-hop builder")
     del bgs
+    uniq = [int(d["gids"].numel()) for d in layers]
+    edges_l = [int(d["indices"].numel()) for d in layers[1:]]
+    # algorithmic bytes of the batch: the sampler's bytes per target (row pointers, id and time, search probes, 60 per sampled
+    # edge, one offset) for both hops + 16 per sampled id and 16 per unique id for dedup / relabel
+    deg = (g.indptr[1:] - g.indptr[:-1])
+    tg0, tg1 = layers[0]["gids"], bg.batch.layers[1]["raw_nbr"][:edges_l[0]]
+    probes = sum(torch.ceil(torch.log2(deg[t_].clamp_min(1).double())).sum().item() for t_ in (tg0, tg1))
+    alg2 = (tg0.numel() + tg1.numel()) * 40 + 8 * probes + sum(edges_l) * 60 + (BATCH + sum(edges_l)) * 16 + sum(uniq) * 16
     out["uniform_10_10_relabel"] = {"ms_per_batch": ms, "ms_per_batch_without_cuda_graph": ms_eager,
                                     "ms_per_batch_4_in_flight": ms_fly, "events_per_s_4_in_flight": BATCH / ms_fly * 1e3,
                                     "events_per_s": BATCH / ms * 1e3, "roots": BATCH,
-                                    "unique_pairs_per_layer": [int(d["gids"].numel()) for d in layers],
-                                    "edges_per_layer": [int(d["indices"].numel()) for d in layers[1:]],
-                                    "note": "sampling + (node, ts) dedup/relabel + CSC per hop: a chain of ~100 short kernels, replayed "
-                                            "as one CUDA graph per batch"}
+                                    "unique_pairs_per_layer": uniq, "edges_per_layer": edges_l,
+                                    "kernel_launches_per_batch": bg.kernel_launches,
+                                    "roofline": {"bound": "hbm", "bytes_per_batch": alg2, "achieved": alg2 / ms / 1e6,
+                                                 "achieved_4_in_flight": alg2 / ms_fly / 1e6, "peak": peak, "unit": "GB/s",
+                                                 "frac": alg2 / ms / 1e6 / peak, "frac_4_in_flight": alg2 / ms_fly / 1e6 / peak},
+                                    "note": "sampling + (node, ts) dedup/relabel + CSC per hop, replayed as one CUDA graph per batch"}
     # ---- node features through the cache ---------------------------------------------------------------------------
     N, D, IDS = 10_000_000, 128, 200_000
     perm = torch.randperm(N, device=dev, generator=gen)
@@ -253,16 +270,18 @@ def secondary_measurements(g, dev, peak):
 
 
 def route_bandwidth(args, rank, world, dev, out_stream):
-    """Side measurement (not the benchmark line): the cache route alone at a message size where NVLink bandwidth, not
-    latency, bounds it.  Every rank pushes ``--route-bw-rows`` rows of 100 x fp32 + ts per step, split evenly over the
-    other ranks, through (a) the peer-memory kernels and (b) the grouped NCCL send/recv path.  GB/s = payload bytes a
-    rank sends per step / step time (device time, max over ranks); every rank receives as much as it sends."""
+    """Side measurement (not the benchmark line): the cache route alone at message sizes where NVLink bandwidth, not
+    latency, bounds it.  Every rank pushes ``--route-bw-rows`` rows of ``--route-bw-dim`` x fp32 + ts per step, split
+    evenly over the other ranks, through (a) the peer-memory kernels, (b) the grouped NCCL send/recv path with its pack
+    and unpack kernels, and (c) a bare ``all_to_all_single`` of the same bytes (the library's ceiling for this message
+    pattern on this box).  GB/s = payload bytes a rank sends per step / step time (device time, max over ranks); every
+    rank receives as much as it sends."""
     import torch.distributed as dist
     from starrygl.cache.cache_route import CacheRoute, CommPlan
     from starrygl.cache.p2p_route import P2PCacheRoute
     from starrygl.cache.NodeState import DistNodeState
     from starrygl.utils.partition_book import PartitionState
-    N, D, rows = 2_000_000, MEM_DIM, int(args.route_bw_rows)
+    N, D, rows = 2_000_000, int(args.route_bw_dim), int(args.route_bw_rows)
     per = rows // (world - 1)
     ranks = torch.cat([torch.full((per,), p, dtype=torch.long) for p in range(world) if p != rank])
     sizes = torch.bincount(ranks, minlength=world)
@@ -274,7 +293,8 @@ def route_bandwidth(args, rank, world, dev, out_stream):
     state = DistNodeState(ps, D, device=dev)
     payload = ranks.numel() * (D + 1) * 4
     K = 50
-    res = {"rows_per_step": int(ranks.numel()), "payload_MB_per_rank_and_step": payload / 1e6, "peers": world - 1}
+    res = {"rows_per_step": int(ranks.numel()), "row": f"{D} x fp32 + ts", "payload_MB_per_rank_and_step": payload / 1e6,
+           "peers": world - 1}
 
     def timed(step_fn, streams):
         for _ in range(5):
@@ -296,12 +316,13 @@ def route_bandwidth(args, rank, world, dev, out_stream):
         return float(t.item())
 
     st_a, st_b = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    p2p = P2PCacheRoute(D, True, cap_rows=max(1024, per), ring=4)
-    step = p2p.bind_step(mem, mts, plan, state, st_a, st_b)
-    ms = timed(step, [st_a, st_b])
-    p2p.status.check("route bandwidth (peer memory)")
-    res["p2p"] = {"ms_per_step": ms, "GBps_per_direction": payload / ms / 1e6}
-    p2p.close()
+    with P2PCacheRoute(D, True, cap_rows=max(1024, per), ring=4) as p2p:
+        step = p2p.bind_step(mem, mts, plan, state, st_a, st_b)
+        ms = timed(step, [st_a, st_b])
+        p2p.status.check("route bandwidth (peer memory)")
+        # the last step's rows are in place: slot by slot what the senders' tables hold
+        res["p2p"] = {"ms_per_step": ms, "GBps_per_direction": payload / ms / 1e6, "frac_of_770": payload / ms / 1e6 / 770,
+                      "frac_of_900": payload / ms / 1e6 / 900}
 
     cr = CacheRoute()
 
@@ -315,22 +336,46 @@ def route_bandwidth(args, rank, world, dev, out_stream):
             for f in cr.update_with_plan(mem, plan, cb, local_ts=mts):
                 f.wait()
     ms = timed(nccl_step, [st_a])
-    res["nccl"] = {"ms_per_step": ms, "GBps_per_direction": payload / ms / 1e6}
+    res["nccl_pack_exchange_unpack"] = {"ms_per_step": ms, "GBps_per_direction": payload / ms / 1e6}
+    send = torch.empty(ranks.numel(), D + 1, device=dev)
+    recv = torch.empty(sum(plan.recv_sizes), D + 1, device=dev)
+
+    def a2a():
+        with torch.cuda.stream(st_a):
+            dist.all_to_all_single(recv, send, plan.recv_sizes, plan.send_list())
+    ms = timed(a2a, [st_a])
+    res["all_to_all_single_alone"] = {"ms_per_step": ms, "GBps_per_direction": payload / ms / 1e6}
     if rank == 0:
         print(json.dumps({"route_bandwidth": res, "n_gpus": world, "nvlink_peak_GBps_per_direction": 900,
                           "measured_peer_copy_GBps": 770}), file=out_stream, flush=True)
 
 
-def cpu_baseline_measure(dev, steps, warmup, budget_s):
+def cpu_two_hop(OC, O, indptr, nbr, tss, eid, roots, root_ts):
+    """The reference's CPU batch builder for uniform [10,10]: its parallel sampler kernel (here the C/OpenMP restatement)
+    per hop, its numpy dedup / relabel / CSC (single-threaded ``np.unique`` / ``lexsort``, as in the reference)."""
+    cur_id, cur_ts, _ = O.unique_pairs(roots, root_ts)
+    last_inv = None
+    for l in range(2):
+        tgt = cur_id if l == 0 else cur_id[last_inv]
+        tgt_t = cur_ts if l == 0 else cur_ts[last_inv]
+        r_n, r_d, r_t, r_dt, r_e, _ = OC.sample_layer(indptr, nbr, tss, eid, tgt, tgt_t, 10, 1, stream=l)
+        d_map = last_inv[r_d] if last_inv is not None else r_d
+        n_id, n_ts, n_inv = O.merge_and_map(cur_id, cur_ts, r_n, r_t)
+        O.build_csc(n_inv, d_map, r_t, r_dt, r_e, len(cur_id))
+        cur_id, cur_ts, last_inv = n_id, n_ts, n_inv
+    return len(cur_id)
+
+
+def cpu_baseline_measure(dev, steps, warmup, budget_s, two_hop=True):
     """Times the C oracle on the same graph and batches.  The graph is generated with the same seeded generator
     (on the GPU when there is one, and copied to the host); the feature table is a 1 M-row host sample
     (edge id modulo 1 M) because 34 GB of host rows are not needed to time a row gather."""
     from oracle import oracle_c as OC
-    gdev = dev if dev is not None else torch.device("cpu")
+    from oracle import oracle_np as O
     if dev is None:
         raise RuntimeError("the benchmark graph is generated on the GPU")
-    src, dst, ts, gen = make_graph(gdev, 0)
-    b_roots, b_ts = make_batches(src, ts, gen, gdev)
+    src, dst, ts, gen = make_graph(dev, 0)
+    b_roots, b_ts = make_batches(src, ts, gen, dev)
     src_h, dst_h, ts_h = src.cpu().numpy(), dst.cpu().numpy(), ts.cpu().numpy()
     del src, dst, ts
     torch.cuda.empty_cache()
@@ -358,11 +403,71 @@ def cpu_baseline_measure(dev, steps, warmup, budget_s):
         n_done += 1
     dt = time.perf_counter() - t0
     val = n_done * BATCH / dt
+    res = {"value": val, "steps": n_done, "ms_per_step": dt / n_done * 1e3,
+           "cpu_baseline": {"value": val, "unit": "events/s", "cores": cores, "kind": "port",
+                            "sample": f"{n_done} of the benchmark's batches (recent-{FANOUT} sampling on the full 50 M-edge graph + gather "
+                                      f"of the sampled rows from a {rows_h}-row host table), C/OpenMP restatement of the reference's numba "
+                                      f"sampler; T-CSR build on the host took {build_s:.1f} s"}}
+    if two_hop:
+        cpu_two_hop(OC, O, indptr, nbr, tss, eid, roots_h[0], rts_h[0])
+        n2, t0 = 0, time.perf_counter()
+        while n2 < 8 and time.perf_counter() - t0 < 10.0:
+            cpu_two_hop(OC, O, indptr, nbr, tss, eid, roots_h[(n2 + 1) % NUM_BATCHES], rts_h[(n2 + 1) % NUM_BATCHES])
+            n2 += 1
+        dt2 = time.perf_counter() - t0
+        res["two_hop"] = {"value": n2 * BATCH / dt2, "unit": "events/s", "ms_per_batch": dt2 / n2 * 1e3, "cores": cores, "kind": "port",
+                          "sample": f"{n2} batches of 4,096 roots, uniform [10,10]: C/OpenMP sampler per hop (all cores) + numpy "
+                                    "unique / searchsorted / lexsort for dedup, relabel and CSC (one thread), the reference's split"}
+    return res
+
+
+def cpu_c4_reference(args):
+    """The partitioned workload's step on the host cores: one partition's batch (12,000 root queries, recent-10) sampled by
+    the C/OpenMP port and the memory / mail rows gathered from host tables -- what ONE CPU box does where N GPUs each run
+    such a step (the exchange between partitions is not part of the CPU arm)."""
+    import bench_c4 as B
+    from oracle import oracle_c as OC
+    cores = os.cpu_count() or 1
+    OC.set_threads(cores)
+    rng = np.random.default_rng(1000)
+    n, e = B.N_PER, B.E_PER
+    dst = rng.integers(0, n, e)
+    src = rng.integers(0, n, e)
+    ts = np.sort(rng.integers(0, B.T_MAX, e))
+    key, nb_, t2 = np.concatenate([dst, src]), np.concatenate([src, dst]), np.concatenate([ts, ts])
+    indptr, nbr, tss, eid, _ = OC.tcsr_build(key, nb_, t2, None, n)
+    lo = e - B.NUM_BATCHES * B.EVENTS
+    roots = np.concatenate([src[lo:].reshape(B.NUM_BATCHES, -1), dst[lo:].reshape(B.NUM_BATCHES, -1),
+                            rng.integers(0, n, (B.NUM_BATCHES, B.EVENTS))], 1)
+    rts = np.concatenate([ts[lo:].reshape(B.NUM_BATCHES, -1)] * 3, 1)
+    del key, nb_, t2, src, dst
+    mem = rng.standard_normal((n, B.MEM_DIM), dtype=np.float32)
+    mail = rng.standard_normal((n, B.MAIL_DIM), dtype=np.float32)
+    o_mem = np.empty((3 * B.EVENTS * (B.FANOUT + 1), B.MEM_DIM), np.float32)
+    o_mail = np.empty((3 * B.EVENTS, B.MAIL_DIM), np.float32)
+
+    def step(i):
+        b = i % B.NUM_BATCHES
+        o = OC.sample_layer(indptr, nbr, tss, eid, roots[b], rts[b], B.FANOUT, 0, trim=False)
+        tot = int(o[5][-1])
+        ids = np.concatenate([roots[b], o[0][:tot]])
+        OC.gather_rows(mem, ids, o_mem[:len(ids)])
+        OC.gather_rows(mail, roots[b], o_mail)
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    n_done, t0 = 0, time.perf_counter()
+    while n_done < max(args.steps, 1) * 20 and time.perf_counter() - t0 < 20.0:
+        step(n_done)
+        n_done += 1
+    dt = time.perf_counter() - t0
+    val = n_done * 3 * B.EVENTS / dt
     return {"value": val, "steps": n_done, "ms_per_step": dt / n_done * 1e3,
             "cpu_baseline": {"value": val, "unit": "events/s", "cores": cores, "kind": "port",
-                             "sample": f"{n_done} of the benchmark's batches (recent-{FANOUT} sampling on the full 50 M-edge graph + gather "
-                                       f"of the sampled rows from a {rows_h}-row host table), C/OpenMP restatement of the reference's numba "
-                                       f"sampler; T-CSR build on the host took {build_s:.1f} s"}}
+                             "sample": f"{n_done} steps of one partition's batch (12,000 root queries, recent-{B.FANOUT}, gather of "
+                                       "memory and mail rows) on one partition's events; C/OpenMP restatement of the reference's "
+                                       "numba sampler + row gather; no exchange between partitions on the CPU arm"},
+            "config": {"workload": "8xB200 distributed TGN data path (BASELINE configs[3]), one partition's step on the host cores",
+                       "events_per_rank_and_step": B.EVENTS, "policy": f"recent-{B.FANOUT}, 1 hop"}}
 
 
 def _protect_stdout():
@@ -374,8 +479,55 @@ def _protect_stdout():
     return os.fdopen(saved, "w")
 
 
+def sampler_roofline(g, pipes, b_roots, b_ts, dev, peak):
+    """Algorithmic bytes of the hop (per root: two row pointers, the root's id and time, the search probes, 24 bytes read
+    and 36 written per sampled edge, one offset) over the device time of the sampler's kernels: one batch alone on one
+    stream, and one batch per stream on all streams at once (how the benchmark step runs them)."""
+    from starrygl import ops
+    S = len(pipes)
+    deg = (g.indptr[1:] - g.indptr[:-1])
+    alg = []
+    for b in range(NUM_BATCHES):
+        d = deg[b_roots[b]].clamp_min(1).double()
+        probes = torch.ceil(torch.log2(d)).sum().item()
+        pipes[0].sample_only(b_roots[b], b_ts[b])
+        pipes[0].stream.synchronize()
+        k_eff = int(pipes[0].offsets[BATCH].item())
+        alg.append(BATCH * (16 + 16 + 8) + 8 * probes + k_eff * 60)
+    alg_mean = statistics.mean(alg)
+
+    def alone():
+        it[0] += 1
+        pipes[0].sample_only(b_roots[it[0] % NUM_BATCHES], b_ts[it[0] % NUM_BATCHES])
+    it = [0]
+    ms_alone = _time_ms(alone, pipes[0].stream, 200, warm=10)
+    main = torch.cuda.Stream(dev)
+    times = []
+    for rep in range(30):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(main)
+        for p_ in pipes:
+            p_.stream.wait_stream(main)
+        for r in range(8):
+            for j, p_ in enumerate(pipes):
+                b = (rep * 8 * S + r * S + j) % NUM_BATCHES
+                p_.sample_only(b_roots[b], b_ts[b])
+        for p_ in pipes:
+            main.wait_stream(p_.stream)
+        e1.record(main)
+        main.synchronize()
+        times.append(e0.elapsed_time(e1) / (8 * S))
+    ms_fly = statistics.median(times)
+    return {"bound": "hbm", "kernel": "sample_count_kernel + sample_fill_kernel", "bytes_per_batch": alg_mean,
+            "unit": "GB/s", "peak": peak,
+            "alone": {"ms_per_batch": ms_alone, "achieved": alg_mean / ms_alone / 1e6, "frac": alg_mean / ms_alone / 1e6 / peak},
+            "in_flight": {"batches": S, "ms_per_batch": ms_fly, "achieved": alg_mean / ms_fly / 1e6,
+                          "frac": alg_mean / ms_fly / 1e6 / peak},
+            "note": "4,096 roots per batch is a latency-bound size; the in-flight figure is the aggregate of one batch per stream"}
+
+
 def main():
-    global NUM_NODES, NUM_EDGES, STREAMS, GRAPHS, ROUTE
+    global NUM_NODES, NUM_EDGES, STREAMS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -383,31 +535,20 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the uniform two-hop and cache-gather measurements")
-    ap.add_argument("--gather-mode", default="auto")
     ap.add_argument("--streams", type=int, default=6, help="mini-batches in flight (one pipeline object + stream each)")
-    ap.add_argument("--graph-value", action="store_true",
-                    help="replay a CUDA graph per step in the device-resident loop too (default: one fused C call per step; "
-                         "the host-buffer loop always replays a graph that includes its copies)")
-    ap.add_argument("--route", default="p2p", choices=["p2p", "nccl", "none"],
-                    help="transport of the cache route at N > 1: peer-memory kernels (default) or grouped NCCL send/recv")
-    ap.add_argument("--e2e-mode", default="native", choices=["native", "torch"],
-                    help="host-buffer step as one library call (copy + captured graph) or as a torch CUDA-graph replay")
-    ap.add_argument("--e2e-export", default="prefix", choices=["prefix", "full"],
-                    help="result copy to the host: device-counted prefix (exact bytes) or whole-capacity copies")
-    ap.add_argument("--no-numa-bind", action="store_true", help="N > 1: do not bind the rank to the CPUs of its GPU's NUMA node")
-    ap.add_argument("--row-align", type=int, default=0, help="pad the feature table's rows in HBM to this many bytes (0 = dense)")
+    ap.add_argument("--repeats", type=int, default=REGION_REPEATS, help="repeats of the K-step timed region (median reported)")
     ap.add_argument("--route-bw-rows", type=int, default=0,
                     help="N > 1: measure the route alone with this many rows per rank and step (bandwidth-bound sizes) and exit")
+    ap.add_argument("--route-bw-dim", type=int, default=MEM_DIM, help="row width (fp32 values) of --route-bw-rows")
     ap.add_argument("--tcsr-only", action="store_true", help="time the T-CSR construction of the benchmark graph and exit")
-    ap.add_argument("--no-step-graph", action="store_true",
-                    help="issue sample+gather as one fused foreign call (three kernel launches) instead of one graph launch")
+    ap.add_argument("--partitioned", action="store_true",
+                    help="N = 1: run the partitioned (multi-GPU) workload on a single partition, the rank being its own peer")
     ap.add_argument("--num-nodes", type=int, default=NUM_NODES, help="smaller graphs are for profiler captures only")
     ap.add_argument("--num-edges", type=int, default=NUM_EDGES)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     out_stream = _protect_stdout()
-    ROUTE = args.route
-    NUM_NODES, NUM_EDGES, STREAMS, GRAPHS = args.num_nodes, args.num_edges, max(1, args.streams), True
+    NUM_NODES, NUM_EDGES, STREAMS = args.num_nodes, args.num_edges, max(1, args.streams)
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -415,24 +556,45 @@ def main():
         return run_reference(args, rank, out_stream)
 
     import torch.distributed as dist
-    from starrygl import ops, _C
-    from starrygl.graph.pipeline import SampleGatherPipeline
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    multi = world > 1
-    from starrygl.utils.affinity import bind_to_gpu_numa_node
-    host_info = bind_to_gpu_numa_node(local) if (multi and not args.no_numa_bind) else {"numa_node": None, "cpus": len(os.sched_getaffinity(0))}
-    if multi:
+    if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-
+        try:
+            if args.route_bw_rows > 0:
+                route_bandwidth(args, rank, world, dev, out_stream)
+            else:
+                import bench_c4
+                line = bench_c4.run(args, rank, world, dev, ClockSampler(local) if rank == 0 else None, peaks())
+                if rank == 0:
+                    print(json.dumps(line), file=out_stream, flush=True)
+        finally:
+            dist.barrier()
+            from starrygl.route.exchange import NativeComm
+            NativeComm.shutdown()
+            dist.destroy_process_group()
+        return
     if args.route_bw_rows > 0:
-        if not multi:
-            raise SystemExit("--route-bw-rows needs at least two ranks")
-        return route_bandwidth(args, rank, world, dev, out_stream)
+        raise SystemExit("--route-bw-rows needs at least two ranks")
+    if args.partitioned:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29577")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+        import bench_c4
+        line = bench_c4.run(args, 0, 1, dev, ClockSampler(local), peaks())
+        print(json.dumps(line), file=out_stream, flush=True)
+        dist.destroy_process_group()
+        return
+    run_single(args, dev, local, out_stream)
 
+
+def run_single(args, dev, local, out_stream):
+    """N = 1: the sampler microbenchmark graph, recent-20 + gather of the sampled edges' feature rows."""
+    from starrygl import ops
+    from starrygl.graph.pipeline import SampleGatherPipeline
     # ---- set-up (untimed): graph, T-CSR, feature table, batches -------------------------------------------
-    src, dst, ts, gen = make_graph(dev, seed=rank)
+    src, dst, ts, gen = make_graph(dev, seed=0)
     if args.tcsr_only:
         # side measurement (not the benchmark line): T-CSR construction of the benchmark graph, CUDA-event timed
         ops.tcsr_build(src, dst, ts, None, NUM_NODES)
@@ -445,280 +607,144 @@ def main():
         torch.cuda.synchronize(dev)
         ms_ = e0_.elapsed_time(e1_) / reps
         alg_ = NUM_EDGES * 56 + (NUM_NODES + 1) * 8 + 6 * 2 * NUM_EDGES * 12
-        if rank == 0:
-            print(json.dumps({"tcsr_build_ms": ms_, "edges": NUM_EDGES, "nodes": NUM_NODES, "algorithmic_bytes": alg_,
-                              "algorithmic_GBps": alg_ / ms_ / 1e6}), file=out_stream, flush=True)
+        print(json.dumps({"tcsr_build_ms": ms_, "edges": NUM_EDGES, "nodes": NUM_NODES, "algorithmic_bytes": alg_,
+                          "algorithmic_GBps": alg_ / ms_ / 1e6}), file=out_stream, flush=True)
         return
     g = ops.tcsr_build(src, dst, ts, None, NUM_NODES)
     b_roots, b_ts = make_batches(src, ts, gen, dev)
     del src, dst, ts
-    # rows padded in HBM to a multiple of --row-align bytes (0 = dense): a 688-byte row that starts on a 64-byte boundary
-    # touches 11 DRAM atoms instead of 11-12 and 22 sectors instead of 22-23
-    pitch_f = EDGE_DIM if args.row_align <= 0 else ((EDGE_DIM * 4 + args.row_align - 1) // args.row_align) * args.row_align // 4
-    feats = torch.empty(NUM_EDGES, pitch_f, dtype=torch.float32, device=dev)[:, :EDGE_DIM]
+    feats = torch.empty(NUM_EDGES, EDGE_DIM, dtype=torch.float32, device=dev)
     for s in range(0, NUM_EDGES, 5_000_000):
         feats[s:s + 5_000_000].normal_(generator=gen)
     h_both = b_roots._base.cpu().pin_memory()           # [batch, 2, BATCH]: one contiguous host block per batch
-    h_roots, h_ts = h_both[:, 0], h_both[:, 1]
     h_ptrs = [h_both[b].data_ptr() for b in range(NUM_BATCHES)]
 
-    S = max(1, args.streams)
+    S, K, W = STREAMS, args.steps, args.warmup
     streams = [torch.cuda.Stream(dev) for _ in range(S)]
-    pipes = [SampleGatherPipeline(g, feats, FANOUT, "recent", BATCH, gather_mode=args.gather_mode, stream=st,
-                                  export=args.e2e_export) for st in streams]
-    pipe, stream = pipes[0], streams[0]
-    use_graph = args.graph_value
+    pipes = [SampleGatherPipeline(g, feats, FANOUT, "recent", BATCH, stream=st) for st in streams]
+    pipe = pipes[0]
     for p_ in pipes:
-        p_.capture()
-        if not args.no_step_graph:
-            p_.capture_native()
-        if args.e2e_mode == "native":
-            p_.capture_native_host()
+        p_.capture_native()
+        p_.capture_native_host()
     main_stream = torch.cuda.Stream(dev)
-    route_stream = torch.cuda.Stream(dev, priority=-1)     # its few CTAs must not queue behind the persistent gather CTAs
-    route_recv_stream = torch.cuda.Stream(dev, priority=-1)
-    route = None
-    route_steps = None
-    if multi and args.route != "none":
-        from starrygl.cache.cache_route import CacheRoute, CommPlan
-        from starrygl.cache.NodeState import DistNodeState
-        from starrygl.utils.partition_book import PartitionState
-        rgen = torch.Generator().manual_seed(100 + rank)
-        # per step: ROUTE_ROWS owned rows go to the other ranks (round-robin), slots on the receiver are unique
-        per = ROUTE_ROWS // (world - 1)
-        ranks = torch.cat([torch.full((per,), p, dtype=torch.long) for p in range(world) if p != rank])
-        sizes = torch.bincount(ranks, minlength=world)
-        plans = []
-        for b in range(NUM_BATCHES):
-            plans.append(CommPlan(send_ranks=ranks, send_sizes=sizes,
-                                  send_indices=torch.randint(0, NUM_NODES, (ranks.numel(),), generator=rgen),
-                                  send_remote_indices=(torch.randperm(NUM_NODES, generator=rgen)[:ranks.numel()])).to(dev))
-        ps = PartitionState(loc_ids=torch.arange(NUM_NODES, device=dev), num_master_nums=NUM_NODES, node_mode='identity',
-                            num_nodes=NUM_NODES)
-        state = DistNodeState(ps, MEM_DIM, device=dev)
-        mem = torch.randn(NUM_NODES, MEM_DIM, device=dev)
-        mem_ts = torch.rand(NUM_NODES, device=dev)
-        cr = CacheRoute()
+    batch_ptrs = [b_roots[b].data_ptr() for b in range(NUM_BATCHES)]
 
-        def cb(idx, rows, mode):
-            state.write_packed(idx, rows)
-        cb.fused_state = state
-        for p in plans:     # receive counts are exchanged once per plan (set-up), steps then need no host sync
-            cr._exchange_counts(p, dev)
-        if args.route == "p2p":
-            from starrygl.cache.p2p_route import P2PCacheRoute
-            p2p = P2PCacheRoute(MEM_DIM, True, cap_rows=max(1024, ROUTE_ROWS), ring=8)
+    def issue(first, count):
+        for i in range(first, first + count):
+            pipes[i % S].replay_ptr(batch_ptrs[i % NUM_BATCHES])    # one call: copy the batch's roots in + one graph launch
 
-            class _P2PAdapter:      # same call shape as CacheRoute.update_with_plan for the loops below
-                def update_with_plan(self, feats, plan, cb_, local_ts=None):
-                    return [p2p.push(feats, plan, state, local_ts)]
-            cr = _P2PAdapter()
-            route_steps = [p2p.bind_step(mem, mem_ts, pl_, state, route_stream, route_recv_stream) for pl_ in plans]
-        route = (cr, plans, mem, mem_ts, cb)
-
-    batch_ptrs = [(b_roots[b].data_ptr(), b_ts[b].data_ptr()) for b in range(NUM_BATCHES)]
-
-    issue_t = {"sample_gather": 0.0, "route_send": 0.0, "route_apply": 0.0}
-
-    def step_device(i, ev=None, route_inline=True):
-        b = i % NUM_BATCHES
-        t_a = time.perf_counter()
-        if ev is not None:
-            pipes[i % S].run_device(b_roots[b], b_ts[b], 0, ev)
-        elif use_graph:
-            pipes[i % S].replay_device(b_roots[b], b_ts[b])
-        elif not args.no_step_graph:
-            pipes[i % S].replay_ptr(batch_ptrs[b][0])       # one call: copy the batch's roots in + one graph launch
-        else:
-            pipes[i % S].run_device_ptr(batch_ptrs[b][0], batch_ptrs[b][1], BATCH)
-        if route is not None and route_inline:
-            # the memory rows pushed to the other partitions do not depend on this batch's samples: the route runs
-            # on its own stream, concurrently with sampling and gather
-            cr, plans, mem, mem_ts, cb = route
-            t_b = time.perf_counter()
-            if route_steps is not None:
-                route_steps[b]()                # one pre-bound foreign call: send + apply of this step
-                t_c = time.perf_counter()
-            else:
-                with torch.cuda.stream(route_stream):
-                    futs = cr.update_with_plan(mem, plans[b], cb, local_ts=mem_ts)
-                    t_c = time.perf_counter()
-                    for f in futs:
-                        f.wait()
-            t_d = time.perf_counter()
-            issue_t["sample_gather"] += t_b - t_a
-            issue_t["route_send"] += t_c - t_b
-            issue_t["route_apply"] += t_d - t_c
-
-    def barrier():
-        if multi:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    # ---- value: inputs resident in HBM --------------------------------------------------------------------
-    for i in range(args.warmup):
-        step_device(i)
-    barrier()
+    # ---- value: inputs resident in HBM ------------------------------------------------------------------------
+    issue(0, W)
+    torch.cuda.synchronize(dev)
     for p_ in pipes:
         p_.status.check("bench warmup")
     clocks = ClockSampler(local)
-    if rank == 0:
-        clocks.start()
-    for k_ in issue_t:
-        issue_t[k_] = 0.0
-    gev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    # K steps, up to S of them in flight: the streams fork from / join into main_stream, whose two events bracket
-    # the whole region on the device
-    e0.record(main_stream)
-    for st in streams + [route_stream, route_recv_stream]:
-        st.wait_stream(main_stream)
-    route_thread = None
-    if route_steps is not None:
-        # the route is driven from its own host thread, as a trainer would (the foreign calls release the GIL): the two
-        # issue loops run side by side, the device-side ring bounds how far a rank can run ahead of its peers
-        def route_loop():
-            torch.cuda.set_device(dev)
-            t_r = time.perf_counter()
-            for i in range(args.steps):
-                route_steps[(args.warmup + i) % NUM_BATCHES]()
-            issue_t["route_thread_total"] = time.perf_counter() - t_r
-        route_thread = threading.Thread(target=route_loop)
-        route_thread.start()
-    t_issue = time.perf_counter()
-    for i in range(args.steps):
-        step_device(args.warmup + i, None, route_inline=route_thread is None)
-    t_issue = time.perf_counter() - t_issue
-    if route_thread is not None:
-        route_thread.join()
-    # where the device time goes: end of the sampler/gather streams and end of the two route chains, each against e0
-    e_pipe = torch.cuda.Event(enable_timing=True)
-    e_rs, e_rr = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    join_stream = torch.cuda.Stream(dev)
-    for st in streams:
-        join_stream.wait_stream(st)
-    e_pipe.record(join_stream)
-    e_rs.record(route_stream)
-    e_rr.record(route_recv_stream)
-    for st in streams + [route_stream, route_recv_stream]:
-        main_stream.wait_stream(st)
-    e1.record(main_stream)
-    barrier()
-    ms = e0.elapsed_time(e1)
+    clocks.start()
+    R = max(1, args.repeats)
+    # K steps, up to S of them in flight: the streams fork from / join into main_stream, whose two events bracket the
+    # region on the device; the region is repeated R times back to back and the median is reported (a single region of
+    # K = 20 steps lasts half a millisecond)
+    regions = []
+    t_issue = 0.0
+    step_no = W
+    for r in range(R):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(main_stream)
+        for st in streams:
+            st.wait_stream(main_stream)
+        t_a = time.perf_counter()
+        issue(step_no, K)
+        t_issue += time.perf_counter() - t_a
+        step_no += K
+        for st in streams:
+            main_stream.wait_stream(st)
+        e1.record(main_stream)
+        regions.append((e0, e1))
+        if r % 16 == 15:
+            main_stream.synchronize()     # bounds the number of launches queued ahead of the device
+    torch.cuda.synchronize(dev)
+    region_ms = sorted(a.elapsed_time(b) for a, b in regions)
+    ms = statistics.median(region_ms)
     for p_ in pipes:
         p_.status.check("bench")
-    if os.environ.get("SGL_P2P_DBG", "0") == "2" and route_steps is not None and os.environ.get("SGL_P2P_TL_OUT"):
-        import ctypes as C_
-        n_tl = min(args.steps + 2 * args.warmup, 4096)
-        buf = (C_.c_uint64 * (n_tl * 8))()
-        _C.lib().sgl_p2p_route_timeline(p2p.ctx, buf, n_tl)
-        np.save(os.environ["SGL_P2P_TL_OUT"] + f".rank{rank}.npy", np.array(buf, dtype=np.uint64).reshape(n_tl, 8))
-    if os.environ.get("SGL_P2P_DBG", "0") == "2" and route_steps is not None and rank == 0:
-        import ctypes as C_
-        n_tl = min(args.steps + 2 * args.warmup, 4096)
-        buf = (C_.c_uint64 * (n_tl * 8))()
-        _C.lib().sgl_p2p_route_timeline(p2p.ctx, buf, n_tl)
-        tl = np.array(buf, dtype=np.uint64).reshape(n_tl, 8).astype(np.float64)[args.warmup + 50:args.warmup + args.steps - 10] / 1e3
-        sys.stderr.write("P2P timeline (us): send dur %.1f | send start->next start %.1f | apply start->first CTA done %.1f | first CTA done->end %.1f | "
-                         "apply start->next start %.1f | send end -> apply first CTA done %.1f | resident before start: send %.1f apply %.1f\n" % (
-                             np.median(tl[:, 1] - tl[:, 0]), np.median(np.diff(tl[:, 0])), np.median(tl[:, 3] - tl[:, 2]),
-                             np.median(tl[:, 4] - tl[:, 3]), np.median(np.diff(tl[:, 2])), np.median(tl[:, 3] - tl[:, 1]),
-                             np.median(tl[:, 0] - tl[:, 5]), np.median(tl[:, 2] - tl[:, 6])))
-    if True:
-        # the step is one foreign call (or one graph replay), so its kernels cannot be bracketed individually:
-        # the dominant kernel is timed in a second pass over the same K batches, kernel by kernel on one stream
-        for i in range(args.steps):
-            pipe.run_device(b_roots[(args.warmup + i) % NUM_BATCHES], b_ts[(args.warmup + i) % NUM_BATCHES], 0, gev[i])
-        pipe.stream.synchronize()
+
+    # the step is one graph replay, so its kernels cannot be bracketed individually: the dominant kernel is timed in a
+    # second pass over K batches, kernel by kernel on one stream
+    gev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(max(K, 50))]
+    for i, ev in enumerate(gev):
+        pipe.run_device(b_roots[(W + i) % NUM_BATCHES], b_ts[(W + i) % NUM_BATCHES], 0, ev)
+    pipe.stream.synchronize()
     gather_ms = [a.elapsed_time(b) for a, b in gev]
-    # edges actually gathered per step (for the algorithmic byte count), read after the timed region
     edges = []
-    for i in range(args.steps):
-        pipe.run_device(b_roots[(args.warmup + i) % NUM_BATCHES], b_ts[(args.warmup + i) % NUM_BATCHES])
+    for i in range(len(gev)):
+        pipe.run_device(b_roots[(W + i) % NUM_BATCHES], b_ts[(W + i) % NUM_BATCHES])
         pipe.stream.synchronize()
         edges.append(int(pipe.offsets[BATCH].item()))
 
-    # ---- e2e: host buffers in, block structure out, up to S batches in flight -------------------------------
+    # ---- e2e: host buffers in, block structure out, up to S batches in flight ---------------------------------
     def e2e_loop(first, count):
         tot = 0
         for i in range(count):
             p_ = pipes[i % S]
             if i >= S:                          # retire the batch that used this pipeline object before reusing it
                 tot += p_.result()[0]
-            b = (first + i) % NUM_BATCHES
-            if args.e2e_mode == "native":
-                p_.submit_host_ptr(h_ptrs[b])   # one call: roots from the pinned block + the captured step with its export
-            else:
-                p_.submit_host(h_roots[b], h_ts[b])
-            if route_steps is not None:
-                route_steps[b]()                # peer-memory route: send + apply of this step
-            elif route is not None:
-                cr, plans, mem, mem_ts, cb = route
-                with torch.cuda.stream(route_stream):
-                    for f in cr.update_with_plan(mem, plans[b], cb, local_ts=mem_ts):
-                        f.wait()
+            p_.submit_host_ptr(h_ptrs[(first + i) % NUM_BATCHES])   # roots from the pinned block + the captured step with its export
         for i in range(max(0, count - S), count):
             tot += pipes[i % S].result()[0]
         return tot
-    e2e_loop(0, args.warmup)
-    barrier()
-    t0 = time.perf_counter()
-    e2e_steps = args.steps
-    e2e_edges = e2e_loop(args.warmup, e2e_steps)
+    e2e_loop(0, W)
     torch.cuda.synchronize(dev)
-    e2e_s = time.perf_counter() - t0
-    barrier()
-    clk = clocks.stop() if rank == 0 else None
+    e2e_times, e2e_edges = [], 0
+    for r in range(max(5, min(R, 40))):
+        t0 = time.perf_counter()
+        e2e_edges = e2e_loop(W + r * K, K)
+        torch.cuda.synchronize(dev)
+        e2e_times.append(time.perf_counter() - t0)
+    e2e_ms = statistics.median(e2e_times) * 1e3
+    clk = clocks.stop()
 
-    t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
-    if multi:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = t.tolist()
-
-    if rank == 0:
-        peak, peak_kind = peaks()
-        row_bytes = EDGE_DIM * 4
-        alg = statistics.mean(edges) * (2 * row_bytes + 8)
-        g_ms = statistics.mean(gather_ms)
-        achieved = alg / g_ms / 1e6
-        line = {"metric": "sampled+gathered events/sec", "value": world * BATCH * args.steps / (ms / 1e3),
-                "unit": "events/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms / args.steps, "host": host_info, "host_issue_ms_per_step": t_issue * 1e3 / args.steps,
-                "host_issue_breakdown_ms": {k: v * 1e3 / args.steps for k, v in issue_t.items()},
-                "device_ms_per_step": {"sample_gather_streams": e0.elapsed_time(e_pipe) / args.steps,
-                                       "route_send_chain": e0.elapsed_time(e_rs) / args.steps,
-                                       "route_apply_chain": e0.elapsed_time(e_rr) / args.steps},
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": "int64", "data": "synthetic", "config": workload_config(world),
-                "e2e": {"value": world * BATCH * e2e_steps / (e2e_ms / 1e3), "unit": "events/s",
-                        "h2d_bytes_per_step": pipe.h2d_bytes(BATCH), "d2h_bytes_per_step": pipe.d2h_bytes(e2e_edges / max(e2e_steps, 1)),
-                        "note": "pinned host roots/times in; offsets, neighbour ids, timestamps, edge ids and dt out; "
-                                "gathered feature rows stay on the GPU for the model", "edges_per_step": e2e_edges / e2e_steps},
-                "gpu_launches": args.steps * (pipe.kernel_launches_per_step + (2 if multi else 0)),
-                "roofline": {"bound": "hbm", "kernel": "gather_bulk_kernel" if pipe.mode != 1 else "gather_lanes_kernel",
-                             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                             "peak_source": peak_kind, "traffic": statistics.mean(edges) * GATHER_TRAFFIC_BYTES_PER_ROW,
-                             "traffic_note": "ncu dram read+write of a 65 k-row launch scaled by rows; the output is still in L2 when "
-                                             "the kernel ends, so write-back is under-counted (see profiles/)",
-                             "bytes_per_launch": alg, "ms_per_launch": g_ms,
-                             "edges_per_step": statistics.mean(edges)},
-                "clocks": clk}
-        if world == 1 and not args.no_secondary:
-            del feats, pipe, pipes
-            feats = pipe = pipes = None
-            torch.cuda.empty_cache()
-            line["secondary"] = secondary_measurements(g, dev, peak)
-        if not args.no_cpu_baseline and world == 1:
-            del feats, pipe, pipes, g
-            torch.cuda.empty_cache()
-            line["cpu_baseline"] = cpu_baseline_measure(dev, args.steps, args.warmup, 20.0)["cpu_baseline"]
-        print(json.dumps(line), file=out_stream, flush=True)
-    if multi:
-        dist.barrier()
-        from starrygl.cache.cache_route import NativeComm
-        NativeComm.shutdown()
-        dist.destroy_process_group()
+    peak, peak_kind = peaks()
+    row_bytes = EDGE_DIM * 4
+    alg = statistics.mean(edges) * (2 * row_bytes + 8)
+    g_ms = statistics.mean(gather_ms)
+    achieved = alg / g_ms / 1e6
+    line = {"metric": "sampled+gathered events/sec", "value": BATCH * K / (ms / 1e3),
+            "unit": "events/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms / K,
+            "timed_region": {"repeats": R, "steps_per_region": K, "median_ms": ms, "p10_ms": region_ms[len(region_ms) // 10],
+                             "p90_ms": region_ms[(len(region_ms) * 9) // 10], "min_ms": region_ms[0], "max_ms": region_ms[-1],
+                             "total_timed_s": sum(region_ms) / 1e3},
+            "host_issue_ms_per_step": t_issue * 1e3 / (R * K),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int64", "data": "synthetic", "config": workload_config(1),
+            "e2e": {"value": BATCH * K / (e2e_ms / 1e3), "unit": "events/s",
+                    "h2d_bytes_per_step": pipe.h2d_bytes(BATCH), "d2h_bytes_per_step": pipe.d2h_bytes(e2e_edges / max(K, 1)),
+                    "note": "pinned host roots/times in; offsets, neighbour ids, timestamps, edge ids and dt out; "
+                            "gathered feature rows stay on the GPU for the model; median of "
+                            f"{len(e2e_times)} repeats of the K-step loop (wall clock around a device synchronisation)",
+                    "edges_per_step": e2e_edges / K},
+            "gpu_launches": R * K * pipe.kernel_launches_per_step,
+            "roofline": {"bound": "hbm", "kernel": "gather_bulk_kernel" if pipe.mode != 1 else "gather_lanes_kernel",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_kind, "traffic": statistics.mean(edges) * GATHER_TRAFFIC_BYTES_PER_ROW,
+                         "traffic_note": "ncu dram read+write of a 65 k-row launch scaled by rows; the output is still in L2 when "
+                                         "the kernel ends, so write-back is under-counted",
+                         "bytes_per_launch": alg, "ms_per_launch": g_ms,
+                         "edges_per_step": statistics.mean(edges)},
+            "roofline_sampler": sampler_roofline(g, pipes, b_roots, b_ts, dev, peak),
+            "clocks": clk}
+    if not args.no_secondary:
+        del feats, pipe, pipes
+        torch.cuda.empty_cache()
+        line["secondary"] = secondary_measurements(g, dev, peak)
+    if not args.no_cpu_baseline:
+        feats = pipe = pipes = None
+        del g
+        torch.cuda.empty_cache()
+        cpu = cpu_baseline_measure(dev, K, W, 20.0, two_hop="secondary" in line)
+        line["cpu_baseline"] = cpu["cpu_baseline"]
+        if "two_hop" in cpu:
+            line["secondary"]["uniform_10_10_relabel"]["cpu_baseline"] = cpu["two_hop"]
+    print(json.dumps(line), file=out_stream, flush=True)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,428 @@
+"""Multi-GPU arm of bench.py: the partitioned TGN data path (BASELINE configs[3]) on N ranks of one box.
+
+Synthetic stand-in for the distributed configuration: a planted-community temporal graph with ONE community per rank
+(312,500 nodes and 12.5 M events per rank -- 2.5 M nodes / 100 M events at 8 ranks; weak scaling), 80 % of an event's
+sources inside the destination's community, the rest uniform over the other communities; partition = community; an
+event belongs to the partition of its destination.  Every rank stores its owned nodes followed by the halo (remote
+sources it has seen) and samples from its own events only (both directions of an event are rows of its T-CSR).
+
+One step per rank = one batch of 4,000 events = 12,000 root queries (source, destination, negative destination):
+
+  A1  (id, ts) relabel of the roots -> the layer-0 list              sgl_unique_pairs
+  A2  most-recent-10 sampling of the 12,000 roots                      sgl_sample_layer
+  A3  gather of node memory (100 x fp32 + ts) for roots and sampled neighbours, of the roots' mails (372 x fp32 + ts)
+      through the global -> local slot map                             sgl_gather_rows
+  A4  stand-in for the model: new memory / mail rows for the layer-0 list, a pure function of (node id, step)
+  A5  local write of those rows                                        sgl_scatter_rows
+  A6  route plan of the step, built on the device from the layer-0 list, the partition book and the replica table
+                                                                       sgl_plan_route
+  R   owners push the fresh memory rows and mails to every rank that holds a replica, over NVLink peer memory, with the
+      plan's sizes read from device memory (no host synchronisation, no count exchange); the receivers apply them
+                                                                       sgl_p2p_route_send_dev / sgl_p2p_route_recv_dev
+
+A1-A2 of step s+1 overlap R of step s; A3 of step s+1 waits for R of step s (it reads what R writes).  After the timed
+loop rank 0 recomputes, from the seeds alone, which step wrote every one of its rows last (its own batches and every
+peer's) and compares its whole memory and mail tables with that expectation bit for bit.
+"""
+import statistics
+import time
+
+import torch
+import torch.distributed as dist
+
+N_PER = 312_500           # nodes per partition
+E_PER = 12_500_000        # events per partition
+T_MAX = 10_000_000
+P_INTRA = 0.8
+EVENTS = 4000             # events per rank and step
+FANOUT = 10
+MEM_DIM = 100
+MAIL_DIM = 2 * MEM_DIM + 172
+NUM_BATCHES = 64
+
+
+def make_partition(rank, world, dev, n_per=N_PER, e_per=E_PER):
+    """Events of partition ``rank`` (seeded by the rank alone, so that any rank can regenerate any partition)."""
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    base = rank * n_per
+    dst = base + torch.randint(0, n_per, (e_per,), device=dev, generator=gen)
+    src = base + torch.randint(0, n_per, (e_per,), device=dev, generator=gen)
+    cross = torch.rand(e_per, device=dev, generator=gen) >= P_INTRA
+    far = torch.randint(0, max(world - 1, 1) * n_per, (e_per,), device=dev, generator=gen)
+    far = far + (far >= base) * n_per                      # skip the own id range
+    if world > 1:
+        src = torch.where(cross, far, src)
+    ts = torch.sort(torch.randint(0, T_MAX, (e_per,), device=dev, generator=gen)).values
+    neg = base + torch.randint(0, n_per, (NUM_BATCHES, EVENTS), device=dev, generator=gen)
+    return src, dst, ts, neg
+
+
+def batches_of(src, dst, ts, neg):
+    """[NUM_BATCHES, 12000] roots and query times: the last NUM_BATCHES * EVENTS events in time order."""
+    e = src.numel()
+    lo = e - NUM_BATCHES * EVENTS
+    s, d, t = (x[lo:].view(NUM_BATCHES, EVENTS) for x in (src, dst, ts))
+    return torch.cat([s, d, neg], 1).contiguous(), torch.cat([t, t, t], 1).contiguous()
+
+
+def model_rows(ids, step_t, dim):
+    """Stand-in for the model's output for the layer list: row of node v at step s = ((131 v + 7 s + j) mod 65536), j the
+    column -- exact in fp32, and a function of (v, s) only, so that the state every rank must hold can be recomputed."""
+    base = ids * 131 + step_t * 7
+    return ((base.unsqueeze(1) + torch.arange(dim, device=ids.device)) % 65536).to(torch.float32)
+
+
+class Partition:
+    """Everything rank ``rank`` holds: T-CSR of its events, node memory and mail tables (owned rows, then halo rows), the
+    global -> local slot map, the partition book and the replica table of the nodes it owns."""
+
+    def __init__(self, rank, world, dev, n_per=N_PER, e_per=E_PER):
+        from starrygl import ops
+        from starrygl.cache.NodeState import DistNodeState
+        from starrygl.cache.replica_table import CSRReplicaTable
+        from starrygl.utils.partition_book import PartitionState
+        self.rank, self.world, self.dev, self.n_per = rank, world, dev, n_per
+        n_glob = world * n_per
+        src, dst, ts, neg = make_partition(rank, world, dev, n_per, e_per)
+        self.roots, self.root_ts = batches_of(src, dst, ts, neg)
+        eid = torch.arange(e_per, device=dev)
+        self.g = ops.tcsr_build(torch.cat([dst, src]), torch.cat([src, dst]), torch.cat([ts, ts]), torch.cat([eid, eid]), n_glob)
+        base = rank * n_per
+        remote = src[(src < base) | (src >= base + n_per)]
+        halo = torch.unique(remote) if remote.numel() else remote
+        del src, dst, ts, eid, remote
+        self.loc_ids = torch.cat([torch.arange(base, base + n_per, device=dev), halo])
+        ps = PartitionState(loc_ids=self.loc_ids, num_master_nums=n_per, node_mode='map', num_nodes=n_glob)
+        self.mem = DistNodeState(ps, MEM_DIM, device=dev)
+        self.mail = DistNodeState(ps, MAIL_DIM, device=dev)
+        self.g2l = ps.node_mapper.g2l_map(dev)
+        self.node_parts = torch.arange(n_glob, device=dev) // n_per
+        # replica table of the nodes owned here: which other ranks hold them as halo, and in which slot
+        n_halo = torch.tensor([halo.numel()], device=dev)
+        if world > 1:
+            counts = [torch.zeros_like(n_halo) for _ in range(world)]
+            dist.all_gather(counts, n_halo)
+            counts = [int(c.item()) for c in counts]
+            pad = torch.zeros(max(max(counts), 1), dtype=torch.int64, device=dev)
+            pad[:halo.numel()] = halo
+            box = [torch.empty_like(pad) for _ in range(world)]
+            dist.all_gather(box, pad)
+        else:
+            counts, box = [0], [halo]
+        self.halo_counts = counts
+        node, rk, lc = [], [], []
+        for q in range(world):
+            if q == rank:
+                continue
+            h = box[q][:counts[q]]
+            mine = (h >= base) & (h < base + n_per)
+            node.append(h[mine])
+            rk.append(torch.full((int(mine.sum()),), q, dtype=torch.int64, device=dev))
+            lc.append(torch.nonzero(mine).reshape(-1) + n_per)          # slot on q: after q's owned rows, halo order
+        node = torch.cat(node) if node else torch.zeros(0, dtype=torch.int64, device=dev)
+        rk = torch.cat(rk) if rk else node.clone()
+        lc = torch.cat(lc) if lc else node.clone()
+        order = torch.argsort(node * world + rk)
+        indptr = torch.zeros(n_glob + 1, dtype=torch.int64, device=dev)
+        indptr[1:] = torch.cumsum(torch.bincount(node, minlength=n_glob), 0)
+        pad1 = torch.zeros(1, dtype=torch.int64, device=dev)      # keeps the arrays non-empty on a single partition
+        self.rep = CSRReplicaTable(indptr, torch.cat([rk[order], pad1]), torch.cat([lc[order], pad1]))
+        self.max_rep = int((indptr[1:] - indptr[:-1]).max().item()) if node.numel() else 0
+
+
+class Step:
+    """The device work of one step, captured once as two CUDA graphs (A1-A2 and A3-A6) over static buffers."""
+
+    def __init__(self, part: Partition, use_graphs=True):
+        from starrygl import _C, ops
+        self.p, self.ops = part, ops
+        dev = part.dev
+        self.n_roots = 3 * EVENTS
+        self.in_roots = torch.zeros(self.n_roots, dtype=torch.int64, device=dev)
+        self.in_ts = torch.zeros(self.n_roots, dtype=torch.int64, device=dev)
+        self.in_roots.copy_(part.roots[0])
+        self.in_ts.copy_(part.root_ts[0])
+        self.step_t = torch.zeros(1, dtype=torch.int64, device=dev)          # number of the step being built
+        self.rows_sent = torch.zeros(1, dtype=torch.int64, device=dev)       # rows this rank pushed so far (one table)
+        self.status = ops.StatusWord(dev)
+        self.id_bits = ops.bits_for(part.g.num_nodes - 1)
+        self.ts_bits = ops.bits_for(T_MAX)
+        self.plan_cap = self.n_roots * max(part.world - 1, 1)
+        self.stream = torch.cuda.Stream(dev)
+        self.use_graphs = use_graphs
+        self.kernel_launches = None
+        # pinned host mirrors of a batch's inputs and of its block structure, for the host-buffer form of the step
+        self.h_in = torch.empty(2, self.n_roots, dtype=torch.int64).pin_memory()
+        self.h_out = None
+        if not use_graphs:
+            return
+        saved = _C.WORKSPACE
+        _C.WORKSPACE = self._ws = _C.Workspace()
+        try:
+            with torch.cuda.stream(self.stream):
+                self._a12()
+                self._a36()
+            self.stream.synchronize()
+            self.step_t.zero_()
+            self.rows_sent.zero_()
+            part.mem.reset(), part.mail.reset()
+            self.g1, self.g2 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            self.g1.enable_debug_mode(), self.g2.enable_debug_mode()
+            with torch.cuda.graph(self.g1, stream=self.stream):
+                self._a12()
+            with torch.cuda.graph(self.g2, stream=self.stream):
+                self._a36()
+        finally:
+            _C.WORKSPACE = saved
+        self.stream.synchronize()
+        from starrygl.graph.batch import count_kernel_nodes
+        k1, k2 = count_kernel_nodes(self.g1), count_kernel_nodes(self.g2)
+        self.kernel_launches = (k1 + k2) if (k1 and k2) else None
+        self.step_t.zero_()
+        self.rows_sent.zero_()
+        part.mem.reset(), part.mail.reset()
+
+    def _a12(self):
+        ops, p = self.ops, self.p
+        self.u_id, self.u_ts, self.inv, _, self.d_n0 = ops.unique_pairs(self.in_roots, self.in_ts, id_bits=self.id_bits,
+                                                                        ts_bits=self.ts_bits, ts_base=0, status=self.status)
+        self.hop = ops.sample_layer(p.g, self.in_roots, self.in_ts, FANOUT, "recent", status=self.status)
+
+    def _a36(self):
+        ops, p = self.ops, self.p
+        st = self.status
+        self.m_roots, self.m_roots_ts = ops.gather_rows(p.mem.data, self.in_roots, map=p.g2l, ts_table=p.mem.ts, status=st)
+        self.m_nbrs, self.m_nbrs_ts = ops.gather_rows(p.mem.data, self.hop.nbr, map=p.g2l, d_n=self.hop.d_total,
+                                                      ts_table=p.mem.ts, status=st)
+        self.mails, self.mails_ts = ops.gather_rows(p.mail.data, self.in_roots, map=p.g2l, ts_table=p.mail.ts, status=st)
+        self.new_mem = model_rows(self.u_id, self.step_t, MEM_DIM)
+        self.new_mail = model_rows(self.u_id, self.step_t, MAIL_DIM)
+        self.new_ts = self.step_t.to(torch.float32).expand(self.u_id.numel()).contiguous()
+        ops.scatter_rows(p.mem.data, self.u_id, self.new_mem, map=p.g2l, d_n=self.d_n0, ts_table=p.mem.ts, ts=self.new_ts, status=st)
+        ops.scatter_rows(p.mail.data, self.u_id, self.new_mail, map=p.g2l, d_n=self.d_n0, ts_table=p.mail.ts, ts=self.new_ts,
+                         status=st)
+        (self.pl_ranks, self.pl_rows, self.pl_locs, self.pl_sizes, self.pl_total) = ops.plan_route(
+            self.u_id, p.node_parts, p.rank, p.rep.indptr, p.rep.indices, p.rep.locs, p.world, self.plan_cap, d_n=self.d_n0,
+            status=st)
+        self.rows_sent += self.pl_total
+        self.step_t += 1
+
+    def sample(self, b):
+        with torch.cuda.stream(self.stream):
+            self.in_roots.copy_(self.p.roots[b], non_blocking=True)
+            self.in_ts.copy_(self.p.root_ts[b], non_blocking=True)
+            self.g1.replay() if self.use_graphs else self._a12()
+
+    def sample_from_host(self, h_roots, h_ts):
+        """A1-A2 for a batch whose roots and query times are in host memory: staged through the pinned mirror."""
+        self.h_in[0].copy_(h_roots)
+        self.h_in[1].copy_(h_ts)
+        with torch.cuda.stream(self.stream):
+            self.in_roots.copy_(self.h_in[0], non_blocking=True)
+            self.in_ts.copy_(self.h_in[1], non_blocking=True)
+            self.g1.replay() if self.use_graphs else self._a12()
+
+    def export_to_host(self):
+        """Block structure of the batch (offsets, neighbour ids, timestamps, edge ids, dt) -> pinned host memory; the
+        gathered rows stay on the GPU for the model."""
+        hop = self.hop
+        if self.h_out is None:
+            self.h_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (hop.offsets, hop.nbr, hop.ts, hop.eid, hop.dt)]
+        with torch.cuda.stream(self.stream):
+            for h, t in zip(self.h_out, (hop.offsets, hop.nbr, hop.ts, hop.eid, hop.dt)):
+                h.copy_(t, non_blocking=True)
+        return sum(h.numel() * h.element_size() for h in self.h_out)
+
+    def gather_update_plan(self):
+        with torch.cuda.stream(self.stream):
+            self.g2.replay() if self.use_graphs else self._a36()
+
+
+def _expected_last_step(rank, world, dev, n_steps_total, routed_from, my_part):
+    """For every global node id: the last step whose write reached rank ``rank``'s copy (-1 = never written).
+    Local writes: every node of the rank's own layer-0 list, at every step.  Pushes: nodes OWNED by the peer that appear in
+    the peer's layer-0 list, from step ``routed_from`` on, if this rank holds a replica."""
+    n_glob = world * my_part.n_per
+    last = torch.full((n_glob,), -1, dtype=torch.int64, device=dev)
+
+    def apply(roots, first_step, only_range=None):
+        # batches are cycled: batch b is used at steps b, b + NUM_BATCHES, ...; visit them in the order of their last use
+        order = []
+        for b in range(NUM_BATCHES):
+            if b >= n_steps_total:
+                continue
+            s_last = b + ((n_steps_total - 1 - b) // NUM_BATCHES) * NUM_BATCHES
+            if s_last >= first_step:
+                order.append((s_last, b))
+        for s_last, b in sorted(order):
+            ids = roots[b]
+            if only_range is not None:
+                ids = ids[(ids >= only_range[0]) & (ids < only_range[1])]
+            last[ids] = torch.maximum(last[ids], torch.full_like(ids, s_last))
+    apply(my_part.roots, 0)
+    for q in range(world):
+        if q == rank:
+            continue
+        src, dst, ts, neg = make_partition(q, world, dev, my_part.n_per, my_part.g.num_edges // 2)
+        roots_q, _ = batches_of(src, dst, ts, neg)
+        del src, dst, ts, neg
+        apply(roots_q, routed_from, (q * my_part.n_per, (q + 1) * my_part.n_per))
+    return last
+
+
+def check_state(part, n_steps_total, routed_from):
+    """Whole memory and mail tables of this rank against the expectation (chunked); returns (ok, rows written)."""
+    dev = part.dev
+    last = _expected_last_step(part.rank, part.world, dev, n_steps_total, routed_from, part)
+    loc_last = last[part.loc_ids]                      # nodes without a local slot cannot be written here
+    ok = True
+    for state, dim in ((part.mem, MEM_DIM), (part.mail, MAIL_DIM)):
+        for a in range(0, part.loc_ids.numel(), 200_000):
+            ids, ls = part.loc_ids[a:a + 200_000], loc_last[a:a + 200_000]
+            want = model_rows(ids, ls.clamp_min(0), dim) * (ls >= 0).unsqueeze(1)
+            want_ts = ls.clamp_min(0).to(torch.float32) * (ls >= 0)
+            ok = ok and torch.equal(state.data[a:a + 200_000], want) and torch.equal(state.ts[a:a + 200_000], want_ts)
+    return bool(ok), int((loc_last >= 0).sum().item())
+
+
+def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
+    from starrygl.cache.p2p_route import P2PCacheRoute
+    K, W = args.steps, max(args.warmup, 3)
+    part = Partition(rank, world, dev, n_per, e_per)
+    step = Step(part)
+    rows_hint = 3 * EVENTS * max(1, min(world - 1, 5))
+    cap_rows = max(16384, 3 * EVENTS)
+    mem_route = P2PCacheRoute(MEM_DIM, True, cap_rows=cap_rows, ring=4)
+    mail_route = P2PCacheRoute(MAIL_DIM, True, cap_rows=cap_rows, ring=4)
+    r_stream = torch.cuda.Stream(dev, priority=-1)
+    a_done = [torch.cuda.Event() for _ in range(2)]
+    r_done = [torch.cuda.Event() for _ in range(2)]
+    n_done = [0]                     # steps issued so far (the device's step counter follows)
+
+    h_roots, h_ts = part.roots.cpu(), part.root_ts.cpu()           # the host-buffer form starts from host tensors
+    d2h = [0]
+
+    def one_step(routed, host=False):
+        s = n_done[0]
+        if host:
+            step.sample_from_host(h_roots[s % NUM_BATCHES], h_ts[s % NUM_BATCHES])
+        else:
+            step.sample(s % NUM_BATCHES)                              # A1-A2: overlaps the route of the step before
+        if routed and s > 0:
+            step.stream.wait_event(r_done[(s - 1) % 2])               # A3 reads the tables the route writes
+        step.gather_update_plan()                                     # A3-A6
+        if routed:
+            a_done[s % 2].record(step.stream)
+            r_stream.wait_event(a_done[s % 2])
+            with torch.cuda.stream(r_stream):
+                sm = mem_route.push_dev(step.new_mem, step.pl_rows, step.pl_locs, step.pl_sizes, rows_hint, step.new_ts)
+                sl = mail_route.push_dev(step.new_mail, step.pl_rows, step.pl_locs, step.pl_sizes, rows_hint, step.new_ts)
+                mem_route.apply_dev(sm, part.mem, rows_hint)
+                mail_route.apply_dev(sl, part.mail, rows_hint)
+                r_done[s % 2].record(r_stream)
+        if host:
+            d2h[0] = step.export_to_host()
+        n_done[0] += 1
+
+    def timed(n_steps, routed, host=False):
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        main = torch.cuda.current_stream(dev)
+        e0.record(main)
+        step.stream.wait_stream(main)
+        r_stream.wait_stream(main)
+        t0 = time.perf_counter()
+        for _ in range(n_steps):
+            one_step(routed, host)
+        t_issue = time.perf_counter() - t0
+        main.wait_stream(step.stream)
+        main.wait_stream(r_stream)
+        e1.record(main)
+        torch.cuda.synchronize(dev)
+        wall = time.perf_counter() - t0
+        t = torch.tensor([e0.elapsed_time(e1), wall * 1e3], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0].item()), t_issue, float(t[1].item())
+
+    # same workload on one partition without the exchange (what a rank does when nothing has to be pushed)
+    timed(W, False)
+    reps = max(3, min(10, 400 // max(K, 1)))
+    local_ms = statistics.median([timed(K, False)[0] for _ in range(reps)])
+    routed_from = n_done[0]
+    # the partitioned step with the route
+    timed(W, True)
+    if clocks is not None:
+        clocks.start()
+    rows0 = int(step.rows_sent.item())
+    regions = [timed(K, True) for _ in range(reps)]
+    rows1 = int(step.rows_sent.item())
+    # end to end: roots from host memory every step, block structure back to pinned host memory every step (wall clock)
+    timed(W, True, host=True)
+    e2e_ms = statistics.median([timed(K, True, host=True)[2] for _ in range(reps)])
+    clk = clocks.stop() if clocks is not None else None
+    ms = statistics.median([r[0] for r in regions])
+    t_issue = statistics.median([r[1] for r in regions])
+    for st, what in ((step.status, "step"), (mem_route.status, "memory route"), (mail_route.status, "mail route"),
+                     (part.mem._status(), "memory table"), (part.mail._status(), "mail table")):
+        st.check(f"bench ({what})")
+    ok, written = check_state(part, n_done[0], routed_from)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if int(flag.item()) != 1:
+        raise SystemExit(f"rank {rank}: routed node state differs from the expectation recomputed from the seeds")
+    edges = int(step.hop.total())
+    rows_per_step = (rows1 - rows0) / (reps * K)
+    rt = torch.tensor([rows_per_step], dtype=torch.float64, device=dev)
+    dist.all_reduce(rt, op=dist.ReduceOp.MAX)
+    rows_per_step = float(rt.item())
+    mem_route.close(), mail_route.close()
+    if rank != 0:
+        return None
+    peak, peak_kind = peak_info
+    wire = (mem_route.pitch + mail_route.pitch) * 4
+    payload = (MEM_DIM + 1 + MAIL_DIM + 1) * 4
+    n_roots = 3 * EVENTS
+    gather_bytes = (n_roots + edges) * (2 * MEM_DIM * 4 + 4 + 8 + 8) + n_roots * (2 * MAIL_DIM * 4 + 4 + 8 + 8)
+    step_ms, local_step_ms = ms / K, local_ms / K
+    route_gbps = rows_per_step * payload / step_ms / 1e6
+    return {"metric": "sampled+gathered events/sec", "value": world * n_roots * K / (ms / 1e3), "unit": "events/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+            "config": {"workload": "8xB200 distributed TGN data path (BASELINE configs[3]): planted-community graph, one partition "
+                                   "per rank, recent-10, memory dim 100, 4,000 events per rank and step, owner -> replica route of "
+                                   "memory rows and mails with plans built on the device every step",
+                       "graph": f"{world * n_per} nodes, {world * e_per} events, {int(P_INTRA * 100)} % intra-partition, both "
+                                "directions of an event sampled, int64 ids, ts U[0,1e7)",
+                       "events_per_rank_and_step": EVENTS, "event": "one root query (4,000 interactions = 12,000 of them: source, "
+                                                                     "destination, negative destination)",
+                       "policy": f"recent-{FANOUT}, 1 hop", "memory_row": f"{MEM_DIM} x fp32 + ts", "mail_row": f"{MAIL_DIM} x fp32 + ts",
+                       "l2": "node tables (0.1-1 GB memory, 0.5-2.7 GB mails) and the 25 M-edge adjacency exceed L2; 64 distinct batches",
+                       "parallelism": f"{world} partitions, one process per GPU; peer-memory route, device-built plans",
+                       "timing": f"median of {reps} repeats of the K-step region (CUDA events, max over ranks)"},
+            "interactions_per_s": world * EVENTS * K / (ms / 1e3),
+            "e2e": {"value": world * n_roots * K / (e2e_ms / 1e3), "unit": "events/s", "h2d_bytes_per_step": 16 * n_roots,
+                    "d2h_bytes_per_step": d2h[0],
+                    "note": "per step: roots and query times from host memory (staged through a pinned buffer), the step with its "
+                            "route, the block structure (offsets, neighbour ids, timestamps, edge ids, dt) to pinned host memory; "
+                            "wall clock around the K-step loop and a device synchronisation, max over ranks"},
+            "same_workload_one_partition": {"ms_per_step": local_step_ms, "events_per_s_per_gpu": n_roots / local_step_ms * 1e3,
+                                            "weak_scaling_efficiency_vs_it": local_step_ms / step_ms,
+                                            "note": "the same step on one partition without the exchange, measured in this run; "
+                                                    "the N = 1 line of this benchmark is a different workload (sampler microbenchmark)"},
+            "host_issue_ms_per_step": t_issue * 1e3 / K,
+            "route": {"rows_per_rank_and_step": rows_per_step, "replicas_per_owned_node_max": part.max_rep,
+                      "payload_bytes_per_rank_and_step": rows_per_step * payload, "wire_bytes_per_rank_and_step": rows_per_step * wire,
+                      "GBps_per_direction_over_the_step": route_gbps, "frac_of_900": route_gbps / 900, "frac_of_770_measured_peer_copy": route_gbps / 770,
+                      "note": "bytes a rank pushes per step / step time: a lower bound of the link rate while the route runs "
+                              "(the step also samples, gathers and plans)"},
+            "e2e_check": {"routed_state_equals_expectation_on_every_rank": True, "rows_written_on_rank0": written,
+                          "steps_checked": n_done[0]},
+            "roofline": {"bound": "hbm", "kernel": "gather_rows (node memory + mails through the slot map)", "unit": "GB/s",
+                         "bytes_per_step": gather_bytes, "achieved_over_the_step": gather_bytes / local_step_ms / 1e6, "peak": peak,
+                         "frac": gather_bytes / local_step_ms / 1e6 / peak, "peak_source": peak_kind,
+                         "note": "algorithmic gather bytes of a step over the whole one-partition step time (sampling, relabel, "
+                                 "plan included): a lower bound for the gather kernels"},
+            "gpu_launches": (None if step.kernel_launches is None else (step.kernel_launches + 4) * K * reps),
+            "kernel_launches_per_step": (None if step.kernel_launches is None else step.kernel_launches + 4),
+            "edges_per_step": edges, "clocks": clk}

@@ -48,7 +48,7 @@ extern "C" {
 
 #define SGL_POLICY_RECENT 0
 #define SGL_POLICY_UNIFORM 1
-#define SGL_MAX_UNIFORM_FANOUT 32
+#define SGL_MAX_UNIFORM_FANOUT 512   /* picks of a target are kept in shared memory: 8 warps x 512 x 8 bytes per CTA */
 
 const char* sgl_last_error(void);
 /* Library version and the SM architecture the kernels were compiled for ("sm_100a"). */
@@ -165,15 +165,17 @@ int sgl_unique_pairs(const int64_t* a_id, const int64_t* a_ts, int64_t n_a, cons
  * CSC of one sampled hop: stable order by (dst_local, ts); indptr over the num_dst rows of the
  * previous node list.  dst_map (optional): dst_local = dst_map[dst[e]] (the previous hop's inverse map),
  * else dst_local = dst[e].  num_dst may be overridden by the device count d_num_dst (indptr is then
- * written for d_num_dst+1 entries; capacity num_dst+1).
+ * written for d_num_dst+1 entries; capacity num_dst+1).  presorted != 0 (dst_map must be NULL): the edges already are
+ * in (dst, ts) order -- the first hop of a batch, whose target i is row i of the list -- and the sort is skipped
+ * (the order is checked: a violation raises SGL_DEV_BAD_INDEX).
  * Replaces: _build_csc_from_pairs (prepare_sample.py:215-229).
  * ---------------------------------------------------------------------------------------------- */
 size_t sgl_build_csc_ws_bytes(int64_t n_edges, int64_t num_dst);
 int sgl_build_csc(const int64_t* src_local, const int64_t* dst, const int64_t* dst_map, const int64_t* ts,
                   const float* dt, const int64_t* eid, int64_t n_edges, const int64_t* d_n_edges, int64_t num_dst,
                   const int64_t* d_num_dst, int dst_bits, int ts_bits, int64_t ts_base, int64_t* out_indptr,
-                  int64_t* out_indices, int64_t* out_ts, float* out_dt, int64_t* out_eid, int32_t* d_status,
-                  void* ws, size_t ws_bytes, void* stream);
+                  int64_t* out_indices, int64_t* out_ts, float* out_dt, int64_t* out_eid, int presorted,
+                  int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Node-level relabel of one id list against an epoch table.  mapper[num_nodes] and mask[num_nodes]

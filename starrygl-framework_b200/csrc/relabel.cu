@@ -106,6 +106,35 @@ csc_emit_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ 
   }
 }
 
+// The same for edges that already are in (dst, ts) order -- the first hop of a batch, whose targets are the layer list
+// itself: target i is row i, and a target's samples come out in ascending time.  No sort: a copy plus the row pointer.
+__global__ void __launch_bounds__(kThreads)
+csc_emit_sorted_kernel(const int64_t* __restrict__ dst, int64_t n_cap, const int64_t* d_n, int64_t num_dst_cap,
+                       const int64_t* d_num_dst, const int64_t* __restrict__ src_local, const int64_t* __restrict__ ts,
+                       const float* __restrict__ dt, const int64_t* __restrict__ eid, int64_t* __restrict__ indptr,
+                       int64_t* __restrict__ out_indices, int64_t* __restrict__ out_ts, float* __restrict__ out_dt,
+                       int64_t* __restrict__ out_eid, int32_t* d_status) {
+  const int64_t n = eff_count(n_cap, d_n);
+  const int64_t num_dst = eff_count(num_dst_cap, d_num_dst);
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  if (n == 0) {
+    for (int64_t v = (int64_t)blockIdx.x * kThreads + threadIdx.x; v <= num_dst; v += stride) indptr[v] = 0;
+    return;
+  }
+  for (int64_t j = (int64_t)blockIdx.x * kThreads + threadIdx.x; j < n; j += stride) {
+    out_indices[j] = src_local[j];
+    out_ts[j] = ts[j];
+    out_dt[j] = dt[j];
+    out_eid[j] = eid[j];
+    const int64_t d = dst[j];
+    const int64_t prev = j == 0 ? -1 : dst[j - 1];
+    if (d < prev || d < 0 || (d == prev && ts[j] < ts[j - 1])) dev_flag(d_status, SGL_DEV_BAD_INDEX);   // not in (dst, ts) order
+    for (int64_t v = prev + 1; v <= d && v <= num_dst; ++v) indptr[v] = j;
+    if (j == n - 1)
+      for (int64_t v = d + 1; v <= num_dst; ++v) indptr[v] = n;
+  }
+}
+
 // ---- node-level relabel ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 nodes_pack_kernel(const int64_t* __restrict__ ids, int64_t n_cap, const int64_t* d_n, int64_t num_nodes,
@@ -311,9 +340,21 @@ extern "C" int sgl_build_csc(const int64_t* src_local, const int64_t* dst, const
                              const float* dt, const int64_t* eid, int64_t n_edges, const int64_t* d_n_edges,
                              int64_t num_dst, const int64_t* d_num_dst, int dst_bits, int ts_bits, int64_t ts_base,
                              int64_t* out_indptr, int64_t* out_indices, int64_t* out_ts, float* out_dt, int64_t* out_eid,
-                             int32_t* d_status, void* ws, size_t ws_bytes, void* stream_) {
+                             int presorted, int32_t* d_status, void* ws, size_t ws_bytes, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n_edges >= 0 && num_dst >= 0, SGL_ERR_ARG, "build_csc: negative size");
+  if (presorted) {
+    SGL_REQUIRE(dst_map == nullptr, SGL_ERR_ARG, "build_csc: presorted input cannot go through a dst_map");
+    SGL_REQUIRE(out_indptr, SGL_ERR_ARG, "build_csc: out_indptr is null");
+    SGL_REQUIRE(n_edges == 0 || (src_local && dst && ts && dt && eid && out_indices && out_ts && out_dt && out_eid), SGL_ERR_ARG,
+                "build_csc: null array");
+    const int64_t work_s = n_edges > num_dst + 1 ? n_edges : num_dst + 1;
+    csc_emit_sorted_kernel<<<stream_grid(work_s, kThreads, 16), kThreads, 0, stream>>>(
+        dst, n_edges, d_n_edges, num_dst, d_num_dst, src_local, ts, dt, eid, out_indptr, out_indices, out_ts, out_dt, out_eid,
+        d_status);
+    SGL_LAUNCH_CHECK();
+    return SGL_OK;
+  }
   SGL_REQUIRE(dst_bits >= 0 && ts_bits >= 0 && dst_bits + ts_bits <= 64, SGL_ERR_UNSUPPORTED,
               "build_csc: dst_bits %d + ts_bits %d exceed the 64-bit sort key", dst_bits, ts_bits);
   SGL_REQUIRE(out_indptr, SGL_ERR_ARG, "build_csc: out_indptr is null");

@@ -179,7 +179,41 @@ sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ 
     const int64_t t = target_ts[i];
     const int64_t off = s_off[slot];
     const int64_t cand = cut - lo;
-    if (policy == SGL_POLICY_UNIFORM && cand > fanout) {
+    if (policy == SGL_POLICY_UNIFORM && cand > fanout && fanout > 32) {
+      // more draws than lanes: the same selection, with the picks of the target kept in this warp's shared memory
+      extern __shared__ uint64_t s_picks_all[];
+      uint64_t* picks = s_picks_all + (size_t)warp * fanout;
+      for (int d = lane; d < fanout; d += 32) {
+        Philox ph((uint32_t)i, (uint32_t)((uint64_t)i >> 32), (uint32_t)d, rng_stream, (uint32_t)seed, (uint32_t)(seed >> 32));
+        const uint64_t u = (uint64_t)ph.c[0] | ((uint64_t)ph.c[1] << 32);
+        picks[d] = u % (uint64_t)(cand - fanout + d + 1);
+      }
+      __syncwarp();
+      for (int d = 1; d < fanout; ++d) {          // draw d against the (final) draws before it
+        const uint64_t mine = picks[d];
+        bool clash = false;
+        for (int q = lane; q < d; q += 32) clash |= picks[q] == mine;
+        clash = __any_sync(0xffffffffu, clash);
+        __syncwarp();
+        if (clash && lane == 0) picks[d] = (uint64_t)(cand - fanout + d);
+        __syncwarp();
+      }
+      for (int d = lane; d < fanout; d += 32) {   // rank ascending, then copy
+        const uint64_t pick = picks[d];
+        int rank = 0;
+        for (int q = 0; q < fanout; ++q) rank += picks[q] < pick ? 1 : 0;
+        const int64_t p = lo + (int64_t)pick;
+        const int64_t o = off + rank;
+        const int64_t ets = __ldg(ts + p);
+        out_nbr[o] = __ldg(nbr + p);
+        out_eid[o] = __ldg(eid + p);
+        out_ts[o] = keep_root_time ? t : ets;
+        out_dt[o] = (float)(t - ets);
+        if (out_dt_i64) out_dt_i64[o] = ets - t;
+        out_dst[o] = i;
+      }
+      __syncwarp();
+    } else if (policy == SGL_POLICY_UNIFORM && cand > fanout) {
       // Floyd's subset selection: draw j picks t_j uniform in [0, cand-k+j]; a repeat is replaced by cand-k+j
       uint64_t pick = 0;
       if (lane < fanout) {
@@ -259,7 +293,8 @@ static void launch_sample(int64_t ctas, cudaStream_t stream, const int64_t* indp
                                                                        n_targets, d_n, fanout, equal_root_time,
                                                                        allowed_offset, win_lo, win_cut, cnt, cta_sums, done,
                                                                        out_offsets, d_status);
-  sample_fill_kernel<TPW><<<(unsigned)ctas, kCtaThreads, 0, stream>>>(nbr, ts, eid, target_ts, n_targets, d_n, fanout,
+  const size_t pick_smem = (policy == SGL_POLICY_UNIFORM && fanout > 32) ? (size_t)kWarpsPerCta * fanout * sizeof(uint64_t) : 0;
+  sample_fill_kernel<TPW><<<(unsigned)ctas, kCtaThreads, pick_smem, stream>>>(nbr, ts, eid, target_ts, n_targets, d_n, fanout,
                                                                       policy, keep_root_time, seed, rng_stream, win_lo,
                                                                       win_cut, cnt, cta_sums, out_nbr, out_dst, out_ts,
                                                                       out_dt, out_dt_i64, out_eid, out_offsets);

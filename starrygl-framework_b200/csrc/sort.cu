@@ -211,6 +211,337 @@ sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Mini-batch sizes (up to kSmallMaxKeys keys): ONE kernel per pass, up to 11 bits per pass.
+//
+// The relabel sorts of a mini-batch are a few hundred thousand keys of 40-odd bits.  At that size the three-kernel pass
+// above is bound by its launches, so the pass is restructured around what is cheap for few tiles:
+//
+//   small_hist_kernel   one read of the keys: the digit totals of EVERY pass (shared-memory histograms flushed with
+//                       global atomics) and the per-tile histogram of the first pass.
+//   small_pass_kernel   tile t finds where its keys of digit d start by itself: digit starts from an in-kernel scan of
+//                       the pass's totals, plus the counts of the tiles before it read straight from the per-tile
+//                       histogram (with <= 64 tiles that read is cheaper than a scan kernel and its launch).  While it
+//                       writes its keys to their sorted places it adds them to the NEXT pass's per-tile histogram
+//                       (the tile a key lands in is known from its destination), so no pass needs a histogram kernel.
+//   small_single_kernel up to one tile (8,192 keys): all passes inside one CTA, the tile never leaves shared memory.
+//
+// Tiles are 8,192 keys (512 threads x 16); ranks inside a tile are stable: a warp owns 512 consecutive keys, counts them
+// per digit in its own 16-bit counters (one lane per digit and round updates a counter, so no atomics), and a key's
+// rank = keys of its digit in earlier warps + in its warp's earlier rounds + in lower lanes of its round.
+// Nothing waits on another CTA: the dependencies between passes are kernel boundaries.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kSmallThreads = 512;
+constexpr int kSmallWarps = kSmallThreads / 32;
+constexpr int kSmallItems = 16;
+constexpr int kSmallTile = kSmallThreads * kSmallItems;   // 8,192 keys
+constexpr int kSmallMaxBits = 11;
+constexpr int kSmallRadix = 1 << kSmallMaxBits;           // 2,048 digits at most
+constexpr int kSmallDpt = kSmallRadix / kSmallThreads;    // digits per thread in the per-digit phases
+constexpr int kSmallMaxTiles = 64;
+constexpr int64_t kSmallMaxKeys = (int64_t)kSmallTile * kSmallMaxTiles;
+constexpr int kSmallMaxPasses = 6;
+
+struct SmallSmem {
+  uint64_t keys[kSmallTile];                       // the tile in digit order
+  uint32_t vals[kSmallTile];
+  unsigned short warp_cnt[kSmallWarps][kSmallRadix];   // per-warp digit counts, then start of the warp's keys of a digit
+  uint32_t glob_base[kSmallRadix];                 // global position of the tile's first key of a digit
+  unsigned short tile_start[kSmallRadix];          // position of the digit's run inside the tile
+  uint32_t scan_tmp[kSmallWarps];
+};
+
+__device__ __forceinline__ uint32_t small_cta_scan(uint32_t v, uint32_t* tmp, uint32_t* total) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  __syncthreads();
+  if (lane == 31) tmp[warp] = x;
+  __syncthreads();
+  uint32_t woff = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < kSmallWarps; ++w) {
+    const uint32_t t = tmp[w];
+    if (w < warp) woff += t;
+    tot += t;
+  }
+  if (total) *total = tot;
+  return woff + x - v;
+}
+
+// Ranks the tile's keys (held in registers, item c of a thread = tile position warp*512 + c*32 + lane; invalid items
+// have valid bit clear) on `digit` and lays keys and payloads out in digit order in shared memory.  On return
+// sm.tile_start[d] is the start of digit d's run; the per-digit counts of the tile are returned through cnt_out
+// (kSmallDpt digits per thread, digit = threadIdx.x * kSmallDpt + q).
+__device__ __forceinline__ void small_rank_tile(SmallSmem& sm, const uint64_t (&k)[kSmallItems], const uint32_t (&v)[kSmallItems],
+                                                uint32_t valid_mask, int shift, uint32_t mask, uint32_t (&cnt_out)[kSmallDpt]) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int d0 = threadIdx.x * kSmallDpt;
+#pragma unroll
+  for (int w = 0; w < kSmallWarps; ++w)
+#pragma unroll
+    for (int q = 0; q < kSmallDpt; ++q) sm.warp_cnt[w][d0 + q] = 0;
+  __syncthreads();
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  unsigned short rk[kSmallItems];
+#pragma unroll
+  for (int c = 0; c < kSmallItems; ++c) {
+    const bool valid = (valid_mask >> c) & 1u;
+    const uint32_t d = valid ? ((uint32_t)(k[c] >> shift) & mask) : 0xFFFFFFFFu;
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    const uint32_t r = __popc(peers & lt_mask);
+    unsigned short base = 0;
+    if (valid) base = sm.warp_cnt[warp][d];
+    __syncwarp();
+    if (valid && r == 0) sm.warp_cnt[warp][d] = (unsigned short)(base + __popc(peers));
+    __syncwarp();
+    rk[c] = (unsigned short)(base + r);
+  }
+  __syncthreads();
+  // per digit: counts of the warps -> start of every warp's keys of the digit (digit-major, then warp order)
+  uint32_t sum = 0;
+#pragma unroll
+  for (int q = 0; q < kSmallDpt; ++q) {
+    uint32_t run = 0;
+#pragma unroll
+    for (int w = 0; w < kSmallWarps; ++w) {
+      const uint32_t c = sm.warp_cnt[w][d0 + q];
+      sm.warp_cnt[w][d0 + q] = (unsigned short)run;
+      run += c;
+    }
+    cnt_out[q] = run;
+    sum += run;
+  }
+  uint32_t start = small_cta_scan(sum, sm.scan_tmp, nullptr);
+#pragma unroll
+  for (int q = 0; q < kSmallDpt; ++q) {
+    sm.tile_start[d0 + q] = (unsigned short)start;
+#pragma unroll
+    for (int w = 0; w < kSmallWarps; ++w) sm.warp_cnt[w][d0 + q] = (unsigned short)(sm.warp_cnt[w][d0 + q] + start);
+    start += cnt_out[q];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int c = 0; c < kSmallItems; ++c) {
+    if ((valid_mask >> c) & 1u) {
+      const uint32_t d = (uint32_t)(k[c] >> shift) & mask;
+      const uint32_t pos = (uint32_t)sm.warp_cnt[warp][d] + rk[c];
+      sm.keys[pos] = k[c];
+      sm.vals[pos] = v[c];
+    }
+  }
+  __syncthreads();
+}
+
+// ghist[pass][digit] += digit totals of this tile for every pass; hist0[digit][tile] = first-pass histogram of the tile
+__global__ void __launch_bounds__(kSmallThreads)
+small_hist_kernel(const uint64_t* __restrict__ keys, int64_t n_cap, const int64_t* d_n, int passes, int bits,
+                  uint32_t* __restrict__ ghist, uint32_t* __restrict__ hist0, int num_tiles) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint32_t* h = (uint32_t*)smem_raw;   // [passes][kSmallRadix]
+  const int64_t n = eff_count(n_cap, d_n);
+  const int64_t tile_base = (int64_t)blockIdx.x * kSmallTile;
+  if (tile_base >= n) return;
+  const uint32_t mask = (1u << bits) - 1u;
+  const int radix = 1 << bits;
+  for (int j = threadIdx.x; j < passes * kSmallRadix; j += kSmallThreads) h[j] = 0;
+  __syncthreads();
+#pragma unroll 4
+  for (int c = 0; c < kSmallItems; ++c) {
+    const int64_t i = tile_base + (int64_t)c * kSmallThreads + threadIdx.x;
+    if (i < n) {
+      const uint64_t key = keys[i];
+      for (int p = 0; p < passes; ++p) atomicAdd(&h[p * kSmallRadix + ((uint32_t)(key >> (p * bits)) & mask)], 1u);
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < passes * kSmallRadix; j += kSmallThreads) {
+    const int p = j / kSmallRadix, d = j - p * kSmallRadix;
+    if (d >= radix) continue;
+    const uint32_t c = h[j];
+    if (c) atomicAdd(&ghist[p * kSmallRadix + d], c);
+    if (p == 0) hist0[(size_t)d * num_tiles + blockIdx.x] = c;
+  }
+}
+
+__global__ void __launch_bounds__(kSmallThreads, 1)
+small_pass_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ vals, int64_t n_cap, const int64_t* d_n,
+                  int shift, int bits, const uint32_t* __restrict__ ghist_p, const uint32_t* __restrict__ hist_p,
+                  uint32_t* __restrict__ hist_next, int next_shift, int num_tiles, uint64_t* __restrict__ out_keys,
+                  uint32_t* __restrict__ out_vals) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  SmallSmem& sm = *(SmallSmem*)smem_raw;
+  const int64_t n = eff_count(n_cap, d_n);
+  const int tile = blockIdx.x;
+  const int64_t tile_base = (int64_t)tile * kSmallTile;
+  if (tile_base >= n) return;
+  const int tile_n = (int)(n - tile_base < kSmallTile ? n - tile_base : kSmallTile);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t mask = (1u << bits) - 1u;
+  const int radix = 1 << bits;
+  const int d0 = threadIdx.x * kSmallDpt;
+
+  // the tile's keys: issued first so that the loads are in flight while the digit bases are computed
+  uint64_t k[kSmallItems];
+  uint32_t v[kSmallItems];
+  uint32_t valid_mask = 0;
+  const int64_t base = tile_base + (int64_t)warp * (kSmallItems * 32) + lane;
+#pragma unroll
+  for (int c = 0; c < kSmallItems; ++c) {
+    const int64_t i = base + c * 32;
+    const bool ok = i < n;
+    k[c] = ok ? keys[i] : 0;
+    v[c] = ok ? (vals ? vals[i] : (uint32_t)i) : 0u;
+    valid_mask |= (ok ? 1u : 0u) << c;
+  }
+  // global start of every digit: exclusive scan of the pass's totals
+  {
+    uint32_t t[kSmallDpt], sum = 0;
+#pragma unroll
+    for (int q = 0; q < kSmallDpt; ++q) {
+      t[q] = (d0 + q < radix) ? ghist_p[d0 + q] : 0u;
+      sum += t[q];
+    }
+    uint32_t start = small_cta_scan(sum, sm.scan_tmp, nullptr);
+#pragma unroll
+    for (int q = 0; q < kSmallDpt; ++q) {
+      sm.glob_base[d0 + q] = start;
+      start += t[q];
+    }
+  }
+  __syncthreads();
+  // + the keys of the digit in the tiles before this one: a warp sums one digit's row of the per-tile histogram
+  for (int d = warp; d < radix; d += kSmallWarps) {
+    const uint32_t* row = hist_p + (size_t)d * num_tiles;
+    uint32_t s = 0;
+    for (int t = lane; t < tile; t += 32) s += row[t];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) sm.glob_base[d] += s;
+  }
+  uint32_t cnt[kSmallDpt];
+  small_rank_tile(sm, k, v, valid_mask, shift, mask, cnt);   // (starts with a barrier: glob_base is complete after it)
+  // write-out: consecutive threads take consecutive tile positions, i.e. runs of one digit -> consecutive addresses
+  const uint32_t next_mask = mask;
+  for (int j = threadIdx.x; j < tile_n; j += kSmallThreads) {
+    const uint64_t key = sm.keys[j];
+    const uint32_t d = (uint32_t)(key >> shift) & mask;
+    const uint32_t g = sm.glob_base[d] + ((uint32_t)j - sm.tile_start[d]);
+    out_keys[g] = key;
+    out_vals[g] = sm.vals[j];
+    if (hist_next) atomicAdd(&hist_next[(size_t)((uint32_t)(key >> next_shift) & next_mask) * num_tiles + g / kSmallTile], 1u);
+  }
+}
+
+// n <= one tile: every pass inside the CTA; (keys, vals) are read once and written once
+__global__ void __launch_bounds__(kSmallThreads, 1)
+small_single_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ vals, int64_t n_cap, const int64_t* d_n,
+                    int passes, int bits, uint64_t* __restrict__ out_keys, uint32_t* __restrict__ out_vals) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  SmallSmem& sm = *(SmallSmem*)smem_raw;
+  int64_t n = eff_count(n_cap, d_n);
+  if (n > kSmallTile) n = kSmallTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t mask = (1u << bits) - 1u;
+  uint64_t k[kSmallItems];
+  uint32_t v[kSmallItems];
+  uint32_t valid_mask = 0;
+  const int pos0 = warp * (kSmallItems * 32) + lane;
+#pragma unroll
+  for (int c = 0; c < kSmallItems; ++c) {
+    const int i = pos0 + c * 32;
+    const bool ok = i < n;
+    k[c] = ok ? keys[i] : 0;
+    v[c] = ok ? (vals ? vals[i] : (uint32_t)i) : 0u;
+    valid_mask |= (ok ? 1u : 0u) << c;
+  }
+  uint32_t cnt[kSmallDpt];
+  for (int p = 0; p < passes; ++p) {
+    small_rank_tile(sm, k, v, valid_mask, p * bits, mask, cnt);
+    if (p + 1 < passes) {
+#pragma unroll
+      for (int c = 0; c < kSmallItems; ++c) {
+        const int i = pos0 + c * 32;
+        if (i < n) {
+          k[c] = sm.keys[i];
+          v[c] = sm.vals[i];
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int j = threadIdx.x; j < n; j += kSmallThreads) {
+    out_keys[j] = sm.keys[j];
+    out_vals[j] = sm.vals[j];
+  }
+}
+
+inline size_t small_ws_bytes() {
+  return align_up((size_t)kSmallMaxPasses * kSmallRadix * 4) + align_up((size_t)kSmallMaxPasses * kSmallRadix * kSmallMaxTiles * 4);
+}
+
+// passes and bits per pass for a key width (balanced: 44 bits -> 4 x 11, 40 bits -> 4 x 10)
+inline void small_plan(int num_bits, bool iota_vals, int* passes, int* bits) {
+  int p = (num_bits + kSmallMaxBits - 1) / kSmallMaxBits;
+  if (p == 0 && iota_vals) p = 1;   // still has to materialise the payload
+  *passes = p;
+  *bits = p ? (num_bits + p - 1) / p : 0;
+  if (*bits < 1) *bits = 1;
+}
+
+int run_small(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_t* vals_alt, int64_t n, const int64_t* d_n,
+              int num_bits, bool iota_vals, int* result_in_alt, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  int passes, bits;
+  small_plan(num_bits, iota_vals, &passes, &bits);
+  *result_in_alt = 0;
+  if (passes == 0) return SGL_OK;
+  static int attr_dev = -1;   // the attribute is per device function and context: set it once per process and device
+  int dev = 0;
+  SGL_CUDA_CHECK(cudaGetDevice(&dev));
+  if (attr_dev != dev) {
+    SGL_CUDA_CHECK(cudaFuncSetAttribute(small_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmallSmem)));
+    SGL_CUDA_CHECK(cudaFuncSetAttribute(small_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SmallSmem)));
+    SGL_CUDA_CHECK(cudaFuncSetAttribute(small_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kSmallMaxPasses * kSmallRadix * 4));
+    attr_dev = dev;
+  }
+  if (n <= kSmallTile) {
+    small_single_kernel<<<1, kSmallThreads, sizeof(SmallSmem), stream>>>(keys, iota_vals ? nullptr : vals, n, d_n, passes, bits,
+                                                                         keys_alt, vals_alt);
+    SGL_LAUNCH_CHECK();
+    *result_in_alt = 1;
+    return SGL_OK;
+  }
+  const int num_tiles = (int)((n + kSmallTile - 1) / kSmallTile);
+  WsCarver c(ws, ws_bytes);
+  uint32_t* ghist = c.take<uint32_t>((size_t)kSmallMaxPasses * kSmallRadix);
+  uint32_t* hist = c.take<uint32_t>((size_t)kSmallMaxPasses * kSmallRadix * kSmallMaxTiles);
+  SGL_REQUIRE(c.ok(), SGL_ERR_WORKSPACE, "radix sort: workspace %zu < %zu bytes", ws_bytes, small_ws_bytes());
+  // per-pass histogram p lives at hist + p * kSmallRadix * num_tiles (packed for the actual tile count: one memset)
+  const size_t per_pass = (size_t)kSmallRadix * num_tiles;
+  SGL_CUDA_CHECK(cudaMemsetAsync(ghist, 0, (size_t)passes * kSmallRadix * 4, stream));
+  SGL_CUDA_CHECK(cudaMemsetAsync(hist, 0, (size_t)passes * per_pass * 4, stream));
+  small_hist_kernel<<<num_tiles, kSmallThreads, (size_t)passes * kSmallRadix * 4, stream>>>(keys, n, d_n, passes, bits, ghist, hist,
+                                                                                          num_tiles);
+  uint64_t *kin = keys, *kout = keys_alt;
+  uint32_t *vin = vals, *vout = vals_alt;
+  for (int p = 0; p < passes; ++p) {
+    uint32_t* next = p + 1 < passes ? hist + (size_t)(p + 1) * per_pass : nullptr;
+    small_pass_kernel<<<num_tiles, kSmallThreads, sizeof(SmallSmem), stream>>>(
+        kin, (p == 0 && iota_vals) ? nullptr : vin, n, d_n, p * bits, bits, ghist + (size_t)p * kSmallRadix,
+        hist + (size_t)p * per_pass, next, (p + 1) * bits, num_tiles, kout, vout);
+    uint64_t* tk = kin; kin = kout; kout = tk;
+    uint32_t* tv = vin; vin = vout; vout = tv;
+  }
+  SGL_LAUNCH_CHECK();
+  *result_in_alt = passes & 1;
+  return SGL_OK;
+}
+
 template <int BITS>
 int run_passes(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_t* vals_alt, int64_t n, const int64_t* d_n,
                int passes, bool iota_vals, uint32_t* block_hist, uint32_t* digit_total, int num_blocks, cudaStream_t stream) {
@@ -242,7 +573,9 @@ int run_passes(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_t* val
 size_t radix_sort_ws_bytes(int64_t n) {
   int64_t nb = (n + kSortTile - 1) / kSortTile;
   if (nb < 1) nb = 1;
-  return align_up((size_t)nb * kMaxRadix * sizeof(uint32_t)) + align_up(kMaxRadix * sizeof(uint32_t));
+  const size_t big = align_up((size_t)nb * kMaxRadix * sizeof(uint32_t)) + align_up(kMaxRadix * sizeof(uint32_t));
+  const size_t small = n <= kSmallMaxKeys ? small_ws_bytes() : 0;
+  return big > small ? big : small;
 }
 
 int radix_sort_pairs(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_t* vals_alt, int64_t n,
@@ -253,6 +586,7 @@ int radix_sort_pairs(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_
   *result_in_alt = 0;
   if (n == 0) return SGL_OK;
   SGL_REQUIRE(keys && vals && keys_alt && vals_alt, SGL_ERR_ARG, "radix sort: null buffer");
+  if (n <= kSmallMaxKeys) return run_small(keys, vals, keys_alt, vals_alt, n, d_n, num_bits, iota_vals, result_in_alt, ws, ws_bytes, stream);
   const int num_blocks = (int)((n + kSortTile - 1) / kSortTile);
   WsCarver c(ws, ws_bytes);
   uint32_t* block_hist = c.take<uint32_t>((size_t)num_blocks * kMaxRadix);

@@ -44,7 +44,7 @@ _SIGNATURES = {
                                 _vp, _sz, _vp]),
     "sgl_build_csc_ws_bytes": (_sz, [_i64, _i64]),
     "sgl_build_csc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp,
-                             _vp, _vp, _sz, _vp]),
+                             _i32, _vp, _vp, _sz, _vp]),
     "sgl_relabel_nodes_ws_bytes": (_sz, [_i64]),
     "sgl_relabel_nodes": (_i32, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "sgl_gather_rows": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _i32, _vp, _vp]),

@@ -95,7 +95,8 @@ def build_batch_async(g: ops.TCSR, roots: torch.Tensor, root_ts: torch.Tensor, f
                                                              d_n_b=hop.d_total, status=status)
         indptr, idx, e_ts, e_dt, e_eid = ops.build_csc(nxt_inv, hop.dst, last_inv, hop.ts, hop.dt, hop.eid, cap_cur,
                                                        dst_bits=ops.bits_for(cap_cur), ts_bits=ts_bits, ts_base=ts_base,
-                                                       d_n_edges=hop.d_total, d_num_dst=d_cur, status=status)
+                                                       d_n_edges=hop.d_total, d_num_dst=d_cur, presorted=last_inv is None,
+                                                       status=status)
         layers.append({"indptr": indptr, "indices": idx, "eid": e_eid, "edge_ts": e_ts, "edge_dt": e_dt,
                        "gids": nxt_id, "ts": nxt_ts, "raw_nbr": hop.nbr, "raw_ts": hop.ts, "inv": nxt_inv, "hop": hop})
         counts += [hop.d_total, d_nxt]
@@ -109,6 +110,24 @@ def build_batch_async(g: ops.TCSR, roots: torch.Tensor, root_ts: torch.Tensor, f
 def build_batch(g, roots, root_ts, fanouts, policy="recent", **kw) -> List[dict]:
     """Synchronous form of :func:`build_batch_async`."""
     return build_batch_async(g, roots, root_ts, fanouts, policy, **kw).finish()
+
+
+def count_kernel_nodes(graph: "torch.cuda.CUDAGraph"):
+    """Number of this library's kernel nodes in a captured graph, read from the runtime's own dump of it (the graph must
+    have been created with ``enable_debug_mode()`` before the capture); None when the dump cannot be read."""
+    import os
+    import re
+    import tempfile
+    path = os.path.join(tempfile.gettempdir(), f"sgl_graph_{os.getpid()}_{id(graph)}.dot")
+    try:
+        graph.debug_dump(path)
+        with open(path) as f:
+            text = f.read()
+        os.remove(path)
+    except Exception:
+        return None
+    n = len(re.findall(r'label="[^"]*(?:sgl|_ZN3sgl)[^"]*"', text))
+    return n or None
 
 
 class BatchGraph:
@@ -140,11 +159,13 @@ class BatchGraph:
                 build_batch_async(g, self.roots, self.root_ts, fanouts, policy, **kw)     # warm-up: sizes the scratch
             self.stream.synchronize()
             self.graph = torch.cuda.CUDAGraph()
+            self.graph.enable_debug_mode()      # keeps the captured graph so that its nodes can be counted below
             with torch.cuda.graph(self.graph, stream=self.stream):
                 self.batch = build_batch_async(g, self.roots, self.root_ts, fanouts, policy, **kw)
         finally:
             _C.WORKSPACE = saved
         self.stream.synchronize()
+        self.kernel_launches = count_kernel_nodes(self.graph)
 
     def run(self, roots: torch.Tensor, root_ts: torch.Tensor) -> DeviceBatch:
         """Enqueue one batch (exactly ``num_roots`` roots, already on the GPU); returns the un-trimmed device batch,

@@ -257,6 +257,20 @@ class SampleGatherPipeline:
                 gather_events[1].record(self.stream)
         return n
 
+    def sample_only(self, roots: torch.Tensor, root_ts: torch.Tensor, rng_stream: int = 0):
+        """The hop without the feature gather (same buffers as :meth:`run_device`)."""
+        n = roots.numel()
+        if n > self.max_roots:
+            raise _C.SglError(f"batch of {n} roots exceeds max_roots={self.max_roots}")
+        L, g, a = self.L, self.g, self.args
+        rc = L.sgl_sample_layer(g.indptr.data_ptr(), g.nbr.data_ptr(), g.ts.data_ptr(), g.eid.data_ptr(), g.num_nodes,
+                                roots.data_ptr(), root_ts.data_ptr(), n, None, self.k, a["pol"], a["eq"], a["off"],
+                                a["keep"], a["seed"], rng_stream, self.nbr.data_ptr(), self.dst.data_ptr(),
+                                self.ts.data_ptr(), self.dt.data_ptr(), None, self.eid.data_ptr(),
+                                self.offsets.data_ptr(), self.status.ptr(), self.ws.data_ptr(), self.ws.numel(),
+                                self.stream.cuda_stream)
+        _C.check(rc)
+
     # ---- host inputs / host results --------------------------------------------------------------------
     def submit_host(self, h_roots: torch.Tensor, h_root_ts: torch.Tensor, rng_stream: int = 0):
         """Enqueue one batch whose roots and query times are in (pinned) host tensors: H2D copy, sampling, gather,

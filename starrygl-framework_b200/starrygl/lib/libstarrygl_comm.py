@@ -66,28 +66,72 @@ class NegativeRoot:
 
 class TemporalNeighbor:
     """One hop: query q owns ``neighbors[root_start_ptr[q]:root_end_ptr[q]]`` (``root_start_ptr`` is the full
-    exclusive prefix with one extra entry, ``root_end_ptr`` its shift by one)."""
+    exclusive prefix with one extra entry, ``root_end_ptr`` its shift by one).
 
-    def __init__(self, hop: ops.Hop):
-        n = hop.total()
-        self.root_start_ptr = hop.offsets
-        self.root_end_ptr = torch.cat([hop.offsets[1:], hop.offsets[-1:]])
-        self.neighbors = hop.nbr[:n]
-        self.neighbors_ts = hop.ts[:n]
-        self.neighbors_eid = hop.eid[:n]
-        self.neighbors_dt = hop.dt_i64[:n]
-        self.neighbor_num = n
+    The hop's arrays are produced at capacity with their length on the device, so building the object costs no
+    synchronisation.  Consumers that stay on the GPU use the capacity views (``hop``: ``nbr`` / ``ts`` / ``eid`` /
+    ``dt_i64`` / ``offsets`` and the device count ``hop.d_total``).  The attributes of the reference's type (trimmed
+    tensors, ``neighbor_num``) are cut to size on first use; all hops of a result are cut with ONE read-back of their
+    counts (``TemporalResult.materialize``)."""
+
+    def __init__(self, hop: ops.Hop, owner: "TemporalResult" = None, n_queries: Optional[int] = None):
+        self.hop = hop
+        self._owner = owner
+        self._n = None                  # number of sampled neighbours, once known on the host
+        self._nq = n_queries            # number of queries (None: known only once the previous hop has been cut)
+        self._neighbors_override = None
+
+    def _cut(self) -> int:
+        if self._n is None:
+            if self._owner is not None:
+                self._owner.materialize()
+            else:
+                self._n = self.hop.total()
+        return self._n
 
     @classmethod
     def from_arrays(cls, start_ptr, neighbors, neighbors_ts, neighbors_eid):
         """Layer given directly by its CSR arrays (``start_ptr`` with one extra entry)."""
-        self = cls.__new__(cls)
-        self.root_start_ptr = start_ptr
-        self.root_end_ptr = torch.cat([start_ptr[1:], start_ptr[-1:]])
-        self.neighbors, self.neighbors_ts, self.neighbors_eid = neighbors, neighbors_ts, neighbors_eid
-        self.neighbors_dt = torch.zeros_like(neighbors_ts)
-        self.neighbor_num = neighbors.numel()
+        hop = ops.Hop(neighbors, None, neighbors_ts, None, neighbors_eid, start_ptr, neighbors.numel(), torch.zeros_like(neighbors_ts))
+        self = cls(hop, None, start_ptr.numel() - 1)
+        self._n = neighbors.numel()
         return self
+
+    @property
+    def neighbor_num(self) -> int:
+        return self._cut()
+
+    @property
+    def root_start_ptr(self):
+        self._cut()
+        return self.hop.offsets if self._nq is None else self.hop.offsets[:self._nq + 1]
+
+    @property
+    def root_end_ptr(self):
+        o = self.root_start_ptr
+        return torch.cat([o[1:], o[-1:]])
+
+    @property
+    def neighbors(self):
+        if self._neighbors_override is not None:
+            return self._neighbors_override[:self._cut()]
+        return self.hop.nbr[:self._cut()]
+
+    @neighbors.setter
+    def neighbors(self, value):
+        self._neighbors_override = value
+
+    @property
+    def neighbors_ts(self):
+        return self.hop.ts[:self._cut()]
+
+    @property
+    def neighbors_eid(self):
+        return self.hop.eid[:self._cut()]
+
+    @property
+    def neighbors_dt(self):
+        return self.hop.dt_i64[:self._cut()]
 
     @property
     def start_ptr(self):   # name used by the reference's block builder (starrygl/graph/graph.py:174)
@@ -102,11 +146,50 @@ class TemporalResult:
         self.roots = roots
         self.neg_roots = neg_roots
         self.neighbors_list: List[TemporalNeighbor] = []
-        self.nodes_remapper_id = _empty(roots.roots.device)
+        self._remap_pieces = []          # (new global ids at capacity, device count) per relabelled list
+        self._remapper = None
+        self._status = None              # device status word of the graph that produced the result
 
     @property
     def neighbors(self):
         return self.neighbors_list
+
+    def materialize(self):
+        """The one read-back of a result: the sizes of every hop (and of every piece of the id map) in a single copy."""
+        hops = [nb for nb in self.neighbors_list if nb._n is None]
+        counts = [nb.hop.d_total for nb in hops] + [d for _, d in self._remap_pieces]
+        if not counts:
+            return
+        if self._status is not None:     # the kernels' error bits ride along in the same copy
+            counts = counts + [self._status.t.to(torch.int64)]
+        host = torch.cat(counts).tolist()
+        if self._status is not None:
+            bits = int(host.pop())
+            if bits:
+                self._status.t.zero_()
+                raise _C.SglError(f"sampling: device status {bits} ({_C.decode_status(bits)})")
+        for nb, n in zip(hops, host):
+            nb._n = int(n)
+        prev = None
+        for nb in self.neighbors_list:      # queries of hop l+1 = neighbours of hop l
+            if nb._nq is None and prev is not None:
+                nb._nq = prev._n
+            prev = nb
+        if self._remap_pieces:
+            sizes = host[len(hops):]
+            dev = self.roots.roots.device
+            self._remapper = (torch.cat([ids[:int(c)] for (ids, _), c in zip(self._remap_pieces, sizes)])
+                              if sizes else _empty(dev))
+            self._remap_pieces = []
+
+    @property
+    def nodes_remapper_id(self):
+        if self._remapper is None:
+            if self._remap_pieces:
+                self.materialize()
+            else:
+                self._remapper = _empty(self.roots.roots.device)
+        return self._remapper
 
     def __repr__(self):
         return f"<TemporalResult with {len(self.neighbors_list)} neighbor layers>"
@@ -156,16 +239,16 @@ class CUDAGraph:
                 q_nodes = torch.cat([q_nodes, negative_root.roots])
                 q_ts = torch.cat([q_ts, negative_root.ts])
             out = TemporalResult(postive_root, negative_root)
-            tgt, tgt_ts, d_n = q_nodes.contiguous(), q_ts.contiguous(), None
+            out._status = self.status
+            tgt, tgt_ts, d_n, n_q = q_nodes.contiguous(), q_ts.contiguous(), None, q_nodes.numel()
             for l in range(int(layers)):
                 hop = ops.sample_layer(self.g, tgt, tgt_ts, int(k), sample_type, d_n=d_n,
                                        equal_root_time=bool(equal_root_time), allowed_offset=int(allowed_offset),
                                        keep_root_time=bool(keep_root_time), rng_stream=l, want_dt_i64=True,
                                        status=self.status)
-                nb = TemporalNeighbor(hop)     # reads the hop's size (one synchronisation per hop)
-                out.neighbors_list.append(nb)
-                tgt, tgt_ts, d_n = nb.neighbors, nb.neighbors_ts, None
-            self.status.check("sample_src_in_chunks_khop")
+                out.neighbors_list.append(TemporalNeighbor(hop, out, n_q))
+                # the next hop queries this hop's neighbours: arrays at capacity, their number stays on the device
+                tgt, tgt_ts, d_n, n_q = hop.nbr, hop.ts, hop.d_total, None
         return out
 
     def slice_by_chunk_ts(self, chunks, time_begin, time_end, using_full_timestamp=False, stream=0) -> "TemporalResult":
@@ -188,16 +271,14 @@ class CUDAGraph:
         """Node-level relabel: roots first, then every hop; local ids in ascending global id among the new ids."""
         if reset:
             self.relabel.reset()
-        pieces = []
+        pieces = result._remap_pieces
         loc, new_ids, d_new = self.relabel.insert(result.roots.roots, status=self.status)
         result.roots = TemporalRoot(loc, result.roots.ts_ptr, result.roots.ts, result.roots.q_ptr, result.roots.q_eid)
         pieces.append((new_ids, d_new))
-        for nb in result.neighbors_list:
-            loc, new_ids, d_new = self.relabel.insert(nb.neighbors, status=self.status)
+        for nb in result.neighbors_list:      # capacity arrays + device counts: no read-back between the hops
+            loc, new_ids, d_new = self.relabel.insert(nb.hop.nbr, d_n=nb.hop.d_total, status=self.status)
             nb.neighbors = loc
             pieces.append((new_ids, d_new))
-        counts = torch.cat([d for _, d in pieces]).tolist()
-        result.nodes_remapper_id = torch.cat([ids[:c] for (ids, _), c in zip(pieces, counts)])
 
     # ---- asynchronous queue ----------------------------------------------------------------------------------
     def submit_query(self, time_start, time_end, chunk_list, test_generate_samples, test_generate_samples_ts,

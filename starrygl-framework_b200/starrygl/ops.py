@@ -273,8 +273,9 @@ def unique_pairs(a_id, a_ts, b_id=None, b_ts=None, *, id_bits, ts_bits, ts_base,
 
 
 def build_csc(src_local, dst, dst_map, ts, dt, eid, num_dst: int, *, dst_bits, ts_bits, ts_base, d_n_edges=None,
-              d_num_dst=None, status: Optional[StatusWord] = None):
-    """CSC of one hop, stable (dst_local, ts) order.  Returns (indptr[num_dst+1], indices, ts, dt, eid)."""
+              d_num_dst=None, presorted: bool = False, status: Optional[StatusWord] = None):
+    """CSC of one hop, stable (dst_local, ts) order.  Returns (indptr[num_dst+1], indices, ts, dt, eid).
+    ``presorted``: the edges already are in that order (first hop: target i is row i) -- no sort."""
     L = _C.lib()
     n = src_local.numel()
     dev = src_local.device
@@ -284,7 +285,7 @@ def build_csc(src_local, dst, dst_map, ts, dt, eid, num_dst: int, *, dst_bits, t
     _, wp, wn = _C.workspace(L.sgl_build_csc_ws_bytes(n, num_dst), dev)
     _C.check(L.sgl_build_csc(_C.ptr(src_local), _C.ptr(dst), _C.ptr(dst_map), _C.ptr(ts), _C.ptr(dt), _C.ptr(eid), n,
                              _C.ptr(d_n_edges), num_dst, _C.ptr(d_num_dst), int(dst_bits), int(ts_bits), int(ts_base),
-                             _C.ptr(indptr), _C.ptr(o_idx), _C.ptr(o_ts), _C.ptr(o_dt), _C.ptr(o_eid),
+                             _C.ptr(indptr), _C.ptr(o_idx), _C.ptr(o_ts), _C.ptr(o_dt), _C.ptr(o_eid), int(bool(presorted)),
                              status.ptr() if status else None, wp, wn, _C.stream_ptr()))
     return indptr, o_idx, o_ts, o_dt, o_eid
 

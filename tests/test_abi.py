@@ -61,7 +61,7 @@ def test_argument_errors_need_no_gpu(lib_path):
     rc = L.sgl_sample_layer(None, None, None, None, 10, None, None, 4, None, 0, 0, 0, -1, 0, 0, 0, None, None, None, None,
                             None, None, None, None, None, 0, None)
     assert rc == -1 and b"fanout" in L.sgl_last_error()
-    rc = L.sgl_sample_layer(None, None, None, None, 10, None, None, 4, None, 64, 1, 0, -1, 0, 0, 0, None, None, None, None,
+    rc = L.sgl_sample_layer(None, None, None, None, 10, None, None, 4, None, 513, 1, 0, -1, 0, 0, 0, None, None, None, None,
                             None, None, None, None, None, 0, None)
     assert rc == -5 and b"uniform fanout" in L.sgl_last_error()
     rc = L.sgl_unique_pairs(None, None, 4, None, None, None, 0, None, 40, 40, 0, None, None, None, None, None, None, None,

@@ -97,9 +97,13 @@ def test_world1_roundtrip_plain_rows_and_tagged_lines(bulk_bytes, dim, counts_on
                                           rows, step, status.ptr(), sp))
             _C.check(L.sgl_p2p_route_recv(ctx, rows, data.data_ptr(), SLOTS, dim, 1, ts.data_ptr(), step, status.ptr(), sp))
         else:
+            # a device-built plan keeps its index arrays at capacity; only the count varies
             d_rows = torch.tensor([n], dtype=torch.int64, device=dev)
-            _C.check(L.sgl_p2p_route_send_dev(ctx, feats.data_ptr(), 50, dim, fts.data_ptr(), send_idx.data_ptr(),
-                                              slots.data_ptr(), d_rows.data_ptr(), 64, step, status.ptr(), sp))
+            idx_cap, slot_cap = torch.zeros(64, dtype=torch.int64, device=dev), torch.zeros(64, dtype=torch.int64, device=dev)
+            idx_cap[:n], slot_cap[:n] = send_idx, slots
+            keep.append((idx_cap, slot_cap))
+            _C.check(L.sgl_p2p_route_send_dev(ctx, feats.data_ptr(), 50, dim, fts.data_ptr(), idx_cap.data_ptr(),
+                                              slot_cap.data_ptr(), d_rows.data_ptr(), 64, step, status.ptr(), sp))
             _C.check(L.sgl_p2p_route_recv_dev(ctx, 64, data.data_ptr(), SLOTS, dim, 1, ts.data_ptr(), step, status.ptr(), sp))
             keep.append(d_rows)
         keep.append((feats, fts, send_idx, slots))

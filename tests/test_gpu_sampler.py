@@ -47,7 +47,7 @@ def random_graph(seed, n, m, tmax, hub=0):
 
 
 @pytest.mark.parametrize("policy", ["recent", "uniform"])
-@pytest.mark.parametrize("k", [1, 7, 20, 32])
+@pytest.mark.parametrize("k", [1, 7, 20, 32, 33, 48, 100])
 def test_matches_oracle_with_hubs_and_options(policy, k):
     """Rows from empty to 60 000 edges (the multi-round warp search), every option of the policy dict."""
     z = random_graph(k, 500, 120000, 50000, hub=60000)
@@ -82,7 +82,7 @@ def test_edge_cases():
     with pytest.raises(_C.SglError, match="node id"):
         st.check("x")
     with pytest.raises(_C.SglError, match="uniform fanout"):
-        ops.sample_layer(g, cu(np.array([3], np.int64)), cu(np.array([50], np.int64)), 33, "uniform")
+        ops.sample_layer(g, cu(np.array([3], np.int64)), cu(np.array([50], np.int64)), 513, "uniform")
 
 
 def test_device_count_chaining():

@@ -9,9 +9,13 @@ from gpu_util import cu, load, npy, build_graph
 pytestmark = pytest.mark.gpu
 
 
-# key widths for which 8-bit digits are used, and widths where 9-bit digits save a pass (9, 17, 27, 44, 63)
+# Sizes on both sides of the mini-batch path's limits (one tile of 8,192 keys: all passes in one kernel; up to 64 tiles:
+# one kernel per pass of up to 11 bits; above: three kernels per pass of 8 or 9 bits) and key widths that need
+# 1 to 6 passes there.
 @pytest.mark.parametrize("n,bits", [(0, 64), (1, 64), (33, 8), (4096, 16), (4097, 40), (100003, 64), (1 << 20, 24),
-                                    (5000, 9), (70001, 17), (12345, 27), (300000, 44), (9999, 63), (40, 1)])
+                                    (5000, 9), (70001, 17), (12345, 27), (300000, 44), (9999, 63), (40, 1),
+                                    (8192, 44), (8193, 44), (8191, 11), (16384, 12), (454656, 44), (454656, 43),
+                                    (524288, 33), (524289, 44), (200000, 22), (65536, 55), (3 * 8192 + 1, 5)])
 def test_radix_sort_stable(n, bits):
     from starrygl import ops
     rng = np.random.default_rng(n + bits)
