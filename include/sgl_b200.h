@@ -425,6 +425,18 @@ int sgl_slice_window(const int64_t* indptr, const int64_t* nbr, const int64_t* t
                      int64_t* out_group_ptr, int64_t* out_nbr, int64_t* out_ts, int64_t* out_eid, int64_t* d_counts,
                      int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
 
+/* Dense per-time-step groups (the reference's use_full_timestamps form, for graphs whose timestamps are snapshot
+ * numbers): every one of the n_nodes nodes of a two-level CSR (node_ptr / group_ts / group_ptr as written by
+ * sgl_slice_window, or roots / ts_ptr / ts / q_ptr as written by sgl_seeds_in_window) gets ALL time steps
+ * t_begin .. t_end-1: out_node_ptr[u] = u * T, out_ts[u * T + j] = t_begin + j, out_group_ptr[u * T + j] = first edge of
+ * the node with timestamp >= t_begin + j (empty groups where the node has no event at that step); capacities
+ * n_nodes + 1, n_nodes * T and n_nodes * T + 1.  d_n_nodes (optional) = device count of nodes.
+ * Replaces: the use_full_timestamps branches of count_edges_kernel / write_edges_kernel and filter_seeds_kernel /
+ * collect_seeds_kernel (csrc/include/starrygl/sample.cu.hpp:353-357, :454-483, :578-581, :667-683). */
+int sgl_densify_time_groups(const int64_t* node_ptr, const int64_t* group_ts, const int64_t* group_ptr, int64_t n_nodes,
+                            const int64_t* d_n_nodes, int64_t t_begin, int64_t t_end, int64_t* out_node_ptr, int64_t* out_ts,
+                            int64_t* out_group_ptr, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Mailbox update of a mini-batch: latest message per node + row assembly, and the write into the mailbox.
  *

@@ -518,3 +518,20 @@ def slice_window(indptr, nbr, ts, eid, node_chunk, chunk_mask, t_begin, t_end):
     node_start = np.nonzero(node_head)[0].astype(I64)
     return (g_src[node_start], np.append(node_start, len(g_src)).astype(I64), g_ts, np.append(group_start, e).astype(I64),
             k_nbr, k_ts, k_eid)
+
+
+def densify_time_groups(node_ptr, group_ts, group_ptr, t_begin, t_end):
+    """The dense form the reference builds when ``use_full_timestamps`` is set (csrc/include/starrygl/sample.cu.hpp:
+    454-483 for the slice, :667-683 for the roots; parity unpinned -- those kernels cannot run): every node gets all time
+    steps ``t_begin .. t_end-1``; the group of (node, t) holds the node's edges with timestamp t, so its start is the
+    first edge of the node with timestamp >= t.  Returns (node_ptr[U+1], ts[U*T], group_ptr[U*T+1])."""
+    U, T = len(node_ptr) - 1, int(t_end - t_begin)
+    o_ts = np.tile(np.arange(t_begin, t_end, dtype=I64), U)
+    o_ptr = np.zeros(U * T + 1, I64)
+    for u in range(U):
+        a, b = int(node_ptr[u]), int(node_ptr[u + 1])
+        for j in range(T):
+            g = a + int(np.searchsorted(group_ts[a:b], t_begin + j, side="left"))
+            o_ptr[u * T + j] = group_ptr[g]
+    o_ptr[U * T] = group_ptr[node_ptr[U]] if U else 0
+    return np.arange(U + 1, dtype=I64) * T, o_ts, o_ptr

@@ -140,6 +140,7 @@ static int exchange(Comm* c, const float* send, const int64_t* h_send_rows, floa
 
 extern "C" int sgl_route_exchange(void* comm, const float* send, const int64_t* h_send_rows, float* recv,
                                   const int64_t* h_recv_rows, int64_t row_floats, void* stream) {
+  SGL_NVTX("sgl_route_exchange");
   SGL_REQUIRE(comm && h_send_rows && h_recv_rows && row_floats > 0, SGL_ERR_ARG, "route_exchange: bad argument");
   return exchange((Comm*)comm, send, h_send_rows, recv, h_recv_rows, row_floats, (cudaStream_t)stream);
 }
@@ -148,6 +149,7 @@ extern "C" int sgl_cache_route_step(void* comm, const float* feats, int64_t n_ro
                                     const int64_t* send_idx, const int64_t* remote_idx, const int64_t* h_send_rows,
                                     const int64_t* h_recv_rows, float* send_buf, float* recv_buf, float* data,
                                     int64_t data_rows, float* ts_table, int apply, int32_t* d_status, void* stream) {
+  SGL_NVTX("sgl_cache_route_step");
   SGL_REQUIRE(comm && h_send_rows && h_recv_rows, SGL_ERR_ARG, "cache_route_step: bad argument");
   Comm* c = (Comm*)comm;
   int64_t n_send = 0, n_recv = 0;

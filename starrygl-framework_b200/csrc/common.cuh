@@ -4,6 +4,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include "../../include/sgl_b200.h"
 
@@ -57,6 +58,14 @@ struct WsCarver {
       return (code);                  \
     }                                 \
   } while (0)
+
+// Named range on the profiler's timeline for the duration of an entry point (one per stage of the data path: T-CSR
+// build, sampling, relabel, gather, plan, route ...).  Header-only NVTX: without an attached tool this is a null check.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
+#define SGL_NVTX(name) sgl::NvtxRange sgl_nvtx_range_(name)
 
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
 

@@ -590,6 +590,7 @@ extern "C" int sgl_gather_rows(const void* table, int64_t table_rows, int64_t ro
                                const int64_t* idx, const int64_t* map, int64_t map_len, int64_t n, const int64_t* d_n,
                                void* out, int64_t dst_pitch, const float* ts_table, float* out_ts, int mode,
                                int32_t* d_status, void* stream_) {
+  SGL_NVTX("sgl_gather_rows");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n >= 0 && table_rows >= 0 && row_bytes > 0, SGL_ERR_ARG, "gather_rows: bad size");
   SGL_REQUIRE(src_pitch >= row_bytes && dst_pitch >= row_bytes, SGL_ERR_ARG, "gather_rows: pitch smaller than row");
@@ -682,6 +683,7 @@ extern "C" int sgl_cache_gather(const void* cache_rows, int64_t cache_slots, con
                                 const void* backing, int64_t row_bytes, const int64_t* ids, int64_t n, void* out,
                                 int64_t* miss_pos, int64_t* miss_ids, int64_t* d_counts, int32_t* d_status, void* ws,
                                 size_t ws_bytes, void* stream_) {
+  SGL_NVTX("sgl_cache_gather");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n >= 0 && row_bytes > 0 && row_bytes % 4 == 0, SGL_ERR_ARG, "cache_gather: bad size");
   SGL_REQUIRE(d_counts, SGL_ERR_ARG, "cache_gather: d_counts is null");
@@ -723,6 +725,7 @@ extern "C" int sgl_scatter_rows(void* table, int64_t table_rows, int64_t row_byt
                                 const int64_t* map, int64_t map_len, int64_t n, const int64_t* d_n, const void* rows,
                                 int64_t src_pitch, float* ts_table, const float* ts, int split_last_col,
                                 int32_t* d_status, void* stream_) {
+  SGL_NVTX("sgl_scatter_rows");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n >= 0 && table_rows >= 0 && row_bytes > 0 && row_bytes % 4 == 0, SGL_ERR_ARG, "scatter_rows: bad size");
   SGL_REQUIRE(dst_pitch >= row_bytes && src_pitch >= row_bytes + (split_last_col ? 4 : 0), SGL_ERR_ARG,
@@ -756,6 +759,7 @@ extern "C" int64_t sgl_wire_pitch(int64_t dim, int has_ts, int has_slot) {
 extern "C" int sgl_route_pack(const float* feats, int64_t n_rows, int64_t dim, const float* ts, const int64_t* send_idx,
                               const int64_t* remote_idx, int64_t n_send, float* packed, int32_t* d_status,
                               void* stream_) {
+  SGL_NVTX("sgl_route_pack");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n_send >= 0 && n_rows >= 0 && dim > 0, SGL_ERR_ARG, "route_pack: bad size");
   if (n_send == 0) return SGL_OK;
@@ -777,6 +781,7 @@ extern "C" int sgl_route_pack(const float* feats, int64_t n_rows, int64_t dim, c
 
 extern "C" int sgl_route_unpack(const float* packed, int64_t n, int64_t width, float* data, int64_t data_rows,
                                 int64_t dim, float* ts_table, int32_t* d_status, void* stream_) {
+  SGL_NVTX("sgl_route_unpack");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n >= 0 && data_rows >= 0 && dim > 0, SGL_ERR_ARG, "route_unpack: bad size");
   SGL_REQUIRE(width == dim || width == dim + 1, SGL_ERR_ARG, "route_unpack: width %lld must be dim or dim+1 (dim=%lld)",
@@ -828,6 +833,7 @@ extern "C" int sgl_route_add_grouped(float* x, int64_t n_rows, int64_t dim, cons
 extern "C" int sgl_shard_gather(const void* const* d_bases, const int64_t* d_shard_rows, int world, int64_t row_bytes,
                                 const int64_t* dist_idx, int64_t n, const int64_t* d_n, void* out, int32_t* d_status,
                                 void* stream_) {
+  SGL_NVTX("sgl_shard_gather");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n >= 0 && world >= 1 && world <= 0x3FFF && row_bytes > 0 && row_bytes % 4 == 0, SGL_ERR_ARG,
               "shard_gather: bad size (rows must be multiples of 4 bytes)");
@@ -877,6 +883,7 @@ extern "C" int sgl_replica_lookup(const int64_t* indptr, const int64_t* ranks, c
                                   const int64_t* ids, int64_t n, int64_t cap, int64_t* out_src, int64_t* out_rank,
                                   int64_t* out_loc, int64_t* out_offsets, int32_t* d_status, void* ws, size_t ws_bytes,
                                   void* stream_) {
+  SGL_NVTX("sgl_replica_lookup");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n >= 0 && cap >= 0 && num_nodes >= 0, SGL_ERR_ARG, "replica_lookup: negative size");
   SGL_REQUIRE(out_offsets, SGL_ERR_ARG, "replica_lookup: out_offsets is null");

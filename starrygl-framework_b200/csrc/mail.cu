@@ -146,6 +146,7 @@ extern "C" int sgl_mail_reduce(const int64_t* ids_a, int64_t n_a, const int64_t*
                                const float* const* seg_b, const int64_t* seg_dim, int64_t* out_index, int64_t* out_pos,
                                float* out_ts, float* out_mail, int64_t* d_num_unique, int32_t* d_status, void* ws,
                                size_t ws_bytes, void* stream_) {
+  SGL_NVTX("sgl_mail_reduce");
   cudaStream_t stream = (cudaStream_t)stream_;
   const int64_t n = n_a + n_b;
   SGL_REQUIRE(n_a >= 0 && n_b >= 0 && num_nodes >= 0 && n <= 0xffffffffll, SGL_ERR_ARG, "mail_reduce: bad size");
@@ -204,6 +205,7 @@ extern "C" int sgl_mail_reduce(const int64_t* ids_a, int64_t n_a, const int64_t*
 extern "C" int sgl_mailbox_write(const int64_t* index, int64_t n, const int64_t* d_n, const float* mail, const float* mail_ts,
                                  int64_t width, float* mailbox, float* mailbox_ts, int64_t* next_mail_pos, int64_t num_nodes,
                                  int64_t mailbox_size, int advance, int32_t* d_status, void* stream_) {
+  SGL_NVTX("sgl_mailbox_write");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n >= 0 && width >= 1 && num_nodes >= 0 && mailbox_size >= 1, SGL_ERR_ARG, "mailbox_write: bad size");
   if (n == 0) return SGL_OK;

@@ -553,6 +553,7 @@ static int send_impl(Ctx* x, const float* feats, int64_t n_rows, int64_t dim, co
 extern "C" int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
                                   const int64_t* send_idx, const int64_t* remote_idx, const int64_t* h_send_rows,
                                   uint64_t step, int32_t* d_status, void* stream) {
+  SGL_NVTX("sgl_p2p_route_send");
   SGL_REQUIRE(ctx && h_send_rows && dim > 0, SGL_ERR_ARG, "p2p_route_send: bad argument");
   Ctx* x = (Ctx*)ctx;
   Splits seg;
@@ -564,6 +565,7 @@ extern "C" int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows,
 extern "C" int sgl_p2p_route_send_dev(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,
                                       const int64_t* send_idx, const int64_t* remote_idx, const int64_t* d_send_rows,
                                       int64_t rows_hint, uint64_t step, int32_t* d_status, void* stream) {
+  SGL_NVTX("sgl_p2p_route_send_dev");
   SGL_REQUIRE(ctx && d_send_rows && dim > 0 && rows_hint >= 0, SGL_ERR_ARG, "p2p_route_send_dev: bad argument");
   Splits seg;
   memset(&seg, 0, sizeof(seg));
@@ -587,6 +589,7 @@ static int recv_impl(Ctx* x, const Splits& expect, int check, int64_t grid_rows,
 
 extern "C" int sgl_p2p_route_recv(void* ctx, const int64_t* h_recv_rows, float* data, int64_t data_rows, int64_t dim,
                                   int has_ts, float* ts_table, uint64_t step, int32_t* d_status, void* stream) {
+  SGL_NVTX("sgl_p2p_route_recv");
   SGL_REQUIRE(ctx && h_recv_rows && dim > 0, SGL_ERR_ARG, "p2p_route_recv: bad argument");
   Ctx* x = (Ctx*)ctx;
   Splits seg;
@@ -597,6 +600,7 @@ extern "C" int sgl_p2p_route_recv(void* ctx, const int64_t* h_recv_rows, float* 
 
 extern "C" int sgl_p2p_route_recv_dev(void* ctx, int64_t rows_hint, float* data, int64_t data_rows, int64_t dim, int has_ts,
                                       float* ts_table, uint64_t step, int32_t* d_status, void* stream) {
+  SGL_NVTX("sgl_p2p_route_recv_dev");
   SGL_REQUIRE(ctx && dim > 0 && rows_hint >= 0 && data, SGL_ERR_ARG, "p2p_route_recv_dev: bad argument");
   Splits seg;
   memset(&seg, 0, sizeof(seg));

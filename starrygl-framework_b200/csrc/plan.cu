@@ -110,6 +110,7 @@ extern "C" int sgl_plan_route(const int64_t* layer_ids, int64_t n, const int64_t
                               const int64_t* rep_locs, int64_t num_parts, int64_t cap, int64_t* out_ranks, int64_t* out_rows,
                               int64_t* out_locs, int64_t* d_send_sizes, int64_t* d_total, int32_t* d_status, void* ws,
                               size_t ws_bytes, void* stream_) {
+  SGL_NVTX("sgl_plan_route");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n >= 0 && cap >= 0 && num_nodes >= 0 && num_parts >= 1 && num_parts <= 256 && pid >= 0 && pid < num_parts,
               SGL_ERR_ARG, "plan_route: bad size (1 <= num_parts <= 256, 0 <= pid < num_parts)");

@@ -290,6 +290,7 @@ extern "C" int sgl_unique_pairs(const int64_t* a_id, const int64_t* a_ts, int64_
                                 int ts_bits, int64_t ts_base, int64_t* out_id, int64_t* out_ts, int64_t* inv_a,
                                 int64_t* inv_b, int64_t* d_n_unique, int32_t* d_status, void* ws, size_t ws_bytes,
                                 void* stream_) {
+  SGL_NVTX("sgl_unique_pairs");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n_a >= 0 && n_b >= 0, SGL_ERR_ARG, "unique_pairs: negative size");
   SGL_REQUIRE(id_bits >= 0 && ts_bits >= 0 && id_bits + ts_bits <= 64, SGL_ERR_UNSUPPORTED,
@@ -341,6 +342,7 @@ extern "C" int sgl_build_csc(const int64_t* src_local, const int64_t* dst, const
                              int64_t num_dst, const int64_t* d_num_dst, int dst_bits, int ts_bits, int64_t ts_base,
                              int64_t* out_indptr, int64_t* out_indices, int64_t* out_ts, float* out_dt, int64_t* out_eid,
                              int presorted, int32_t* d_status, void* ws, size_t ws_bytes, void* stream_) {
+  SGL_NVTX("sgl_build_csc");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n_edges >= 0 && num_dst >= 0, SGL_ERR_ARG, "build_csc: negative size");
   if (presorted) {
@@ -397,6 +399,7 @@ extern "C" int sgl_relabel_nodes(const int64_t* ids, int64_t n, const int64_t* d
                                  int64_t* mask, int64_t epoch, int64_t* d_next_local, int64_t* out_local,
                                  int64_t* out_new_ids, int64_t* d_n_new, int32_t* d_status, void* ws, size_t ws_bytes,
                                  void* stream_) {
+  SGL_NVTX("sgl_relabel_nodes");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n >= 0 && num_nodes >= 0, SGL_ERR_ARG, "relabel_nodes: negative size");
   SGL_REQUIRE(d_next_local && d_n_new, SGL_ERR_ARG, "relabel_nodes: null counter");
@@ -455,6 +458,7 @@ extern "C" int sgl_seeds_in_window(const int64_t* ev_src, const int64_t* ev_ts, 
                                    int64_t num_nodes, int id_bits, int ts_bits, int64_t ts_base, int64_t* out_roots,
                                    int64_t* out_ts_ptr, int64_t* out_ts, int64_t* out_q_ptr, int64_t* out_q_eid,
                                    int64_t* d_counts, int32_t* d_status, void* ws, size_t ws_bytes, void* stream_) {
+  SGL_NVTX("sgl_seeds_in_window");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n_events >= 0 && num_nodes >= 0, SGL_ERR_ARG, "seeds_in_window: negative size");
   SGL_REQUIRE(id_bits >= 0 && ts_bits >= 0 && id_bits + ts_bits < 64, SGL_ERR_UNSUPPORTED,

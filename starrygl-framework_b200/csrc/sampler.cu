@@ -307,6 +307,7 @@ extern "C" int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const
                                 int64_t* out_dst, int64_t* out_ts, float* out_dt, int64_t* out_dt_i64,
                                 int64_t* out_eid, int64_t* out_offsets, int32_t* d_status, void* ws, size_t ws_bytes,
                                 void* stream_) {
+  SGL_NVTX("sgl_sample_layer");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n_targets >= 0 && num_nodes >= 0, SGL_ERR_ARG, "sample_layer: negative size");
   SGL_REQUIRE(fanout >= 1, SGL_ERR_ARG, "sample_layer: fanout=%d must be >= 1", fanout);
@@ -352,6 +353,7 @@ extern "C" int sgl_sample_gather(const int64_t* indptr, const int64_t* nbr, cons
                                  float* out_dt, int64_t* out_eid, int64_t* out_offsets, const void* feat_table,
                                  int64_t feat_rows, int64_t row_bytes, int64_t src_pitch, void* out_feats, int gather_mode,
                                  int32_t* d_status, void* ws, size_t ws_bytes, void* stream) {
+  SGL_NVTX("sgl_sample_gather");
   int rc = sgl_sample_layer(indptr, nbr, ts, eid, num_nodes, targets, target_ts, n_targets, nullptr, fanout, policy,
                             equal_root_time, allowed_offset, keep_root_time, seed, rng_stream, out_nbr, out_dst, out_ts,
                             out_dt, nullptr, out_eid, out_offsets, d_status, ws, ws_bytes, stream);

@@ -169,6 +169,37 @@ slice_write_kernel(SliceArgs a, const int64_t* __restrict__ eid, const uint32_t*
   }
 }
 
+// Dense per-time-step groups out of the sparse ones: node u of the sparse form owns the groups
+// [node_ptr[u], node_ptr[u+1]) with ascending timestamps group_ts and edge ranges group_ptr; the dense form gives every
+// node ALL time steps t_begin .. t_end-1 (T = t_end - t_begin groups per node, empty where the node has no event).
+// One thread per (node, time step): the first sparse group of the node with timestamp >= t by binary search.
+__global__ void __launch_bounds__(kThreads)
+densify_groups_kernel(const int64_t* __restrict__ node_ptr, const int64_t* __restrict__ group_ts,
+                      const int64_t* __restrict__ group_ptr, int64_t u_cap, const int64_t* d_u, int64_t t_begin, int64_t T,
+                      int64_t* __restrict__ out_node_ptr, int64_t* __restrict__ out_ts, int64_t* __restrict__ out_group_ptr) {
+  const int64_t U = eff_count(u_cap, d_u);
+  const int64_t total = U * T;
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  for (int64_t q = (int64_t)blockIdx.x * kThreads + threadIdx.x; q <= total; q += stride) {
+    if (q == total) {                       // closing entries
+      out_group_ptr[total] = U ? group_ptr[node_ptr[U]] : 0;
+      out_node_ptr[U] = total;
+      break;
+    }
+    const int64_t u = q / T, t = t_begin + (q - u * T);
+    int64_t lo = node_ptr[u], hi = node_ptr[u + 1];
+    const int64_t end = hi;
+    while (lo < hi) {
+      const int64_t mid = lo + ((hi - lo) >> 1);
+      if (group_ts[mid] < t) lo = mid + 1; else hi = mid;
+    }
+    out_ts[q] = t;
+    out_group_ptr[q] = group_ptr[lo];       // lo == end: the start of the next node's edges = the end of this node's
+    (void)end;
+    if (q == u * T) out_node_ptr[u] = q;
+  }
+}
+
 inline unsigned ctas_for(int64_t n) { return (unsigned)((n + kThreads - 1) / kThreads < 1 ? 1 : (n + kThreads - 1) / kThreads); }
 
 }  // namespace
@@ -187,6 +218,7 @@ extern "C" int sgl_slice_window(const int64_t* indptr, const int64_t* nbr, const
                                 int64_t* out_group_ts, int64_t* out_group_ptr, int64_t* out_nbr, int64_t* out_ts,
                                 int64_t* out_eid, int64_t* d_counts, int32_t* d_status, void* ws, size_t ws_bytes,
                                 void* stream_) {
+  SGL_NVTX("sgl_slice_window");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(num_nodes >= 0 && cap_edges >= 0 && num_chunks >= 0, SGL_ERR_ARG, "slice_window: negative size");
   SGL_REQUIRE(d_counts && out_node_ptr && out_group_ptr, SGL_ERR_ARG, "slice_window: null counter / pointer array");
@@ -219,6 +251,22 @@ extern "C" int sgl_slice_window(const int64_t* indptr, const int64_t* nbr, const
   slice_write_kernel<<<grid, kThreads, 0, stream>>>(a, eid, cnt_edges, loc_node, loc_group, loc_edge, cta_nodes, cta_groups,
                                                     cta_edges, d_counts, cap_edges, out_nodes, out_node_ptr, out_group_ts,
                                                     out_group_ptr, out_nbr, out_ts, out_eid, d_status);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}
+
+extern "C" int sgl_densify_time_groups(const int64_t* node_ptr, const int64_t* group_ts, const int64_t* group_ptr, int64_t n_nodes,
+                                       const int64_t* d_n_nodes, int64_t t_begin, int64_t t_end, int64_t* out_node_ptr,
+                                       int64_t* out_ts, int64_t* out_group_ptr, void* stream_) {
+  SGL_REQUIRE(n_nodes >= 0 && t_end >= t_begin, SGL_ERR_ARG, "densify_time_groups: bad size");
+  SGL_REQUIRE(out_node_ptr && out_group_ptr, SGL_ERR_ARG, "densify_time_groups: null output");
+  const int64_t T = t_end - t_begin;
+  SGL_REQUIRE(T == 0 || n_nodes <= (((int64_t)1 << 40) / T), SGL_ERR_UNSUPPORTED,
+              "densify_time_groups: %lld nodes x %lld time steps is too large for dense groups", (long long)n_nodes, (long long)T);
+  SGL_REQUIRE(n_nodes == 0 || (node_ptr && group_ptr && (T == 0 || (group_ts && out_ts))), SGL_ERR_ARG,
+              "densify_time_groups: null array");
+  densify_groups_kernel<<<stream_grid(n_nodes * T + 1, kThreads, 16), kThreads, 0, (cudaStream_t)stream_>>>(
+      node_ptr, group_ts, group_ptr, n_nodes, d_n_nodes, t_begin, T, out_node_ptr, out_ts, out_group_ptr);
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }

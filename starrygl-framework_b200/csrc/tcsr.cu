@@ -119,6 +119,7 @@ extern "C" size_t sgl_tcsr_build_ws_bytes(int64_t num_nodes, int64_t m) {
 extern "C" int sgl_tcsr_build(int64_t num_nodes, int64_t m, const int64_t* key, const int64_t* nbr, const int64_t* ts,
                               const int64_t* eid, int64_t* indptr, int64_t* out_nbr, int64_t* out_ts, int64_t* out_eid,
                               int64_t* out_perm, int64_t* h_ts_range, void* ws, size_t ws_bytes, void* stream_) {
+  SGL_NVTX("sgl_tcsr_build");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(num_nodes >= 0 && m >= 0, SGL_ERR_ARG, "tcsr_build: negative size");
   SGL_REQUIRE(m < ((int64_t)1 << 32), SGL_ERR_UNSUPPORTED, "tcsr_build: m=%lld needs a 64-bit permutation", (long long)m);

@@ -69,6 +69,7 @@ _SIGNATURES = {
     "sgl_p2p_route_destroy": (_i32, [_vp]),
     "sgl_p2p_route_send": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _vp, C.POINTER(C.c_int64), _u64, _vp, _vp]),
     "sgl_p2p_route_recv": (_i32, [_vp, C.POINTER(C.c_int64), _vp, _i64, _i64, _i32, _vp, _u64, _vp, _vp]),
+    "sgl_densify_time_groups": (_i32, [_vp, _vp, _vp, _i64, _vp, _i64, _i64, _vp, _vp, _vp, _vp]),
     "sgl_comm_info": (_i32, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "sgl_init_p2p": (_i32, [C.POINTER(C.c_int), _i32, C.POINTER(C.c_int)]),
     "sgl_route_add_grouped": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp]),

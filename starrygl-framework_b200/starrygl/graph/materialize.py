@@ -29,6 +29,35 @@ def _dev_i64(x, dev):
     return x.to(dev, torch.int64).contiguous()
 
 
+def prepare_distributed_metadata(node_parts, edge_index, num_parts: int, output_dir=None):
+    """Partition book and replica table of a partitioned graph, in the reference's file layout
+    (``prepare_distributed_metadata``, prepare_nparts_louvain.py:457-484).
+
+    An event belongs to the partition of its destination.  ``partition_book[p]`` = the nodes partition p stores: the ones
+    it owns (ascending id) followed by its halo -- sources of its events that another partition owns (ascending id).
+    ``partition_book.pt`` holds ``(partition_book, node_parts, edge_parts)``, ``replica_table.pt`` the CSR over node id of
+    every ``(rank, local slot)`` copy.  One-time set-up on whatever device the inputs live on; the files hold CPU tensors.
+    Returns ``(partition_book, replica_table)``."""
+    import os
+
+    from ..cache.replica_table import build_replica_table
+    node_parts = torch.as_tensor(node_parts, dtype=torch.int64)
+    src, dst = (torch.as_tensor(x, dtype=torch.int64).to(node_parts.device) for x in edge_index)
+    edge_parts = node_parts[dst]
+    src_parts = node_parts[src]
+    book = []
+    for pid in range(int(num_parts)):
+        owned = torch.nonzero(node_parts == pid, as_tuple=True)[0]
+        halo = torch.unique(src[(edge_parts == pid) & (src_parts != pid)])
+        book.append(torch.cat([owned, halo]).cpu())
+    table = build_replica_table(node_parts.numel(), book, int(num_parts))
+    if output_dir is not None:
+        os.makedirs(output_dir, exist_ok=True)
+        torch.save((book, node_parts.cpu(), edge_parts.cpu()), os.path.join(output_dir, "partition_book.pt"))
+        torch.save(table, os.path.join(output_dir, "replica_table.pt"))
+    return book, table
+
+
 class MaterializedMultiLayerBuilder:
     def __init__(self, partition_data, num_nodes, node_parts, rep_table, pid, num_parts, device=None):
         dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())

@@ -217,12 +217,13 @@ class CUDAGraph:
 
     def get_seeds_in_chunks(self, chunks: torch.Tensor, time_begin: int, time_end: int,
                             using_full_timestamp: bool = False) -> TemporalRoot:
-        if using_full_timestamp:
-            raise NotImplementedError("dense per-timestep roots (using_full_timestamp) are not provided")
         with torch.cuda.stream(self.stream):
-            r = ops.seeds_in_window(self.ev, self.g, chunks, self.mapper, int(time_begin), int(time_end),
-                                    status=self.status)
-        return TemporalRoot(*r)
+            roots, ts_ptr, ts, q_ptr, q_eid = ops.seeds_in_window(self.ev, self.g, chunks, self.mapper, int(time_begin),
+                                                                  int(time_end), status=self.status)
+            if using_full_timestamp:
+                # every root gets all time steps of the window (snapshot graphs): time steps without an event own no event
+                ts_ptr, ts, q_ptr = ops.densify_time_groups(ts_ptr, ts, q_ptr, int(time_begin), int(time_end))
+        return TemporalRoot(roots, ts_ptr, ts, q_ptr, q_eid)
 
     def sample_src_in_chunks_khop(self, postive_root: TemporalRoot, negative_root: Optional[NegativeRoot], k: int,
                                   layers: int, allowed_offset: int, equal_root_time: bool, keep_root_time: bool,
@@ -255,14 +256,15 @@ class CUDAGraph:
         """Sub-graph of the chunks' nodes inside ``[time_begin, time_end)``: ``roots`` = the nodes that keep an edge with
         their distinct timestamps (``ts_ptr`` / ``ts``), one neighbour layer whose ``root_start_ptr`` has one entry per
         (node, timestamp) group (reference: csrc/include/starrygl/sample.cu.hpp:1189-1291)."""
-        if using_full_timestamp:
-            raise NotImplementedError("dense per-timestep groups (using_full_timestamp) are not provided")
         ev_ts = self.ev[1]
         with torch.cuda.stream(self.stream):
             lo, hi = ops.lower_bound(ev_ts, torch.tensor([int(time_begin), int(time_end)], dtype=torch.int64,
                                                          device=ev_ts.device)).tolist()
             nodes, node_ptr, group_ts, group_ptr, nbr, ts, eid = ops.slice_window(
                 self.g, chunks, self.mapper, int(time_begin), int(time_end), max(hi - lo, 0), status=self.status)
+            if using_full_timestamp:
+                node_ptr, group_ts, group_ptr = ops.densify_time_groups(node_ptr, group_ts, group_ptr, int(time_begin),
+                                                                        int(time_end))
         out = TemporalResult(TemporalRoot(nodes, node_ptr, group_ts))
         out.neighbors_list.append(TemporalNeighbor.from_arrays(group_ptr, nbr, ts, eid))
         return out
@@ -309,10 +311,14 @@ class CUDAGraph:
                 return
             fut, (t0, t1, chunks, neg, stype, layers, fanout, off, eq, keep, op) = item
             try:
-                if stype not in ("recent", "uniform"):
-                    raise NotImplementedError("cluster slices are not part of the sampling data path")
-                roots = self.get_seeds_in_chunks(chunks, t0, t1, False)
-                res = self.sample_src_in_chunks_khop(roots, neg, fanout, layers, off, eq, keep, stype)
+                if stype in ("recent", "uniform"):
+                    roots = self.get_seeds_in_chunks(chunks, t0, t1, False)
+                    res = self.sample_src_in_chunks_khop(roots, neg, fanout, layers, off, eq, keep, stype)
+                else:
+                    # any other policy name is the "cluster" slice: the chunks' whole sub-graph inside the window, dense
+                    # time steps (csrc/include/starrygl/sample.cu.hpp:1953-1961)
+                    res = self.slice_by_chunk_ts(chunks, t0, t1, True)
+                    res._status = self.status
                 with torch.cuda.stream(self.stream):
                     self._remap(res, op == "f")     # the reference restarts the numbering on "f"
                     self.status.check("submit_query")

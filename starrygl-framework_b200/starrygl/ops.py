@@ -243,6 +243,21 @@ def slice_window(g: TCSR, chunks, node_chunk, t_begin: int, t_end: int, cap_edge
     return nodes[:u], node_ptr[:u + 1], group_ts[:gcnt], group_ptr[:gcnt + 1], nbr[:e], ts[:e], eid[:e]
 
 
+def densify_time_groups(node_ptr, group_ts, group_ptr, t_begin: int, t_end: int):
+    """Dense per-time-step groups out of sparse ones (see ``sgl_densify_time_groups``).  Returns
+    (node_ptr[U+1], ts[U*T], group_ptr[U*T+1])."""
+    L = _C.lib()
+    U, T = node_ptr.numel() - 1, int(t_end) - int(t_begin)
+    dev = node_ptr.device
+    o_node = torch.empty(U + 1, dtype=I64, device=dev)
+    o_ts = torch.empty(max(U * T, 1), dtype=I64, device=dev)
+    o_ptr = torch.empty(U * T + 1, dtype=I64, device=dev)
+    _C.check(L.sgl_densify_time_groups(_C.ptr(_i64(node_ptr)), _C.ptr(_i64(group_ts)) if group_ts.numel() else None,
+                                       _C.ptr(_i64(group_ptr)), U, None, int(t_begin), int(t_end), _C.ptr(o_node), _C.ptr(o_ts),
+                                       _C.ptr(o_ptr), _C.stream_ptr()))
+    return o_node, o_ts[:U * T], o_ptr
+
+
 # --------------------------------------------------------------------------------------------------------------
 # relabel
 # --------------------------------------------------------------------------------------------------------------

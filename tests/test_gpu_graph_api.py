@@ -82,10 +82,45 @@ def test_bad_inputs_raise():
     with pytest.raises(RuntimeError, match="outside"):
         L.from_edge_index(10, 1, cu(src), cu(dst), cu(ts), cu(eid))
     g = L.from_edge_index(n, 1, cu(src), cu(dst), cu(ts), cu(eid))
-    g.submit_query(0, 10, torch.zeros(1, dtype=torch.int64).cuda(), cu(np.zeros(0, np.int64)), cu(np.zeros(0, np.int64)),
-                   "nonsense", 1, 5, -1, False, False, "r")
-    with pytest.raises(NotImplementedError):
-        g.get()
+    with pytest.raises(RuntimeError, match="undefined sampling strategy"):
+        g.sample_src_in_chunks_khop(g.get_seeds_in_chunks(torch.zeros(1, dtype=torch.int64).cuda(), 0, 10, False), None, 5, 1,
+                                    -1, False, False, "nonsense")
+    g.close()
+
+
+def test_dense_time_steps_and_the_cluster_policy():
+    """Snapshot graph (timestamps = small step numbers): ``using_full_timestamp`` gives every root / node ALL steps of the
+    window, and any policy name other than recent / uniform queues that dense slice (the reference's cluster branch)."""
+    from starrygl.lib import libstarrygl_comm as L
+    n, src, dst, ts, eid = make_events(seed=5, n=60, m=3000, tmax=12)
+    g = L.from_edge_index(n, 1, cu(src), cu(dst), cu(ts), cu(eid))
+    chunk0 = torch.zeros(1, dtype=torch.int64).cuda()
+    t0, t1 = 3, 9
+    # roots
+    r = g.get_seeds_in_chunks(chunk0, t0, t1, True)
+    roots, ts_ptr, rts, q_ptr, q_eid = ref_seeds(src, ts, eid, t0, t1)
+    d_ptr, d_ts, d_q = O.densify_time_groups(ts_ptr, rts, q_ptr, t0, t1)
+    assert np.array_equal(npy(r.roots), roots) and np.array_equal(npy(r.ts_ptr), d_ptr) and np.array_equal(npy(r.ts), d_ts)
+    assert np.array_equal(npy(r.q_ptr), d_q) and np.array_equal(npy(r.q_eid), q_eid)
+    # brute force: the events behind (root, step) are exactly the root's events of that step
+    qp = npy(r.q_ptr)
+    for i in range(0, len(roots) * (t1 - t0), 7):
+        u, t = roots[i // (t1 - t0)], t0 + i % (t1 - t0)
+        assert sorted(npy(r.q_eid)[qp[i]:qp[i + 1]].tolist()) == sorted(eid[(src == u) & (ts == t)].tolist())
+    # slice, directly and through the queue with the cluster policy
+    indptr, s_nbr, s_ts, s_eid, _ = O.tcsr_build(src, dst, ts, eid, n)
+    nodes, node_ptr, group_ts, group_ptr, k_nbr, k_ts, k_eid = O.slice_window(indptr, s_nbr, s_ts, s_eid, None, None, t0, t1)
+    w_ptr, w_ts, w_g = O.densify_time_groups(node_ptr, group_ts, group_ptr, t0, t1)
+    res = g.slice_by_chunk_ts(None, t0, t1, True)
+    assert np.array_equal(npy(res.roots.roots), nodes) and np.array_equal(npy(res.roots.ts_ptr), w_ptr)
+    assert np.array_equal(npy(res.roots.ts), w_ts) and np.array_equal(npy(res.neighbors[0].root_start_ptr), w_g)
+    assert np.array_equal(npy(res.neighbors[0].neighbors_eid), k_eid)
+    g.submit_query(t0, t1, chunk0, cu(np.zeros(0, np.int64)), cu(np.zeros(0, np.int64)), "cluster", 1, 0, 0, False, False, "f")
+    q = g.get()
+    assert np.array_equal(npy(q.neighbors[0].root_start_ptr), w_g) and np.array_equal(npy(q.neighbors[0].neighbors_eid), k_eid)
+    loc, mapper = O.relabel_nodes([nodes, k_nbr])
+    assert np.array_equal(npy(q.roots.roots), loc[0]) and np.array_equal(npy(q.neighbors[0].neighbors), loc[1])
+    assert np.array_equal(npy(q.nodes_remapper_id), mapper)
     g.close()
 
 
