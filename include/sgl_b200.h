@@ -79,6 +79,15 @@ int sgl_tcsr_build(int64_t num_nodes, int64_t m, const int64_t* key, const int64
                    const int64_t* eid, int64_t* indptr, int64_t* out_nbr, int64_t* out_ts, int64_t* out_eid,
                    int64_t* out_perm, int64_t* h_ts_range, void* ws, size_t ws_bytes, void* stream);
 
+/* Search index over the T-CSR rows ("fence"): the timestamp of the last edge of every block of 32 consecutive edges of a
+ * row; row r with edges [s, e) owns out_fence[(s >> 5) + r + j], j < ceil((e - s) / 32).  sgl_tcsr_fence_len() entries
+ * (about 1.6 % of the adjacency, small enough to stay in L2).  The *_fenced sampling entry points search it first and
+ * then read one block of the row instead of probing the row itself round after round; results are identical.
+ * Replaces: the dependent probes of binary_lower_bound / binary_upper_bound over the whole row
+ * (csrc/include/starrygl/sample.cu.hpp:218-295). */
+int64_t sgl_tcsr_fence_len(int64_t num_nodes, int64_t m);
+int sgl_tcsr_fence(const int64_t* indptr, const int64_t* ts, int64_t num_nodes, int64_t m, int64_t* out_fence, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * One hop of temporal neighbour sampling, one warp per target.
  * Target i = (targets[i], target_ts[i]).  Candidates: row edges with ts < t (ts <= t when
@@ -103,6 +112,21 @@ int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const int64_t* t
                      int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* out_nbr, int64_t* out_dst,
                      int64_t* out_ts, float* out_dt, int64_t* out_dt_i64, int64_t* out_eid, int64_t* out_offsets,
                      int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
+
+/* sgl_sample_layer / sgl_sample_gather with the rows' fence (sgl_tcsr_fence; NULL = search the rows directly). */
+int sgl_sample_layer_fenced(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                            const int64_t* fence, int64_t num_nodes, const int64_t* targets, const int64_t* target_ts,
+                            int64_t n_targets, const int64_t* d_n, int fanout, int policy, int equal_root_time,
+                            int64_t allowed_offset, int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* out_nbr,
+                            int64_t* out_dst, int64_t* out_ts, float* out_dt, int64_t* out_dt_i64, int64_t* out_eid,
+                            int64_t* out_offsets, int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
+int sgl_sample_gather_fenced(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                             const int64_t* fence, int64_t num_nodes, const int64_t* targets, const int64_t* target_ts,
+                             int64_t n_targets, int fanout, int policy, int equal_root_time, int64_t allowed_offset,
+                             int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* out_nbr, int64_t* out_dst,
+                             int64_t* out_ts, float* out_dt, int64_t* out_eid, int64_t* out_offsets, const void* feat_table,
+                             int64_t feat_rows, int64_t row_bytes, int64_t src_pitch, void* out_feats, int gather_mode,
+                             int32_t* d_status, void* ws, size_t ws_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * sgl_sample_layer for callers that cannot provide scratch memory.  (No counterpart in the reference: its
@@ -307,8 +331,9 @@ int sgl_cache_route_step(void* comm, const float* feats, int64_t n_rows, int64_t
  * Cache route over NVLink peer memory (one node): the pack and the transfer are ONE kernel that stores the wire
  * rows straight into the receivers' staging buffers, as 16-byte lines that carry the step's tag next to the data
  * (the receiver polls the lines themselves; there is no separate flag and no fence); a second kernel on the
- * receiver applies them and acknowledges the step.  A pair's message of 2 MiB and more (sgl_p2p_route_configure
- * changes the limit) is bandwidth-bound and travels as plain rows followed by a fence and a per-pair word instead.
+ * receiver applies them and acknowledges the step.  A pair's message of 256 KiB and more, and every message of a step
+ * in which the sender pushes four times that in total (sgl_p2p_route_configure changes the limit), is bandwidth-bound
+ * and travels as plain rows followed by a fence and a per-pair word instead.
  * Every sender also tells every receiver how many rows it pushed (one 8-byte word per pair and step), so the
  * receiver needs no count exchange: a plan whose sizes exist only in device memory (sgl_plan_route's d_send_sizes)
  * is routed without a host synchronisation (sgl_p2p_route_send_dev / sgl_p2p_route_recv_dev).
@@ -338,7 +363,8 @@ int sgl_p2p_free(void* ptr);
 int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_rows, int64_t pitch_floats, void* const* h_bases,
                          void** out_ctx);
 /* wait_ms: bound of every device-side wait (1..60000); bulk_bytes: message size from which a pair uses plain rows
- * (0 = always).  A negative value leaves the setting as it is.  All ranks must use the same bulk_bytes. */
+ * (0 = always; a sender whose step totals four times that uses them for all its pairs).  A negative value leaves the
+ * setting as it is.  The sender tells the receiver which form it used, so ranks may differ in this setting. */
 int sgl_p2p_route_configure(void* ctx, int64_t wait_ms, int64_t bulk_bytes);
 int sgl_p2p_route_destroy(void* ctx);
 int sgl_p2p_route_send(void* ctx, const float* feats, int64_t n_rows, int64_t dim, const float* ts,

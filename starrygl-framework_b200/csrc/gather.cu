@@ -39,6 +39,34 @@ __device__ __forceinline__ void st_stream(uint32_t* p, uint32_t v) {
   asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Flattened lane q -> (row i, lane l inside the row).  Rows of a power-of-two number of lanes split with a shift; other
+// rows with a 32-bit division while the lane count fits 32 bits (a 64-bit division costs several times as much, and
+// these kernels execute one split per 16 bytes moved).
+struct LaneSplit {
+  uint32_t lanes;
+  int shift;        // log2(lanes) or -1
+  bool small;       // every flattened index of the launch fits 32 bits
+  __host__ LaneSplit(uint32_t lanes_, int64_t total) : lanes(lanes_), shift(-1), small(total <= 0xffffffffll) {
+    if ((lanes & (lanes - 1)) == 0) {
+      shift = 0;
+      while ((1u << shift) < lanes) ++shift;
+    }
+  }
+  __device__ __forceinline__ void operator()(int64_t q, int64_t* i, uint32_t* l) const {
+    if (shift >= 0) {
+      *i = q >> shift;
+      *l = (uint32_t)q & (lanes - 1);
+    } else if (small) {
+      const uint32_t qq = (uint32_t)q, ii = qq / lanes;
+      *i = ii;
+      *l = qq - ii * lanes;
+    } else {
+      *i = q / lanes;
+      *l = (uint32_t)(q - *i * lanes);
+    }
+  }
+};
+
 // resolve the source/destination row of item i; returns false when the row must be skipped
 __device__ __forceinline__ bool resolve_row(const int64_t* __restrict__ idx, const int64_t* __restrict__ map,
                                             int64_t map_len, int64_t table_rows, int64_t i, bool wrap_negative,
@@ -65,12 +93,12 @@ __device__ __forceinline__ bool resolve_row(const int64_t* __restrict__ idx, con
 
 template <typename V>
 __global__ void __launch_bounds__(kLaneThreads)
-gather_lanes_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t lanes_per_row, int64_t src_pitch,
+gather_lanes_kernel(const char* __restrict__ table, int64_t table_rows, LaneSplit split, int64_t src_pitch,
                     const int64_t* __restrict__ idx, const int64_t* __restrict__ map, int64_t map_len, int64_t n_cap,
                     const int64_t* d_n, char* __restrict__ out, int64_t dst_pitch, const float* __restrict__ ts_table,
                     float* __restrict__ out_ts, int32_t* d_status) {
   const int64_t n = eff_count(n_cap, d_n);
-  const int64_t total = n * lanes_per_row;
+  const int64_t total = n * split.lanes;
   const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
   for (int64_t q0 = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q0 < total; q0 += stride * kLaneUnroll) {
     V v[kLaneUnroll];
@@ -80,8 +108,9 @@ gather_lanes_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t
       int64_t q = q0 + u * stride;
       dst[u] = nullptr;
       if (q < total) {
-        int64_t i = q / lanes_per_row;
-        uint32_t l = (uint32_t)(q - i * lanes_per_row);
+        int64_t i;
+        uint32_t l;
+        split(q, &i, &l);
         int64_t r;
         if (resolve_row(idx, map, map_len, table_rows, i, true, d_status, &r)) {
           v[u] = ld_stream((const V*)(table + r * src_pitch) + l);
@@ -258,11 +287,11 @@ cache_lookup_kernel(const int32_t* __restrict__ hitmap, int64_t num_ids, const i
 template <typename V>
 __global__ void __launch_bounds__(kLaneThreads)
 cache_copy_kernel(const char* __restrict__ cache_rows, int64_t cache_slots, const char* __restrict__ backing,
-                  uint32_t lanes_per_row, int64_t row_bytes, const int64_t* __restrict__ ids, int64_t n,
+                  LaneSplit split, int64_t row_bytes, const int64_t* __restrict__ ids, int64_t n,
                   const int32_t* __restrict__ slot_ws, const int32_t* __restrict__ rank_ws,
                   const int64_t* __restrict__ cta_miss, char* __restrict__ out, int64_t* __restrict__ miss_pos,
                   int64_t* __restrict__ miss_ids, int64_t* d_counts, int32_t* d_status) {
-  const int64_t total = n * lanes_per_row;
+  const int64_t total = n * split.lanes;
   const int64_t stride = (int64_t)gridDim.x * kLaneThreads;
   if (blockIdx.x == 0 && threadIdx.x == 0) d_counts[0] = n - d_counts[1];
   for (int64_t q0 = (int64_t)blockIdx.x * kLaneThreads + threadIdx.x; q0 < total; q0 += stride * kLaneUnroll) {
@@ -273,8 +302,9 @@ cache_copy_kernel(const char* __restrict__ cache_rows, int64_t cache_slots, cons
       int64_t q = q0 + u * stride;
       dst[u] = nullptr;
       if (q < total) {
-        int64_t i = q / lanes_per_row;
-        uint32_t l = (uint32_t)(q - i * lanes_per_row);
+        int64_t i;
+        uint32_t l;
+        split(q, &i, &l);
         int32_t slot = __ldg(slot_ws + i);
         const char* src = nullptr;
         if (slot >= 0) {
@@ -636,13 +666,13 @@ extern "C" int sgl_gather_rows(const void* table, int64_t table_rows, int64_t ro
     SGL_REQUIRE(vec_ok, SGL_ERR_UNSUPPORTED, "gather_rows: 128-bit mode needs 16-byte aligned rows");
     const uint32_t lanes = (uint32_t)(row_bytes / 16);
     const int grid = stream_grid(n * lanes, kLaneThreads * kLaneUnroll, 8);
-    gather_lanes_kernel<uint4><<<grid, kLaneThreads, 0, stream>>>((const char*)table, table_rows, lanes, src_pitch, idx,
+    gather_lanes_kernel<uint4><<<grid, kLaneThreads, 0, stream>>>((const char*)table, table_rows, LaneSplit(lanes, n * lanes), src_pitch, idx,
                                                                  map, map_len, n, d_n, (char*)out, dst_pitch, ts_table,
                                                                  out_ts, d_status);
   } else {
     const uint32_t lanes = (uint32_t)(row_bytes / 4);
     const int grid = stream_grid(n * lanes, kLaneThreads * kLaneUnroll, 8);
-    gather_lanes_kernel<uint32_t><<<grid, kLaneThreads, 0, stream>>>((const char*)table, table_rows, lanes, src_pitch,
+    gather_lanes_kernel<uint32_t><<<grid, kLaneThreads, 0, stream>>>((const char*)table, table_rows, LaneSplit(lanes, n * lanes), src_pitch,
                                                                     idx, map, map_len, n, d_n, (char*)out, dst_pitch,
                                                                     ts_table, out_ts, d_status);
   }
@@ -707,13 +737,13 @@ extern "C" int sgl_cache_gather(const void* cache_rows, int64_t cache_slots, con
     const uint32_t lanes = (uint32_t)(row_bytes / 16);
     const int grid = stream_grid(n * lanes, kLaneThreads * kLaneUnroll, 8);
     cache_copy_kernel<uint4><<<grid, kLaneThreads, 0, stream>>>((const char*)cache_rows, cache_slots, (const char*)backing,
-                                                               lanes, row_bytes, ids, n, slot_ws, rank_ws, cta_miss,
+                                                               LaneSplit(lanes, n * lanes), row_bytes, ids, n, slot_ws, rank_ws, cta_miss,
                                                                (char*)out, miss_pos, miss_ids, d_counts, d_status);
   } else {
     const uint32_t lanes = (uint32_t)(row_bytes / 4);
     const int grid = stream_grid(n * lanes, kLaneThreads * kLaneUnroll, 8);
     cache_copy_kernel<uint32_t><<<grid, kLaneThreads, 0, stream>>>((const char*)cache_rows, cache_slots,
-                                                                  (const char*)backing, lanes, row_bytes, ids, n, slot_ws,
+                                                                  (const char*)backing, LaneSplit(lanes, n * lanes), row_bytes, ids, n, slot_ws,
                                                                   rank_ws, cta_miss, (char*)out, miss_pos, miss_ids,
                                                                   d_counts, d_status);
   }

@@ -2,8 +2,8 @@
 //
 // Every rank owns a buffer that all ranks of the node map (CUDA IPC):
 //     acks [world]         acks[p] = number of this rank's steps that receiver p has applied (written by p)
-//     meta [world][ring]   meta[q][slot] = (rows << 32) | tag: how many rows sender q pushed here in the step that uses
-//                          the slot.  The receiver learns its row counts from these words, so a plan that was built on
+//     meta [world][ring]   meta[q][slot] = (plain << 63) | (rows << 32) | tag: how many rows sender q pushed here in the
+//                          step that uses the slot, and in which of the two wire forms (below).  The receiver learns its row counts from these words, so a plan that was built on
 //                          the device (its sizes never visit the host) needs no count exchange and no host sync.
 //     stage[world][ring][cap_rows][pitch / 2]   16-byte lines from sender q, ring slot = step % ring
 //
@@ -22,7 +22,8 @@
 //     work as route_unpack_kernel); the last CTA to finish acknowledges the step to every sender.
 //
 // Large messages: tagging doubles the bytes on the wire, which is the wrong trade once a message is bandwidth-bound.
-// A (sender, receiver) pair whose message of a step has at least `bulk_rows` rows (both ends know that count) uses
+// A pair whose message of a step has at least `bulk_rows` rows, and every pair of a step in which the sender pushes at
+// least `bulk_total_rows` rows in total (the link out of a GPU is shared by its pairs), uses
 // plain wire rows instead -- 128-bit stores into the first half of the same staging region -- followed by one
 // system-scope fence per CTA and an arrival counter; the last CTA of the send kernel then writes the pair's meta word,
 // which for such a pair doubles as the "rows have landed" flag (for a small pair the meta word is written up front and
@@ -51,7 +52,8 @@ struct P2PCfg {
   int rank, world, ring;
   int64_t cap_rows;
   uint32_t pitch;           // 32-bit words per wire row; a row occupies pitch / 2 lines
-  int64_t bulk_rows;        // a pair's message with at least this many rows travels as plain rows + flag
+  int64_t bulk_rows;        // a pair's message with at least this many rows travels as plain rows + completion word
+  int64_t bulk_total_rows;  // ... and so does every pair of a step in which this rank sends at least this many rows
   unsigned long long* acks;
   unsigned long long* meta;
   uint4* stage;
@@ -153,8 +155,8 @@ __device__ __forceinline__ int segment_of(const int64_t* off, int world, int64_t
   return p;
 }
 
-__device__ __forceinline__ unsigned long long meta_word(int64_t rows, unsigned long long step) {
-  return ((unsigned long long)rows << 32) | (unsigned long long)(uint32_t)(step + 1);
+__device__ __forceinline__ unsigned long long meta_word(int64_t rows, unsigned long long step, bool plain) {
+  return ((unsigned long long)plain << 63) | ((unsigned long long)rows << 32) | (unsigned long long)(uint32_t)(step + 1);
 }
 
 // A route kernel competes for issue slots with whatever else runs on its SM (warps are scheduled round robin, stream
@@ -204,14 +206,18 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
   const uint32_t quads = c.pitch / 4;
   const uint32_t lane = threadIdx.x & 31u;
   const int64_t ring_slot = (int64_t)(step % c.ring);
+  const bool all_plain = s_off[c.world] >= c.bulk_total_rows;
   bool any_bulk = false;
-  for (int p = 0; p < c.world; ++p) any_bulk |= s_off[p + 1] - s_off[p] >= c.bulk_rows;
+  for (int p = 0; p < c.world; ++p) {
+    const int64_t cnt = s_off[p + 1] - s_off[p];
+    any_bulk |= cnt > 0 && (all_plain || cnt >= c.bulk_rows);
+  }
   // small pairs: the count goes out first, the tagged lines validate themselves
   if (ok && blockIdx.x == 0 && threadIdx.x < c.world) {
     const int64_t cnt = s_off[threadIdx.x + 1] - s_off[threadIdx.x];
-    if (cnt < c.bulk_rows) {
+    if (!(cnt > 0 && (all_plain || cnt >= c.bulk_rows))) {
       volatile unsigned long long* m = c.peer_meta[threadIdx.x] + (int64_t)c.rank * c.ring + ring_slot;
-      *m = meta_word(cnt, step);
+      *m = meta_word(cnt, step, false);
     }
   }
   const int64_t n_send = ok ? s_off[c.world] : 0;
@@ -228,7 +234,7 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
       if (lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
       r = -2;                                             // sent as zeros with slot -1, which the receiver skips
     }
-    const bool bulk = s_off[p + 1] - s_off[p] >= c.bulk_rows;
+    const bool bulk = all_plain || s_off[p + 1] - s_off[p] >= c.bulk_rows;
     // the pair's region starts at the same place in both layouts; a plain row takes pitch / 4 lines, a tagged one pitch / 2
     uint4* region = c.peer_stage[p] + slot_base * (c.pitch / 2);
     uint4* dst = region + in_seg * (bulk ? c.pitch / 4 : c.pitch / 2);
@@ -258,9 +264,9 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
   const bool failed = !ok || (d_status && (*(volatile int32_t*)d_status & SGL_DEV_TIMEOUT));
   if (threadIdx.x < c.world && !failed) {
     const int64_t cnt = s_off[threadIdx.x + 1] - s_off[threadIdx.x];
-    if (cnt >= c.bulk_rows) {
+    if (cnt > 0 && (all_plain || cnt >= c.bulk_rows)) {
       volatile unsigned long long* m = c.peer_meta[threadIdx.x] + (int64_t)c.rank * c.ring + ring_slot;
-      *m = meta_word(cnt, step);
+      *m = meta_word(cnt, step, true);
     }
   }
   if (threadIdx.x == 0) *done_counter = 0;
@@ -277,6 +283,7 @@ p2p_recv_kernel(P2PCfg c, Splits expect, int check, uint32_t width, float* __res
   __shared__ bool s_last;
   __shared__ int64_t s_cnt[kMaxWorld];
   __shared__ int64_t s_off[kMaxWorld + 1];
+  __shared__ bool s_plain[kMaxWorld];
   pdl_wait();
   pdl_release();
   if (threadIdx.x == 0) s_ok = 1;
@@ -301,7 +308,8 @@ p2p_recv_kernel(P2PCfg c, Splits expect, int check, uint32_t width, float* __res
       }
       if (!got) { s_ok = 0; w = 0; }
     }
-    int64_t cnt = (int64_t)(w >> 32);
+    int64_t cnt = (int64_t)((w >> 32) & 0x7fffffffull);
+    s_plain[threadIdx.x] = (w >> 63) != 0;
     if (cnt > c.cap_rows) cnt = c.cap_rows;
     if (check && s_ok && cnt != expect.off[threadIdx.x + 1] - expect.off[threadIdx.x]) dev_flag(d_status, SGL_DEV_MISMATCH);
     s_cnt[threadIdx.x] = cnt;
@@ -318,7 +326,7 @@ p2p_recv_kernel(P2PCfg c, Splits expect, int check, uint32_t width, float* __res
   for (int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i < n_recv && ok; i += n_warps) {
     const int sdr = segment_of(s_off, c.world, i);
     const uint4* region = c.stage + ((int64_t)sdr * c.ring + ring_slot) * c.cap_rows * (c.pitch / 2);
-    if (s_cnt[sdr] >= c.bulk_rows) {
+    if (s_plain[sdr]) {
       // plain wire row (pitch / 4 quads); volatile loads: the row was written by another GPU
       const uint4* prow = region + (i - s_off[sdr]) * (c.pitch / 4);
       const uint4 qa = load_line(prow + width / 4), qb = load_line(prow + (width + 1) / 4);
@@ -479,8 +487,10 @@ extern "C" int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_r
   c.acks = c.peer_acks[rank];
   c.meta = c.peer_meta[rank];
   c.stage = c.peer_stage[rank];
-  // pairs whose message is at least 2 MiB travel as plain rows (sgl_p2p_route_configure changes the limit)
-  c.bulk_rows = ((2 << 20) + pitch_floats * 4 - 1) / (pitch_floats * 4);
+  // a pair's message of 256 KiB and more, and every pair of a step in which this rank sends four times that in total,
+  // travels as plain rows (sgl_p2p_route_configure changes the limit)
+  c.bulk_rows = ((256 << 10) + pitch_floats * 4 - 1) / (pitch_floats * 4);
+  c.bulk_total_rows = 4 * c.bulk_rows;
   *out_ctx = x;
   return SGL_OK;
 }
@@ -493,7 +503,10 @@ extern "C" int sgl_p2p_route_configure(void* ctx, int64_t wait_ms, int64_t bulk_
                 (long long)wait_ms);
     c.wait_ns = (unsigned long long)wait_ms * 1000000ull;
   }
-  if (bulk_bytes >= 0) c.bulk_rows = bulk_bytes == 0 ? 0 : (bulk_bytes + c.pitch * 4 - 1) / ((int64_t)c.pitch * 4);
+  if (bulk_bytes >= 0) {
+    c.bulk_rows = bulk_bytes == 0 ? 1 : (bulk_bytes + c.pitch * 4 - 1) / ((int64_t)c.pitch * 4);
+    c.bulk_total_rows = 4 * c.bulk_rows;
+  }
   return SGL_OK;
 }
 

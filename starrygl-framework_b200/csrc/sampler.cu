@@ -71,9 +71,36 @@ __device__ __forceinline__ int64_t lane_lower_bound(const int64_t* __restrict__ 
   return lo;
 }
 
+// The same bound through the fence of the row (timestamp of the last edge of every 32-edge block, see sgl_tcsr_fence):
+// the block that holds the answer is found in the fence -- a small array that lives in L2 -- and only that block of the
+// row is read: one or two 128-byte lines of the timestamps per search instead of 32 scattered sectors per round.
+__device__ __forceinline__ int64_t warp_fenced_lower_bound(const int64_t* __restrict__ ts, const int64_t* __restrict__ fence_row,
+                                                           int64_t s, int64_t e, int64_t bound, int lane) {
+  int64_t p0 = s;
+  if (e - s > 32) {
+    const int64_t nb = (e - s + 31) >> 5;
+    const int64_t j = warp_lower_bound(fence_row, 0, nb, bound, lane);
+    if (j >= nb) return e;
+    p0 = s + (j << 5);
+  }
+  const bool less = (p0 + lane < e) && (__ldg(ts + p0 + lane) < bound);
+  return p0 + __popc(__ballot_sync(0xffffffffu, less));
+}
+
+__device__ __forceinline__ int64_t lane_fenced_lower_bound(const int64_t* __restrict__ ts, const int64_t* __restrict__ fence_row,
+                                                           int64_t s, int64_t e, int64_t bound) {
+  if (e - s <= 32) return lane_lower_bound(ts, s, e, bound);
+  const int64_t nb = (e - s + 31) >> 5;
+  const int64_t j = lane_lower_bound(fence_row, 0, nb, bound);
+  if (j >= nb) return e;
+  const int64_t p0 = s + (j << 5), p1 = p0 + 32 < e ? p0 + 32 : e;
+  return lane_lower_bound(ts, p0, p1, bound);
+}
+
 template <int TPW>
 __global__ void __launch_bounds__(kCtaThreads)
-sample_count_kernel(const int64_t* __restrict__ indptr, const int64_t* __restrict__ ts, int64_t num_nodes,
+sample_count_kernel(const int64_t* __restrict__ indptr, const int64_t* __restrict__ ts, const int64_t* __restrict__ fence,
+                    int64_t num_nodes,
                     const int64_t* __restrict__ targets, const int64_t* __restrict__ target_ts, int64_t n_cap,
                     const int64_t* d_n, int fanout, int equal_root_time, int64_t allowed_offset,
                     int64_t* __restrict__ win_lo, int64_t* __restrict__ win_cut, int32_t* __restrict__ cnt,
@@ -91,8 +118,18 @@ sample_count_kernel(const int64_t* __restrict__ indptr, const int64_t* __restric
         dev_flag(d_status, SGL_DEV_BAD_NODE);
       } else {
         int64_t s = __ldg(indptr + node), e = __ldg(indptr + node + 1);
-        cut = lane_lower_bound(ts, s, e, t + (equal_root_time ? 1 : 0));
-        lo = allowed_offset >= 0 ? lane_lower_bound(ts, s, cut, t - allowed_offset) : s;
+        if (fence) {
+          const int64_t* frow = fence + (s >> 5) + node;
+          cut = lane_fenced_lower_bound(ts, frow, s, e, t + (equal_root_time ? 1 : 0));
+          lo = s;
+          if (allowed_offset >= 0) {
+            lo = lane_fenced_lower_bound(ts, frow, s, e, t - allowed_offset);
+            if (lo > cut) lo = cut;
+          }
+        } else {
+          cut = lane_lower_bound(ts, s, e, t + (equal_root_time ? 1 : 0));
+          lo = allowed_offset >= 0 ? lane_lower_bound(ts, s, cut, t - allowed_offset) : s;
+        }
       }
       int64_t cand = cut - lo;
       my_cnt = (int32_t)(cand < fanout ? cand : fanout);
@@ -117,7 +154,14 @@ sample_count_kernel(const int64_t* __restrict__ indptr, const int64_t* __restric
           int64_t s = __ldg(indptr + node), e = __ldg(indptr + node + 1);
           lo = s;
           cut = s;
-          if (e > s) {
+          if (e > s && fence) {
+            const int64_t* frow = fence + (s >> 5) + node;
+            cut = warp_fenced_lower_bound(ts, frow, s, e, t + (equal_root_time ? 1 : 0), lane);
+            if (allowed_offset >= 0 && cut > s) {
+              lo = warp_fenced_lower_bound(ts, frow, s, e, t - allowed_offset, lane);
+              if (lo > cut) lo = cut;
+            }
+          } else if (e > s) {
             cut = warp_lower_bound(ts, s, e, t + (equal_root_time ? 1 : 0), lane);
             if (allowed_offset >= 0 && cut > s) lo = warp_lower_bound(ts, s, cut, t - allowed_offset, lane);
           }
@@ -283,13 +327,13 @@ extern "C" size_t sgl_sample_ws_bytes(int64_t n_targets) {
 
 template <int TPW>
 static void launch_sample(int64_t ctas, cudaStream_t stream, const int64_t* indptr, const int64_t* nbr, const int64_t* ts,
-                          const int64_t* eid, int64_t num_nodes, const int64_t* targets, const int64_t* target_ts,
+                          const int64_t* eid, const int64_t* fence, int64_t num_nodes, const int64_t* targets, const int64_t* target_ts,
                           int64_t n_targets, const int64_t* d_n, int fanout, int policy, int equal_root_time,
                           int64_t allowed_offset, int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* win_lo,
                           int64_t* win_cut, int32_t* cnt, int64_t* cta_sums, unsigned int* done, int64_t* out_nbr,
                           int64_t* out_dst, int64_t* out_ts, float* out_dt, int64_t* out_dt_i64, int64_t* out_eid,
                           int64_t* out_offsets, int32_t* d_status) {
-  sample_count_kernel<TPW><<<(unsigned)ctas, kCtaThreads, 0, stream>>>(indptr, ts, num_nodes, targets, target_ts,
+  sample_count_kernel<TPW><<<(unsigned)ctas, kCtaThreads, 0, stream>>>(indptr, ts, fence, num_nodes, targets, target_ts,
                                                                        n_targets, d_n, fanout, equal_root_time,
                                                                        allowed_offset, win_lo, win_cut, cnt, cta_sums, done,
                                                                        out_offsets, d_status);
@@ -300,13 +344,12 @@ static void launch_sample(int64_t ctas, cudaStream_t stream, const int64_t* indp
                                                                       out_dt, out_dt_i64, out_eid, out_offsets);
 }
 
-extern "C" int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
-                                int64_t num_nodes, const int64_t* targets, const int64_t* target_ts, int64_t n_targets,
-                                const int64_t* d_n, int fanout, int policy, int equal_root_time, int64_t allowed_offset,
-                                int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* out_nbr,
-                                int64_t* out_dst, int64_t* out_ts, float* out_dt, int64_t* out_dt_i64,
-                                int64_t* out_eid, int64_t* out_offsets, int32_t* d_status, void* ws, size_t ws_bytes,
-                                void* stream_) {
+static int sample_layer_impl(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                             const int64_t* fence, int64_t num_nodes, const int64_t* targets, const int64_t* target_ts,
+                             int64_t n_targets, const int64_t* d_n, int fanout, int policy, int equal_root_time,
+                             int64_t allowed_offset, int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* out_nbr,
+                             int64_t* out_dst, int64_t* out_ts, float* out_dt, int64_t* out_dt_i64, int64_t* out_eid,
+                             int64_t* out_offsets, int32_t* d_status, void* ws, size_t ws_bytes, void* stream_) {
   SGL_NVTX("sgl_sample_layer");
   cudaStream_t stream = (cudaStream_t)stream_;
   SGL_REQUIRE(n_targets >= 0 && num_nodes >= 0, SGL_ERR_ARG, "sample_layer: negative size");
@@ -335,7 +378,7 @@ extern "C" int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const
               sgl_sample_ws_bytes(n_targets));
   SGL_CUDA_CHECK(cudaMemsetAsync(done, 0, sizeof(unsigned int), stream));
 #define SGL_SAMPLE_ARGS                                                                                               \
-  ctas, stream, indptr, nbr, ts, eid, num_nodes, targets, target_ts, n_targets, d_n, fanout, policy, equal_root_time, \
+  ctas, stream, indptr, nbr, ts, eid, fence, num_nodes, targets, target_ts, n_targets, d_n, fanout, policy, equal_root_time, \
       allowed_offset, keep_root_time, seed, rng_stream, win_lo, win_cut, cnt, cta_sums, done, out_nbr, out_dst,       \
       out_ts, out_dt, out_dt_i64, out_eid, out_offsets, d_status
   if (tpw == 1) launch_sample<1>(SGL_SAMPLE_ARGS);
@@ -344,6 +387,45 @@ extern "C" int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const
 #undef SGL_SAMPLE_ARGS
   SGL_LAUNCH_CHECK();
   return SGL_OK;
+}
+
+extern "C" int sgl_sample_layer(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                                int64_t num_nodes, const int64_t* targets, const int64_t* target_ts, int64_t n_targets,
+                                const int64_t* d_n, int fanout, int policy, int equal_root_time, int64_t allowed_offset,
+                                int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* out_nbr,
+                                int64_t* out_dst, int64_t* out_ts, float* out_dt, int64_t* out_dt_i64,
+                                int64_t* out_eid, int64_t* out_offsets, int32_t* d_status, void* ws, size_t ws_bytes,
+                                void* stream) {
+  return sample_layer_impl(indptr, nbr, ts, eid, nullptr, num_nodes, targets, target_ts, n_targets, d_n, fanout, policy,
+                           equal_root_time, allowed_offset, keep_root_time, seed, rng_stream, out_nbr, out_dst, out_ts, out_dt,
+                           out_dt_i64, out_eid, out_offsets, d_status, ws, ws_bytes, stream);
+}
+
+extern "C" int sgl_sample_layer_fenced(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                                       const int64_t* fence, int64_t num_nodes, const int64_t* targets, const int64_t* target_ts,
+                                       int64_t n_targets, const int64_t* d_n, int fanout, int policy, int equal_root_time,
+                                       int64_t allowed_offset, int keep_root_time, uint64_t seed, uint32_t rng_stream,
+                                       int64_t* out_nbr, int64_t* out_dst, int64_t* out_ts, float* out_dt, int64_t* out_dt_i64,
+                                       int64_t* out_eid, int64_t* out_offsets, int32_t* d_status, void* ws, size_t ws_bytes,
+                                       void* stream) {
+  return sample_layer_impl(indptr, nbr, ts, eid, fence, num_nodes, targets, target_ts, n_targets, d_n, fanout, policy,
+                           equal_root_time, allowed_offset, keep_root_time, seed, rng_stream, out_nbr, out_dst, out_ts, out_dt,
+                           out_dt_i64, out_eid, out_offsets, d_status, ws, ws_bytes, stream);
+}
+
+extern "C" int sgl_sample_gather_fenced(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
+                                        const int64_t* fence, int64_t num_nodes, const int64_t* targets, const int64_t* target_ts,
+                                        int64_t n_targets, int fanout, int policy, int equal_root_time, int64_t allowed_offset,
+                                        int keep_root_time, uint64_t seed, uint32_t rng_stream, int64_t* out_nbr, int64_t* out_dst,
+                                        int64_t* out_ts, float* out_dt, int64_t* out_eid, int64_t* out_offsets,
+                                        const void* feat_table, int64_t feat_rows, int64_t row_bytes, int64_t src_pitch,
+                                        void* out_feats, int gather_mode, int32_t* d_status, void* ws, size_t ws_bytes, void* stream) {
+  int rc = sample_layer_impl(indptr, nbr, ts, eid, fence, num_nodes, targets, target_ts, n_targets, nullptr, fanout, policy,
+                             equal_root_time, allowed_offset, keep_root_time, seed, rng_stream, out_nbr, out_dst, out_ts, out_dt,
+                             nullptr, out_eid, out_offsets, d_status, ws, ws_bytes, stream);
+  if (rc != SGL_OK || n_targets == 0) return rc;
+  return sgl_gather_rows(feat_table, feat_rows, row_bytes, src_pitch, out_eid, nullptr, 0, n_targets * fanout,
+                         out_offsets + n_targets, out_feats, row_bytes, nullptr, nullptr, gather_mode, d_status, stream);
 }
 
 extern "C" int sgl_sample_gather(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,

@@ -190,3 +190,42 @@ extern "C" int sgl_tcsr_build(int64_t num_nodes, int64_t m, const int64_t* key, 
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Search index over the time-sorted rows ("fence"): for every block of 32 consecutive edges of a row the timestamp of
+// the block's last edge.  Row r (edges [s, e)) owns the entries fence[(s >> 5) + r + j], j < ceil((e - s) / 32) -- a
+// placement that needs no pointer array of its own: consecutive rows never overlap because
+// floor((s + d) / 32) - floor(s / 32) >= ceil(d / 32) - 1.  About 1.6 % of the adjacency's size, so it stays in L2 while
+// the timestamps themselves (8 bytes per edge) do not; a time-range search walks the fence and then reads ONE block of
+// the row.
+// ---------------------------------------------------------------------------------------------------------------
+namespace sgl {
+namespace {
+__global__ void __launch_bounds__(256)
+tcsr_fence_kernel(const int64_t* __restrict__ indptr, const int64_t* __restrict__ ts, int64_t num_nodes, int64_t* __restrict__ fence) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * 8;
+  for (int64_t r = ((int64_t)blockIdx.x * 256 + threadIdx.x) >> 5; r < num_nodes; r += warps) {
+    const int64_t s = __ldg(indptr + r), e = __ldg(indptr + r + 1);
+    const int64_t nb = (e - s + 31) >> 5;
+    int64_t* row = fence + (s >> 5) + r;
+    for (int64_t j = lane; j < nb; j += 32) {
+      const int64_t last = s + (j << 5) + 31;
+      row[j] = __ldg(ts + (last < e ? last : e - 1));
+    }
+  }
+}
+}  // namespace
+}  // namespace sgl
+
+extern "C" int64_t sgl_tcsr_fence_len(int64_t num_nodes, int64_t m) { return (m >> 5) + num_nodes + 1; }
+
+extern "C" int sgl_tcsr_fence(const int64_t* indptr, const int64_t* ts, int64_t num_nodes, int64_t m, int64_t* out_fence,
+                              void* stream_) {
+  SGL_REQUIRE(num_nodes >= 0 && m >= 0, SGL_ERR_ARG, "tcsr_fence: negative size");
+  if (num_nodes == 0 || m == 0) return SGL_OK;
+  SGL_REQUIRE(indptr && ts && out_fence, SGL_ERR_ARG, "tcsr_fence: null array");
+  tcsr_fence_kernel<<<stream_grid(num_nodes, 8, 16), 256, 0, (cudaStream_t)stream_>>>(indptr, ts, num_nodes, out_fence);
+  SGL_LAUNCH_CHECK();
+  return SGL_OK;
+}

@@ -35,10 +35,16 @@ _SIGNATURES = {
     "sgl_sample_ws_bytes": (_sz, [_i64]),
     "sgl_sample_layer": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i64, _i32, _u64, _u32,
                                 _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "sgl_tcsr_fence_len": (_i64, [_i64, _i64]),
+    "sgl_tcsr_fence": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
+    "sgl_sample_layer_fenced": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _vp, _i32, _i32, _i32, _i64, _i32, _u64, _u32,
+                                       _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "sgl_sample_layer_static": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _i32, _u64, _u32,
                                        _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "sgl_sample_gather": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _i32, _u64, _u32,
                                  _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _vp, _vp, _sz, _vp]),
+    "sgl_sample_gather_fenced": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _i64, _i32, _u64, _u32,
+                                        _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i32, _vp, _vp, _sz, _vp]),
     "sgl_unique_pairs_ws_bytes": (_sz, [_i64]),
     "sgl_unique_pairs": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i32, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp,
                                 _vp, _sz, _vp]),

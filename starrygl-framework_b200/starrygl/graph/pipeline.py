@@ -110,7 +110,7 @@ class SampleGatherPipeline:
             v = C.c_void_p
             self._a_roots, self._a_ts, self._a_n, self._a_rng = v(0), v(0), C.c_int64(0), C.c_uint32(0)
             self._fused = [v(g_.indptr.data_ptr()), v(g_.nbr.data_ptr()), v(g_.ts.data_ptr()), v(g_.eid.data_ptr()),
-                           C.c_int64(g_.num_nodes), self._a_roots, self._a_ts, self._a_n, C.c_int(self.k),
+                           v(g_.fence.data_ptr() if g_.fence is not None else 0), C.c_int64(g_.num_nodes), self._a_roots, self._a_ts, self._a_n, C.c_int(self.k),
                            C.c_int(a["pol"]), C.c_int(a["eq"]), C.c_int64(a["off"]), C.c_int(a["keep"]),
                            C.c_uint64(a["seed"]), self._a_rng, v(self.nbr.data_ptr()), v(self.dst.data_ptr()),
                            v(self.ts.data_ptr()), v(self.dt.data_ptr()), v(self.eid.data_ptr()),
@@ -118,7 +118,7 @@ class SampleGatherPipeline:
                            C.c_int64(self.row_bytes), C.c_int64(self.src_pitch), v(self.out_feats.data_ptr()),
                            C.c_int(self.mode), v(self.status.ptr()), v(self.ws.data_ptr()), C.c_size_t(self.ws.numel()),
                            v(self.stream.cuda_stream)]
-            self._fn = self.L.sgl_sample_gather
+            self._fn = self.L.sgl_sample_gather_fenced
 
     def run_device_ptr(self, roots_ptr: int, root_ts_ptr: int, n: int, rng_stream: int = 0):
         """:meth:`run_device` for callers that already hold raw device pointers: one foreign call per batch
@@ -239,11 +239,12 @@ class SampleGatherPipeline:
         if n > self.max_roots:
             raise _C.SglError(f"batch of {n} roots exceeds max_roots={self.max_roots}")
         L, g, a, sp = self.L, self.g, self.args, self.stream.cuda_stream
-        rc = L.sgl_sample_layer(g.indptr.data_ptr(), g.nbr.data_ptr(), g.ts.data_ptr(), g.eid.data_ptr(), g.num_nodes,
-                                roots.data_ptr(), root_ts.data_ptr(), n, None, self.k, a["pol"], a["eq"], a["off"],
-                                a["keep"], a["seed"], rng_stream, self.nbr.data_ptr(), self.dst.data_ptr(),
-                                self.ts.data_ptr(), self.dt.data_ptr(), None, self.eid.data_ptr(),
-                                self.offsets.data_ptr(), self.status.ptr(), self.ws.data_ptr(), self.ws.numel(), sp)
+        rc = L.sgl_sample_layer_fenced(g.indptr.data_ptr(), g.nbr.data_ptr(), g.ts.data_ptr(), g.eid.data_ptr(),
+                                       None if g.fence is None else g.fence.data_ptr(), g.num_nodes,
+                                       roots.data_ptr(), root_ts.data_ptr(), n, None, self.k, a["pol"], a["eq"], a["off"],
+                                       a["keep"], a["seed"], rng_stream, self.nbr.data_ptr(), self.dst.data_ptr(),
+                                       self.ts.data_ptr(), self.dt.data_ptr(), None, self.eid.data_ptr(),
+                                       self.offsets.data_ptr(), self.status.ptr(), self.ws.data_ptr(), self.ws.numel(), sp)
         _C.check(rc)
         if self.feats is not None:
             if gather_events:
@@ -263,12 +264,13 @@ class SampleGatherPipeline:
         if n > self.max_roots:
             raise _C.SglError(f"batch of {n} roots exceeds max_roots={self.max_roots}")
         L, g, a = self.L, self.g, self.args
-        rc = L.sgl_sample_layer(g.indptr.data_ptr(), g.nbr.data_ptr(), g.ts.data_ptr(), g.eid.data_ptr(), g.num_nodes,
-                                roots.data_ptr(), root_ts.data_ptr(), n, None, self.k, a["pol"], a["eq"], a["off"],
-                                a["keep"], a["seed"], rng_stream, self.nbr.data_ptr(), self.dst.data_ptr(),
-                                self.ts.data_ptr(), self.dt.data_ptr(), None, self.eid.data_ptr(),
-                                self.offsets.data_ptr(), self.status.ptr(), self.ws.data_ptr(), self.ws.numel(),
-                                self.stream.cuda_stream)
+        rc = L.sgl_sample_layer_fenced(g.indptr.data_ptr(), g.nbr.data_ptr(), g.ts.data_ptr(), g.eid.data_ptr(),
+                                       None if g.fence is None else g.fence.data_ptr(), g.num_nodes,
+                                       roots.data_ptr(), root_ts.data_ptr(), n, None, self.k, a["pol"], a["eq"], a["off"],
+                                       a["keep"], a["seed"], rng_stream, self.nbr.data_ptr(), self.dst.data_ptr(),
+                                       self.ts.data_ptr(), self.dt.data_ptr(), None, self.eid.data_ptr(),
+                                       self.offsets.data_ptr(), self.status.ptr(), self.ws.data_ptr(), self.ws.numel(),
+                                       self.stream.cuda_stream)
         _C.check(rc)
 
     # ---- host inputs / host results --------------------------------------------------------------------

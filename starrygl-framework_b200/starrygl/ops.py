@@ -69,6 +69,7 @@ class TCSR:
     perm: Optional[torch.Tensor]
     ts_min: int
     ts_max: int
+    fence: Optional[torch.Tensor] = None    # timestamp of the last edge of every 32-edge block of a row (search index)
 
     @property
     def num_edges(self):
@@ -79,8 +80,9 @@ class TCSR:
         return self.indptr.device
 
 
-def tcsr_build(key, nbr, ts, eid, num_nodes: int, want_perm: bool = False) -> TCSR:
-    """Build the T-CSR keyed by ``key``.  Synchronises the stream once.  Raises on out-of-range keys."""
+def tcsr_build(key, nbr, ts, eid, num_nodes: int, want_perm: bool = False, want_fence: bool = True) -> TCSR:
+    """Build the T-CSR keyed by ``key`` (and, unless ``want_fence`` is off, the search index the sampler walks before it
+    touches a row).  Synchronises the stream once.  Raises on out-of-range keys."""
     L = _C.lib()
     key, nbr, ts = _i64(key), _i64(nbr), _i64(ts)
     eid = None if eid is None else _i64(eid)
@@ -95,7 +97,11 @@ def tcsr_build(key, nbr, ts, eid, num_nodes: int, want_perm: bool = False) -> TC
     _, wp, wn = _C.workspace(L.sgl_tcsr_build_ws_bytes(num_nodes, m), dev)
     _C.check(L.sgl_tcsr_build(num_nodes, m, _C.ptr(key), _C.ptr(nbr), _C.ptr(ts), _C.ptr(eid), _C.ptr(indptr),
                               _C.ptr(o_nbr), _C.ptr(o_ts), _C.ptr(o_eid), _C.ptr(perm), rng, wp, wn, _C.stream_ptr()))
-    return TCSR(num_nodes, indptr, o_nbr, o_ts, o_eid, perm, int(rng[0]), int(rng[1]))
+    fence = None
+    if want_fence and m and num_nodes:
+        fence = torch.empty(L.sgl_tcsr_fence_len(num_nodes, m), dtype=I64, device=dev)
+        _C.check(L.sgl_tcsr_fence(_C.ptr(indptr), _C.ptr(o_ts), num_nodes, m, _C.ptr(fence), _C.stream_ptr()))
+    return TCSR(num_nodes, indptr, o_nbr, o_ts, o_eid, perm, int(rng[0]), int(rng[1]), fence)
 
 
 # --------------------------------------------------------------------------------------------------------------
@@ -145,7 +151,7 @@ def sample_layer(g: TCSR, targets, target_ts, fanout: int, policy="recent", *, d
     o_dti = torch.empty(cap, dtype=I64, device=dev) if want_dt_i64 else None
     pol = _C.POLICY[policy] if isinstance(policy, str) else int(policy)
     _, wp, wn = _C.workspace(L.sgl_sample_ws_bytes(n), dev)
-    _C.check(L.sgl_sample_layer(_C.ptr(g.indptr), _C.ptr(g.nbr), _C.ptr(g.ts), _C.ptr(g.eid), g.num_nodes,
+    _C.check(L.sgl_sample_layer_fenced(_C.ptr(g.indptr), _C.ptr(g.nbr), _C.ptr(g.ts), _C.ptr(g.eid), _C.ptr(g.fence), g.num_nodes,
                                 _C.ptr(targets), _C.ptr(target_ts), n, _C.ptr(d_n), int(fanout), pol,
                                 int(bool(equal_root_time)), int(allowed_offset), int(bool(keep_root_time)),
                                 int(seed) & (2 ** 64 - 1), int(rng_stream) & 0xFFFFFFFF, _C.ptr(o_nbr), _C.ptr(o_dst),

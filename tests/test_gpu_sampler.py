@@ -155,3 +155,33 @@ def test_large_batch_properties():
         cut = np.searchsorted(row, qt[i], side="left")
         assert cnt[i] == min(cut, 20)
         assert np.array_equal(o_ts[offs[i]:offs[i + 1]], row[cut - cnt[i]:cut])
+
+
+def test_fence_index_and_search_through_it():
+    """The per-row search index (timestamp of the last edge of every 32-edge block) against numpy, and sampling with and
+    without it: identical results -- it only changes which memory the time-range search reads."""
+    from starrygl import ops
+    z = random_graph(3, 300, 90000, 40000, hub=50000)
+    key, nbr = z["dst"], z["src"]
+    g = ops.tcsr_build(cu(key), cu(nbr), cu(z["ts"]), cu(z["eid"]), int(z["n"]))
+    g0 = ops.tcsr_build(cu(key), cu(nbr), cu(z["ts"]), cu(z["eid"]), int(z["n"]), want_fence=False)
+    assert g0.fence is None and g.fence is not None
+    indptr, ts, fence = npy(g.indptr), npy(g.ts), npy(g.fence)
+    assert len(fence) == (len(ts) >> 5) + int(z["n"]) + 1
+    for r in range(int(z["n"])):
+        s, e = indptr[r], indptr[r + 1]
+        nb = (e - s + 31) // 32
+        last = np.minimum(s + 32 * np.arange(nb) + 31, e - 1)
+        assert np.array_equal(fence[(s >> 5) + r:(s >> 5) + r + nb], ts[last]), r
+    rng = np.random.default_rng(5)
+    for n_q in (700, 20000, 300000):          # one, four and thirty-two targets per warp
+        q = rng.integers(0, z["n"], n_q).astype(np.int64)
+        q[: n_q // 10] = 0                     # the hub row
+        qt = rng.integers(-5, 40010, n_q).astype(np.int64)
+        for kw in ({}, {"allowed_offset": 300, "equal_root_time": True}):
+            for policy in ("recent", "uniform"):
+                a = ops.sample_layer(g, cu(q), cu(qt), 10, policy, seed=9, **kw)
+                b = ops.sample_layer(g0, cu(q), cu(qt), 10, policy, seed=9, **kw)
+                n = a.total()
+                assert n == b.total() and torch.equal(a.offsets, b.offsets)
+                assert torch.equal(a.eid[:n], b.eid[:n]) and torch.equal(a.nbr[:n], b.nbr[:n]) and torch.equal(a.ts[:n], b.ts[:n])
