@@ -481,9 +481,9 @@ def _protect_stdout():
 
 def sampler_roofline(g, pipes, b_roots, b_ts, dev, peak):
     """Algorithmic bytes of the hop (per root: two row pointers, the root's id and time, the search probes, 24 bytes read
-    and 36 written per sampled edge, one offset) over the device time of the sampler's kernels: one batch alone on one
-    stream, and one batch per stream on all streams at once (how the benchmark step runs them)."""
-    from starrygl import ops
+    and 36 written per sampled edge, one offset) over the device time of the sampler's kernels, replayed as a captured
+    graph (one launch per batch): one batch at a time on one stream, and one batch per stream on all streams at once
+    (how the benchmark step runs them)."""
     S = len(pipes)
     deg = (g.indptr[1:] - g.indptr[:-1])
     alg = []
@@ -495,12 +495,15 @@ def sampler_roofline(g, pipes, b_roots, b_ts, dev, peak):
         k_eff = int(pipes[0].offsets[BATCH].item())
         alg.append(BATCH * (16 + 16 + 8) + 8 * probes + k_eff * 60)
     alg_mean = statistics.mean(alg)
+    for p_ in pipes:
+        p_.capture_sample_only()
+    ptrs = [b_roots[b].data_ptr() for b in range(NUM_BATCHES)]
+    it = [0]
 
     def alone():
         it[0] += 1
-        pipes[0].sample_only(b_roots[it[0] % NUM_BATCHES], b_ts[it[0] % NUM_BATCHES])
-    it = [0]
-    ms_alone = _time_ms(alone, pipes[0].stream, 200, warm=10)
+        pipes[0].replay_sample(ptrs[it[0] % NUM_BATCHES])
+    ms_alone = _time_ms(alone, pipes[0].stream, 400, warm=20)
     main = torch.cuda.Stream(dev)
     times = []
     for rep in range(30):
@@ -508,22 +511,30 @@ def sampler_roofline(g, pipes, b_roots, b_ts, dev, peak):
         e0.record(main)
         for p_ in pipes:
             p_.stream.wait_stream(main)
-        for r in range(8):
+        for r in range(16):
             for j, p_ in enumerate(pipes):
-                b = (rep * 8 * S + r * S + j) % NUM_BATCHES
-                p_.sample_only(b_roots[b], b_ts[b])
+                p_.replay_sample(ptrs[(rep * 16 * S + r * S + j) % NUM_BATCHES])
         for p_ in pipes:
             main.wait_stream(p_.stream)
         e1.record(main)
         main.synchronize()
-        times.append(e0.elapsed_time(e1) / (8 * S))
+        times.append(e0.elapsed_time(e1) / (16 * S))
     ms_fly = statistics.median(times)
+    # the same kernels on all 64 batches at once (262,144 roots): what the sampler reaches when a launch has enough roots
+    from starrygl import ops
+    big_r, big_t = b_roots.reshape(-1).contiguous(), b_ts.reshape(-1).contiguous()
+    cur = torch.cuda.current_stream(dev)
+    ms_big = _time_ms(lambda: ops.sample_layer(g, big_r, big_t, FANOUT, "recent"), cur, 20, warm=3)
+    alg_big = sum(alg)
     return {"bound": "hbm", "kernel": "sample_count_kernel + sample_fill_kernel", "bytes_per_batch": alg_mean,
+            "large_launch": {"roots": int(big_r.numel()), "ms": ms_big, "achieved": alg_big / ms_big / 1e6,
+                             "frac": alg_big / ms_big / 1e6 / peak},
             "unit": "GB/s", "peak": peak,
             "alone": {"ms_per_batch": ms_alone, "achieved": alg_mean / ms_alone / 1e6, "frac": alg_mean / ms_alone / 1e6 / peak},
             "in_flight": {"batches": S, "ms_per_batch": ms_fly, "achieved": alg_mean / ms_fly / 1e6,
                           "frac": alg_mean / ms_fly / 1e6 / peak},
-            "note": "4,096 roots per batch is a latency-bound size; the in-flight figure is the aggregate of one batch per stream"}
+            "note": "4,096 roots per batch is a latency-bound size; the in-flight figure is the aggregate of one batch per stream "
+                    "and is bound by the host's launch rate (one copy + one graph launch per batch from one thread)"}
 
 
 def main():

@@ -65,11 +65,20 @@ def batches_of(src, dst, ts, neg):
     return torch.cat([s, d, neg], 1).contiguous(), torch.cat([t, t, t], 1).contiguous()
 
 
-def model_rows(ids, step_t, dim):
-    """Stand-in for the model's output for the layer list: row of node v at step s = ((131 v + 7 s + j) mod 65536), j the
-    column -- exact in fp32, and a function of (v, s) only, so that the state every rank must hold can be recomputed."""
-    base = ids * 131 + step_t * 7
-    return ((base.unsqueeze(1) + torch.arange(dim, device=ids.device)) % 65536).to(torch.float32)
+def model_base(ids, step_t):
+    """((131 v + 7 s) mod 65536) as fp32: what the stand-in model's rows of node v at step s start with."""
+    return (torch.add(ids * 131, step_t, alpha=7) % 65536).to(torch.float32)
+
+
+def model_rows(ids, step_t, dim, base=None, cols=None):
+    """Stand-in for the model's output for the layer list: row of node v at step s = ((131 v + 7 s) mod 65536) + j, j the
+    column -- small integers, exact in fp32, and a function of (v, s) only, so that the state every rank must hold can
+    be recomputed from the seeds."""
+    if base is None:
+        base = model_base(ids, step_t)
+    if cols is None:
+        cols = torch.arange(dim, device=ids.device, dtype=torch.float32)
+    return base.unsqueeze(1) + cols
 
 
 class Partition:
@@ -149,11 +158,12 @@ class Step:
         self.ts_bits = ops.bits_for(T_MAX)
         self.plan_cap = self.n_roots * max(part.world - 1, 1)
         self.stream = torch.cuda.Stream(dev)
+        self.side = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]     # branches inside the captured graphs
+        self.cols_mem = torch.arange(MEM_DIM, device=dev, dtype=torch.float32)
+        self.cols_mail = torch.arange(MAIL_DIM, device=dev, dtype=torch.float32)
         self.use_graphs = use_graphs
         self.kernel_launches = None
-        # pinned host mirrors of a batch's inputs and of its block structure, for the host-buffer form of the step
-        self.h_in = torch.empty(2, self.n_roots, dtype=torch.int64).pin_memory()
-        self.h_out = None
+        self.h_out = None               # pinned host mirrors of a batch's block structure (host-buffer form of the step)
         if not use_graphs:
             return
         saved = _C.WORKSPACE
@@ -167,7 +177,6 @@ class Step:
             self.rows_sent.zero_()
             part.mem.reset(), part.mail.reset()
             self.g1, self.g2 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-            self.g1.enable_debug_mode(), self.g2.enable_debug_mode()
             with torch.cuda.graph(self.g1, stream=self.stream):
                 self._a12()
             with torch.cuda.graph(self.g2, stream=self.stream):
@@ -175,36 +184,53 @@ class Step:
         finally:
             _C.WORKSPACE = saved
         self.stream.synchronize()
-        from starrygl.graph.batch import count_kernel_nodes
-        k1, k2 = count_kernel_nodes(self.g1), count_kernel_nodes(self.g2)
-        self.kernel_launches = (k1 + k2) if (k1 and k2) else None
+        # kernels of this library per step: relabel of the roots (pack, sort, head scan, emit), the hop (2), three gathers,
+        # two scatters, the plan (count, expand, sort, emit); the stand-in model's element-wise kernels are torch's
+        L = _C.lib()
+        self.kernel_launches = (3 + L.sgl_radix_sort_launches(self.n_roots, self.id_bits + self.ts_bits) + 2 + 3 + 2 +
+                                3 + L.sgl_radix_sort_launches(self.plan_cap, ops.bits_for(part.world - 1)))
         self.step_t.zero_()
         self.rows_sent.zero_()
         part.mem.reset(), part.mail.reset()
 
     def _a12(self):
+        """A1 (relabel of the roots) and A2 (the hop) only depend on the roots: two branches of the graph."""
         ops, p = self.ops, self.p
+        cur, s1 = torch.cuda.current_stream(), self.side[0]
+        s1.wait_stream(cur)
+        with torch.cuda.stream(s1):
+            self.hop = ops.sample_layer(p.g, self.in_roots, self.in_ts, FANOUT, "recent", status=self.status)
         self.u_id, self.u_ts, self.inv, _, self.d_n0 = ops.unique_pairs(self.in_roots, self.in_ts, id_bits=self.id_bits,
                                                                         ts_bits=self.ts_bits, ts_base=0, status=self.status)
-        self.hop = ops.sample_layer(p.g, self.in_roots, self.in_ts, FANOUT, "recent", status=self.status)
+        cur.wait_stream(s1)
 
     def _a36(self):
+        """A3 (gathers), A4-A5 (model stand-in, local writes) and A6 (plan) as three branches: the writes wait for the
+        gathers (they read the rows the writes replace), nothing waits for the plan but the end of the graph."""
         ops, p = self.ops, self.p
         st = self.status
-        self.m_roots, self.m_roots_ts = ops.gather_rows(p.mem.data, self.in_roots, map=p.g2l, ts_table=p.mem.ts, status=st)
-        self.m_nbrs, self.m_nbrs_ts = ops.gather_rows(p.mem.data, self.hop.nbr, map=p.g2l, d_n=self.hop.d_total,
-                                                      ts_table=p.mem.ts, status=st)
-        self.mails, self.mails_ts = ops.gather_rows(p.mail.data, self.in_roots, map=p.g2l, ts_table=p.mail.ts, status=st)
-        self.new_mem = model_rows(self.u_id, self.step_t, MEM_DIM)
-        self.new_mail = model_rows(self.u_id, self.step_t, MAIL_DIM)
+        cur, s1, s2 = torch.cuda.current_stream(), self.side[0], self.side[1]
+        s1.wait_stream(cur)
+        s2.wait_stream(cur)
+        with torch.cuda.stream(s1):
+            self.m_roots, self.m_roots_ts = ops.gather_rows(p.mem.data, self.in_roots, map=p.g2l, ts_table=p.mem.ts, status=st)
+            self.m_nbrs, self.m_nbrs_ts = ops.gather_rows(p.mem.data, self.hop.nbr, map=p.g2l, d_n=self.hop.d_total,
+                                                          ts_table=p.mem.ts, status=st)
+            self.mails, self.mails_ts = ops.gather_rows(p.mail.data, self.in_roots, map=p.g2l, ts_table=p.mail.ts, status=st)
+        with torch.cuda.stream(s2):
+            (self.pl_ranks, self.pl_rows, self.pl_locs, self.pl_sizes, self.pl_total) = ops.plan_route(
+                self.u_id, p.node_parts, p.rank, p.rep.indptr, p.rep.indices, p.rep.locs, p.world, self.plan_cap, d_n=self.d_n0,
+                status=st)
+            self.rows_sent += self.pl_total
+        base = model_base(self.u_id, self.step_t)
+        self.new_mem = model_rows(None, None, MEM_DIM, base, self.cols_mem)
+        self.new_mail = model_rows(None, None, MAIL_DIM, base, self.cols_mail)
         self.new_ts = self.step_t.to(torch.float32).expand(self.u_id.numel()).contiguous()
+        cur.wait_stream(s1)
         ops.scatter_rows(p.mem.data, self.u_id, self.new_mem, map=p.g2l, d_n=self.d_n0, ts_table=p.mem.ts, ts=self.new_ts, status=st)
         ops.scatter_rows(p.mail.data, self.u_id, self.new_mail, map=p.g2l, d_n=self.d_n0, ts_table=p.mail.ts, ts=self.new_ts,
                          status=st)
-        (self.pl_ranks, self.pl_rows, self.pl_locs, self.pl_sizes, self.pl_total) = ops.plan_route(
-            self.u_id, p.node_parts, p.rank, p.rep.indptr, p.rep.indices, p.rep.locs, p.world, self.plan_cap, d_n=self.d_n0,
-            status=st)
-        self.rows_sent += self.pl_total
+        cur.wait_stream(s2)
         self.step_t += 1
 
     def sample(self, b):
@@ -214,12 +240,11 @@ class Step:
             self.g1.replay() if self.use_graphs else self._a12()
 
     def sample_from_host(self, h_roots, h_ts):
-        """A1-A2 for a batch whose roots and query times are in host memory: staged through the pinned mirror."""
-        self.h_in[0].copy_(h_roots)
-        self.h_in[1].copy_(h_ts)
+        """A1-A2 for a batch whose roots and query times are in PINNED host memory (the copies are asynchronous: the
+        caller keeps the two tensors untouched until the step has run)."""
         with torch.cuda.stream(self.stream):
-            self.in_roots.copy_(self.h_in[0], non_blocking=True)
-            self.in_ts.copy_(self.h_in[1], non_blocking=True)
+            self.in_roots.copy_(h_roots, non_blocking=True)
+            self.in_ts.copy_(h_ts, non_blocking=True)
             self.g1.replay() if self.use_graphs else self._a12()
 
     def export_to_host(self):
@@ -271,18 +296,26 @@ def _expected_last_step(rank, world, dev, n_steps_total, routed_from, my_part):
 
 
 def check_state(part, n_steps_total, routed_from):
-    """Whole memory and mail tables of this rank against the expectation (chunked); returns (ok, rows written)."""
+    """Whole memory and mail tables of this rank against the expectation (chunked); returns (ok, rows written, text that
+    describes the first difference)."""
     dev = part.dev
     last = _expected_last_step(part.rank, part.world, dev, n_steps_total, routed_from, part)
     loc_last = last[part.loc_ids]                      # nodes without a local slot cannot be written here
-    ok = True
-    for state, dim in ((part.mem, MEM_DIM), (part.mail, MAIL_DIM)):
+    bad, why = 0, ""
+    for name, state, dim in (("memory", part.mem, MEM_DIM), ("mail", part.mail, MAIL_DIM)):
         for a in range(0, part.loc_ids.numel(), 200_000):
             ids, ls = part.loc_ids[a:a + 200_000], loc_last[a:a + 200_000]
             want = model_rows(ids, ls.clamp_min(0), dim) * (ls >= 0).unsqueeze(1)
             want_ts = ls.clamp_min(0).to(torch.float32) * (ls >= 0)
-            ok = ok and torch.equal(state.data[a:a + 200_000], want) and torch.equal(state.ts[a:a + 200_000], want_ts)
-    return bool(ok), int((loc_last >= 0).sum().item())
+            diff = (state.data[a:a + 200_000] != want).any(1) | (state.ts[a:a + 200_000] != want_ts)
+            n_bad = int(diff.sum().item())
+            if n_bad and not why:
+                j = int(torch.nonzero(diff)[0].item())
+                why = (f"{name} table: {n_bad} rows differ in slots [{a}, {a + ids.numel()}); first: slot {a + j} node {int(ids[j])} "
+                       f"expected last write at step {int(ls[j])}, table holds ts {float(state.ts[a + j])} row[0] {float(state.data[a + j, 0])} "
+                       f"(want {float(want[j, 0])})")
+            bad += n_bad
+    return bad == 0, int((loc_last >= 0).sum().item()), why
 
 
 def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
@@ -299,7 +332,7 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     r_done = [torch.cuda.Event() for _ in range(2)]
     n_done = [0]                     # steps issued so far (the device's step counter follows)
 
-    h_roots, h_ts = part.roots.cpu(), part.root_ts.cpu()           # the host-buffer form starts from host tensors
+    h_roots, h_ts = part.roots.cpu().pin_memory(), part.root_ts.cpu().pin_memory()   # the host-buffer form starts here
     d2h = [0]
 
     def one_step(routed, host=False):
@@ -366,11 +399,11 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     for st, what in ((step.status, "step"), (mem_route.status, "memory route"), (mail_route.status, "mail route"),
                      (part.mem._status(), "memory table"), (part.mail._status(), "mail table")):
         st.check(f"bench ({what})")
-    ok, written = check_state(part, n_done[0], routed_from)
+    ok, written, why = check_state(part, n_done[0], routed_from)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if int(flag.item()) != 1:
-        raise SystemExit(f"rank {rank}: routed node state differs from the expectation recomputed from the seeds")
+        raise SystemExit(f"rank {rank}: node state differs from the expectation recomputed from the seeds ({why or 'on another rank'})")
     edges = int(step.hop.total())
     rows_per_step = (rows1 - rows0) / (reps * K)
     rt = torch.tensor([rows_per_step], dtype=torch.float64, device=dev)

@@ -61,6 +61,8 @@ const char* sgl_build_info(void);
  * Replaces: thrust::sort calls in csrc/include/starrygl/sample.cu.hpp:1078, :1197, :1795.
  * ---------------------------------------------------------------------------------------------- */
 size_t sgl_radix_sort_ws_bytes(int64_t n);
+/* kernels launched by one sort of n keys of num_bits key bits (launch accounting of callers that replay captured graphs) */
+int sgl_radix_sort_launches(int64_t n, int num_bits);
 int sgl_radix_sort_u64_u32(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_t* vals_alt, int64_t n,
                            int num_bits, int* h_result_in_alt, void* ws, size_t ws_bytes, void* stream);
 

@@ -1,7 +1,7 @@
 // Stable LSD radix sort, 8 or 9 bits per pass (whichever needs fewer passes for the key width), three kernels per pass:
 //   1. sort_hist_kernel    per-CTA digit histogram of its tile (4096 keys)          -> block_hist[digit][cta]
 //   2. sort_scan_kernel    one CTA per digit: exclusive scan over CTAs + digit total
-//   3. sort_scatter_kernel re-reads the tile, ranks keys stably (warp match + per-warp running counters), lays the
+//   3. sort_scatter_kernel re-reads the tile, ranks keys stably (per-bit ballots + per-warp running counters), lays the
 //                          tile out in digit order in shared memory and writes every digit's run with consecutive
 //                          threads (coalesced runs instead of scattered 8- and 4-byte stores)
 // HBM traffic per pass and key: 8 B (histogram read) + 12 B read + 12 B write.
@@ -187,8 +187,15 @@ sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
   for (int c = 0; c < kSortItems; ++c) {
     const int64_t i = base + c * 32;
     const bool valid = i < n;
-    const uint32_t d = valid ? digit_of<BITS>(k[c], shift) : (uint32_t)RADIX;
-    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    const uint32_t d = valid ? digit_of<BITS>(k[c], shift) : 0u;
+    // lanes holding the same digit: one ballot per digit bit (with 256 / 512 digits most lanes of a round differ, the
+    // slow case of the hardware's match instruction)
+    uint32_t peers = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+    for (int b = 0; b < BITS; ++b) {
+      const uint32_t bal = __ballot_sync(0xffffffffu, (d >> b) & 1u);
+      peers &= ((d >> b) & 1u) ? bal : ~bal;
+    }
     const uint32_t rank = __popc(peers & lt_mask);
     uint32_t pos = 0;
     if (valid) pos = warp_cnt[warp][d] + rank;
@@ -221,7 +228,8 @@ sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
 //                       global atomics) and the per-tile histogram of the first pass.
 //   small_pass_kernel   tile t finds where its keys of digit d start by itself: digit starts from an in-kernel scan of
 //                       the pass's totals, plus the counts of the tiles before it read straight from the per-tile
-//                       histogram (with <= 64 tiles that read is cheaper than a scan kernel and its launch).  While it
+//                       histogram (tile-major, so a thread adds up its four digits with one 128-bit load per earlier
+//                       tile, all loads independent; with <= 64 tiles that is cheaper than a scan kernel and its launch).  While it
 //                       writes its keys to their sorted places it adds them to the NEXT pass's per-tile histogram
 //                       (the tile a key lands in is known from its destination), so no pass needs a histogram kernel.
 //   small_single_kernel up to one tile (8,192 keys): all passes inside one CTA, the tile never leaves shared memory.
@@ -278,7 +286,8 @@ __device__ __forceinline__ uint32_t small_cta_scan(uint32_t v, uint32_t* tmp, ui
 // sm.tile_start[d] is the start of digit d's run; the per-digit counts of the tile are returned through cnt_out
 // (kSmallDpt digits per thread, digit = threadIdx.x * kSmallDpt + q).
 __device__ __forceinline__ void small_rank_tile(SmallSmem& sm, const uint64_t (&k)[kSmallItems], const uint32_t (&v)[kSmallItems],
-                                                uint32_t valid_mask, int shift, uint32_t mask, uint32_t (&cnt_out)[kSmallDpt]) {
+                                                uint32_t valid_mask, int shift, int bits, uint32_t (&cnt_out)[kSmallDpt]) {
+  const uint32_t mask = (1u << bits) - 1u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d0 = threadIdx.x * kSmallDpt;
 #pragma unroll
@@ -291,8 +300,14 @@ __device__ __forceinline__ void small_rank_tile(SmallSmem& sm, const uint64_t (&
 #pragma unroll
   for (int c = 0; c < kSmallItems; ++c) {
     const bool valid = (valid_mask >> c) & 1u;
-    const uint32_t d = valid ? ((uint32_t)(k[c] >> shift) & mask) : 0xFFFFFFFFu;
-    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    const uint32_t d = valid ? ((uint32_t)(k[c] >> shift) & mask) : 0u;
+    // lanes with the same digit: one ballot per digit bit.  (With up to 2,048 digits nearly all 32 lanes of a round
+    // differ, the case in which the hardware's match instruction is slowest -- it measured at half of this kernel's time.)
+    uint32_t peers = __ballot_sync(0xffffffffu, valid);
+    for (int b = 0; b < bits; ++b) {
+      const uint32_t bal = __ballot_sync(0xffffffffu, (d >> b) & 1u);
+      peers &= ((d >> b) & 1u) ? bal : ~bal;
+    }
     const uint32_t r = __popc(peers & lt_mask);
     unsigned short base = 0;
     if (valid) base = sm.warp_cnt[warp][d];
@@ -337,7 +352,7 @@ __device__ __forceinline__ void small_rank_tile(SmallSmem& sm, const uint64_t (&
   __syncthreads();
 }
 
-// ghist[pass][digit] += digit totals of this tile for every pass; hist0[digit][tile] = first-pass histogram of the tile
+// ghist[pass][digit] += digit totals of this tile for every pass; hist0[tile][digit] = first-pass histogram of the tile
 __global__ void __launch_bounds__(kSmallThreads)
 small_hist_kernel(const uint64_t* __restrict__ keys, int64_t n_cap, const int64_t* d_n, int passes, int bits,
                   uint32_t* __restrict__ ghist, uint32_t* __restrict__ hist0, int num_tiles) {
@@ -364,7 +379,7 @@ small_hist_kernel(const uint64_t* __restrict__ keys, int64_t n_cap, const int64_
     if (d >= radix) continue;
     const uint32_t c = h[j];
     if (c) atomicAdd(&ghist[p * kSmallRadix + d], c);
-    if (p == 0) hist0[(size_t)d * num_tiles + blockIdx.x] = c;
+    if (p == 0) hist0[(size_t)blockIdx.x * kSmallRadix + d] = c;
   }
 }
 
@@ -414,17 +429,32 @@ small_pass_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict_
     }
   }
   __syncthreads();
-  // + the keys of the digit in the tiles before this one: a warp sums one digit's row of the per-tile histogram
-  for (int d = warp; d < radix; d += kSmallWarps) {
-    const uint32_t* row = hist_p + (size_t)d * num_tiles;
-    uint32_t s = 0;
-    for (int t = lane; t < tile; t += 32) s += row[t];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) sm.glob_base[d] += s;
+  // + the keys of the digit in the tiles before this one: the thread's four digits are one 128-bit word of a tile's
+  // histogram; the loads of the earlier tiles are independent of each other
+  {
+    static_assert(kSmallDpt == 4, "one uint4 per thread and tile");
+    const uint4* col = (const uint4*)hist_p + threadIdx.x;
+    uint4 acc = make_uint4(0, 0, 0, 0);
+    int t = 0;
+    for (; t + 4 <= tile; t += 4) {
+      const uint4 a = __ldg(col + (size_t)(t + 0) * (kSmallRadix / 4)), b = __ldg(col + (size_t)(t + 1) * (kSmallRadix / 4));
+      const uint4 c2 = __ldg(col + (size_t)(t + 2) * (kSmallRadix / 4)), d2 = __ldg(col + (size_t)(t + 3) * (kSmallRadix / 4));
+      acc.x += a.x + b.x + c2.x + d2.x;
+      acc.y += a.y + b.y + c2.y + d2.y;
+      acc.z += a.z + b.z + c2.z + d2.z;
+      acc.w += a.w + b.w + c2.w + d2.w;
+    }
+    for (; t < tile; ++t) {
+      const uint4 a = __ldg(col + (size_t)t * (kSmallRadix / 4));
+      acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+    }
+    sm.glob_base[d0 + 0] += acc.x;
+    sm.glob_base[d0 + 1] += acc.y;
+    sm.glob_base[d0 + 2] += acc.z;
+    sm.glob_base[d0 + 3] += acc.w;
   }
   uint32_t cnt[kSmallDpt];
-  small_rank_tile(sm, k, v, valid_mask, shift, mask, cnt);   // (starts with a barrier: glob_base is complete after it)
+  small_rank_tile(sm, k, v, valid_mask, shift, bits, cnt);   // (starts with a barrier: glob_base is complete after it)
   // write-out: consecutive threads take consecutive tile positions, i.e. runs of one digit -> consecutive addresses
   const uint32_t next_mask = mask;
   for (int j = threadIdx.x; j < tile_n; j += kSmallThreads) {
@@ -433,7 +463,7 @@ small_pass_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict_
     const uint32_t g = sm.glob_base[d] + ((uint32_t)j - sm.tile_start[d]);
     out_keys[g] = key;
     out_vals[g] = sm.vals[j];
-    if (hist_next) atomicAdd(&hist_next[(size_t)((uint32_t)(key >> next_shift) & next_mask) * num_tiles + g / kSmallTile], 1u);
+    if (hist_next) atomicAdd(&hist_next[(size_t)(g / kSmallTile) * kSmallRadix + ((uint32_t)(key >> next_shift) & next_mask)], 1u);
   }
 }
 
@@ -461,7 +491,7 @@ small_single_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
   }
   uint32_t cnt[kSmallDpt];
   for (int p = 0; p < passes; ++p) {
-    small_rank_tile(sm, k, v, valid_mask, p * bits, mask, cnt);
+    small_rank_tile(sm, k, v, valid_mask, p * bits, bits, cnt);
     if (p + 1 < passes) {
 #pragma unroll
       for (int c = 0; c < kSmallItems; ++c) {
@@ -521,7 +551,7 @@ int run_small(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_t* vals
   uint32_t* ghist = c.take<uint32_t>((size_t)kSmallMaxPasses * kSmallRadix);
   uint32_t* hist = c.take<uint32_t>((size_t)kSmallMaxPasses * kSmallRadix * kSmallMaxTiles);
   SGL_REQUIRE(c.ok(), SGL_ERR_WORKSPACE, "radix sort: workspace %zu < %zu bytes", ws_bytes, small_ws_bytes());
-  // per-pass histogram p lives at hist + p * kSmallRadix * num_tiles (packed for the actual tile count: one memset)
+  // per-pass histogram p ([tile][digit]) lives at hist + p * kSmallRadix * num_tiles (packed for the actual tile count)
   const size_t per_pass = (size_t)kSmallRadix * num_tiles;
   SGL_CUDA_CHECK(cudaMemsetAsync(ghist, 0, (size_t)passes * kSmallRadix * 4, stream));
   SGL_CUDA_CHECK(cudaMemsetAsync(hist, 0, (size_t)passes * per_pass * 4, stream));
@@ -607,6 +637,18 @@ int radix_sort_pairs(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_
 }  // namespace sgl
 
 extern "C" size_t sgl_radix_sort_ws_bytes(int64_t n) { return sgl::radix_sort_ws_bytes(n); }
+
+// number of kernels one sort of n keys of num_bits bits launches (for launch accounting; memsets are not kernels)
+extern "C" int sgl_radix_sort_launches(int64_t n, int num_bits) {
+  if (n <= 0) return 0;
+  if (n <= sgl::kSmallMaxKeys) {
+    int passes, bits;
+    sgl::small_plan(num_bits, true, &passes, &bits);
+    return n <= sgl::kSmallTile ? (passes ? 1 : 0) : 1 + passes;
+  }
+  const int p8 = (num_bits + 7) / 8, p9 = (num_bits + 8) / 9;
+  return 3 * (p9 < p8 ? p9 : p8);
+}
 
 extern "C" int sgl_radix_sort_u64_u32(uint64_t* keys, uint32_t* vals, uint64_t* keys_alt, uint32_t* vals_alt, int64_t n,
                                       int num_bits, int* h_result_in_alt, void* ws, size_t ws_bytes, void* stream) {

@@ -29,6 +29,7 @@ _SIGNATURES = {
     "sgl_last_error": (C.c_char_p, []),
     "sgl_build_info": (C.c_char_p, []),
     "sgl_radix_sort_ws_bytes": (_sz, [_i64]),
+    "sgl_radix_sort_launches": (_i32, [_i64, _i32]),
     "sgl_radix_sort_u64_u32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, C.POINTER(C.c_int), _vp, _sz, _vp]),
     "sgl_tcsr_build_ws_bytes": (_sz, [_i64, _i64]),
     "sgl_tcsr_build": (_i32, [_i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.POINTER(C.c_int64), _vp, _sz, _vp]),

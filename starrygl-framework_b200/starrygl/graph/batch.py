@@ -112,22 +112,22 @@ def build_batch(g, roots, root_ts, fanouts, policy="recent", **kw) -> List[dict]
     return build_batch_async(g, roots, root_ts, fanouts, policy, **kw).finish()
 
 
-def count_kernel_nodes(graph: "torch.cuda.CUDAGraph"):
-    """Number of this library's kernel nodes in a captured graph, read from the runtime's own dump of it (the graph must
-    have been created with ``enable_debug_mode()`` before the capture); None when the dump cannot be read."""
-    import os
-    import re
-    import tempfile
-    path = os.path.join(tempfile.gettempdir(), f"sgl_graph_{os.getpid()}_{id(graph)}.dot")
-    try:
-        graph.debug_dump(path)
-        with open(path) as f:
-            text = f.read()
-        os.remove(path)
-    except Exception:
-        return None
-    n = len(re.findall(r'label="[^"]*(?:sgl|_ZN3sgl)[^"]*"', text))
-    return n or None
+def batch_kernel_launches(num_nodes: int, num_roots: int, fanouts: Sequence[int], ts_span: int) -> int:
+    """Kernels of this library that one mini-batch of :func:`build_batch_async` launches at the given capacities (pack,
+    sort, head scan and emit of every relabel; count and fill of every hop; pack, sort and emit of every CSC after the
+    first, which needs no sort).  Counted from the structure of the calls; the sorts' share comes from the library."""
+    from .. import _C
+    L = _C.lib()
+    id_bits, ts_bits = ops.bits_for(num_nodes - 1), ops.bits_for(ts_span)
+    total = 3 + L.sgl_radix_sort_launches(num_roots, id_bits + ts_bits)          # relabel of the roots
+    cur, targets = num_roots, num_roots
+    for l, k in enumerate(fanouts):
+        edges = targets * k
+        total += 2                                                               # count + fill
+        total += 3 + L.sgl_radix_sort_launches(cur + edges, id_bits + ts_bits)   # merged list of the hop
+        total += 1 if l == 0 else 2 + L.sgl_radix_sort_launches(edges, ops.bits_for(cur) + ts_bits)   # CSC
+        cur, targets = cur + edges, edges
+    return int(total)
 
 
 class BatchGraph:
@@ -159,13 +159,12 @@ class BatchGraph:
                 build_batch_async(g, self.roots, self.root_ts, fanouts, policy, **kw)     # warm-up: sizes the scratch
             self.stream.synchronize()
             self.graph = torch.cuda.CUDAGraph()
-            self.graph.enable_debug_mode()      # keeps the captured graph so that its nodes can be counted below
             with torch.cuda.graph(self.graph, stream=self.stream):
                 self.batch = build_batch_async(g, self.roots, self.root_ts, fanouts, policy, **kw)
         finally:
             _C.WORKSPACE = saved
         self.stream.synchronize()
-        self.kernel_launches = count_kernel_nodes(self.graph)
+        self.kernel_launches = batch_kernel_launches(g.num_nodes, self.num_roots, fanouts, int(ts_range[1]) - min(g.ts_min, int(ts_range[0])))
 
     def run(self, roots: torch.Tensor, root_ts: torch.Tensor) -> DeviceBatch:
         """Enqueue one batch (exactly ``num_roots`` roots, already on the GPU); returns the un-trimmed device batch,

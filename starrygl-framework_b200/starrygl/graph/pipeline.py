@@ -273,6 +273,33 @@ class SampleGatherPipeline:
                                        self.stream.cuda_stream)
         _C.check(rc)
 
+    def capture_sample_only(self):
+        """Record the hop alone (full batch, this object's root buffers) as a graph; :meth:`replay_sample` then costs one
+        copy + one graph launch -- for callers that gather later, and for timing the sampler without launch overhead."""
+        sp = self.stream.cuda_stream
+        self.roots_ts.zero_()
+        torch.cuda.synchronize(self.dev)
+        self.sample_only(self.roots, self.root_ts)
+        self.stream.synchronize()
+        _C.check(self.L.sgl_graph_capture_begin(sp))
+        try:
+            self.sample_only(self.roots, self.root_ts)
+        finally:
+            ex = C.c_void_p()
+            rc = self.L.sgl_graph_capture_end(sp, C.byref(ex))
+        _C.check(rc)
+        v = C.c_void_p
+        self._a_ssrc = v(0)
+        self._slaunch_args = [ex, self._a_ssrc, v(self.roots_ts.data_ptr()), C.c_size_t(self.roots_ts.numel() * 8), v(sp)]
+        self.stream.synchronize()
+        return self
+
+    def replay_sample(self, roots_ts_ptr: int):
+        self._a_ssrc.value = roots_ts_ptr
+        rc = self.L.sgl_graph_launch(*self._slaunch_args)
+        if rc:
+            _C.check(rc)
+
     # ---- host inputs / host results --------------------------------------------------------------------
     def submit_host(self, h_roots: torch.Tensor, h_root_ts: torch.Tensor, rng_stream: int = 0):
         """Enqueue one batch whose roots and query times are in (pinned) host tensors: H2D copy, sampling, gather,

@@ -57,6 +57,13 @@ def test_static_scratch_entry_point_matches_workspace_entry_point():
         assert tot > 0 and torch.equal(out[5], ref.offsets), f"call {call}: offsets differ"
         for name, a, b in zip(("nbr", "dst", "ts", "dt", "eid"), out[:5], (ref.nbr, ref.dst, ref.ts, ref.dt, ref.eid)):
             assert torch.equal(a[:tot], b[:tot]), f"call {call}: {name} differs"   # bit-exact, as in the other tests
+        # and against the CPU oracle directly
+        from oracle import oracle_np as O
+        cpu = lambda t: t.cpu().numpy()
+        want = O.sample_layer(cpu(g.indptr), cpu(g.nbr), cpu(g.ts), cpu(g.eid), cpu(q), cpu(qt), k,
+                              O.RECENT if policy == "recent" else O.UNIFORM, seed=11)
+        for name, a, w in zip(("nbr", "dst", "ts", "dt", "eid"), out[:5], want[:5]):
+            assert np.array_equal(cpu(a[:tot]), w), f"call {call}: {name} differs from the oracle"
 
 
 def test_static_scratch_entry_point_rejects_oversized_batches():
