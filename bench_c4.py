@@ -58,11 +58,13 @@ def make_partition(rank, world, dev, n_per=N_PER, e_per=E_PER):
 
 
 def batches_of(src, dst, ts, neg):
-    """[NUM_BATCHES, 12000] roots and query times: the last NUM_BATCHES * EVENTS events in time order."""
+    """[NUM_BATCHES, 12000] roots and query times (views of one [NUM_BATCHES, 2, 12000] block, so that a batch is one
+    contiguous copy): the last NUM_BATCHES * EVENTS events in time order."""
     e = src.numel()
     lo = e - NUM_BATCHES * EVENTS
     s, d, t = (x[lo:].view(NUM_BATCHES, EVENTS) for x in (src, dst, ts))
-    return torch.cat([s, d, neg], 1).contiguous(), torch.cat([t, t, t], 1).contiguous()
+    both = torch.stack([torch.cat([s, d, neg], 1), torch.cat([t, t, t], 1)], 1).contiguous()
+    return both[:, 0], both[:, 1]
 
 
 def model_base(ids, step_t):
@@ -147,10 +149,10 @@ class Step:
         self.p, self.ops = part, ops
         dev = part.dev
         self.n_roots = 3 * EVENTS
-        self.in_roots = torch.zeros(self.n_roots, dtype=torch.int64, device=dev)
-        self.in_ts = torch.zeros(self.n_roots, dtype=torch.int64, device=dev)
-        self.in_roots.copy_(part.roots[0])
-        self.in_ts.copy_(part.root_ts[0])
+        self.in_rt = torch.zeros(2, self.n_roots, dtype=torch.int64, device=dev)      # roots and query times of the batch
+        self.in_roots, self.in_ts = self.in_rt[0], self.in_rt[1]
+        self.batches = part.roots._base                                              # [NUM_BATCHES, 2, n_roots]
+        self.in_rt.copy_(self.batches[0])
         self.step_t = torch.zeros(1, dtype=torch.int64, device=dev)          # number of the step being built
         self.rows_sent = torch.zeros(1, dtype=torch.int64, device=dev)       # rows this rank pushed so far (one table)
         self.status = ops.StatusWord(dev)
@@ -233,19 +235,17 @@ class Step:
         cur.wait_stream(s2)
         self.step_t += 1
 
+    # The methods below enqueue on the CURRENT stream, which the caller sets to ``self.stream`` once for a whole loop
+    # (a stream context manager per call costs more host time than the calls themselves).
     def sample(self, b):
-        with torch.cuda.stream(self.stream):
-            self.in_roots.copy_(self.p.roots[b], non_blocking=True)
-            self.in_ts.copy_(self.p.root_ts[b], non_blocking=True)
-            self.g1.replay() if self.use_graphs else self._a12()
+        self.in_rt.copy_(self.batches[b], non_blocking=True)
+        self.g1.replay() if self.use_graphs else self._a12()
 
-    def sample_from_host(self, h_roots, h_ts):
-        """A1-A2 for a batch whose roots and query times are in PINNED host memory (the copies are asynchronous: the
-        caller keeps the two tensors untouched until the step has run)."""
-        with torch.cuda.stream(self.stream):
-            self.in_roots.copy_(h_roots, non_blocking=True)
-            self.in_ts.copy_(h_ts, non_blocking=True)
-            self.g1.replay() if self.use_graphs else self._a12()
+    def sample_from_host(self, h_batch):
+        """A1-A2 for a batch whose roots and query times ([2, n_roots]) are in PINNED host memory (the copy is asynchronous:
+        the caller keeps the tensor untouched until the step has run)."""
+        self.in_rt.copy_(h_batch, non_blocking=True)
+        self.g1.replay() if self.use_graphs else self._a12()
 
     def export_to_host(self):
         """Block structure of the batch (offsets, neighbour ids, timestamps, edge ids, dt) -> pinned host memory; the
@@ -253,14 +253,12 @@ class Step:
         hop = self.hop
         if self.h_out is None:
             self.h_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (hop.offsets, hop.nbr, hop.ts, hop.eid, hop.dt)]
-        with torch.cuda.stream(self.stream):
-            for h, t in zip(self.h_out, (hop.offsets, hop.nbr, hop.ts, hop.eid, hop.dt)):
-                h.copy_(t, non_blocking=True)
+        for h, t in zip(self.h_out, (hop.offsets, hop.nbr, hop.ts, hop.eid, hop.dt)):
+            h.copy_(t, non_blocking=True)
         return sum(h.numel() * h.element_size() for h in self.h_out)
 
     def gather_update_plan(self):
-        with torch.cuda.stream(self.stream):
-            self.g2.replay() if self.use_graphs else self._a36()
+        self.g2.replay() if self.use_graphs else self._a36()
 
 
 def _expected_last_step(rank, world, dev, n_steps_total, routed_from, my_part):
@@ -332,13 +330,17 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     r_done = [torch.cuda.Event() for _ in range(2)]
     n_done = [0]                     # steps issued so far (the device's step counter follows)
 
-    h_roots, h_ts = part.roots.cpu().pin_memory(), part.root_ts.cpu().pin_memory()   # the host-buffer form starts here
+    h_batches = step.batches.cpu().pin_memory()                     # the host-buffer form starts here
     d2h = [0]
+    send_mem, apply_mem = mem_route.bind_dev(step.new_mem, step.pl_rows, step.pl_locs, step.pl_sizes, rows_hint, step.new_ts,
+                                             part.mem, r_stream)
+    send_mail, apply_mail = mail_route.bind_dev(step.new_mail, step.pl_rows, step.pl_locs, step.pl_sizes, rows_hint, step.new_ts,
+                                                part.mail, r_stream)
 
     def one_step(routed, host=False):
         s = n_done[0]
         if host:
-            step.sample_from_host(h_roots[s % NUM_BATCHES], h_ts[s % NUM_BATCHES])
+            step.sample_from_host(h_batches[s % NUM_BATCHES])
         else:
             step.sample(s % NUM_BATCHES)                              # A1-A2: overlaps the route of the step before
         if routed and s > 0:
@@ -347,12 +349,9 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         if routed:
             a_done[s % 2].record(step.stream)
             r_stream.wait_event(a_done[s % 2])
-            with torch.cuda.stream(r_stream):
-                sm = mem_route.push_dev(step.new_mem, step.pl_rows, step.pl_locs, step.pl_sizes, rows_hint, step.new_ts)
-                sl = mail_route.push_dev(step.new_mail, step.pl_rows, step.pl_locs, step.pl_sizes, rows_hint, step.new_ts)
-                mem_route.apply_dev(sm, part.mem, rows_hint)
-                mail_route.apply_dev(sl, part.mail, rows_hint)
-                r_done[s % 2].record(r_stream)
+            send_mem(), send_mail()
+            apply_mem(), apply_mail()
+            r_done[s % 2].record(r_stream)
         if host:
             d2h[0] = step.export_to_host()
         n_done[0] += 1
@@ -366,8 +365,10 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         step.stream.wait_stream(main)
         r_stream.wait_stream(main)
         t0 = time.perf_counter()
+        torch.cuda.set_stream(step.stream)
         for _ in range(n_steps):
             one_step(routed, host)
+        torch.cuda.set_stream(main)
         t_issue = time.perf_counter() - t0
         main.wait_stream(step.stream)
         main.wait_stream(r_stream)

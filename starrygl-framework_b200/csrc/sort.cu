@@ -1,7 +1,7 @@
 // Stable LSD radix sort, 8 or 9 bits per pass (whichever needs fewer passes for the key width), three kernels per pass:
 //   1. sort_hist_kernel    per-CTA digit histogram of its tile (4096 keys)          -> block_hist[digit][cta]
 //   2. sort_scan_kernel    one CTA per digit: exclusive scan over CTAs + digit total
-//   3. sort_scatter_kernel re-reads the tile, ranks keys stably (per-bit ballots + per-warp running counters), lays the
+//   3. sort_scatter_kernel re-reads the tile, ranks keys stably (warp match + per-warp running counters), lays the
 //                          tile out in digit order in shared memory and writes every digit's run with consecutive
 //                          threads (coalesced runs instead of scattered 8- and 4-byte stores)
 // HBM traffic per pass and key: 8 B (histogram read) + 12 B read + 12 B write.
@@ -187,15 +187,8 @@ sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
   for (int c = 0; c < kSortItems; ++c) {
     const int64_t i = base + c * 32;
     const bool valid = i < n;
-    const uint32_t d = valid ? digit_of<BITS>(k[c], shift) : 0u;
-    // lanes holding the same digit: one ballot per digit bit (with 256 / 512 digits most lanes of a round differ, the
-    // slow case of the hardware's match instruction)
-    uint32_t peers = __ballot_sync(0xffffffffu, valid);
-#pragma unroll
-    for (int b = 0; b < BITS; ++b) {
-      const uint32_t bal = __ballot_sync(0xffffffffu, (d >> b) & 1u);
-      peers &= ((d >> b) & 1u) ? bal : ~bal;
-    }
+    const uint32_t d = valid ? digit_of<BITS>(k[c], shift) : (uint32_t)RADIX;
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
     const uint32_t rank = __popc(peers & lt_mask);
     uint32_t pos = 0;
     if (valid) pos = warp_cnt[warp][d] + rank;
@@ -235,8 +228,8 @@ sort_scatter_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restric
 //   small_single_kernel up to one tile (8,192 keys): all passes inside one CTA, the tile never leaves shared memory.
 //
 // Tiles are 8,192 keys (512 threads x 16); ranks inside a tile are stable: a warp owns 512 consecutive keys, counts them
-// per digit in its own 16-bit counters (one lane per digit and round updates a counter, so no atomics), and a key's
-// rank = keys of its digit in earlier warps + in its warp's earlier rounds + in lower lanes of its round.
+// per digit in its own 16-bit counters, and a key's rank = keys of its digit in earlier warps + in its warp's earlier
+// rounds + in lower lanes of its round.
 // Nothing waits on another CTA: the dependencies between passes are kernel boundaries.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kSmallThreads = 512;
@@ -285,59 +278,71 @@ __device__ __forceinline__ uint32_t small_cta_scan(uint32_t v, uint32_t* tmp, ui
 // have valid bit clear) on `digit` and lays keys and payloads out in digit order in shared memory.  On return
 // sm.tile_start[d] is the start of digit d's run; the per-digit counts of the tile are returned through cnt_out
 // (kSmallDpt digits per thread, digit = threadIdx.x * kSmallDpt + q).
+//
+// Counting: every lane adds 1 to its digit's 16-bit counter of the warp with one shared-memory atomic on the 32-bit word
+// that holds two counters; the value it gets back is its rank among the warp's earlier keys of that digit -- unless
+// another lane of the same round hit the same digit, in which case the hardware's order among them is arbitrary.  With
+// up to 2,048 digits that is rare; it is detected (a counter that moved by more than one past a lane's own value) and
+// only then are the round's ranks recomputed in lane order with a warp match.
 __device__ __forceinline__ void small_rank_tile(SmallSmem& sm, const uint64_t (&k)[kSmallItems], const uint32_t (&v)[kSmallItems],
                                                 uint32_t valid_mask, int shift, int bits, uint32_t (&cnt_out)[kSmallDpt]) {
+  static_assert(kSmallDpt == 4, "four 16-bit counters = one 64-bit word per thread and warp row");
   const uint32_t mask = (1u << bits) - 1u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int d0 = threadIdx.x * kSmallDpt;
 #pragma unroll
-  for (int w = 0; w < kSmallWarps; ++w)
-#pragma unroll
-    for (int q = 0; q < kSmallDpt; ++q) sm.warp_cnt[w][d0 + q] = 0;
+  for (int w = 0; w < kSmallWarps; ++w) *(uint2*)&sm.warp_cnt[w][d0] = make_uint2(0u, 0u);
   __syncthreads();
   const uint32_t lt_mask = (1u << lane) - 1u;
+  uint32_t* my_words = (uint32_t*)sm.warp_cnt[warp];
   unsigned short rk[kSmallItems];
 #pragma unroll
   for (int c = 0; c < kSmallItems; ++c) {
     const bool valid = (valid_mask >> c) & 1u;
     const uint32_t d = valid ? ((uint32_t)(k[c] >> shift) & mask) : 0u;
-    // lanes with the same digit: one ballot per digit bit.  (With up to 2,048 digits nearly all 32 lanes of a round
-    // differ, the case in which the hardware's match instruction is slowest -- it measured at half of this kernel's time.)
-    uint32_t peers = __ballot_sync(0xffffffffu, valid);
-    for (int b = 0; b < bits; ++b) {
-      const uint32_t bal = __ballot_sync(0xffffffffu, (d >> b) & 1u);
-      peers &= ((d >> b) & 1u) ? bal : ~bal;
+    const uint32_t sh = (d & 1u) * 16u;
+    uint32_t mine = 0;
+    if (valid) mine = (atomicAdd(&my_words[d >> 1], 1u << sh) >> sh) & 0xffffu;
+    __syncwarp();
+    uint32_t now = 0;
+    if (valid) now = sm.warp_cnt[warp][d];
+    if (__any_sync(0xffffffffu, valid && now - mine > 1u)) {
+      // two lanes of this round share a digit: ranks in lane order.  now = count before the round + size of the group
+      const uint32_t peers = __match_any_sync(0xffffffffu, valid ? d : 0xffffffffu);
+      mine = now - __popc(peers) + __popc(peers & lt_mask);
     }
-    const uint32_t r = __popc(peers & lt_mask);
-    unsigned short base = 0;
-    if (valid) base = sm.warp_cnt[warp][d];
     __syncwarp();
-    if (valid && r == 0) sm.warp_cnt[warp][d] = (unsigned short)(base + __popc(peers));
-    __syncwarp();
-    rk[c] = (unsigned short)(base + r);
+    rk[c] = (unsigned short)mine;
   }
   __syncthreads();
-  // per digit: counts of the warps -> start of every warp's keys of the digit (digit-major, then warp order)
-  uint32_t sum = 0;
+  // per digit: counts of the warps -> start of every warp's keys of the digit (digit-major, then warp order); a thread's
+  // four digits are one 64-bit word of a warp's counter row
+  uint32_t run[kSmallDpt] = {0u, 0u, 0u, 0u};
 #pragma unroll
-  for (int q = 0; q < kSmallDpt; ++q) {
-    uint32_t run = 0;
-#pragma unroll
-    for (int w = 0; w < kSmallWarps; ++w) {
-      const uint32_t c = sm.warp_cnt[w][d0 + q];
-      sm.warp_cnt[w][d0 + q] = (unsigned short)run;
-      run += c;
-    }
-    cnt_out[q] = run;
-    sum += run;
+  for (int w = 0; w < kSmallWarps; ++w) {
+    const uint2 c = *(const uint2*)&sm.warp_cnt[w][d0];
+    run[0] += c.x & 0xffffu;
+    run[1] += c.x >> 16;
+    run[2] += c.y & 0xffffu;
+    run[3] += c.y >> 16;
   }
-  uint32_t start = small_cta_scan(sum, sm.scan_tmp, nullptr);
+  uint32_t start = small_cta_scan(run[0] + run[1] + run[2] + run[3], sm.scan_tmp, nullptr);
+  uint32_t off[kSmallDpt];
 #pragma unroll
   for (int q = 0; q < kSmallDpt; ++q) {
+    cnt_out[q] = run[q];
     sm.tile_start[d0 + q] = (unsigned short)start;
+    off[q] = start;
+    start += run[q];
+  }
 #pragma unroll
-    for (int w = 0; w < kSmallWarps; ++w) sm.warp_cnt[w][d0 + q] = (unsigned short)(sm.warp_cnt[w][d0 + q] + start);
-    start += cnt_out[q];
+  for (int w = 0; w < kSmallWarps; ++w) {
+    const uint2 c = *(const uint2*)&sm.warp_cnt[w][d0];
+    *(uint2*)&sm.warp_cnt[w][d0] = make_uint2((off[0] & 0xffffu) | (off[1] << 16), (off[2] & 0xffffu) | (off[3] << 16));
+    off[0] += c.x & 0xffffu;
+    off[1] += c.x >> 16;
+    off[2] += c.y & 0xffffu;
+    off[3] += c.y >> 16;
   }
   __syncthreads();
 #pragma unroll

@@ -179,6 +179,41 @@ class P2PCacheRoute:
                                            self.status.ptr(), _C.stream_ptr(stream))
         _C.check(rc)
 
+    def bind_dev(self, feats: torch.Tensor, send_idx: torch.Tensor, remote_idx: torch.Tensor, d_send_sizes: torch.Tensor,
+                 rows_hint: int, local_ts: Optional[torch.Tensor], state, stream):
+        """:meth:`push_dev` + :meth:`apply_dev` for buffers that stay the same from step to step (a captured step writes
+        its plan and rows into fixed tensors): every argument is converted once; returns ``(send, apply)``, two
+        callables without arguments that enqueue the step's send / apply kernels on ``stream``."""
+        if (local_ts is not None) != self.has_ts or feats.shape[1] != self.dim or feats.dtype != torch.float32:
+            raise _C.SglError("P2PCacheRoute.bind_dev: row layout differs from the one the route was created for")
+        v = C.c_void_p
+        step_a, step_b = C.c_uint64(0), C.c_uint64(0)
+        sp = v(stream.cuda_stream)
+        a_send = [self.ctx, v(feats.data_ptr()), C.c_int64(feats.shape[0]), C.c_int64(self.dim),
+                  v(local_ts.data_ptr()) if local_ts is not None else None, v(send_idx.data_ptr()), v(remote_idx.data_ptr()),
+                  v(d_send_sizes.data_ptr()), C.c_int64(int(rows_hint)), step_a, v(self.status.ptr()), sp]
+        a_recv = [self.ctx, C.c_int64(int(rows_hint)), v(state._d_data.data_ptr()), C.c_int64(state._d_data.shape[0]),
+                  C.c_int64(self.dim), C.c_int(int(self.has_ts)), v(state._d_ts.data_ptr()) if self.has_ts else None, step_b,
+                  v(self.status.ptr()), sp]
+        f_send, f_recv = self.L.sgl_p2p_route_send_dev, self.L.sgl_p2p_route_recv_dev
+        keep = (feats, send_idx, remote_idx, d_send_sizes, local_ts, state)
+        pending = []
+
+        def send(_keep=keep):
+            step_a.value = self.step
+            rc = f_send(*a_send)
+            if rc:
+                _C.check(rc)
+            pending.append(self.step)
+            self.step += 1
+
+        def apply():
+            step_b.value = pending.pop(0)
+            rc = f_recv(*a_recv)
+            if rc:
+                _C.check(rc)
+        return send, apply
+
     # ---- life cycle ---------------------------------------------------------------------------------------------
     def close(self, collective: bool = True):
         """Release the context, the peer mappings and the staging buffer.  ``collective=False`` skips the barrier (for

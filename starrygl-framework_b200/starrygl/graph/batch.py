@@ -61,12 +61,19 @@ class DeviceBatch:
 
 def build_batch_async(g: ops.TCSR, roots: torch.Tensor, root_ts: torch.Tensor, fanouts: Sequence[int],
                       policy: str = "recent", *, ts_range: Optional[Sequence[int]] = None, equal_root_time=False,
-                      allowed_offset=-1, seed=0, status: Optional[ops.StatusWord] = None) -> DeviceBatch:
+                      allowed_offset=-1, seed=0, status: Optional[ops.StatusWord] = None,
+                      side_streams: Optional[Sequence[torch.cuda.Stream]] = None) -> DeviceBatch:
     """Enqueue the whole batch construction on the current stream.
 
     ``ts_range`` = (lowest, highest) timestamp that can occur among the roots' query times; together with the
     graph's own timestamp range it fixes the width of the (id, ts) sort key.  When omitted it is read from
     ``root_ts`` (one extra synchronisation).
+
+    ``side_streams`` (two streams): the independent chains of the construction run side by side -- hop l+1 samples the
+    raw output of hop l, so the sampling of all hops proceeds while the relabel of the earlier hops is still sorting, and
+    the CSC's sort (keyed by destination row and time) runs next to the relabel's sort; only its column indices need the
+    relabel's result, and they are filled in with one gather at the end.  Everything is joined into the current stream
+    before the function returns.  Captured into a CUDA graph this becomes a graph with parallel branches.
     """
     dev = g.device
     status = status or ops.StatusWord(dev)
@@ -79,30 +86,62 @@ def build_batch_async(g: ops.TCSR, roots: torch.Tensor, root_ts: torch.Tensor, f
     ts_base = min(g.ts_min, int(ts_range[0]))
     ts_bits = ops.bits_for(max(g.ts_max, int(ts_range[1])) - ts_base)
     id_bits = ops.bits_for(g.num_nodes - 1)
+    main = torch.cuda.current_stream(dev)
+    s_sample, s_csc = (side_streams[0], side_streams[1]) if side_streams else (main, main)
+
+    def after(stream_done, stream_wait):
+        if stream_done is not stream_wait:
+            ev = torch.cuda.Event()
+            ev.record(stream_done)
+            stream_wait.wait_event(ev)
 
     cur_id, cur_ts, inv0, _, d_cur = ops.unique_pairs(roots, root_ts, id_bits=id_bits, ts_bits=ts_bits, ts_base=ts_base,
                                                       status=status)
     layers = [{"gids": cur_id, "ts": cur_ts, "inv_map": inv0[:roots.numel()]}]
     counts = [d_cur]
-    last_inv = None
+    # the sampling chain: hop 0 queries the layer-0 list, hop l+1 one target per edge sampled by hop l at that edge's
+    # timestamp (prepare_sample.py:345-346) -- no hop waits for a relabel but the first
+    after(main, s_sample)
+    hops = []
     tgt, tgt_ts, d_tgt = cur_id, cur_ts, d_cur
-    for l, k in enumerate(fanouts):
+    with torch.cuda.stream(s_sample):
+        for l, k in enumerate(fanouts):
+            hop = ops.sample_layer(g, tgt, tgt_ts, k, policy, d_n=d_tgt, equal_root_time=equal_root_time,
+                                   allowed_offset=allowed_offset, seed=seed, rng_stream=l, status=status)
+            hops.append(hop)
+            tgt, tgt_ts, d_tgt = hop.nbr, hop.ts, hop.d_total
+    after(s_sample, main)
+    if side_streams and len(hops) > 1:          # (a stream that joins a capture has to be joined back: only fork it for work)
+        after(s_sample, s_csc)
+    last_inv = None
+    pending = []
+    for l, hop in enumerate(hops):
         cap_cur = cur_id.numel()
-        hop = ops.sample_layer(g, tgt, tgt_ts, k, policy, d_n=d_tgt, equal_root_time=equal_root_time,
-                               allowed_offset=allowed_offset, seed=seed, rng_stream=l, status=status)
+        first = last_inv is None
+        if not first and side_streams:
+            # CSC of a later hop: its order does not depend on this hop's relabel -- sort it on the side with the edge
+            # number as column index, translate the columns once the relabel is there
+            after(main, s_csc)                      # last_inv / d_cur of the previous relabel
+            with torch.cuda.stream(s_csc):
+                iota = torch.arange(hop.capacity, dtype=torch.int64, device=dev)
+                indptr, edge_no, e_ts, e_dt, e_eid = ops.build_csc(iota, hop.dst, last_inv, hop.ts, hop.dt, hop.eid, cap_cur,
+                                                                   dst_bits=ops.bits_for(cap_cur), ts_bits=ts_bits,
+                                                                   ts_base=ts_base, d_n_edges=hop.d_total, d_num_dst=d_cur,
+                                                                   status=status)
         nxt_id, nxt_ts, _, nxt_inv, d_nxt = ops.unique_pairs(cur_id, cur_ts, hop.nbr, hop.ts, id_bits=id_bits,
                                                              ts_bits=ts_bits, ts_base=ts_base, d_n_a=d_cur,
                                                              d_n_b=hop.d_total, status=status)
-        indptr, idx, e_ts, e_dt, e_eid = ops.build_csc(nxt_inv, hop.dst, last_inv, hop.ts, hop.dt, hop.eid, cap_cur,
-                                                       dst_bits=ops.bits_for(cap_cur), ts_bits=ts_bits, ts_base=ts_base,
-                                                       d_n_edges=hop.d_total, d_num_dst=d_cur, presorted=last_inv is None,
-                                                       status=status)
+        if first or not side_streams:
+            indptr, idx, e_ts, e_dt, e_eid = ops.build_csc(nxt_inv, hop.dst, last_inv, hop.ts, hop.dt, hop.eid, cap_cur,
+                                                           dst_bits=ops.bits_for(cap_cur), ts_bits=ts_bits, ts_base=ts_base,
+                                                           d_n_edges=hop.d_total, d_num_dst=d_cur, presorted=first,
+                                                           status=status)
+        else:
+            after(s_csc, main)
+            idx = ops.gather_rows(nxt_inv, edge_no, d_n=hop.d_total, status=status)
         layers.append({"indptr": indptr, "indices": idx, "eid": e_eid, "edge_ts": e_ts, "edge_dt": e_dt,
                        "gids": nxt_id, "ts": nxt_ts, "raw_nbr": hop.nbr, "raw_ts": hop.ts, "inv": nxt_inv, "hop": hop})
         counts += [hop.d_total, d_nxt]
-        # the next hop samples one target per edge sampled here, at that edge's timestamp (prepare_sample.py:345-346);
-        # cur_id[last_inv[j]] is by construction the j-th sampled neighbour, so no extra gather is needed
-        tgt, tgt_ts, d_tgt = hop.nbr, hop.ts, hop.d_total
         cur_id, cur_ts, d_cur, last_inv = nxt_id, nxt_ts, d_nxt, nxt_inv
     return DeviceBatch(g, layers, counts, status, fanouts, None)
 
@@ -125,7 +164,8 @@ def batch_kernel_launches(num_nodes: int, num_roots: int, fanouts: Sequence[int]
         edges = targets * k
         total += 2                                                               # count + fill
         total += 3 + L.sgl_radix_sort_launches(cur + edges, id_bits + ts_bits)   # merged list of the hop
-        total += 1 if l == 0 else 2 + L.sgl_radix_sort_launches(edges, ops.bits_for(cur) + ts_bits)   # CSC
+        # CSC: a copy for the first hop; pack, sort, emit and the gather that fills in the column indices for the others
+        total += 1 if l == 0 else 3 + L.sgl_radix_sort_launches(edges, ops.bits_for(cur) + ts_bits)
         cur, targets = cur + edges, edges
     return int(total)
 
@@ -148,8 +188,9 @@ class BatchGraph:
         self.roots = torch.zeros(self.num_roots, dtype=torch.int64, device=dev)
         self.root_ts = torch.full((self.num_roots,), int(ts_range[0]), dtype=torch.int64, device=dev)
         self.status = ops.StatusWord(dev)
+        self._side = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]
         kw = dict(ts_range=ts_range, equal_root_time=equal_root_time, allowed_offset=allowed_offset, seed=seed,
-                  status=self.status)
+                  status=self.status, side_streams=self._side)
         # scratch used inside the graph must not be shared with eager calls: the capture gets its own workspace
         saved = _C.WORKSPACE
         _C.WORKSPACE = self._workspace = _C.Workspace()

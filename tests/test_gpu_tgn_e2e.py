@@ -1,7 +1,7 @@
 """End-to-end TGN steps: the same model fed by (a) the CUDA data path and (b) the CPU oracle must produce the same
 loss (tolerance 1e-4 relative, fp32) over several training steps, including the memory / mailbox write-back between
 steps.  Graph shape follows the small reference configuration (bipartite, 9,000 + 1,000 nodes, 172-d edge features,
-recent-10, one layer, batch 200 with one negative destination per event), scaled to 20,000 events."""
+recent-10, one layer, memory dim 100, time dim 100, batch 200 with one negative destination per event, 160,000 events)."""
 import numpy as np
 import pytest
 import torch
@@ -12,10 +12,11 @@ from tgn_torch import TGN
 
 pytestmark = pytest.mark.gpu
 REL_TOL = 1e-4
-DIM_MEM, DIM_EDGE, DIM_TIME, K, B = 32, 172, 16, 10, 200
+DIM_MEM, DIM_EDGE, DIM_TIME, K, B = 100, 172, 100, 10, 200
+FIRST = 80000          # index of the first training event: half of the stream is history
 
 
-def make_data(seed=0, n_src=9000, n_dst=1000, m=20000):
+def make_data(seed=0, n_src=9000, n_dst=1000, m=160000):
     rng = np.random.default_rng(seed)
     zs = np.minimum(rng.zipf(1.2, m) - 1, n_src - 1)
     zd = np.minimum(rng.zipf(1.5, m) - 1, n_dst - 1)
@@ -94,7 +95,7 @@ def run(path_cls, steps=4):
     rng = np.random.default_rng(1)
     losses = []
     for s in range(steps):
-        sl = slice(10000 + s * B, 10000 + (s + 1) * B)
+        sl = slice(FIRST + s * B, FIRST + (s + 1) * B)
         e_src, e_dst, e_ts = src[sl], dst[sl], ts[sl]
         neg = (9000 + rng.integers(0, 1000, B)).astype(np.int64)
         roots = np.concatenate([e_src, e_dst, neg])
@@ -150,7 +151,7 @@ def test_tgn_inputs_and_state_are_bit_exact_in_lockstep():
     model = TGN(DIM_MEM, DIM_EDGE, DIM_TIME).cuda()
     rng = np.random.default_rng(1)
     for s in range(4):
-        sl = slice(10000 + s * B, 10000 + (s + 1) * B)
+        sl = slice(FIRST + s * B, FIRST + (s + 1) * B)
         e_src, e_dst, e_ts = src[sl], dst[sl], ts[sl]
         neg = (9000 + rng.integers(0, 1000, B)).astype(np.int64)
         roots, rts = np.concatenate([e_src, e_dst, neg]), np.concatenate([e_ts, e_ts, e_ts])
