@@ -142,9 +142,11 @@ class Partition:
 
 
 class Step:
-    """The device work of one step, captured once as two CUDA graphs (A1-A2 and A3-A6) over static buffers."""
+    """The device work of one step, captured once as two CUDA graphs (A1-A2 and A3-A6) over static buffers.  Two such
+    objects alternate (``shared`` = the first one: step counter and row counter are common): while one runs A3-A6 and the
+    route of step s, the other already relabels and samples step s+1 into its own buffers -- what a prefetcher does."""
 
-    def __init__(self, part: Partition, use_graphs=True):
+    def __init__(self, part: Partition, use_graphs=True, shared: "Step" = None):
         from starrygl import _C, ops
         self.p, self.ops = part, ops
         dev = part.dev
@@ -153,9 +155,12 @@ class Step:
         self.in_roots, self.in_ts = self.in_rt[0], self.in_rt[1]
         self.batches = part.roots._base                                              # [NUM_BATCHES, 2, n_roots]
         self.in_rt.copy_(self.batches[0])
-        self.step_t = torch.zeros(1, dtype=torch.int64, device=dev)          # number of the step being built
-        self.rows_sent = torch.zeros(1, dtype=torch.int64, device=dev)       # rows this rank pushed so far (one table)
-        self.status = ops.StatusWord(dev)
+        if shared is None:
+            self.step_t = torch.zeros(1, dtype=torch.int64, device=dev)      # number of the step being built
+            self.rows_sent = torch.zeros(1, dtype=torch.int64, device=dev)   # rows this rank pushed so far (one table)
+            self.status = ops.StatusWord(dev)
+        else:
+            self.step_t, self.rows_sent, self.status = shared.step_t, shared.rows_sent, shared.status
         self.id_bits = ops.bits_for(part.g.num_nodes - 1)
         self.ts_bits = ops.bits_for(T_MAX)
         self.plan_cap = self.n_roots * max(part.world - 1, 1)
@@ -321,39 +326,46 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     K, W = args.steps, max(args.warmup, 3)
     part = Partition(rank, world, dev, n_per, e_per)
     step = Step(part)
+    steps = [step, Step(part, shared=step)]          # double buffering: A1-A2 of step s+1 next to A3-A6 + route of step s
     rows_hint = 3 * EVENTS * max(1, min(world - 1, 5))
     cap_rows = max(16384, 3 * EVENTS)
     mem_route = P2PCacheRoute(MEM_DIM, True, cap_rows=cap_rows, ring=4)
     mail_route = P2PCacheRoute(MAIL_DIM, True, cap_rows=cap_rows, ring=4)
     r_stream = torch.cuda.Stream(dev, priority=-1)
-    a_done = [torch.cuda.Event() for _ in range(2)]
-    r_done = [torch.cuda.Event() for _ in range(2)]
+    a_done = [torch.cuda.Event() for _ in range(2)]      # A3-A6 of a step have finished (table writes, plan)
+    r_done = [torch.cuda.Event() for _ in range(2)]      # the step's pushes have been applied here
     n_done = [0]                     # steps issued so far (the device's step counter follows)
 
     h_batches = step.batches.cpu().pin_memory()                     # the host-buffer form starts here
     d2h = [0]
-    send_mem, apply_mem = mem_route.bind_dev(step.new_mem, step.pl_rows, step.pl_locs, step.pl_sizes, rows_hint, step.new_ts,
-                                             part.mem, r_stream)
-    send_mail, apply_mail = mail_route.bind_dev(step.new_mail, step.pl_rows, step.pl_locs, step.pl_sizes, rows_hint, step.new_ts,
-                                                part.mail, r_stream)
+    routes = []
+    for st in steps:
+        routes.append(mem_route.bind_dev(st.new_mem, st.pl_rows, st.pl_locs, st.pl_sizes, rows_hint, st.new_ts, part.mem, r_stream)
+                      + mail_route.bind_dev(st.new_mail, st.pl_rows, st.pl_locs, st.pl_sizes, rows_hint, st.new_ts, part.mail,
+                                            r_stream))
 
     def one_step(routed, host=False):
         s = n_done[0]
+        st = steps[s % 2]
+        torch.cuda.set_stream(st.stream)
         if host:
-            step.sample_from_host(h_batches[s % NUM_BATCHES])
+            st.sample_from_host(h_batches[s % NUM_BATCHES])
         else:
-            step.sample(s % NUM_BATCHES)                              # A1-A2: overlaps the route of the step before
-        if routed and s > 0:
-            step.stream.wait_event(r_done[(s - 1) % 2])               # A3 reads the tables the route writes
-        step.gather_update_plan()                                     # A3-A6
+            st.sample(s % NUM_BATCHES)                                # A1-A2: next to A3-A6 and the route of the step before
+        if s > 0:
+            st.stream.wait_event(a_done[(s - 1) % 2])                 # the tables are read and written in step order
+            if routed:
+                st.stream.wait_event(r_done[(s - 1) % 2])             # ... and A3 reads what the route of step s-1 wrote
+        st.gather_update_plan()                                       # A3-A6
+        a_done[s % 2].record(st.stream)
         if routed:
-            a_done[s % 2].record(step.stream)
+            send_mem, apply_mem, send_mail, apply_mail = routes[s % 2]
             r_stream.wait_event(a_done[s % 2])
             send_mem(), send_mail()
             apply_mem(), apply_mail()
             r_done[s % 2].record(r_stream)
         if host:
-            d2h[0] = step.export_to_host()
+            d2h[0] = st.export_to_host()
         n_done[0] += 1
 
     def timed(n_steps, routed, host=False):
@@ -362,15 +374,16 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         main = torch.cuda.current_stream(dev)
         e0.record(main)
-        step.stream.wait_stream(main)
+        for st in steps:
+            st.stream.wait_stream(main)
         r_stream.wait_stream(main)
         t0 = time.perf_counter()
-        torch.cuda.set_stream(step.stream)
         for _ in range(n_steps):
             one_step(routed, host)
         torch.cuda.set_stream(main)
         t_issue = time.perf_counter() - t0
-        main.wait_stream(step.stream)
+        for st in steps:
+            main.wait_stream(st.stream)
         main.wait_stream(r_stream)
         e1.record(main)
         torch.cuda.synchronize(dev)
@@ -405,7 +418,7 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if int(flag.item()) != 1:
         raise SystemExit(f"rank {rank}: node state differs from the expectation recomputed from the seeds ({why or 'on another rank'})")
-    edges = int(step.hop.total())
+    edges = int(steps[(n_done[0] - 1) % 2].hop.total())
     rows_per_step = (rows1 - rows0) / (reps * K)
     rt = torch.tensor([rows_per_step], dtype=torch.float64, device=dev)
     dist.all_reduce(rt, op=dist.ReduceOp.MAX)

@@ -257,13 +257,8 @@ gather_bulk_kernel(const char* __restrict__ table, int64_t table_rows, uint32_t 
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kCacheThreads = 256;
 
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
-
-// The lookup also asks the memory system for the row it has just located (one prefetch per 128-byte line, into L2):
-// the copy kernel that follows then finds its rows on chip instead of starting its own chain of DRAM accesses.
 __global__ void __launch_bounds__(kCacheThreads)
 cache_lookup_kernel(const int32_t* __restrict__ hitmap, int64_t num_ids, const int64_t* __restrict__ ids, int64_t n,
-                    const char* __restrict__ cache_rows, int64_t cache_slots, int64_t row_bytes,
                     int32_t* __restrict__ slot_ws, int32_t* __restrict__ rank_ws, int64_t* __restrict__ cta_miss,
                     unsigned int* done_counter, int64_t* d_counts, int32_t* d_status) {
   const int64_t i = (int64_t)blockIdx.x * kCacheThreads + threadIdx.x;
@@ -278,11 +273,6 @@ cache_lookup_kernel(const int32_t* __restrict__ hitmap, int64_t num_ids, const i
       slot = __ldg(hitmap + id);
       miss = slot < 0 ? 1 : 0;
       if (slot < 0) slot = -1;
-      // (hits only: the cache is device memory by contract, the backing store may be mapped host memory)
-      if (slot >= 0 && slot < cache_slots && row_bytes <= 2048) {
-        const char* row = cache_rows + (int64_t)slot * row_bytes;
-        for (int64_t b = 0; b < row_bytes; b += 128) prefetch_l2(row + b);
-      }
     }
   }
   int total;
@@ -740,8 +730,8 @@ extern "C" int sgl_cache_gather(const void* cache_rows, int64_t cache_slots, con
   unsigned int* done = c.take<unsigned int>(1);
   SGL_REQUIRE(c.ok(), SGL_ERR_WORKSPACE, "cache_gather: workspace %zu < %zu bytes", ws_bytes, sgl_cache_gather_ws_bytes(n));
   SGL_CUDA_CHECK(cudaMemsetAsync(done, 0, sizeof(unsigned int), stream));
-  cache_lookup_kernel<<<(unsigned)ctas, kCacheThreads, 0, stream>>>(hitmap, num_ids, ids, n, (const char*)cache_rows, cache_slots,
-                                                                   row_bytes, slot_ws, rank_ws, cta_miss, done, d_counts, d_status);
+  cache_lookup_kernel<<<(unsigned)ctas, kCacheThreads, 0, stream>>>(hitmap, num_ids, ids, n, slot_ws, rank_ws, cta_miss,
+                                                                   done, d_counts, d_status);
   const bool vec_ok = row_bytes % 16 == 0 && aligned16(cache_rows) && aligned16(out) && (backing == nullptr || aligned16(backing));
   if (vec_ok) {
     const uint32_t lanes = (uint32_t)(row_bytes / 16);

@@ -201,17 +201,24 @@ extern "C" int sgl_tcsr_build(int64_t num_nodes, int64_t m, const int64_t* key, 
 // ---------------------------------------------------------------------------------------------------------------
 namespace sgl {
 namespace {
+// One thread per fence entry x: its row is the last r with (indptr[r] >> 5) + r <= x (that start position is strictly
+// increasing in r), found by binary search over the row pointer -- so a hub row's tens of thousands of entries are
+// written by as many threads, not by one warp.
 __global__ void __launch_bounds__(256)
-tcsr_fence_kernel(const int64_t* __restrict__ indptr, const int64_t* __restrict__ ts, int64_t num_nodes, int64_t* __restrict__ fence) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warps = (int64_t)gridDim.x * 8;
-  for (int64_t r = ((int64_t)blockIdx.x * 256 + threadIdx.x) >> 5; r < num_nodes; r += warps) {
-    const int64_t s = __ldg(indptr + r), e = __ldg(indptr + r + 1);
-    const int64_t nb = (e - s + 31) >> 5;
-    int64_t* row = fence + (s >> 5) + r;
-    for (int64_t j = lane; j < nb; j += 32) {
+tcsr_fence_kernel(const int64_t* __restrict__ indptr, const int64_t* __restrict__ ts, int64_t num_nodes, int64_t len,
+                  int64_t* __restrict__ fence) {
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  for (int64_t x = (int64_t)blockIdx.x * 256 + threadIdx.x; x < len; x += stride) {
+    int64_t lo = 0, hi = num_nodes;          // invariant: start(lo) <= x; rows >= hi start after x
+    while (hi - lo > 1) {
+      const int64_t mid = lo + ((hi - lo) >> 1);
+      if ((__ldg(indptr + mid) >> 5) + mid <= x) lo = mid; else hi = mid;
+    }
+    const int64_t s = __ldg(indptr + lo), e = __ldg(indptr + lo + 1);
+    const int64_t j = x - ((s >> 5) + lo);
+    if (j < ((e - s + 31) >> 5)) {
       const int64_t last = s + (j << 5) + 31;
-      row[j] = __ldg(ts + (last < e ? last : e - 1));
+      fence[x] = __ldg(ts + (last < e ? last : e - 1));
     }
   }
 }
@@ -225,7 +232,8 @@ extern "C" int sgl_tcsr_fence(const int64_t* indptr, const int64_t* ts, int64_t 
   SGL_REQUIRE(num_nodes >= 0 && m >= 0, SGL_ERR_ARG, "tcsr_fence: negative size");
   if (num_nodes == 0 || m == 0) return SGL_OK;
   SGL_REQUIRE(indptr && ts && out_fence, SGL_ERR_ARG, "tcsr_fence: null array");
-  tcsr_fence_kernel<<<stream_grid(num_nodes, 8, 16), 256, 0, (cudaStream_t)stream_>>>(indptr, ts, num_nodes, out_fence);
+  const int64_t len = sgl_tcsr_fence_len(num_nodes, m);
+  tcsr_fence_kernel<<<stream_grid(len, 256, 16), 256, 0, (cudaStream_t)stream_>>>(indptr, ts, num_nodes, len, out_fence);
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }
