@@ -20,8 +20,9 @@ One step per rank = one batch of 4,000 events = 12,000 root queries (source, des
       plan's sizes read from device memory (no host synchronisation, no count exchange); the receivers apply them
                                                                        sgl_p2p_route_send_dev / sgl_p2p_route_recv_dev
 
-A1-A2 of step s+1 overlap R of step s; A3 of step s+1 waits for R of step s (it reads what R writes).  After the timed
-loop rank 0 recomputes, from the seeds alone, which step wrote every one of its rows last (its own batches and every
+A1, A2, A4 and A6 touch no table and run ahead on their own stream (two sets of buffers alternate); the pushes of R leave
+as soon as they are done.  A3, A5 and the applies of R form one chain in step order: A3 of step s+1 reads what A5 and R
+of step s wrote.  After the timed loop every rank recomputes, from the seeds alone, which step wrote every one of its rows last (its own batches and every
 peer's) and compares its whole memory and mail tables with that expectation bit for bit.
 """
 import statistics
@@ -39,6 +40,7 @@ FANOUT = 10
 MEM_DIM = 100
 MAIL_DIM = 2 * MEM_DIM + 172
 NUM_BATCHES = 64
+NBUF = 3                  # steps in preparation at a time (sets of step buffers)
 
 
 def make_partition(rank, world, dev, n_per=N_PER, e_per=E_PER):
@@ -142,9 +144,10 @@ class Partition:
 
 
 class Step:
-    """The device work of one step, captured once as two CUDA graphs (A1-A2 and A3-A6) over static buffers.  Two such
-    objects alternate (``shared`` = the first one: step counter and row counter are common): while one runs A3-A6 and the
-    route of step s, the other already relabels and samples step s+1 into its own buffers -- what a prefetcher does."""
+    """The device work of one step, captured once as three CUDA graphs over static buffers: what touches no node table
+    and can be prefetched (A1, A2, A6), the table reads with the model stand-in behind them (A3, A4), and the local writes
+    (A5).  Several such objects take turns (``shared`` = the first one: step counter, row counter and status word are
+    common): while the tables serve step s, the next objects already prepare steps s+1, s+2 in their own buffers."""
 
     def __init__(self, part: Partition, use_graphs=True, shared: "Step" = None):
         from starrygl import _C, ops
@@ -165,7 +168,8 @@ class Step:
         self.ts_bits = ops.bits_for(T_MAX)
         self.plan_cap = self.n_roots * max(part.world - 1, 1)
         self.stream = torch.cuda.Stream(dev)
-        self.side = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]     # branches inside the captured graphs
+        self.side = [torch.cuda.Stream(dev) for _ in range(3)]           # branches inside the captured graphs
+        self.c131 = torch.tensor([131], dtype=torch.int64, device=dev)
         self.cols_mem = torch.arange(MEM_DIM, device=dev, dtype=torch.float32)
         self.cols_mail = torch.arange(MAIL_DIM, device=dev, dtype=torch.float32)
         self.use_graphs = use_graphs
@@ -177,17 +181,20 @@ class Step:
         _C.WORKSPACE = self._ws = _C.Workspace()
         try:
             with torch.cuda.stream(self.stream):
-                self._a12()
-                self._a36()
+                self._prepare()
+                self._read()
+                self._write()
             self.stream.synchronize()
             self.step_t.zero_()
             self.rows_sent.zero_()
             part.mem.reset(), part.mail.reset()
-            self.g1, self.g2 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            self.g1, self.g2, self.g3 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.g1, stream=self.stream):
-                self._a12()
+                self._prepare()
             with torch.cuda.graph(self.g2, stream=self.stream):
-                self._a36()
+                self._read()
+            with torch.cuda.graph(self.g3, stream=self.stream):
+                self._write()
         finally:
             _C.WORKSPACE = saved
         self.stream.synchronize()
@@ -200,57 +207,76 @@ class Step:
         self.rows_sent.zero_()
         part.mem.reset(), part.mail.reset()
 
-    def _a12(self):
-        """A1 (relabel of the roots) and A2 (the hop) only depend on the roots: two branches of the graph."""
+    def _prepare(self):
+        """What a prefetcher can do ahead of the model, because it touches no node table: A1 relabel of the roots, then A6,
+        the route plan from the layer-0 list; next to them A2, the hop."""
         ops, p = self.ops, self.p
+        st = self.status
         cur, s1 = torch.cuda.current_stream(), self.side[0]
         s1.wait_stream(cur)
         with torch.cuda.stream(s1):
-            self.hop = ops.sample_layer(p.g, self.in_roots, self.in_ts, FANOUT, "recent", status=self.status)
+            self.hop = ops.sample_layer(p.g, self.in_roots, self.in_ts, FANOUT, "recent", status=st)
         self.u_id, self.u_ts, self.inv, _, self.d_n0 = ops.unique_pairs(self.in_roots, self.in_ts, id_bits=self.id_bits,
-                                                                        ts_bits=self.ts_bits, ts_base=0, status=self.status)
+                                                                        ts_bits=self.ts_bits, ts_base=0, status=st)
+        (self.pl_ranks, self.pl_rows, self.pl_locs, self.pl_sizes, self.pl_total) = ops.plan_route(
+            self.u_id, p.node_parts, p.rank, p.rep.indptr, p.rep.indices, p.rep.locs, p.world, self.plan_cap, d_n=self.d_n0,
+            status=st)
         cur.wait_stream(s1)
 
-    def _a36(self):
-        """A3 (gathers), A4-A5 (model stand-in, local writes) and A6 (plan) as three branches: the writes wait for the
-        gathers (they read the rows the writes replace), nothing waits for the plan but the end of the graph."""
+    def _read(self):
+        """A3, the three gathers side by side, then A4: the stand-in model's rows (a real model computes them from what A3
+        gathered, so they are placed behind it), and the step counters."""
         ops, p = self.ops, self.p
         st = self.status
-        cur, s1, s2 = torch.cuda.current_stream(), self.side[0], self.side[1]
+        cur, s1, s2 = torch.cuda.current_stream(), self.side[1], self.side[2]
         s1.wait_stream(cur)
         s2.wait_stream(cur)
         with torch.cuda.stream(s1):
-            self.m_roots, self.m_roots_ts = ops.gather_rows(p.mem.data, self.in_roots, map=p.g2l, ts_table=p.mem.ts, status=st)
             self.m_nbrs, self.m_nbrs_ts = ops.gather_rows(p.mem.data, self.hop.nbr, map=p.g2l, d_n=self.hop.d_total,
                                                           ts_table=p.mem.ts, status=st)
-            self.mails, self.mails_ts = ops.gather_rows(p.mail.data, self.in_roots, map=p.g2l, ts_table=p.mail.ts, status=st)
         with torch.cuda.stream(s2):
-            (self.pl_ranks, self.pl_rows, self.pl_locs, self.pl_sizes, self.pl_total) = ops.plan_route(
-                self.u_id, p.node_parts, p.rank, p.rep.indptr, p.rep.indices, p.rep.locs, p.world, self.plan_cap, d_n=self.d_n0,
-                status=st)
-            self.rows_sent += self.pl_total
-        base = model_base(self.u_id, self.step_t)
-        self.new_mem = model_rows(None, None, MEM_DIM, base, self.cols_mem)
-        self.new_mail = model_rows(None, None, MAIL_DIM, base, self.cols_mail)
-        self.new_ts = self.step_t.to(torch.float32).expand(self.u_id.numel()).contiguous()
+            self.mails, self.mails_ts = ops.gather_rows(p.mail.data, self.in_roots, map=p.g2l, ts_table=p.mail.ts, status=st)
+        self.m_roots, self.m_roots_ts = ops.gather_rows(p.mem.data, self.in_roots, map=p.g2l, ts_table=p.mem.ts, status=st)
         cur.wait_stream(s1)
-        ops.scatter_rows(p.mem.data, self.u_id, self.new_mem, map=p.g2l, d_n=self.d_n0, ts_table=p.mem.ts, ts=self.new_ts, status=st)
-        ops.scatter_rows(p.mail.data, self.u_id, self.new_mail, map=p.g2l, d_n=self.d_n0, ts_table=p.mail.ts, ts=self.new_ts,
-                         status=st)
+        cur.wait_stream(s2)
+        # (the stand-in costs kernel launches, not bandwidth: keep its chain short -- the counters go on a side branch)
+        s2.wait_stream(cur)
+        with torch.cuda.stream(s2):
+            self.new_ts = self.step_t.to(torch.float32).expand(self.u_id.numel()).contiguous()
+            self.rows_sent += self.pl_total
+        step7 = self.step_t * 7
+        base = torch.remainder(torch.addcmul(step7, self.u_id, self.c131), 65536, out=torch.empty_like(self.u_id, dtype=torch.float32))
+        s1.wait_stream(cur)
+        with torch.cuda.stream(s1):
+            self.new_mail = model_rows(None, None, MAIL_DIM, base, self.cols_mail)
+        self.new_mem = model_rows(None, None, MEM_DIM, base, self.cols_mem)
         cur.wait_stream(s2)
         self.step_t += 1
+        cur.wait_stream(s1)
+
+    def _write(self):
+        """A5: the two local writes side by side (they replace rows A3 read)."""
+        ops, p = self.ops, self.p
+        st = self.status
+        cur, s1 = torch.cuda.current_stream(), self.side[1]
+        s1.wait_stream(cur)
+        with torch.cuda.stream(s1):
+            ops.scatter_rows(p.mail.data, self.u_id, self.new_mail, map=p.g2l, d_n=self.d_n0, ts_table=p.mail.ts, ts=self.new_ts,
+                             status=st)
+        ops.scatter_rows(p.mem.data, self.u_id, self.new_mem, map=p.g2l, d_n=self.d_n0, ts_table=p.mem.ts, ts=self.new_ts, status=st)
+        cur.wait_stream(s1)
 
     # The methods below enqueue on the CURRENT stream, which the caller sets to ``self.stream`` once for a whole loop
     # (a stream context manager per call costs more host time than the calls themselves).
     def sample(self, b):
         self.in_rt.copy_(self.batches[b], non_blocking=True)
-        self.g1.replay() if self.use_graphs else self._a12()
+        self.g1.replay() if self.use_graphs else self._prepare()
 
     def sample_from_host(self, h_batch):
         """A1-A2 for a batch whose roots and query times ([2, n_roots]) are in PINNED host memory (the copy is asynchronous:
         the caller keeps the tensor untouched until the step has run)."""
         self.in_rt.copy_(h_batch, non_blocking=True)
-        self.g1.replay() if self.use_graphs else self._a12()
+        self.g1.replay() if self.use_graphs else self._prepare()
 
     def export_to_host(self):
         """Block structure of the batch (offsets, neighbour ids, timestamps, edge ids, dt) -> pinned host memory; the
@@ -262,8 +288,11 @@ class Step:
             h.copy_(t, non_blocking=True)
         return sum(h.numel() * h.element_size() for h in self.h_out)
 
-    def gather_update_plan(self):
-        self.g2.replay() if self.use_graphs else self._a36()
+    def read_tables(self):
+        self.g2.replay() if self.use_graphs else self._read()
+
+    def write_tables(self):
+        self.g3.replay() if self.use_graphs else self._write()
 
 
 def _expected_last_step(rank, world, dev, n_steps_total, routed_from, my_part):
@@ -326,47 +355,90 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     K, W = args.steps, max(args.warmup, 3)
     part = Partition(rank, world, dev, n_per, e_per)
     step = Step(part)
-    steps = [step, Step(part, shared=step)]          # double buffering: A1-A2 of step s+1 next to A3-A6 + route of step s
+    steps = [step] + [Step(part, shared=step) for _ in range(NBUF - 1)]      # steps s+1, s+2 are prepared while the tables serve step s
     rows_hint = 3 * EVENTS * max(1, min(world - 1, 5))
     cap_rows = max(16384, 3 * EVENTS)
     mem_route = P2PCacheRoute(MEM_DIM, True, cap_rows=cap_rows, ring=4)
     mail_route = P2PCacheRoute(MAIL_DIM, True, cap_rows=cap_rows, ring=4)
-    r_stream = torch.cuda.Stream(dev, priority=-1)
-    a_done = [torch.cuda.Event() for _ in range(2)]      # A3-A6 of a step have finished (table writes, plan)
-    r_done = [torch.cuda.Event() for _ in range(2)]      # the step's pushes have been applied here
+    r_streams = [torch.cuda.Stream(dev, priority=-1) for _ in range(2)]     # the pushes: memory rows and mails side by side
+    t_stream = torch.cuda.Stream(dev, priority=-1)       # everything that touches the node tables, in step order
+    p_done = [torch.cuda.Event() for _ in range(NBUF)]   # a step's layer-0 list, hop and route plan exist
+    m_done = [torch.cuda.Event() for _ in range(NBUF)]   # ... its fresh rows exist (A4)
+    t_done = [torch.cuda.Event() for _ in range(NBUF)]   # ... its table reads and local writes have finished
+    s_done = [[torch.cuda.Event() for _ in range(2)] for _ in range(NBUF)]   # ... its pushes have left its buffers
     n_done = [0]                     # steps issued so far (the device's step counter follows)
+    marks, marking = [], [False]
+
+    def mark(s, what, stream):
+        if marking[0]:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(stream)
+            marks.append((s, what, e))
 
     h_batches = step.batches.cpu().pin_memory()                     # the host-buffer form starts here
     d2h = [0]
     routes = []
     for st in steps:
-        routes.append(mem_route.bind_dev(st.new_mem, st.pl_rows, st.pl_locs, st.pl_sizes, rows_hint, st.new_ts, part.mem, r_stream)
+        routes.append(mem_route.bind_dev(st.new_mem, st.pl_rows, st.pl_locs, st.pl_sizes, rows_hint, st.new_ts, part.mem,
+                                         r_streams[0], t_stream)
                       + mail_route.bind_dev(st.new_mail, st.pl_rows, st.pl_locs, st.pl_sizes, rows_hint, st.new_ts, part.mail,
-                                            r_stream))
+                                            r_streams[1], t_stream))
 
     def one_step(routed, host=False):
+        # Two chains.  (1) On the step object's own stream: relabel, hop, plan -- nothing of it touches the tables, so
+        # it runs ahead by up to NBUF - 1 steps.  (2) On t_stream, in step order: gathers, model stand-in, local writes,
+        # then the rows the peers pushed for this step -- the chain that carries the dependence "step s+1 reads what
+        # step s wrote", local or remote.  The pushes leave on their own streams as soon as the fresh rows exist and
+        # travel while the local writes run.
         s = n_done[0]
-        st = steps[s % 2]
+        i = s % NBUF
+        st = steps[i]
         torch.cuda.set_stream(st.stream)
+        if s >= NBUF:
+            st.stream.wait_event(t_done[i])                           # step s - NBUF used the same buffers
+            if routed:
+                st.stream.wait_event(s_done[i][0])
+                st.stream.wait_event(s_done[i][1])
+        mark(s, "prepare>", st.stream)
         if host:
             st.sample_from_host(h_batches[s % NUM_BATCHES])
         else:
-            st.sample(s % NUM_BATCHES)                                # A1-A2: next to A3-A6 and the route of the step before
-        if s > 0:
-            st.stream.wait_event(a_done[(s - 1) % 2])                 # the tables are read and written in step order
-            if routed:
-                st.stream.wait_event(r_done[(s - 1) % 2])             # ... and A3 reads what the route of step s-1 wrote
-        st.gather_update_plan()                                       # A3-A6
-        a_done[s % 2].record(st.stream)
-        if routed:
-            send_mem, apply_mem, send_mail, apply_mail = routes[s % 2]
-            r_stream.wait_event(a_done[s % 2])
-            send_mem(), send_mail()
-            apply_mem(), apply_mail()
-            r_done[s % 2].record(r_stream)
+            st.sample(s % NUM_BATCHES)
+        p_done[i].record(st.stream)
+        mark(s, "prepare<", st.stream)
         if host:
             d2h[0] = st.export_to_host()
+        torch.cuda.set_stream(t_stream)
+        t_stream.wait_event(p_done[i])
+        mark(s, "read>", t_stream)
+        st.read_tables()
+        mark(s, "read<", t_stream)
+        if routed:
+            send_mem, apply_mem, send_mail, apply_mail = routes[i]
+            m_done[i].record(t_stream)
+            for r, send in zip(r_streams, (send_mail, send_mem)):
+                r.wait_event(m_done[i])
+            send_mail(), send_mem()
+            for j, r in enumerate(r_streams):
+                s_done[i][j].record(r)
+            mark(s, "push mem<", r_streams[0])
+            mark(s, "push mail<", r_streams[1])
+        st.write_tables()
+        t_done[i].record(t_stream)
+        mark(s, "write<", t_stream)
+        if routed:
+            apply_mem(), apply_mail()
+            mark(s, "apply<", t_stream)
         n_done[0] += 1
+
+    def print_marks():
+        torch.cuda.synchronize(dev)
+        if rank == 0:
+            import sys
+            t0 = marks[0][2]
+            for s, what, e in marks:
+                print(f"timeline step {s:4d} {what:11s} {t0.elapsed_time(e):9.4f} ms", file=sys.stderr)
+        marks.clear()
 
     def timed(n_steps, routed, host=False):
         torch.cuda.synchronize(dev)
@@ -376,7 +448,9 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         e0.record(main)
         for st in steps:
             st.stream.wait_stream(main)
-        r_stream.wait_stream(main)
+        for r in r_streams:
+            r.wait_stream(main)
+        t_stream.wait_stream(main)
         t0 = time.perf_counter()
         for _ in range(n_steps):
             one_step(routed, host)
@@ -384,7 +458,9 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         t_issue = time.perf_counter() - t0
         for st in steps:
             main.wait_stream(st.stream)
-        main.wait_stream(r_stream)
+        for r in r_streams:
+            main.wait_stream(r)
+        main.wait_stream(t_stream)
         e1.record(main)
         torch.cuda.synchronize(dev)
         wall = time.perf_counter() - t0
@@ -408,6 +484,11 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     timed(W, True, host=True)
     e2e_ms = statistics.median([timed(K, True, host=True)[2] for _ in range(reps)])
     clk = clocks.stop() if clocks is not None else None
+    if getattr(args, "timeline", False):             # one more routed region with an event after every stage, printed by rank 0
+        marking[0] = True
+        timed(4 * NBUF, True)
+        marking[0] = False
+        print_marks()
     ms = statistics.median([r[0] for r in regions])
     t_issue = statistics.median([r[1] for r in regions])
     for st, what in ((step.status, "step"), (mem_route.status, "memory route"), (mail_route.status, "mail route"),
@@ -418,7 +499,21 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if int(flag.item()) != 1:
         raise SystemExit(f"rank {rank}: node state differs from the expectation recomputed from the seeds ({why or 'on another rank'})")
-    edges = int(steps[(n_done[0] - 1) % 2].hop.total())
+    edges = int(steps[(n_done[0] - 1) % NBUF].hop.total())
+    # the two captured chains of a step, each replayed alone (after the state check: these replays advance the step counter)
+    chain_ms = {}
+    if step.use_graphs:
+        for name, g in (("prepare", step.g1), ("read_and_model", step.g2), ("write", step.g3)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(step.stream):
+                for _ in range(5):
+                    g.replay()
+                e0.record()
+                for _ in range(50):
+                    g.replay()
+                e1.record()
+            torch.cuda.synchronize(dev)
+            chain_ms[name] = e0.elapsed_time(e1) / 50
     rows_per_step = (rows1 - rows0) / (reps * K)
     rt = torch.tensor([rows_per_step], dtype=torch.float64, device=dev)
     dist.all_reduce(rt, op=dist.ReduceOp.MAX)
@@ -458,6 +553,9 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
                                             "note": "the same step on one partition without the exchange, measured in this run; "
                                                     "the N = 1 line of this benchmark is a different workload (sampler microbenchmark)"},
             "host_issue_ms_per_step": t_issue * 1e3 / K,
+            "chains_alone_ms": dict(chain_ms, note="each captured graph replayed back to back on rank 0: 'prepare' = relabel, hop, "
+                                    "plan (runs ahead, several steps in flight); 'read_and_model' = gathers + stand-in rows and "
+                                    "'write' = local writes (in step order)"),
             "route": {"rows_per_rank_and_step": rows_per_step, "replicas_per_owned_node_max": part.max_rep,
                       "payload_bytes_per_rank_and_step": rows_per_step * payload, "wire_bytes_per_rank_and_step": rows_per_step * wire,
                       "GBps_per_direction_over_the_step": route_gbps, "frac_of_900": route_gbps / 900, "frac_of_770_measured_peer_copy": route_gbps / 770,

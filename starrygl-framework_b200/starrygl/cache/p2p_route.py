@@ -180,10 +180,12 @@ class P2PCacheRoute:
         _C.check(rc)
 
     def bind_dev(self, feats: torch.Tensor, send_idx: torch.Tensor, remote_idx: torch.Tensor, d_send_sizes: torch.Tensor,
-                 rows_hint: int, local_ts: Optional[torch.Tensor], state, stream):
+                 rows_hint: int, local_ts: Optional[torch.Tensor], state, stream, apply_stream=None):
         """:meth:`push_dev` + :meth:`apply_dev` for buffers that stay the same from step to step (a captured step writes
         its plan and rows into fixed tensors): every argument is converted once; returns ``(send, apply)``, two
-        callables without arguments that enqueue the step's send / apply kernels on ``stream``."""
+        callables without arguments that enqueue the step's send kernel on ``stream`` and its apply kernel on
+        ``apply_stream`` (default: the same stream).  With two streams the pushes of a step can leave as soon as its rows
+        exist, while the applies stay in step order with the caller's own table work."""
         if (local_ts is not None) != self.has_ts or feats.shape[1] != self.dim or feats.dtype != torch.float32:
             raise _C.SglError("P2PCacheRoute.bind_dev: row layout differs from the one the route was created for")
         v = C.c_void_p
@@ -194,7 +196,7 @@ class P2PCacheRoute:
                   v(d_send_sizes.data_ptr()), C.c_int64(int(rows_hint)), step_a, v(self.status.ptr()), sp]
         a_recv = [self.ctx, C.c_int64(int(rows_hint)), v(state._d_data.data_ptr()), C.c_int64(state._d_data.shape[0]),
                   C.c_int64(self.dim), C.c_int(int(self.has_ts)), v(state._d_ts.data_ptr()) if self.has_ts else None, step_b,
-                  v(self.status.ptr()), sp]
+                  v(self.status.ptr()), v(apply_stream.cuda_stream) if apply_stream is not None else sp]
         f_send, f_recv = self.L.sgl_p2p_route_send_dev, self.L.sgl_p2p_route_recv_dev
         keep = (feats, send_idx, remote_idx, d_send_sizes, local_ts, state)
         pending = []
