@@ -574,6 +574,8 @@ def main():
                     help="N > 1: measure the route alone with this many rows per rank and step (bandwidth-bound sizes) and exit")
     ap.add_argument("--route-bw-dim", type=int, default=MEM_DIM, help="row width (fp32 values) of --route-bw-rows")
     ap.add_argument("--tcsr-only", action="store_true", help="time the T-CSR construction of the benchmark graph and exit")
+    ap.add_argument("--sampler-large-only", action="store_true",
+                    help="time the hop on all batches in one launch pair (262,144 roots) and exit")
     ap.add_argument("--partitioned", action="store_true",
                     help="N = 1: run the partitioned (multi-GPU) workload on a single partition, the rank being its own peer")
     ap.add_argument("--timeline", action="store_true",
@@ -648,6 +650,14 @@ def run_single(args, dev, local, out_stream):
     g = ops.tcsr_build(src, dst, ts, None, NUM_NODES)
     b_roots, b_ts = make_batches(src, ts, gen, dev)
     del src, dst, ts
+    if args.sampler_large_only:
+        # side measurement (not the benchmark line): the hop on all 64 batches in ONE launch pair (262,144 roots) -- the case a
+        # profiler capture of the sampler's kernels is taken on (no feature table, a few hundred MB on the device)
+        big_r, big_t = b_roots.reshape(-1).contiguous(), b_ts.reshape(-1).contiguous()
+        ms_ = _time_ms(lambda: ops.sample_layer(g, big_r, big_t, FANOUT, "recent"), torch.cuda.current_stream(dev), 5, warm=2)
+        print(json.dumps({"sampler_large_launch_ms": ms_, "roots": int(big_r.numel()), "edges": NUM_EDGES, "nodes": NUM_NODES}),
+              file=out_stream, flush=True)
+        return
     feats = torch.empty(NUM_EDGES, EDGE_DIM, dtype=torch.float32, device=dev)
     for s in range(0, NUM_EDGES, 5_000_000):
         feats[s:s + 5_000_000].normal_(generator=gen)

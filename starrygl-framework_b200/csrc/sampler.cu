@@ -5,8 +5,11 @@
 //                        CTA to finish turns the per-CTA totals into CTA base offsets (no spinning: a
 //                        fence + counter decides who is last).
 //   sample_fill_kernel   CTA-local exclusive scan of the counts (+ CTA base) gives every target its
-//                        output offset; lane j of the target's warp copies element j (recent: the tail
-//                        of the window; uniform: Floyd's k-subset with Philox4x32-10, ranked ascending).
+//                        output offset.  Windows that are copied as they are (recent: the tail of the
+//                        window; uniform with no more candidates than the fan-out) are written one
+//                        OUTPUT ELEMENT per thread -- every lane busy, stores coalesced, all loads of a
+//                        thread independent of each other; a target that draws (uniform: Floyd's
+//                        k-subset with Philox4x32-10, ranked ascending) is handled by one warp.
 //
 // Algorithmic HBM bytes per target: 16 (indptr pair) + 16 (target id, time) + 8*ceil(log2 deg) (search
 // probes) + k_eff*24 (nbr, ts, eid reads) + k_eff*36 (five output arrays) + 8 (offset).
@@ -18,10 +21,11 @@ namespace {
 
 constexpr int kWarpsPerCta = 8;
 constexpr int kCtaThreads = kWarpsPerCta * 32;
-// Targets per warp (TPW) is chosen per launch: 1 for small batches (every target gets its own warp, shortest
-// dependent-load chain), 4 for medium ones, 32 for very large ones, where the searches run one target per LANE
-// (plain binary search: one 32-byte sector per step instead of 32 sectors per warp-wide step) and the number of
-// CTAs -- hence the length of the last-CTA scan -- stays small.
+// Targets per warp (TPW) of the count kernel is chosen per launch: 1 for small batches (every target gets its own
+// warp: enough warps to hide the latency of the few dependent loads), 32 for larger ones, where the searches run one
+// target per LANE (8-ary steps: seven independent probes per round, so a 32-edge block takes two rounds) and the
+// number of CTAs -- hence the length of the last-CTA scan -- stays small.
+constexpr int kFillTargets = 32;   // targets per CTA of the fill kernel when the count kernel ran 256 per CTA
 
 // first position p in [lo, hi) with ts[p] >= bound (hi when none); all 32 lanes cooperate and agree
 __device__ __forceinline__ int64_t warp_lower_bound(const int64_t* __restrict__ ts, int64_t lo, int64_t hi,
@@ -63,12 +67,22 @@ struct Philox {
   }
 };
 
+// first position p in [lo, hi) with ts[p] >= bound, one lane on its own: 8-ary steps (seven independent probes per
+// round), then the last <= 8 candidates at once
 __device__ __forceinline__ int64_t lane_lower_bound(const int64_t* __restrict__ ts, int64_t lo, int64_t hi, int64_t bound) {
-  while (lo < hi) {
-    int64_t mid = lo + ((hi - lo) >> 1);
-    if (__ldg(ts + mid) < bound) lo = mid + 1; else hi = mid;
+  while (hi - lo > 8) {
+    const int64_t q = (hi - lo) >> 3;   // >= 1, and lo + 7 q < hi
+    int c = 0;                          // the probes are monotone: the first c of them are "less"
+#pragma unroll
+    for (int j = 1; j < 8; ++j) c += (__ldg(ts + lo + j * q) < bound) ? 1 : 0;
+    const int64_t nlo = c ? lo + c * q + 1 : lo;
+    if (c < 7) hi = lo + (c + 1) * q;
+    lo = nlo;
   }
-  return lo;
+  int c = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) c += (lo + j < hi && __ldg(ts + lo + j) < bound) ? 1 : 0;
+  return lo + c;
 }
 
 // The same bound through the fence of the row (timestamp of the last edge of every 32-edge block, see sgl_tcsr_fence):
@@ -185,7 +199,10 @@ sample_count_kernel(const int64_t* __restrict__ indptr, const int64_t* __restric
   publish_and_scan_cta_totals<kCtaThreads>((int64_t)cta_total, cta_sums, done_counter, out_offsets + n_cap);
 }
 
-template <int TPW>
+// CT = targets per CTA of the count kernel (whose scanned totals are the CTA bases), FT = targets of this CTA
+// (FT divides CT): the CTA rebuilds the prefix inside its count CTA from the counts, which are a coalesced read of at
+// most 1 KB that hits L2.
+template <int CT, int FT>
 __global__ void __launch_bounds__(kCtaThreads)
 sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ ts, const int64_t* __restrict__ eid,
                    const int64_t* __restrict__ target_ts, int64_t n_cap, const int64_t* d_n, int fanout, int policy,
@@ -194,36 +211,75 @@ sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ 
                    const int64_t* __restrict__ cta_base, int64_t* __restrict__ out_nbr, int64_t* __restrict__ out_dst,
                    int64_t* __restrict__ out_ts, float* __restrict__ out_dt, int64_t* __restrict__ out_dt_i64,
                    int64_t* __restrict__ out_eid, int64_t* __restrict__ out_offsets) {
-  constexpr int TPC = kWarpsPerCta * TPW;
-  __shared__ int64_t s_off[TPC];
+  static_assert(CT % FT == 0 && CT <= kCtaThreads && FT % kWarpsPerCta == 0, "fill CTAs tile the count CTAs");
+  __shared__ int32_t s_ex[FT + 1];   // offset of the target's first element inside the count CTA's output; [FT] = end
+  __shared__ int32_t s_cnt[FT];
+  __shared__ int64_t s_lo[FT], s_cut[FT], s_t[FT];
   const int64_t n = eff_count(n_cap, d_n);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t first = (int64_t)blockIdx.x * TPC;
+  const int64_t first = (int64_t)blockIdx.x * FT;          // this CTA's first target
+  const int64_t count_cta = first / CT;
+  const int sub = (int)(first - count_cta * CT);           // where this CTA's targets start inside the count CTA
+  const int64_t base = cta_base[count_cta];
   {
-    const int64_t i = first + threadIdx.x;
-    const bool mine = threadIdx.x < TPC;
-    int c = (mine && i < n) ? cnt[i] : 0;
-    int ex = cta_exclusive_scan<kCtaThreads, int>(c, nullptr);
+    const int64_t i = count_cta * CT + threadIdx.x;
+    const bool in_ct = threadIdx.x < CT;
+    const int slot = (int)threadIdx.x - sub;
+    const bool mine = in_ct && slot >= 0 && slot < FT;
+    const int c = (in_ct && i < n) ? cnt[i] : 0;
+    int64_t lo = 0, cut = 0, t = 0;
+    if (mine && i < n) {
+      lo = win_lo[i];
+      cut = win_cut[i];
+      t = target_ts[i];
+    }
+    const int ex = cta_exclusive_scan<kCtaThreads, int>(c, nullptr);
     if (mine) {
-      int64_t off = cta_base[blockIdx.x] + ex;
-      s_off[threadIdx.x] = off;
+      s_ex[slot] = ex;
+      s_cnt[slot] = c;
+      s_lo[slot] = lo;
+      s_cut[slot] = cut;
+      s_t[slot] = t;
+      if (slot == FT - 1) s_ex[FT] = ex + c;
       // offsets past the valid targets all equal the total, so out_offsets[n..n_cap] stays a valid prefix array
-      if (i < n_cap) out_offsets[i] = off;
+      if (i < n_cap) out_offsets[i] = base + ex;
     }
   }
   __syncthreads();
+  const bool draws = policy == SGL_POLICY_UNIFORM;
+  // windows copied as they are: one output element per thread
+  for (int o = s_ex[0] + (int)threadIdx.x; o < s_ex[FT]; o += kCtaThreads) {
+    int a = 0, b = FT;               // last slot with s_ex[slot] <= o (its next offset is > o, so it is not empty)
+    while (b - a > 1) {
+      const int m = (a + b) >> 1;
+      if (s_ex[m] <= o) a = m; else b = m;
+    }
+    const int c = s_cnt[a];
+    const int64_t cut = s_cut[a];
+    if (draws && cut - s_lo[a] > fanout) continue;
+    const int64_t p = cut - c + (o - s_ex[a]);   // recent: tail of the window; uniform with cand <= k: the whole window
+    const int64_t t = s_t[a];
+    const int64_t ets = __ldg(ts + p);
+    const int64_t g = base + o;
+    out_nbr[g] = __ldg(nbr + p);
+    out_eid[g] = __ldg(eid + p);
+    out_ts[g] = keep_root_time ? t : ets;
+    out_dt[g] = (float)(t - ets);
+    if (out_dt_i64) out_dt_i64[g] = ets - t;
+    out_dst[g] = first + a;
+  }
+  if (!draws) return;
+  // targets that draw: one warp per target
 #pragma unroll 1
-  for (int j = 0; j < TPW; ++j) {
-    const int slot = warp * TPW + j;
+  for (int slot = warp; slot < FT; slot += kWarpsPerCta) {
     const int64_t i = first + slot;
     if (i >= n) break;
-    const int32_t c = cnt[i];
-    if (c == 0) continue;
-    const int64_t lo = win_lo[i], cut = win_cut[i];
-    const int64_t t = target_ts[i];
-    const int64_t off = s_off[slot];
+    const int64_t lo = s_lo[slot], cut = s_cut[slot];
     const int64_t cand = cut - lo;
-    if (policy == SGL_POLICY_UNIFORM && cand > fanout && fanout > 32) {
+    if (cand <= fanout) continue;
+    const int64_t t = s_t[slot];
+    const int64_t off = base + s_ex[slot];
+    if (fanout > 32) {
       // more draws than lanes: the same selection, with the picks of the target kept in this warp's shared memory
       extern __shared__ uint64_t s_picks_all[];
       uint64_t* picks = s_picks_all + (size_t)warp * fanout;
@@ -257,7 +313,7 @@ sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ 
         out_dst[o] = i;
       }
       __syncwarp();
-    } else if (policy == SGL_POLICY_UNIFORM && cand > fanout) {
+    } else {
       // Floyd's subset selection: draw j picks t_j uniform in [0, cand-k+j]; a repeat is replaced by cand-k+j
       uint64_t pick = 0;
       if (lane < fanout) {
@@ -289,19 +345,6 @@ sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ 
         if (out_dt_i64) out_dt_i64[o] = ets - t;
         out_dst[o] = i;
       }
-    } else {
-      const int64_t start = cut - c;  // recent: tail of the window; uniform with cand <= k: the whole window
-      for (int e = lane; e < c; e += 32) {
-        int64_t p = start + e;
-        int64_t o = off + e;
-        int64_t ets = __ldg(ts + p);
-        out_nbr[o] = __ldg(nbr + p);
-        out_eid[o] = __ldg(eid + p);
-        out_ts[o] = keep_root_time ? t : ets;
-        out_dt[o] = (float)(t - ets);
-        if (out_dt_i64) out_dt_i64[o] = ets - t;
-        out_dst[o] = i;
-      }
     }
   }
 }
@@ -311,7 +354,7 @@ sample_fill_kernel(const int64_t* __restrict__ nbr, const int64_t* __restrict__ 
 
 using namespace sgl;
 
-static inline int sample_tpw(int64_t n) { return n <= 16384 ? 1 : (n <= 262144 ? 4 : 32); }
+static inline int sample_tpw(int64_t n) { return n <= 16384 ? 1 : 32; }
 
 static inline int64_t sample_num_ctas(int64_t n, int tpw) {
   int64_t tpc = (int64_t)kWarpsPerCta * tpw;
@@ -338,10 +381,12 @@ static void launch_sample(int64_t ctas, cudaStream_t stream, const int64_t* indp
                                                                        allowed_offset, win_lo, win_cut, cnt, cta_sums, done,
                                                                        out_offsets, d_status);
   const size_t pick_smem = (policy == SGL_POLICY_UNIFORM && fanout > 32) ? (size_t)kWarpsPerCta * fanout * sizeof(uint64_t) : 0;
-  sample_fill_kernel<TPW><<<(unsigned)ctas, kCtaThreads, pick_smem, stream>>>(nbr, ts, eid, target_ts, n_targets, d_n, fanout,
-                                                                      policy, keep_root_time, seed, rng_stream, win_lo,
-                                                                      win_cut, cnt, cta_sums, out_nbr, out_dst, out_ts,
-                                                                      out_dt, out_dt_i64, out_eid, out_offsets);
+  constexpr int CT = kWarpsPerCta * TPW, FT = CT < kFillTargets ? CT : kFillTargets;
+  const unsigned fill_ctas = (unsigned)((n_targets + FT - 1) / FT);
+  sample_fill_kernel<CT, FT><<<fill_ctas, kCtaThreads, pick_smem, stream>>>(nbr, ts, eid, target_ts, n_targets, d_n, fanout, policy,
+                                                                           keep_root_time, seed, rng_stream, win_lo, win_cut, cnt,
+                                                                           cta_sums, out_nbr, out_dst, out_ts, out_dt, out_dt_i64,
+                                                                           out_eid, out_offsets);
 }
 
 static int sample_layer_impl(const int64_t* indptr, const int64_t* nbr, const int64_t* ts, const int64_t* eid,
@@ -382,7 +427,6 @@ static int sample_layer_impl(const int64_t* indptr, const int64_t* nbr, const in
       allowed_offset, keep_root_time, seed, rng_stream, win_lo, win_cut, cnt, cta_sums, done, out_nbr, out_dst,       \
       out_ts, out_dt, out_dt_i64, out_eid, out_offsets, d_status
   if (tpw == 1) launch_sample<1>(SGL_SAMPLE_ARGS);
-  else if (tpw == 4) launch_sample<4>(SGL_SAMPLE_ARGS);
   else launch_sample<32>(SGL_SAMPLE_ARGS);
 #undef SGL_SAMPLE_ARGS
   SGL_LAUNCH_CHECK();

@@ -67,6 +67,28 @@ def test_matches_oracle_with_hubs_and_options(policy, k):
         assert np.array_equal(np.diff(offs), ref[5])
 
 
+@pytest.mark.parametrize("policy", ["recent", "uniform"])
+@pytest.mark.parametrize("n_q", [16384, 16385, 40000])
+def test_large_launch_matches_oracle(policy, n_q):
+    """Launches on both sides of the size where the searches switch from one warp per target to one lane per target
+    (and the fill CTAs become a fraction of a count CTA): the C restatement of the oracle on the same queries."""
+    from oracle import oracle_c as OC
+    z = random_graph(11, 3000, 400000, 50000, hub=70000)
+    g = build_graph(z)
+    indptr, nbr, ts, eid, _ = OC.tcsr_build(z["dst"], z["src"], z["ts"], z["eid"], z["n"])
+    rng = np.random.default_rng(n_q)
+    q = rng.integers(0, z["n"], n_q).astype(np.int64)
+    q[: n_q // 20] = 0                         # the hub row
+    qt = rng.integers(-5, 50010, n_q).astype(np.int64)
+    pol = O.RECENT if policy == "recent" else O.UNIFORM
+    for k, kw in ((10, {}), (20, {"allowed_offset": 2000, "equal_root_time": True}), (40, {"keep_root_time": True})):
+        out, offs = run(g, q, qt, k, policy, seed=77, rng_stream=1, **kw)
+        ref = OC.sample_layer(indptr, nbr, ts, eid, q, qt, k, pol, seed=77, stream=1, **kw)
+        for nm, a, r in zip(NAMES, out, ref[:5]):
+            assert a.dtype == r.dtype and np.array_equal(a, r), (policy, k, kw, nm)
+        assert np.array_equal(np.diff(offs), ref[5])
+
+
 def test_edge_cases():
     z = random_graph(5, 40, 300, 100)
     g = build_graph(z)
@@ -174,7 +196,7 @@ def test_fence_index_and_search_through_it():
         last = np.minimum(s + 32 * np.arange(nb) + 31, e - 1)
         assert np.array_equal(fence[(s >> 5) + r:(s >> 5) + r + nb], ts[last]), r
     rng = np.random.default_rng(5)
-    for n_q in (700, 20000, 300000):          # one, four and thirty-two targets per warp
+    for n_q in (700, 20000, 300000):          # one warp per target, and one lane per target
         q = rng.integers(0, z["n"], n_q).astype(np.int64)
         q[: n_q // 10] = 0                     # the hub row
         qt = rng.integers(-5, 40010, n_q).astype(np.int64)
