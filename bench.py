@@ -55,9 +55,9 @@ TS_MAX = 10_000_000
 NUM_BATCHES = 64          # distinct pre-generated batches cycled through the steps
 STREAMS = 6
 REGION_REPEATS = 200      # the K-step timed region is repeated this often; the median is reported
-# DRAM bytes per gathered row measured with ncu on a small case (57.1 MB for 65,160 rows of 688 bytes);
+# DRAM bytes per gathered row measured with ncu on a small case (61.2 MB for 68.2 k rows of 688 bytes);
 # roofline.traffic scales it by the rows of a full-size launch
-GATHER_TRAFFIC_BYTES_PER_ROW = 876.0
+GATHER_TRAFFIC_BYTES_PER_ROW = 897.0
 
 
 def peaks():
@@ -146,7 +146,8 @@ def workload_config(n_gpus):
             "graph": f"{NUM_NODES} nodes, {NUM_EDGES} edges, out-degree power law alpha 2.1, int64 ids, ts U[0,1e7)",
             "batch_roots": BATCH, "policy": f"recent-{FANOUT}, 1 hop", "edge_feat": f"{EDGE_DIM} x fp32",
             "edge_feat_rows": NUM_EDGES, "event": "one root query (a link-prediction interaction = three of them: source, destination, negative destination)",
-            "l2": "inputs larger than L2: 64 distinct batches over a 34 GB feature table and a 1.2 GB adjacency",
+            "l2": f"inputs larger than L2: 64 distinct batches over a {NUM_EDGES * EDGE_DIM * 4 / 1e9:.1f} GB feature table and a "
+                  f"{NUM_EDGES * 24 / 1e9:.1f} GB adjacency",
             "batches_in_flight": STREAMS, "parallelism": f"{n_gpus} partition(s), one process per GPU",
             "timing": f"median of {REGION_REPEATS} repeats of the K-step region (CUDA events)"}
 
