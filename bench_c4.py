@@ -20,9 +20,10 @@ One step per rank = one batch of 4,000 events = 12,000 root queries (source, des
       plan's sizes read from device memory (no host synchronisation, no count exchange); the receivers apply them
                                                                        sgl_p2p_route_send_dev / sgl_p2p_route_recv_dev
 
-A1, A2, A4 and A6 touch no table and run ahead on their own stream (two sets of buffers alternate); the pushes of R leave
-as soon as they are done.  A3, A5 and the applies of R form one chain in step order: A3 of step s+1 reads what A5 and R
-of step s wrote.  After the timed loop every rank recomputes, from the seeds alone, which step wrote every one of its rows last (its own batches and every
+A1, A2 and A6 touch no table and run ahead on their own streams (NBUF sets of buffers take turns).  A3, A4, the applies of
+R and A5 form one chain in step order; the pushes of R leave as soon as A4 is done.  A step's received rows are written when
+the next step updates the tables, after that step's reads -- the reference's order (starrygl/cache/NodeState.py:269-274) --
+so A3 of step s+1 reads what A5 of step s and R of step s-1 wrote.  After the timed loop every rank recomputes, from the seeds alone, which step wrote every one of its rows last (its own batches and every
 peer's) and compares its whole memory and mail tables with that expectation bit for bit.
 """
 import statistics
@@ -40,7 +41,7 @@ FANOUT = 10
 MEM_DIM = 100
 MAIL_DIM = 2 * MEM_DIM + 172
 NUM_BATCHES = 64
-NBUF = 3                  # steps in preparation at a time (sets of step buffers)
+NBUF = 4                  # steps in preparation at a time (sets of step buffers)
 
 
 def make_partition(rank, world, dev, n_per=N_PER, e_per=E_PER):
@@ -147,7 +148,7 @@ class Step:
     """The device work of one step, captured once as three CUDA graphs over static buffers: what touches no node table
     and can be prefetched (A1, A2, A6), the table reads with the model stand-in behind them (A3, A4), and the local writes
     (A5).  Several such objects take turns (``shared`` = the first one: step counter, row counter and status word are
-    common): while the tables serve step s, the next objects already prepare steps s+1, s+2 in their own buffers."""
+    common): while the tables serve step s, the next objects already prepare the steps after it in their own buffers."""
 
     def __init__(self, part: Partition, use_graphs=True, shared: "Step" = None):
         from starrygl import _C, ops
@@ -355,13 +356,16 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     K, W = args.steps, max(args.warmup, 3)
     part = Partition(rank, world, dev, n_per, e_per)
     step = Step(part)
-    steps = [step] + [Step(part, shared=step) for _ in range(NBUF - 1)]      # steps s+1, s+2 are prepared while the tables serve step s
+    steps = [step] + [Step(part, shared=step) for _ in range(NBUF - 1)]      # the next steps are prepared while the tables serve step s
     rows_hint = 3 * EVENTS * max(1, min(world - 1, 5))
     cap_rows = max(16384, 3 * EVENTS)
     mem_route = P2PCacheRoute(MEM_DIM, True, cap_rows=cap_rows, ring=4)
     mail_route = P2PCacheRoute(MAIL_DIM, True, cap_rows=cap_rows, ring=4)
-    r_streams = [torch.cuda.Stream(dev, priority=-1) for _ in range(2)]     # the pushes: memory rows and mails side by side
-    t_stream = torch.cuda.Stream(dev, priority=-1)       # everything that touches the node tables, in step order
+    hi_prio = min(torch.cuda.Stream.priority_range())    # the table chain is the critical one: its CTAs are placed first
+    r_streams = [torch.cuda.Stream(dev) for _ in range(2)]                  # the pushes: memory rows and mails side by side
+    t_stream = torch.cuda.Stream(dev, priority=hi_prio)  # everything that touches the node tables, in step order
+    t_side = torch.cuda.Stream(dev, priority=hi_prio)    # the mail table's applies, next to the memory table's
+    fork, join = torch.cuda.Event(), torch.cuda.Event()
     p_done = [torch.cuda.Event() for _ in range(NBUF)]   # a step's layer-0 list, hop and route plan exist
     m_done = [torch.cuda.Event() for _ in range(NBUF)]   # ... its fresh rows exist (A4)
     t_done = [torch.cuda.Event() for _ in range(NBUF)]   # ... its table reads and local writes have finished
@@ -382,14 +386,29 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         routes.append(mem_route.bind_dev(st.new_mem, st.pl_rows, st.pl_locs, st.pl_sizes, rows_hint, st.new_ts, part.mem,
                                          r_streams[0], t_stream)
                       + mail_route.bind_dev(st.new_mail, st.pl_rows, st.pl_locs, st.pl_sizes, rows_hint, st.new_ts, part.mail,
-                                            r_streams[1], t_stream))
+                                            r_streams[1], t_side))
+
+    owed = []                        # bound applies of the step whose pushes have not been applied here yet
+
+    def apply_owed():
+        while owed:                  # the two tables' applies side by side (each is a short, latency-bound kernel)
+            s_prev, apply_mem, apply_mail = owed.pop(0)
+            fork.record(t_stream)
+            t_side.wait_event(fork)
+            apply_mail()
+            join.record(t_side)
+            apply_mem()
+            t_stream.wait_event(join)
+            mark(s_prev, "apply<", t_stream)
 
     def one_step(routed, host=False):
         # Two chains.  (1) On the step object's own stream: relabel, hop, plan -- nothing of it touches the tables, so
-        # it runs ahead by up to NBUF - 1 steps.  (2) On t_stream, in step order: gathers, model stand-in, local writes,
-        # then the rows the peers pushed for this step -- the chain that carries the dependence "step s+1 reads what
-        # step s wrote", local or remote.  The pushes leave on their own streams as soon as the fresh rows exist and
-        # travel while the local writes run.
+        # it runs ahead by up to NBUF - 1 steps.  (2) On t_stream, in step order: gathers and model stand-in of step s,
+        # then the rows the peers pushed in step s-1, then the local writes of step s.  That is the reference's order: a
+        # step's received rows are written when the NEXT update is called (starrygl/cache/NodeState.py:269-274: the
+        # future of the previous update is waited on first), so a step reads the local writes of the step before it and
+        # the remote rows of the step before that, and the transfer of step s has the whole of step s+1's reads to land.
+        # The pushes leave on their own streams as soon as the fresh rows exist.
         s = n_done[0]
         i = s % NBUF
         st = steps[i]
@@ -416,19 +435,18 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         if routed:
             send_mem, apply_mem, send_mail, apply_mail = routes[i]
             m_done[i].record(t_stream)
-            for r, send in zip(r_streams, (send_mail, send_mem)):
+            for r in r_streams:
                 r.wait_event(m_done[i])
             send_mail(), send_mem()
             for j, r in enumerate(r_streams):
                 s_done[i][j].record(r)
             mark(s, "push mem<", r_streams[0])
             mark(s, "push mail<", r_streams[1])
+            apply_owed()                                              # the pushes of step s-1
+            owed.append((s, apply_mem, apply_mail))
         st.write_tables()
         t_done[i].record(t_stream)
         mark(s, "write<", t_stream)
-        if routed:
-            apply_mem(), apply_mail()
-            mark(s, "apply<", t_stream)
         n_done[0] += 1
 
     def print_marks():
@@ -451,9 +469,11 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         for r in r_streams:
             r.wait_stream(main)
         t_stream.wait_stream(main)
+        t_side.wait_stream(main)
         t0 = time.perf_counter()
         for _ in range(n_steps):
             one_step(routed, host)
+        apply_owed()                 # the last step's pushes are applied inside the region that sent them
         torch.cuda.set_stream(main)
         t_issue = time.perf_counter() - t0
         for st in steps:
@@ -461,6 +481,7 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         for r in r_streams:
             main.wait_stream(r)
         main.wait_stream(t_stream)
+        main.wait_stream(t_side)
         e1.record(main)
         torch.cuda.synchronize(dev)
         wall = time.perf_counter() - t0

@@ -18,8 +18,10 @@
 //
 // send kernel (rank r, step s):  waits until every receiver has applied step s - ring (so the slot is free), builds
 //     the wire rows and stores the tagged lines straight into the receivers' stage[r][s % ring] over NVLink.
-// recv kernel (rank p, step s):  polls the lines of all senders, scatters the rows into the node-state table (same
-//     work as route_unpack_kernel); the last CTA to finish acknowledges the step to every sender.
+// gate kernel (rank p, step s):  one warp waits for every sender's meta word of the step.
+// recv kernel (rank p, step s):  behind the gate in the stream; polls the lines of all senders (tagged form), scatters
+//     the rows into the node-state table (same work as route_unpack_kernel); the last CTA to finish acknowledges the
+//     step to every sender.
 //
 // Large messages: tagging doubles the bytes on the wire, which is the wrong trade once a message is bandwidth-bound.
 // A pair whose message of a step has at least `bulk_rows` rows, and every pair of a step in which the sender pushes at
@@ -43,7 +45,8 @@ namespace sgl {
 namespace {
 
 constexpr int kMaxWorld = 16;
-constexpr int kThreads = 128;   // 4 warps per CTA, one row per warp at a time
+constexpr int kThreads = 128;   // 4 warps per CTA, one or two rows per warp at a time
+constexpr int kSendThreads = kThreads;
 constexpr int kRowsInFlight = 1;   // rows per warp and iteration; more in flight measured slower (299 vs 371 GB/s at 40 MB)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // default bound of every device-side wait (sgl_p2p_route_configure changes it)
 
@@ -68,7 +71,7 @@ struct Splits {
 
 struct Ctx {
   P2PCfg cfg;
-  unsigned int* counters;   // device: arrival counters of the send ([0]) and recv ([32]) kernels
+  unsigned int* counters;   // device: arrival counters of the send ([0]) and recv ([32]) kernels, credit words [16..24), then the gate words
 };
 
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -77,14 +80,12 @@ __device__ __forceinline__ unsigned long long now_ns() {
   return t;
 }
 
-// Programmatic dependent launch: the route kernels of consecutive steps sit back to back in one stream.  A kernel
-// launched with the programmatic-serialization attribute may become resident while its predecessor still runs; it
-// blocks in pdl_wait() until the predecessor has completed and its writes are visible, so nothing below that call can
-// overtake the previous step.  pdl_release() (issued right after the wait) lets the NEXT kernel of the stream become
-// resident in turn -- at most one successor is ever waiting.  This takes the launch + CTA placement latency of a busy
-// GPU off the per-step chain.  Without a programmatic predecessor both calls do nothing.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// No kernel of this file may hold an SM's registers and thread slots while it waits for another GPU: the work it waits
+// for (the peer's send or apply kernel) may in turn be waiting for a kernel of THIS GPU that then finds no room to become
+// resident -- with several steps queued on two streams that is a cycle, which only the wait limits would break.  So
+// every wait for a peer is done by a one-warp kernel in front of the wide kernel it guards (the "credit" kernel before a
+// send, the "gate" kernel before an apply), and the kernels are launched plainly, in stream order (no programmatic
+// dependent launch: a dependent that becomes resident early would hold resources while its predecessor waits).
 
 // spin until *p >= want; false when the limit expires
 __device__ __forceinline__ bool wait_at_least(const unsigned long long* p, unsigned long long want, unsigned long long limit_ns) {
@@ -159,6 +160,20 @@ __device__ __forceinline__ unsigned long long meta_word(int64_t rows, unsigned l
   return ((unsigned long long)plain << 63) | ((unsigned long long)rows << 32) | (unsigned long long)(uint32_t)(step + 1);
 }
 
+// Flow control of a step's send, one warp: the ring slot may be overwritten once every receiver has applied the step
+// that used it last.  *credit = 1 when all acknowledgements are there, 0 (and SGL_DEV_TIMEOUT) when the wait ran out.
+__global__ void __launch_bounds__(32)
+p2p_credit_kernel(P2PCfg c, unsigned long long step, unsigned int* __restrict__ credit, int32_t* d_status) {
+  bool ok = true;
+  if ((int)threadIdx.x < c.world && step >= (unsigned long long)c.ring)
+    ok = wait_at_least(c.acks + threadIdx.x, step - c.ring + 1, c.wait_ns);
+  const bool all_ok = __all_sync(0xffffffffu, ok);
+  if (threadIdx.x == 0) {
+    if (!all_ok) dev_flag(d_status, SGL_DEV_TIMEOUT);
+    *credit = all_ok ? 1u : 0u;
+  }
+}
+
 // A route kernel competes for issue slots with whatever else runs on its SM (warps are scheduled round robin, stream
 // priority only decides which CTA is placed first), so on a busy GPU its duration is set by its instruction count per
 // warp, not by memory latency.  Hence one WARP per row: the row's index, destination and segment are computed once
@@ -167,19 +182,18 @@ __device__ __forceinline__ unsigned long long meta_word(int64_t rows, unsigned l
 //
 // Row counts per destination come from the host (seg, d_sizes == nullptr) or from device memory (d_sizes[world], the
 // send sizes a device-built plan left there); counts above the staging capacity are cut and flagged.
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kSendThreads)
 p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint32_t dim, const float* __restrict__ ts,
                 const int64_t* __restrict__ send_idx, const int64_t* __restrict__ remote_idx, Splits seg,
                 const int64_t* __restrict__ d_sizes, unsigned long long step, int vec_ok, unsigned int* done_counter,
-                int32_t* d_status) {
+                const unsigned int* __restrict__ credit, int32_t* d_status) {
   __shared__ int s_ok;
   __shared__ bool s_last;
   __shared__ int64_t s_off[kMaxWorld + 1];   // exclusive prefix of the row counts per destination (what is SENT)
   __shared__ int64_t s_src[kMaxWorld + 1];   // the same prefix over the plan's own counts (where the rows sit in send_idx)
-  pdl_wait();
-  pdl_release();
   if (threadIdx.x == 0) {
-    s_ok = 1;
+    s_ok = *credit != 0;                      // 0: the credit kernel's wait for the receivers ran out -- send nothing
+
     s_off[0] = s_src[0] = 0;
     for (int p = 0; p < c.world; ++p) {
       int64_t have = d_sizes ? d_sizes[p] : seg.off[p + 1] - seg.off[p];
@@ -194,13 +208,7 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
     }
   }
   __syncthreads();
-  // flow control: the ring slot may be overwritten once every receiver has applied the step that used it last
-  if (threadIdx.x < c.world && step >= (unsigned long long)c.ring) {
-    if (!wait_at_least(c.acks + threadIdx.x, step - c.ring + 1, c.wait_ns)) s_ok = 0;
-  }
-  __syncthreads();
   const bool ok = s_ok != 0;
-  if (!ok && threadIdx.x == 0) dev_flag(d_status, SGL_DEV_TIMEOUT);
   const uint32_t tag = (uint32_t)(step + 1);
   const uint32_t payload = dim + (ts ? 1u : 0u);
   const uint32_t quads = c.pitch / 4;
@@ -221,30 +229,54 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
     }
   }
   const int64_t n_send = ok ? s_off[c.world] : 0;
-  const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
+  const int64_t n_warps = (int64_t)gridDim.x * (kSendThreads / 32);
   const int64_t slot_base = ((int64_t)c.rank * c.ring + ring_slot) * c.cap_rows;
-  for (int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i < n_send; i += n_warps) {
-    const int p = segment_of(s_off, c.world, i);
-    const int64_t in_seg = i - s_off[p];
-    const int64_t src = s_src[p] + in_seg;                // position in the plan's index arrays
-    int64_t r = __ldg(send_idx + src);                    // one address per warp: a single broadcast load
-    const uint64_t slotv = (uint64_t)__ldg(remote_idx + src);
-    if (r < 0) r += n_rows;
-    if (r < 0 || r >= n_rows) {
-      if (lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
-      r = -2;                                             // sent as zeros with slot -1, which the receiver skips
+  // Two rows per warp and round: the index loads of both are in flight together, and per quad both rows' table loads are
+  // issued before either store (a warp is alone with the latency of its dependent loads: few CTAs, many rows per warp).
+  for (int64_t i0 = ((int64_t)blockIdx.x * kSendThreads + threadIdx.x) >> 5; i0 < n_send; i0 += 2 * n_warps) {
+    int64_t r[2];
+    uint64_t slotv[2];
+    uint4* dst[2];
+    bool bulk[2], have[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int64_t i = i0 + k * n_warps;
+      have[k] = i < n_send;
+      r[k] = -2; slotv[k] = 0; dst[k] = nullptr; bulk[k] = false;
+      if (!have[k]) continue;
+      const int p = segment_of(s_off, c.world, i);
+      const int64_t in_seg = i - s_off[p];
+      const int64_t src = s_src[p] + in_seg;                // position in the plan's index arrays
+      r[k] = __ldg(send_idx + src);                         // one address per warp: a single broadcast load
+      slotv[k] = (uint64_t)__ldg(remote_idx + src);
+      bulk[k] = all_plain || s_off[p + 1] - s_off[p] >= c.bulk_rows;
+      // the pair's region starts at the same place in both layouts; a plain row takes pitch / 4 lines, a tagged one pitch / 2
+      uint4* region = c.peer_stage[p] + slot_base * (c.pitch / 2);
+      dst[k] = region + in_seg * (bulk[k] ? c.pitch / 4 : c.pitch / 2);
     }
-    const bool bulk = all_plain || s_off[p + 1] - s_off[p] >= c.bulk_rows;
-    // the pair's region starts at the same place in both layouts; a plain row takes pitch / 4 lines, a tagged one pitch / 2
-    uint4* region = c.peer_stage[p] + slot_base * (c.pitch / 2);
-    uint4* dst = region + in_seg * (bulk ? c.pitch / 4 : c.pitch / 2);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (!have[k]) continue;
+      if (r[k] < 0) r[k] += n_rows;
+      if (r[k] < 0 || r[k] >= n_rows) {
+        if (lane == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
+        r[k] = -2;                                          // sent as zeros with slot -1, which the receiver skips
+      }
+    }
     for (uint32_t l = lane; l < quads; l += 32) {
-      const uint4 q = wire_quad(l, dim, payload, vec_ok, feats, ts, r, slotv);
-      if (bulk) {
-        dst[l] = q;
-      } else {
-        store_line(dst + 2 * l, q.x, q.y, tag);
-        store_line(dst + 2 * l + 1, q.z, q.w, tag);
+      uint4 q[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k)
+        if (have[k]) q[k] = wire_quad(l, dim, payload, vec_ok, feats, ts, r[k], slotv[k]);
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        if (!have[k]) continue;
+        if (bulk[k]) {
+          dst[k][l] = q[k];
+        } else {
+          store_line(dst[k] + 2 * l, q[k].x, q[k].y, tag);
+          store_line(dst[k] + 2 * l + 1, q[k].z, q[k].w, tag);
+        }
       }
     }
   }
@@ -272,20 +304,46 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
   if (threadIdx.x == 0) *done_counter = 0;
 }
 
+// The wait for the senders is NOT done by the wide apply kernel: CTAs that spin on a word another GPU has yet to write
+// hold their SM's registers and thread slots, and enough of them keep this GPU's own send kernel -- which the peers'
+// apply kernels are waiting for in the same way -- from ever becoming resident.  One warp waits instead (bounded), leaves
+// the senders' words in gate[world], and the wide kernel behind it in the stream starts when every sender has at least
+// begun (tagged lines) or finished (plain rows) this step.
+__global__ void __launch_bounds__(32)
+p2p_gate_kernel(P2PCfg c, unsigned long long step, unsigned long long* __restrict__ gate, int32_t* d_status) {
+  const uint32_t tag = (uint32_t)(step + 1);
+  if ((int)threadIdx.x >= c.world) return;
+  const volatile unsigned long long* m = c.meta + (int64_t)threadIdx.x * c.ring + (int64_t)(step % c.ring);
+  unsigned long long w = *m;
+  if ((uint32_t)w != tag) {
+    const unsigned long long t0 = now_ns();
+    bool got = false;
+    while (now_ns() - t0 < c.wait_ns) {
+      w = *m;
+      if ((uint32_t)w == tag) { got = true; break; }
+      __nanosleep(100);
+    }
+    if (!got) {
+      w = 0;
+      dev_flag(d_status, SGL_DEV_TIMEOUT);
+    }
+  }
+  __threadfence_system();   // acquire side: plain rows written before the meta word are visible to what follows
+  gate[threadIdx.x] = w;
+}
+
 // One warp per incoming row: every lane reads the line(s) holding the row's slot (one broadcast load per line) and
 // the 2 lines of its own quad, and re-polls (bounded) only what has not landed yet.  The number of rows per sender is
 // what the sender's meta word says; when the host also named a count (expect.off, check != 0) a difference is flagged.
 __global__ void __launch_bounds__(kThreads)
 p2p_recv_kernel(P2PCfg c, Splits expect, int check, uint32_t width, float* __restrict__ data, int64_t data_rows, uint32_t dim,
                 float* __restrict__ ts_table, unsigned long long step, int vec_ok, unsigned int* done_counter,
-                int32_t* d_status) {
+                const unsigned long long* __restrict__ gate, int32_t* d_status) {
   __shared__ int s_ok;
   __shared__ bool s_last;
   __shared__ int64_t s_cnt[kMaxWorld];
   __shared__ int64_t s_off[kMaxWorld + 1];
   __shared__ bool s_plain[kMaxWorld];
-  pdl_wait();
-  pdl_release();
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   const uint32_t tag = (uint32_t)(step + 1);
@@ -294,26 +352,17 @@ p2p_recv_kernel(P2PCfg c, Splits expect, int check, uint32_t width, float* __res
   const uint32_t lane = threadIdx.x & 31u;
   const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
   const int64_t ring_slot = (int64_t)(step % c.ring);
-  // every sender's meta word of this step: its row count; for a large pair also the sign that its plain rows landed
+  // every sender's meta word of this step, as the gate kernel saw it: its row count; for a large pair also the sign that
+  // its plain rows landed (a word without the step's tag: the gate's wait ran out)
   if (threadIdx.x < c.world) {
-    const volatile unsigned long long* m = c.meta + (int64_t)threadIdx.x * c.ring + ring_slot;
-    unsigned long long w = *m;
-    if ((uint32_t)w != tag) {
-      const unsigned long long t0 = now_ns();
-      bool got = false;
-      while (now_ns() - t0 < c.wait_ns) {
-        w = *m;
-        if ((uint32_t)w == tag) { got = true; break; }
-        __nanosleep(100);
-      }
-      if (!got) { s_ok = 0; w = 0; }
-    }
-    int64_t cnt = (int64_t)((w >> 32) & 0x7fffffffull);
+    const unsigned long long w = gate[threadIdx.x];
+    if ((uint32_t)w != tag) s_ok = 0;
+    int64_t cnt = (uint32_t)w == tag ? (int64_t)((w >> 32) & 0x7fffffffull) : 0;
     s_plain[threadIdx.x] = (w >> 63) != 0;
     if (cnt > c.cap_rows) cnt = c.cap_rows;
     if (check && s_ok && cnt != expect.off[threadIdx.x + 1] - expect.off[threadIdx.x]) dev_flag(d_status, SGL_DEV_MISMATCH);
     s_cnt[threadIdx.x] = cnt;
-    __threadfence_system();   // acquire side: plain rows written before the meta word are visible after this fence ...
+    __threadfence_system();   // the rows were written by another GPU: order this CTA's loads after the gate's acquire
   }
   __syncthreads();            // ... and, through the barrier, to every thread of the CTA
   if (threadIdx.x == 0) {
@@ -465,9 +514,10 @@ extern "C" int sgl_p2p_route_create(int rank, int world, int ring, int64_t cap_r
               SGL_ERR_ARG, "p2p_route_create: bad argument (world <= %d, ring >= 2, pitch a multiple of 4)", kMaxWorld);
   for (int p = 0; p < world; ++p)
     SGL_REQUIRE(h_bases[p], SGL_ERR_ARG, "p2p_route_create: base pointer of rank %d is null", p);
-  unsigned int* counters = nullptr;
-  SGL_CUDA_CHECK(cudaMalloc(&counters, 256));
-  if (cudaMemset(counters, 0, 256) != cudaSuccess) {
+  unsigned int* counters = nullptr;   // 256 bytes of arrival counters, then the gate words [ring][kMaxWorld]
+  const size_t aux_bytes = 256 + (size_t)ring * kMaxWorld * sizeof(unsigned long long);
+  SGL_CUDA_CHECK(cudaMalloc(&counters, aux_bytes));
+  if (cudaMemset(counters, 0, aux_bytes) != cudaSuccess) {
     cudaFree(counters);
     set_error("p2p_route_create: cudaMemset of the arrival counters failed");
     return SGL_ERR_CUDA;
@@ -521,22 +571,7 @@ extern "C" int sgl_p2p_route_destroy(void* ctx) {
 // number of CTAs of a route kernel: enough for the rows, at most eight per SM -- small messages are latency-bound and
 // every extra CTA adds fence traffic and a longer wait for the last one
 static int p2p_grid(int64_t rows) { return stream_grid(rows, kThreads / 32, 8); }
-
-// Launch with the programmatic-serialization attribute (see pdl_wait).
-template <typename... KArgs, typename... Args>
-static cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, cudaStream_t stream, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
+static int send_grid(int64_t rows) { return stream_grid((rows + 1) / 2, kSendThreads / 32, 8); }   // two rows per warp and round
 
 static int make_splits(const Ctx* x, const int64_t* h_rows, Splits* s, const char* what) {
   s->off[0] = 0;
@@ -557,8 +592,11 @@ static int send_impl(Ctx* x, const float* feats, int64_t n_rows, int64_t dim, co
               (long long)pitch, x->cfg.pitch);
   SGL_REQUIRE(grid_rows == 0 || (feats && send_idx && remote_idx), SGL_ERR_ARG, "p2p_route_send: null array");
   const int vec_ok = dim % 4 == 0 && ((uintptr_t)feats & 15) == 0;
-  SGL_CUDA_CHECK(launch_pdl(p2p_send_kernel, p2p_grid(grid_rows), (cudaStream_t)stream_, x->cfg, feats, n_rows, (uint32_t)dim,
-                            ts, send_idx, remote_idx, seg, d_sizes, (unsigned long long)step, vec_ok, x->counters, d_status));
+  unsigned int* credit = x->counters + 16 + (unsigned)(step % 8);   // one word per step in flight (8 >= streams' depth)
+  p2p_credit_kernel<<<1, 32, 0, (cudaStream_t)stream_>>>(x->cfg, (unsigned long long)step, credit, d_status);
+  p2p_send_kernel<<<send_grid(grid_rows), kSendThreads, 0, (cudaStream_t)stream_>>>(
+      x->cfg, feats, n_rows, (uint32_t)dim, ts, send_idx, remote_idx, seg, d_sizes, (unsigned long long)step, vec_ok, x->counters,
+      credit, d_status);
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }
@@ -593,9 +631,11 @@ static int recv_impl(Ctx* x, const Splits& expect, int check, int64_t grid_rows,
   SGL_REQUIRE(sgl_wire_pitch(dim, has_ts, 1) == x->cfg.pitch, SGL_ERR_ARG, "p2p_route_recv: wire pitch differs from the context's");
   SGL_REQUIRE(grid_rows == 0 || data, SGL_ERR_ARG, "p2p_route_recv: null table");
   const int vec_ok = dim % 4 == 0 && ((uintptr_t)data & 15) == 0;
-  SGL_CUDA_CHECK(launch_pdl(p2p_recv_kernel, p2p_grid(grid_rows), (cudaStream_t)stream_, x->cfg, expect, check, (uint32_t)width,
-                            data, data_rows, (uint32_t)dim, has_ts ? ts_table : (float*)nullptr, (unsigned long long)step, vec_ok,
-                            x->counters + 32, d_status));
+  unsigned long long* gate = (unsigned long long*)((char*)x->counters + 256) + (size_t)(step % x->cfg.ring) * kMaxWorld;
+  p2p_gate_kernel<<<1, 32, 0, (cudaStream_t)stream_>>>(x->cfg, (unsigned long long)step, gate, d_status);
+  p2p_recv_kernel<<<p2p_grid(grid_rows), kThreads, 0, (cudaStream_t)stream_>>>(
+      x->cfg, expect, check, (uint32_t)width, data, data_rows, (uint32_t)dim, has_ts ? ts_table : (float*)nullptr,
+      (unsigned long long)step, vec_ok, x->counters + 32, (const unsigned long long*)gate, d_status);
   SGL_LAUNCH_CHECK();
   return SGL_OK;
 }

@@ -67,12 +67,22 @@ struct Philox {
   }
 };
 
-// first position p in [lo, hi) with ts[p] >= bound, one lane on its own: 8-ary steps (seven independent probes per
-// round), then the last <= 8 candidates at once
+// first position p in [lo, hi) with ts[p] >= bound, one lane on its own: k-ary steps with independent probes (every
+// probe of a lane is its own 32-byte sector, so far-apart probes cost load/store-unit slots: 3 per round while the
+// range is wide, 7 once it is narrow and the probes share a few lines), then the last <= 8 candidates at once
 __device__ __forceinline__ int64_t lane_lower_bound(const int64_t* __restrict__ ts, int64_t lo, int64_t hi, int64_t bound) {
+  while (hi - lo > 256) {
+    const int64_t q = (hi - lo) >> 2;
+    int c = 0;                          // the probes are monotone: the first c of them are "less"
+#pragma unroll
+    for (int j = 1; j < 4; ++j) c += (__ldg(ts + lo + j * q) < bound) ? 1 : 0;
+    const int64_t nlo = c ? lo + c * q + 1 : lo;
+    if (c < 3) hi = lo + (c + 1) * q;
+    lo = nlo;
+  }
   while (hi - lo > 8) {
     const int64_t q = (hi - lo) >> 3;   // >= 1, and lo + 7 q < hi
-    int c = 0;                          // the probes are monotone: the first c of them are "less"
+    int c = 0;
 #pragma unroll
     for (int j = 1; j < 8; ++j) c += (__ldg(ts + lo + j * q) < bound) ? 1 : 0;
     const int64_t nlo = c ? lo + c * q + 1 : lo;
