@@ -450,12 +450,11 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         n_done[0] += 1
 
     def print_marks():
+        import sys
         torch.cuda.synchronize(dev)
-        if rank == 0:
-            import sys
-            t0 = marks[0][2]
-            for s, what, e in marks:
-                print(f"timeline step {s:4d} {what:11s} {t0.elapsed_time(e):9.4f} ms", file=sys.stderr)
+        t0 = marks[0][2]
+        for s, what, e in marks:
+            print(f"timeline rank {rank} step {s:4d} {what:11s} {t0.elapsed_time(e):9.4f} ms", file=sys.stderr)
         marks.clear()
 
     def timed(n_steps, routed, host=False):
@@ -589,6 +588,7 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
                          "frac": gather_bytes / local_step_ms / 1e6 / peak, "peak_source": peak_kind,
                          "note": "algorithmic gather bytes of a step over the whole one-partition step time (sampling, relabel, "
                                  "plan included): a lower bound for the gather kernels"},
-            "gpu_launches": (None if step.kernel_launches is None else (step.kernel_launches + 4) * K * reps),
-            "kernel_launches_per_step": (None if step.kernel_launches is None else step.kernel_launches + 4),
+            # + the route's kernels: credit + send and gate + apply, for each of the two tables
+            "gpu_launches": (None if step.kernel_launches is None else (step.kernel_launches + 8) * K * reps),
+            "kernel_launches_per_step": (None if step.kernel_launches is None else step.kernel_launches + 8),
             "edges_per_step": edges, "clocks": clk}

@@ -362,9 +362,10 @@ p2p_recv_kernel(P2PCfg c, Splits expect, int check, uint32_t width, float* __res
     if (cnt > c.cap_rows) cnt = c.cap_rows;
     if (check && s_ok && cnt != expect.off[threadIdx.x + 1] - expect.off[threadIdx.x]) dev_flag(d_status, SGL_DEV_MISMATCH);
     s_cnt[threadIdx.x] = cnt;
-    __threadfence_system();   // the rows were written by another GPU: order this CTA's loads after the gate's acquire
   }
-  __syncthreads();            // ... and, through the barrier, to every thread of the CTA
+  // No fence here: the gate kernel saw the senders' words, fenced, and COMPLETED before this kernel started; the rows sit
+  // in this GPU's own memory and are read with volatile loads (L2, the point of coherence for peer writes), never from L1.
+  __syncthreads();
   if (threadIdx.x == 0) {
     s_off[0] = 0;
     for (int p = 0; p < c.world; ++p) s_off[p + 1] = s_off[p] + s_cnt[p];
