@@ -47,6 +47,7 @@ namespace {
 constexpr int kMaxWorld = 16;
 constexpr int kThreads = 128;   // 4 warps per CTA, one or two rows per warp at a time
 constexpr int kSendThreads = kThreads;
+constexpr int kFlatUnroll = 4;   // quads in flight per thread in the plain-rows form of the send kernel
 constexpr int kRowsInFlight = 1;   // rows per warp and iteration; more in flight measured slower (299 vs 371 GB/s at 40 MB)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // default bound of every device-side wait (sgl_p2p_route_configure changes it)
 
@@ -106,6 +107,14 @@ __device__ __forceinline__ void store_line(uint4* p, uint32_t w0, uint32_t w1, u
 __device__ __forceinline__ uint4 load_line(const uint4* p) {
   uint4 v;
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// a quad of a plain wire row in this GPU's staging buffer: written by a peer, so never through L1 (cached at L2 only);
+// unlike load_line the compiler may keep several of these in flight
+__device__ __forceinline__ uint4 load_quad_l2(const uint4* p) {
+  uint4 v;
+  asm("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
 
@@ -231,9 +240,58 @@ p2p_send_kernel(P2PCfg c, const float* __restrict__ feats, int64_t n_rows, uint3
   const int64_t n_send = ok ? s_off[c.world] : 0;
   const int64_t n_warps = (int64_t)gridDim.x * (kSendThreads / 32);
   const int64_t slot_base = ((int64_t)c.rank * c.ring + ring_slot) * c.cap_rows;
+  // A step whose pairs all travel as plain rows is bandwidth work: one 16-byte quad per thread over the flattened
+  // (row, quad) index, kFlatUnroll quads in flight per thread, every load independent of every other -- the layout of the
+  // row-gather kernel, whose stores fill a peer's memory at 0.8 of the copy engine's rate (measured), where one warp per
+  // row reached 0.5-0.6.
+  bool flat = n_send > 0;
+  for (int p = 0; p < c.world; ++p) {
+    const int64_t cnt = s_off[p + 1] - s_off[p];
+    flat = flat && (cnt == 0 || all_plain || cnt >= c.bulk_rows);
+  }
+  if (flat) {
+    const int64_t total = n_send * quads;
+    const int64_t stride = (int64_t)gridDim.x * kSendThreads;
+    const bool small = total <= 0xffffffffll;
+    for (int64_t q0 = (int64_t)blockIdx.x * kSendThreads + threadIdx.x; q0 < total; q0 += stride * kFlatUnroll) {
+      uint4 v[kFlatUnroll];
+      uint4* d[kFlatUnroll];
+#pragma unroll
+      for (int u = 0; u < kFlatUnroll; ++u) {
+        const int64_t q = q0 + u * stride;
+        d[u] = nullptr;
+        if (q >= total) continue;
+        int64_t i;
+        uint32_t l;
+        if (small) {
+          const uint32_t qq = (uint32_t)q, ii = qq / quads;
+          i = ii;
+          l = qq - ii * quads;
+        } else {
+          i = q / quads;
+          l = (uint32_t)(q - i * quads);
+        }
+        const int p = segment_of(s_off, c.world, i);
+        const int64_t in_seg = i - s_off[p];
+        const int64_t src = s_src[p] + in_seg;
+        int64_t r = __ldg(send_idx + src);
+        const uint64_t slotv = (uint64_t)__ldg(remote_idx + src);
+        if (r < 0) r += n_rows;
+        if (r < 0 || r >= n_rows) {
+          if (l == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
+          r = -2;                                           // sent as zeros with slot -1, which the receiver skips
+        }
+        v[u] = wire_quad(l, dim, payload, vec_ok, feats, ts, r, slotv);
+        d[u] = c.peer_stage[p] + slot_base * (c.pitch / 2) + in_seg * (c.pitch / 4) + l;
+      }
+#pragma unroll
+      for (int u = 0; u < kFlatUnroll; ++u)
+        if (d[u]) *d[u] = v[u];
+    }
+  }
   // Two rows per warp and round: the index loads of both are in flight together, and per quad both rows' table loads are
   // issued before either store (a warp is alone with the latency of its dependent loads: few CTAs, many rows per warp).
-  for (int64_t i0 = ((int64_t)blockIdx.x * kSendThreads + threadIdx.x) >> 5; i0 < n_send; i0 += 2 * n_warps) {
+  for (int64_t i0 = ((int64_t)blockIdx.x * kSendThreads + threadIdx.x) >> 5; i0 < n_send && !flat; i0 += 2 * n_warps) {
     int64_t r[2];
     uint64_t slotv[2];
     uint4* dst[2];
@@ -373,7 +431,66 @@ p2p_recv_kernel(P2PCfg c, Splits expect, int check, uint32_t width, float* __res
   __syncthreads();
   bool ok = s_ok != 0;
   const int64_t n_recv = ok ? s_off[c.world] : 0;
-  for (int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i < n_recv && ok; i += n_warps) {
+  // Every sender's rows arrived as plain rows: bandwidth work, one quad per thread over the flattened (row, quad) index,
+  // kFlatUnroll quads in flight per thread (the row's slot words are one or two more loads that hit L2).
+  bool flat = n_recv > 0;
+  for (int p = 0; p < c.world; ++p) flat = flat && (s_cnt[p] == 0 || s_plain[p]);
+  if (flat) {
+    const int64_t total = n_recv * quads;
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    const bool small = total <= 0xffffffffll;
+    for (int64_t q0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; q0 < total; q0 += stride * kFlatUnroll) {
+      uint4 v[kFlatUnroll];
+      int64_t ds[kFlatUnroll];
+      uint32_t ll[kFlatUnroll];
+#pragma unroll
+      for (int u = 0; u < kFlatUnroll; ++u) {
+        const int64_t q = q0 + u * stride;
+        ds[u] = -1;
+        ll[u] = 0;
+        if (q >= total) continue;
+        int64_t i;
+        uint32_t l;
+        if (small) {
+          const uint32_t qq = (uint32_t)q, ii = qq / quads;
+          i = ii;
+          l = qq - ii * quads;
+        } else {
+          i = q / quads;
+          l = (uint32_t)(q - i * quads);
+        }
+        const int sdr = segment_of(s_off, c.world, i);
+        const uint4* prow = c.stage + ((int64_t)sdr * c.ring + ring_slot) * c.cap_rows * (c.pitch / 2) + (i - s_off[sdr]) * (c.pitch / 4);
+        const uint4 qa = load_quad_l2(prow + width / 4);
+        const uint4 qb = (width + 1) / 4 == width / 4 ? qa : load_quad_l2(prow + (width + 1) / 4);
+        v[u] = load_quad_l2(prow + l);
+        const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
+        const int64_t dslot = (int64_t)((uint64_t)wa[width & 3] | ((uint64_t)wb[(width + 1) & 3] << 32));
+        if (dslot < 0 || dslot >= data_rows) {
+          if (l == 0) dev_flag(d_status, SGL_DEV_BAD_INDEX);
+        } else {
+          ds[u] = dslot;
+          ll[u] = l;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kFlatUnroll; ++u) {
+        if (ds[u] < 0) continue;
+        if (vec_ok && (ll[u] + 1) * 4 <= dim) {
+          ((uint4*)(data + ds[u] * dim))[ll[u]] = v[u];
+        } else {
+          const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t e = 4 * ll[u] + k;
+            if (e < dim) data[ds[u] * dim + e] = __uint_as_float(w[k]);
+            else if (e < width && ts_table) ts_table[ds[u]] = __uint_as_float(w[k]);
+          }
+        }
+      }
+    }
+  }
+  for (int64_t i = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5; i < n_recv && ok && !flat; i += n_warps) {
     const int sdr = segment_of(s_off, c.world, i);
     const uint4* region = c.stage + ((int64_t)sdr * c.ring + ring_slot) * c.cap_rows * (c.pitch / 2);
     if (s_plain[sdr]) {
@@ -569,10 +686,15 @@ extern "C" int sgl_p2p_route_destroy(void* ctx) {
   return SGL_OK;
 }
 
-// number of CTAs of a route kernel: enough for the rows, at most eight per SM -- small messages are latency-bound and
+// number of CTAs of a route kernel: enough for the rows, at most four per SM -- small messages are latency-bound and
 // every extra CTA adds fence traffic and a longer wait for the last one
-static int p2p_grid(int64_t rows) { return stream_grid(rows, kThreads / 32, 8); }
-static int send_grid(int64_t rows) { return stream_grid((rows + 1) / 2, kSendThreads / 32, 8); }   // two rows per warp and round
+static int p2p_grid(int64_t rows) { return stream_grid(rows, kThreads / 32, 4); }
+// Send kernel: two rows per warp and round in the tagged form; the flattened plain-rows form strides over whatever grid it
+// gets.  Four CTAs per SM for both kernels is the measured optimum on two B200s (40-96 MB per step, send and apply
+// running side by side): with eight the two kernels and the incoming writes slow each other, with two or fewer too few
+// stores are in flight for the link (send/apply CTAs per SM -> GB/s per direction at 40 MB: 8/8 356, 4/4 437, 2/8 287,
+// 1/8 167).
+static int send_grid(int64_t rows) { return stream_grid((rows + 1) / 2, kSendThreads / 32, 4); }
 
 static int make_splits(const Ctx* x, const int64_t* h_rows, Splits* s, const char* what) {
   s->off[0] = 0;
