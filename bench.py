@@ -319,6 +319,8 @@ def route_bandwidth(args, rank, world, dev, out_stream):
     res = {"rows_per_step": int(ranks.numel()), "row": f"{D} x fp32 + ts", "payload_MB_per_rank_and_step": payload / 1e6,
            "peers": world - 1}
 
+    host_ms = [0.0]
+
     def timed(step_fn, streams):
         for _ in range(5):
             step_fn()
@@ -328,8 +330,10 @@ def route_bandwidth(args, rank, world, dev, out_stream):
         e0.record(streams[0])
         for st in streams[1:]:
             st.wait_stream(streams[0])
+        h0 = time.perf_counter()
         for _ in range(K):
             step_fn()
+        host_ms[0] = (time.perf_counter() - h0) * 1e3 / K
         for st in streams[1:]:
             streams[0].wait_stream(st)
         e1.record(streams[0])
@@ -345,7 +349,7 @@ def route_bandwidth(args, rank, world, dev, out_stream):
         p2p.status.check("route bandwidth (peer memory)")
         # the last step's rows are in place: slot by slot what the senders' tables hold
         res["p2p"] = {"ms_per_step": ms, "GBps_per_direction": payload / ms / 1e6, "frac_of_770": payload / ms / 1e6 / 770,
-                      "frac_of_900": payload / ms / 1e6 / 900}
+                      "frac_of_900": payload / ms / 1e6 / 900, "host_issue_ms_per_step": host_ms[0]}
 
     cr = CacheRoute()
 
