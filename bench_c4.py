@@ -184,16 +184,19 @@ class Step:
             with torch.cuda.stream(self.stream):
                 self._prepare()
                 self._read()
+                self._model()
                 self._write()
             self.stream.synchronize()
             self.step_t.zero_()
             self.rows_sent.zero_()
             part.mem.reset(), part.mail.reset()
-            self.g1, self.g2, self.g3 = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            self.g1, self.g2, self.g2m, self.g3 = (torch.cuda.CUDAGraph() for _ in range(4))
             with torch.cuda.graph(self.g1, stream=self.stream):
                 self._prepare()
             with torch.cuda.graph(self.g2, stream=self.stream):
                 self._read()
+            with torch.cuda.graph(self.g2m, stream=self.stream):
+                self._model()
             with torch.cuda.graph(self.g3, stream=self.stream):
                 self._write()
         finally:
@@ -225,8 +228,7 @@ class Step:
         cur.wait_stream(s1)
 
     def _read(self):
-        """A3, the three gathers side by side, then A4: the stand-in model's rows (a real model computes them from what A3
-        gathered, so they are placed behind it), and the step counters."""
+        """A3, the three gathers side by side."""
         ops, p = self.ops, self.p
         st = self.status
         cur, s1, s2 = torch.cuda.current_stream(), self.side[1], self.side[2]
@@ -240,6 +242,11 @@ class Step:
         self.m_roots, self.m_roots_ts = ops.gather_rows(p.mem.data, self.in_roots, map=p.g2l, ts_table=p.mem.ts, status=st)
         cur.wait_stream(s1)
         cur.wait_stream(s2)
+
+    def _model(self):
+        """A4: the stand-in model's rows (a real model computes them from what A3 gathered, so the caller places this behind
+        A3), and the step counters.  It touches no table, so it can run next to the applies of the step before."""
+        cur, s1, s2 = torch.cuda.current_stream(), self.side[1], self.side[2]
         # (the stand-in costs kernel launches, not bandwidth: keep its chain short -- the counters go on a side branch)
         s2.wait_stream(cur)
         with torch.cuda.stream(s2):
@@ -291,6 +298,9 @@ class Step:
 
     def read_tables(self):
         self.g2.replay() if self.use_graphs else self._read()
+
+    def model(self):
+        self.g2m.replay() if self.use_graphs else self._model()
 
     def write_tables(self):
         self.g3.replay() if self.use_graphs else self._write()
@@ -365,6 +375,8 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     r_streams = [torch.cuda.Stream(dev) for _ in range(2)]                  # the pushes: memory rows and mails side by side
     t_stream = torch.cuda.Stream(dev, priority=hi_prio)  # everything that touches the node tables, in step order
     t_side = torch.cuda.Stream(dev, priority=hi_prio)    # the mail table's applies, next to the memory table's
+    m_stream = torch.cuda.Stream(dev, priority=hi_prio)  # the model stand-in: behind a step's gathers, next to the applies
+    g_done = [torch.cuda.Event() for _ in range(NBUF)]   # a step's gathers have finished
     fork, join = torch.cuda.Event(), torch.cuda.Event()
     p_done = [torch.cuda.Event() for _ in range(NBUF)]   # a step's layer-0 list, hop and route plan exist
     m_done = [torch.cuda.Event() for _ in range(NBUF)]   # ... its fresh rows exist (A4)
@@ -403,8 +415,9 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
 
     def one_step(routed, host=False):
         # Two chains.  (1) On the step object's own stream: relabel, hop, plan -- nothing of it touches the tables, so
-        # it runs ahead by up to NBUF - 1 steps.  (2) On t_stream, in step order: gathers and model stand-in of step s,
-        # then the rows the peers pushed in step s-1, then the local writes of step s.  That is the reference's order: a
+        # it runs ahead by up to NBUF - 1 steps.  (2) On t_stream, in step order: the gathers of step s, then the rows the
+        # peers pushed in step s-1 (next to them, on its own stream, the model stand-in of step s, which needs the gathered
+        # rows but no table), then the local writes of step s.  That is the reference's order: a
         # step's received rows are written when the NEXT update is called (starrygl/cache/NodeState.py:269-274: the
         # future of the previous update is waited on first), so a step reads the local writes of the step before it and
         # the remote rows of the step before that, and the transfer of step s has the whole of step s+1's reads to land.
@@ -431,10 +444,16 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
         t_stream.wait_event(p_done[i])
         mark(s, "read>", t_stream)
         st.read_tables()
+        g_done[i].record(t_stream)
         mark(s, "read<", t_stream)
+        torch.cuda.set_stream(m_stream)
+        m_stream.wait_event(g_done[i])
+        st.model()
+        m_done[i].record(m_stream)
+        mark(s, "model<", m_stream)
+        torch.cuda.set_stream(t_stream)
         if routed:
             send_mem, apply_mem, send_mail, apply_mail = routes[i]
-            m_done[i].record(t_stream)
             for r in r_streams:
                 r.wait_event(m_done[i])
             send_mail(), send_mem()
@@ -442,8 +461,9 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
                 s_done[i][j].record(r)
             mark(s, "push mem<", r_streams[0])
             mark(s, "push mail<", r_streams[1])
-            apply_owed()                                              # the pushes of step s-1
+            apply_owed()                                              # the pushes of step s-1, next to the model of step s
             owed.append((s, apply_mem, apply_mail))
+        t_stream.wait_event(m_done[i])
         st.write_tables()
         t_done[i].record(t_stream)
         mark(s, "write<", t_stream)
@@ -469,6 +489,7 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
             r.wait_stream(main)
         t_stream.wait_stream(main)
         t_side.wait_stream(main)
+        m_stream.wait_stream(main)
         t0 = time.perf_counter()
         for _ in range(n_steps):
             one_step(routed, host)
@@ -481,6 +502,7 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
             main.wait_stream(r)
         main.wait_stream(t_stream)
         main.wait_stream(t_side)
+        main.wait_stream(m_stream)
         e1.record(main)
         torch.cuda.synchronize(dev)
         wall = time.perf_counter() - t0
@@ -523,7 +545,7 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
     # the two captured chains of a step, each replayed alone (after the state check: these replays advance the step counter)
     chain_ms = {}
     if step.use_graphs:
-        for name, g in (("prepare", step.g1), ("read_and_model", step.g2), ("write", step.g3)):
+        for name, g in (("prepare", step.g1), ("gathers", step.g2), ("model_stand_in", step.g2m), ("write", step.g3)):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             with torch.cuda.stream(step.stream):
                 for _ in range(5):
@@ -574,8 +596,8 @@ def run(args, rank, world, dev, clocks, peak_info, n_per=N_PER, e_per=E_PER):
                                                     "the N = 1 line of this benchmark is a different workload (sampler microbenchmark)"},
             "host_issue_ms_per_step": t_issue * 1e3 / K,
             "chains_alone_ms": dict(chain_ms, note="each captured graph replayed back to back on rank 0: 'prepare' = relabel, hop, "
-                                    "plan (runs ahead, several steps in flight); 'read_and_model' = gathers + stand-in rows and "
-                                    "'write' = local writes (in step order)"),
+                                    "plan (runs ahead, several steps in flight); 'gathers', 'model_stand_in' and 'write' = local "
+                                    "writes follow each other in step order"),
             "route": {"rows_per_rank_and_step": rows_per_step, "replicas_per_owned_node_max": part.max_rep,
                       "payload_bytes_per_rank_and_step": rows_per_step * payload, "wire_bytes_per_rank_and_step": rows_per_step * wire,
                       "GBps_per_direction_over_the_step": route_gbps, "frac_of_900": route_gbps / 900, "frac_of_770_measured_peer_copy": route_gbps / 770,
