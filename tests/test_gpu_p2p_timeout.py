@@ -148,3 +148,45 @@ def test_world1_count_mismatch_and_overflow_are_reported():
     assert torch.equal(data[:64], feats[0].expand(64, DIM))
     _C.check(L.sgl_p2p_route_destroy(ctx))
     _C.check(L.sgl_p2p_free(base))
+
+
+def test_send_without_credit_gives_up_and_publishes_nothing():
+    """Ring flow control: a step may reuse a ring slot only after the receiver has acknowledged the step that used it last.
+    With a ring of 2 and no apply in between, the third send finds no acknowledgement: its one-warp credit kernel gives up
+    after the (shortened) bound, the status word carries the timeout, and the send kernel behind it stores nothing -- the
+    two steps that were sent are applied intact afterwards."""
+    from starrygl import _C, ops
+    L = _C.lib()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ctx, base = make_ctx(L, _C, wait_ms=200)
+    data, ts = torch.zeros(SLOTS, DIM, device=dev), torch.zeros(SLOTS, device=dev)
+    status = ops.StatusWord(dev)
+    sp = _C.stream_ptr()
+    n_rows = (C.c_int64 * 1)(ROWS)
+    g = torch.Generator().manual_seed(11)
+    sent = []
+    for step in range(3):
+        feats = torch.randn(50, DIM, generator=g).to(dev)
+        fts = torch.rand(50, generator=g).to(dev)
+        send_idx = torch.randint(0, 50, (ROWS,), generator=g).to(dev)
+        slots = (torch.randperm(30, generator=g)[:ROWS] + 30 * step).to(dev)        # disjoint slots per step
+        sent.append((feats, fts, send_idx, slots))
+        _C.check(L.sgl_p2p_route_send(ctx, feats.data_ptr(), 50, DIM, fts.data_ptr(), send_idx.data_ptr(), slots.data_ptr(), n_rows,
+                                      step, status.ptr(), sp))
+        torch.cuda.synchronize()
+        if step < 2:
+            status.check(f"send of step {step}")
+    with pytest.raises(_C.SglError, match="(?i)timeout|wait"):
+        status.check("third send without an acknowledgement")
+    status2 = ops.StatusWord(dev)
+    for step in range(2):
+        _C.check(L.sgl_p2p_route_recv(ctx, n_rows, data.data_ptr(), SLOTS, DIM, 1, ts.data_ptr(), step, status2.ptr(), sp))
+    torch.cuda.synchronize()
+    status2.check("apply of the two steps that were sent")
+    want_d, want_t = torch.zeros(SLOTS, DIM, device=dev), torch.zeros(SLOTS, device=dev)
+    for feats, fts, send_idx, slots in sent[:2]:
+        want_d[slots] = feats[send_idx]
+        want_t[slots] = fts[send_idx]
+    assert torch.equal(data, want_d) and torch.equal(ts, want_t)      # step 2's rows (slots 60..89) never arrived
+    _C.check(L.sgl_p2p_route_destroy(ctx))
+    _C.check(L.sgl_p2p_free(base))
