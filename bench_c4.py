@@ -41,7 +41,8 @@ FANOUT = 10
 MEM_DIM = 100
 MAIL_DIM = 2 * MEM_DIM + 172
 NUM_BATCHES = 64
-NBUF = 4                  # steps in preparation at a time (sets of step buffers)
+NBUF = 4                  # steps in preparation at a time (sets of step buffers; measured at N = 2: 2 -> 0.212, 3 -> 0.181,
+                          # 4 -> 0.168-0.191 ms per step)
 
 
 def make_partition(rank, world, dev, n_per=N_PER, e_per=E_PER):
