@@ -42,7 +42,7 @@ MEM_DIM = 100
 MAIL_DIM = 2 * MEM_DIM + 172
 NUM_BATCHES = 64
 NBUF = 4                  # steps in preparation at a time (sets of step buffers; measured at N = 2: 2 -> 0.212, 3 -> 0.181,
-                          # 4 -> 0.168-0.191 ms per step)
+                          # 4 -> 0.168, 6 -> 0.168, 8 -> 0.186 ms per step)
 
 
 def make_partition(rank, world, dev, n_per=N_PER, e_per=E_PER):
